@@ -1,0 +1,292 @@
+/*
+ * rfk.h — C ABI of librfk.so: the sm_100a layer-kernel family of a RenderFormer
+ * inference engine (RMSNorm with fused residual and fp16 cast, triangle-vertex
+ * RoPE, NeRF positional encoding, row softmax, activations, ray generation,
+ * world->camera transform) plus the layout helpers that sit between its GEMMs.
+ *
+ * Conventions
+ *   - every entry point returns an int status: RFK_OK (0), a negative RFK_E*
+ *     code for a rejected argument, or a positive cudaError_t from the launch;
+ *   - all pointers are device pointers unless a comment says otherwise;
+ *   - `rfk_half` is an IEEE binary16 stored in 16 bits (the CUDA `half`);
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *   - no entry point allocates, frees or synchronises unless its comment says
+ *     so: every call is asynchronous on `stream` and may be captured in a CUDA
+ *     graph;
+ *   - in-place aliasing that the reference relies on (y == x for the norms,
+ *     out == a for SiLU*b, elu/pow10 in place) is supported where stated.
+ *
+ * "replaces" comments give the interface of the reference engine
+ * (BANANASJIM/renderformer-cuda, paths relative to that project) whose
+ * arguments, meaning and numerics the entry point reproduces.
+ */
+#ifndef RFK_H
+#define RFK_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef uint16_t rfk_half;      /* IEEE binary16 bit pattern               */
+typedef void*    rfk_stream_t;  /* cudaStream_t                            */
+
+enum {
+    RFK_OK          = 0,
+    RFK_EINVAL      = -1,  /* null pointer, negative size, unsupported shape */
+    RFK_EUNSUPPORTED= -2,  /* shape outside what the kernels implement       */
+    RFK_ETOOBIG     = -3   /* size beyond a documented fixed maximum         */
+};
+
+/* Library identification: returns a static string "rfk <version> sm_100a". */
+const char* rfk_version(void);
+/* Human-readable text for a status returned by any entry point. */
+const char* rfk_status_string(int status);
+/* Number of kernels this library has launched in the calling process so far
+ * (host-side counter, incremented per launch; used by benchmarks). */
+unsigned long long rfk_launch_count(void);
+
+/* ------------------------------------------------------------------ RMSNorm */
+
+/* y[r,:] = half((float(x[r,:]) * rsqrt(mean(x[r,:]^2) + eps)) * gamma), y may alias x.
+ * replaces rf::rmsnorm — src/kernels/rmsnorm.h:13, src/kernels/rmsnorm.cu:8-57 */
+int rfk_rmsnorm(const rfk_half* x, const float* gamma, rfk_half* y,
+                int rows, int dim, float eps, rfk_stream_t stream);
+
+/* fp32 in / fp32 out variant, y may alias x.
+ * replaces rf::rmsnorm_f32 — src/kernels/rmsnorm.h:18, src/kernels/rmsnorm.cu:59-96 */
+int rfk_rmsnorm_f32(const float* x, const float* gamma, float* y,
+                    int rows, int dim, float eps, rfk_stream_t stream);
+
+/* Fused: h += r (fp32, written back); y16 = half(rmsnorm(h) * gamma).
+ * One launch instead of the reference's residual_add_f32 -> rmsnorm_f32 ->
+ * cast_fp32_to_fp16 triple (src/layers/transformer.cu:21-30, 32-45;
+ * src/kernels/rmsnorm.cu:59-96; sequence at src/layers/transformer.cu:216,220-221).
+ * r may be NULL (no residual; h is then not rewritten). */
+int rfk_rmsnorm_residual_f32_cast16(float* h, const float* r, const float* gamma,
+                                    rfk_half* y16, int rows, int dim, float eps,
+                                    rfk_stream_t stream);
+
+/* Same with an fp16 residual (the encoder's fp32 hidden += fp16 sub-layer output).
+ * replaces residual_add_mixed -> rmsnorm_f32 -> cast_fp32_to_fp16 —
+ * src/layers/transformer.cu:52-61, 216, 220-221 */
+int rfk_rmsnorm_residual_mixed_cast16(float* h, const rfk_half* r, const float* gamma,
+                                      rfk_half* y16, int rows, int dim, float eps,
+                                      rfk_stream_t stream);
+
+/* fp16 hidden state (decoder): x = half(float(x) + float(r)) written back, then
+ * y = rmsnorm(x). r may be NULL. y must not alias x when r != NULL.
+ * replaces residual_add -> rmsnorm — src/layers/transformer.cu:9-19, 179-182 */
+int rfk_rmsnorm_residual_f16(rfk_half* x, const rfk_half* r, const float* gamma,
+                             rfk_half* y, int rows, int dim, float eps,
+                             rfk_stream_t stream);
+
+/* ----------------------------------------------- residual / cast plumbing */
+
+/* y = half(float(y) + float(r)) — replaces rf::residual_add, src/layers/transformer.cu:9-19 */
+int rfk_residual_add(rfk_half* y, const rfk_half* r, long long n, rfk_stream_t stream);
+/* y += r (fp32) — replaces rf::residual_add_f32, src/layers/transformer.cu:21-30 */
+int rfk_residual_add_f32(float* y, const float* r, long long n, rfk_stream_t stream);
+/* y(fp32) += float(r(fp16)) — replaces rf::residual_add_mixed, src/layers/transformer.cu:52-61 */
+int rfk_residual_add_mixed(float* y, const rfk_half* r, long long n, rfk_stream_t stream);
+/* replaces rf::cast_fp32_to_fp16 / cast_fp16_to_fp32 — src/layers/transformer.cu:32-50 */
+int rfk_cast_fp32_to_fp16(const float* in, rfk_half* out, long long n, rfk_stream_t stream);
+int rfk_cast_fp16_to_fp32(const rfk_half* in, float* out, long long n, rfk_stream_t stream);
+/* out[i] = half(float(out[i]) + float(bc[i % dim])) — replaces k_broadcast_add_s,
+ * src/pipeline/render_session.cu:44-47 */
+int rfk_broadcast_add(rfk_half* out, const rfk_half* bc, long long n, int dim,
+                      rfk_stream_t stream);
+
+/* --------------------------------------------------------------------- RoPE */
+
+/* cos/sin tables [B,1,S,head_dim] fp16 from 9-D triangle positions [B,S,9] fp16 and
+ * num_freqs fp32 frequencies; each half of head_dim holds 9*num_freqs angles then zeros.
+ * replaces rf::triangle_rope_freqs — src/kernels/rope.h:12, src/kernels/rope.cu:11-57 */
+int rfk_triangle_rope_freqs(const rfk_half* pos, const float* learned_freqs,
+                            rfk_half* out_cos, rfk_half* out_sin,
+                            int batch, int seq_len, int num_freqs, int head_dim,
+                            rfk_stream_t stream);
+
+/* In-place rotate-half RoPE on q and k [B,H,S,D] fp16 with tables [B,1,S,D] fp16.
+ * replaces rf::apply_rope — src/kernels/rope.h:20, src/kernels/rope.cu:61-105 */
+int rfk_apply_rope(rfk_half* q, rfk_half* k, const rfk_half* cos_vals, const rfk_half* sin_vals,
+                   int batch, int num_heads, int seq_len, int head_dim, rfk_stream_t stream);
+/* replaces rf::apply_rope_one — src/kernels/rope.h:25, src/kernels/rope.cu:108-145 */
+int rfk_apply_rope_one(rfk_half* x, const rfk_half* cos_vals, const rfk_half* sin_vals,
+                       int batch, int num_heads, int seq_len, int head_dim, rfk_stream_t stream);
+/* fp32 data, fp16 tables — replaces rf::apply_rope_f32 / apply_rope_one_f32,
+ * src/kernels/rope.h:30-36, src/kernels/rope.cu:148-211 */
+int rfk_apply_rope_f32(float* q, float* k, const rfk_half* cos_vals, const rfk_half* sin_vals,
+                       int batch, int num_heads, int seq_len, int head_dim, rfk_stream_t stream);
+int rfk_apply_rope_one_f32(float* x, const rfk_half* cos_vals, const rfk_half* sin_vals,
+                           int batch, int num_heads, int seq_len, int head_dim, rfk_stream_t stream);
+
+/* Out-of-place RoPE: dst = rope(src). Replaces the per-layer pair
+ * cudaMemcpyAsync(K_bhsd <- K_cached) + apply_rope_one(K_bhsd) —
+ * src/layers/attention.cu:355-361. src_seq_stride/dst_seq_stride are the row
+ * counts per head of src and dst (>= seq_len; rows [seq_len, dst_seq_stride) of
+ * dst are copied unrotated from src when copy_tail != 0). */
+int rfk_rope_one_oop(const rfk_half* src, rfk_half* dst,
+                     const rfk_half* cos_vals, const rfk_half* sin_vals,
+                     int batch, int num_heads, int seq_len, int head_dim,
+                     int src_seq_stride, int dst_seq_stride, int copy_tail,
+                     rfk_stream_t stream);
+
+/* Fused projection epilogue: for each of the n_parts (1..3) column blocks of a
+ * [B*S, row_stride] fp16 GEMM output (block p starts at column p*dim), do
+ *   optional RMSNorm over the full dim-wide vector (gamma[p] != NULL),
+ *   [B,S,H,D] -> [B,H,S,D] transpose,
+ *   optional rotate-half RoPE (use_rope[p] != 0, tables [B,1,S,D]),
+ * writing out[p]. One launch instead of deinterleave_qkv + rmsnorm x2 +
+ * transpose_bshd_to_bhsd x3 (+ memcpy x3) + apply_rope —
+ * src/layers/attention.cu:73-85,184-210 (self), :341-361 (cross Q), :510-530 (swin).
+ * Intermediate roundings match the unfused sequence (the normalised value is
+ * rounded to fp16 before the rotation). gamma/out/use_rope are HOST arrays. */
+int rfk_qkv_norm_rope_transpose(const rfk_half* x, long long row_stride, int n_parts,
+                                const float* const* gamma, rfk_half* const* out,
+                                const int* use_rope,
+                                const rfk_half* cos_vals, const rfk_half* sin_vals,
+                                int batch, int seq_len, int num_heads, int head_dim,
+                                float eps, rfk_stream_t stream);
+
+/* [B,S,H,D] -> [B,H,S,D] — replaces transpose_bshd_to_bhsd, src/layers/attention.cu:17-31 */
+int rfk_transpose_bshd_to_bhsd(const rfk_half* in, rfk_half* out,
+                               int batch, int seq_len, int num_heads, int head_dim,
+                               rfk_stream_t stream);
+/* [B,H,S,D] -> [B,S,H*D] — replaces transpose_bhsd_to_bsd, src/layers/attention.cu:34-48 */
+int rfk_transpose_bhsd_to_bsd(const rfk_half* in, rfk_half* out,
+                              int batch, int num_heads, int seq_len, int head_dim,
+                              rfk_stream_t stream);
+
+/* ------------------------------------------------------------------ NeRF PE */
+
+/* out[b,s,:] = [x (if include_input), sin(x_d * f_k) (d major, k minor), cos(...)] fp16,
+ * f_k = 2^(min_exp + (max_exp-min_exp) * k / max(num_freqs-1,1)). num_freqs <= 32.
+ * Unlike the reference wrapper this does not allocate or synchronise.
+ * replaces rf::nerf_pe / rf::nerf_pe_f32 — src/kernels/nerf_pe.h:11-20,
+ * src/kernels/nerf_pe.cu:9-132 */
+int rfk_nerf_pe(const rfk_half* input, rfk_half* output,
+                int batch, int seq_len, int in_dim, int num_freqs,
+                float min_freq_exp, float max_freq_exp, int include_input,
+                rfk_stream_t stream);
+int rfk_nerf_pe_f32(const float* input, rfk_half* output,
+                    int batch, int seq_len, int in_dim, int num_freqs,
+                    float min_freq_exp, float max_freq_exp, int include_input,
+                    rfk_stream_t stream);
+
+/* ------------------------------------------------------------------ softmax */
+
+/* In-place fp32 row softmax — replaces rf::softmax_inplace,
+ * src/kernels/softmax.h:9, src/kernels/softmax.cu:7-53 */
+int rfk_softmax_inplace(float* data, int rows, int cols, rfk_stream_t stream);
+/* mask [mask_rows, cols] of bytes (0 = excluded), row r uses mask row r % mask_rows.
+ * replaces rf::masked_softmax_inplace — src/kernels/softmax.h:13, softmax.cu:55-106 */
+int rfk_masked_softmax_inplace(float* data, const uint8_t* mask, int rows, int cols,
+                               int mask_rows, rfk_stream_t stream);
+/* scores [BnW*H, ws2, ws2], mask [nW, ws2, ws2]; row (bh,sq) uses mask[(bh/H) % nW][sq].
+ * replaces rf::swin_masked_softmax_inplace — src/kernels/softmax.h:21, softmax.cu:108-165 */
+int rfk_swin_masked_softmax_inplace(float* data, const uint8_t* mask, int BnW, int num_heads,
+                                    int ws2, int nW, rfk_stream_t stream);
+/* fp32 scores -> fp16 probabilities, strided rows, columns [cols,out_stride) zero-filled,
+ * input columns >= cols never read.
+ * replaces rf::softmax_cast_fp16 — src/kernels/softmax.h:27, softmax.cu:168-248 */
+int rfk_softmax_cast_fp16(const float* in, rfk_half* out, int rows, int cols,
+                          int in_stride, int out_stride, rfk_stream_t stream);
+/* replaces rf::softmax_cast_fp16_masked — src/kernels/softmax.h:31, softmax.cu:250-300 */
+int rfk_softmax_cast_fp16_masked(const float* in, rfk_half* out, const uint8_t* mask,
+                                 int rows, int cols, int in_stride, int out_stride,
+                                 int mask_rows, rfk_stream_t stream);
+/* softmax(scale * in): lets the caller keep alpha = 1 in the score GEMM. */
+int rfk_softmax_cast_fp16_scaled(const float* in, rfk_half* out, int rows, int cols,
+                                 int in_stride, int out_stride, float scale,
+                                 rfk_stream_t stream);
+/* Swin window scores fp32 -> fp16 probabilities in one pass (mask may be NULL).
+ * replaces swin_masked_softmax_inplace | softmax_inplace followed by fp32_to_fp16 —
+ * src/layers/attention.cu:549-555 */
+int rfk_swin_softmax_cast_fp16(const float* in, rfk_half* out, const uint8_t* mask,
+                               int BnW, int num_heads, int ws2, int nW, rfk_stream_t stream);
+
+/* -------------------------------------------------------------- activations */
+
+/* out = half(silu(a) * b), out may alias a — replaces rf::fused_silu_mul,
+ * src/kernels/activations.h:8, activations.cu:5-21 */
+int rfk_fused_silu_mul(const rfk_half* a, const rfk_half* b, rfk_half* out, long long n,
+                       rfk_stream_t stream);
+/* replaces rf::fused_silu_mul_f32 — activations.h:12, activations.cu:23-36 */
+int rfk_fused_silu_mul_f32(const float* a, const float* b, float* out, long long n,
+                           rfk_stream_t stream);
+/* SwiGLU on one concatenated GEMM output: gate_up [rows, 2*hidden] (gate | up per row),
+ * out [rows, hidden] = half(silu(gate) * up). Serves a single w1||w3 GEMM in place of the
+ * two GEMMs + fused_silu_mul of rf::ffn_swiglu, src/layers/transformer.cu:63-79. */
+int rfk_swiglu(const rfk_half* gate_up, rfk_half* out, int rows, int hidden,
+               rfk_stream_t stream);
+/* y = x > 0 ? x : alpha*(exp(x)-1), fp16, in place allowed — replaces rf::elu,
+ * activations.h:16, activations.cu:38-50 */
+int rfk_elu(const rfk_half* x, rfk_half* y, long long n, float alpha, rfk_stream_t stream);
+/* y = 10^x - 1 fp32, in place allowed — replaces rf::pow10_minus1,
+ * activations.h:20, activations.cu:52-63 */
+int rfk_pow10_minus1(const float* x, float* y, long long n, rfk_stream_t stream);
+/* y32 = 10^float(half(elu(x16))) - 1 in one launch — replaces the chain
+ * elu -> k_fp16_to_fp32_s -> pow10_minus1, src/pipeline/render_session.cu:249-253 */
+int rfk_post_elu_pow10(const rfk_half* x, float* y, long long n, float alpha,
+                       rfk_stream_t stream);
+
+/* ------------------------------------------------- per-view ray front end */
+
+/* Pinhole rays: c2w [B,4,4] fp32 row-major, fov [B] radians, rays_o [B,3] fp32,
+ * rays_d [B,res,res,3] fp16 unit directions. Bit-identical to the reference kernel.
+ * replaces rf::ray_gen — src/kernels/ray_gen.h:11, ray_gen.cu:6-53 */
+int rfk_ray_gen(const float* c2w, const float* fov, float* rays_o, rfk_half* rays_d,
+                int batch, int img_res, rfk_stream_t stream);
+/* Same rays written directly as patch tokens [B, (res/ps)^2, 3*ps*ps]
+ * (feature = c*ps*ps + p1*ps + p2). rays_o may be NULL.
+ * replaces ray_gen + k_patchify_s — src/pipeline/render_session.cu:48-59,207-212 */
+int rfk_ray_gen_patchify(const float* c2w, const float* fov, float* rays_o, rfk_half* ray_pat,
+                         int batch, int img_res, int patch_size, rfk_stream_t stream);
+/* [H,W,C] -> [pH*pW, C*ps*ps] — replaces k_patchify_s, render_session.cu:48-59 */
+int rfk_patchify(const rfk_half* in, rfk_half* out, int H, int W, int C, int ps,
+                 rfk_stream_t stream);
+
+/* In place: tri <- R^T (v - t), vn <- R^T n; tri, vn [B,N,3,3] fp16 (vn may be NULL).
+ * Bit-identical to the reference kernel.
+ * replaces rf::world_to_cam — src/kernels/coord_transform.h:12, coord_transform.cu:7-55 */
+int rfk_world_to_cam(const float* c2w, rfk_half* tri, rfk_half* vn, int batch, int n_tris,
+                     rfk_stream_t stream);
+/* fp32 storage variant of the same transform on [B, n_verts, 3] arrays (normals may be NULL). */
+int rfk_world_to_cam_f32(const float* c2w, float* verts, float* normals, int batch, int n_verts,
+                         rfk_stream_t stream);
+/* Per-view geometry front end in one launch (single camera):
+ *   vtri = world_to_cam(tri_world), vvn = world_to_cam_normals(vn_world)  [N,3,3] fp16
+ *   vpos[0:nr]    = camera-space scene centre repeated 3x               [nr,9]
+ *   vpos[nr:nr+N] = vtri ; vpos[nr+N : seq_pad] = 0
+ *   k_cos,k_sin [seq_pad, head_dim] = triangle RoPE tables of vpos
+ * replaces 2 D2D copies + world_to_cam + k_center_pos_from_c2w + D2D copy +
+ * triangle_rope_freqs — src/pipeline/render_session.cu:73-88,192-203.
+ * vvn / vn_world may be NULL. */
+int rfk_view_geometry(const float* c2w, const rfk_half* tri_world, const rfk_half* vn_world,
+                      const float* world_center, const float* learned_freqs,
+                      rfk_half* vtri, rfk_half* vvn, rfk_half* vpos,
+                      rfk_half* k_cos, rfk_half* k_sin,
+                      int n_tris, int n_register, int seq_pad, int num_freqs, int head_dim,
+                      rfk_stream_t stream);
+
+/* ----------------------------------------------------- swin window layout */
+
+/* windows[b*nW + wh*(W/ws) + ww][lh*ws+lw][:] = x[b][(h-shift) mod H][(w-shift) mod W][:],
+ * h = wh*ws+lh, w = ww*ws+lw: cyclic_shift_2d(-shift) then window partition, one launch.
+ * replaces cyclic_shift_2d(-s) + window_partition — src/layers/attention.cu:377-407,443-472,498-505 */
+int rfk_window_gather(const rfk_half* x, rfk_half* windows, int B, int H, int W, int C,
+                      int ws, int shift, rfk_stream_t stream);
+/* Inverse of rfk_window_gather (window reverse then cyclic shift by +shift).
+ * If residual_into != 0, x = half(float(x) + float(value)) instead of x = value.
+ * replaces window_reverse + cyclic_shift_2d(+s) (+ residual_add) —
+ * src/layers/attention.cu:409-439,569-575; src/layers/transformer.cu:188 */
+int rfk_window_scatter(const rfk_half* windows, rfk_half* x, int B, int H, int W, int C,
+                       int ws, int shift, int residual_into, rfk_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RFK_H */

@@ -1,0 +1,22 @@
+// Library-level entry points of the C ABI: identification, status text, launch counter.
+#include "common.cuh"
+
+namespace rfk {
+unsigned long long g_launches = 0;
+}
+
+extern "C" const char* rfk_version(void) { return "rfk 0.1 sm_100a"; }
+
+extern "C" const char* rfk_status_string(int status) {
+    switch (status) {
+        case RFK_OK: return "ok";
+        case RFK_EINVAL: return "invalid argument (null pointer, negative size or inconsistent shape)";
+        case RFK_EUNSUPPORTED: return "shape or alignment not supported by this entry point";
+        case RFK_ETOOBIG: return "size exceeds a fixed maximum of this entry point";
+        default: break;
+    }
+    if (status > 0) return cudaGetErrorString((cudaError_t)status);
+    return "unknown rfk status";
+}
+
+extern "C" unsigned long long rfk_launch_count(void) { return rfk::g_launches; }

@@ -1,0 +1,159 @@
+// Pinhole ray generation, optionally written directly as 8x8 patch tokens.
+//
+// Reference semantics (BANANASJIM/renderformer-cuda, src/kernels/ray_gen.cu:25-44):
+//   cx = res*0.5 ; fx = cx / tanf(0.5*fov) ; x = (px+0.5-cx)/fx ; y = -(py+0.5-cx)/fx ; z = -1
+//   d = R*(x,y,z), sums in the order M0*x + M1*y + M2*z ; d *= rsqrtf(d.d) ; 3 halves per pixel
+//   rays_o = c2w[:3,3]
+// and src/pipeline/render_session.cu:48-59 for the patch layout
+//   token = patch (row-major), feature = c*ps*ps + p1*ps + p2.
+//
+// The per-pixel arithmetic below is written with the same expression trees as the
+// reference so that the compiler contracts the same multiply-adds: the outputs are
+// required to be bit-identical. What changes is the memory side: the reference issues
+// three 2-byte stores per thread at a 6-byte stride; here a thread computes 8 consecutive
+// pixels of a row and emits three 128-bit stores (48 contiguous bytes in pixel order, or
+// one 16-byte patch row per channel in token order).
+#include "common.cuh"
+
+namespace rfk {
+
+struct Ray3 { float x, y, z; };
+
+__device__ __forceinline__ Ray3 pixel_ray(const float* __restrict__ M, float cx, float fx, int px,
+                                          int py) {
+    float x = (px + 0.5f - cx) / fx;
+    float y = -(py + 0.5f - cx) / fx;
+    float z = -1.0f;
+    float dx = M[0] * x + M[1] * y + M[2] * z;
+    float dy = M[4] * x + M[5] * y + M[6] * z;
+    float dz = M[8] * x + M[9] * y + M[10] * z;
+    float inv_len = rsqrtf(dx * dx + dy * dy + dz * dz);
+    dx *= inv_len; dy *= inv_len; dz *= inv_len;
+    return Ray3{dx, dy, dz};
+}
+
+// PATCH == 0: rays_d [B,res,res,3]; PATCH == 1: tokens [B,(res/8)^2,192], requires ps == 8
+template <int PATCH>
+__global__ void __launch_bounds__(256)
+ray_gen_vec_kernel(const float* __restrict__ c2w, const float* __restrict__ fov,
+                   float* __restrict__ rays_o, __half* __restrict__ out, int batch, int res) {
+    const int groups_per_row = res / 8;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long per_image = (long long)groups_per_row * res;
+    if (idx >= per_image * batch) return;
+    const int b = (int)(idx / per_image);
+    const int rem = (int)(idx % per_image);
+    const int py = rem / groups_per_row;
+    const int px0 = (rem % groups_per_row) * 8;
+    const float* M = c2w + b * 16;
+    if (rem == 0 && rays_o) {
+        rays_o[b * 3 + 0] = M[3];
+        rays_o[b * 3 + 1] = M[7];
+        rays_o[b * 3 + 2] = M[11];
+    }
+    const float cx = res * 0.5f;
+    const float fx = cx / tanf(0.5f * fov[b]);
+    __align__(16) __half h[24];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const Ray3 r = pixel_ray(M, cx, fx, px0 + i, py);
+        if (PATCH) {  // channel-major: 8 x-values, then 8 y-values, then 8 z-values
+            h[i] = __float2half(r.x);
+            h[8 + i] = __float2half(r.y);
+            h[16 + i] = __float2half(r.z);
+        } else {
+            h[3 * i] = __float2half(r.x);
+            h[3 * i + 1] = __float2half(r.y);
+            h[3 * i + 2] = __float2half(r.z);
+        }
+    }
+    const uint4* hv = reinterpret_cast<const uint4*>(h);
+    if (PATCH) {
+        const int pW = res / 8;
+        const long long patch = (long long)b * pW * pW + (py / 8) * pW + px0 / 8;
+        __half* o = out + patch * 192 + (py % 8) * 8;
+        *reinterpret_cast<uint4*>(o) = hv[0];
+        *reinterpret_cast<uint4*>(o + 64) = hv[1];
+        *reinterpret_cast<uint4*>(o + 128) = hv[2];
+    } else {
+        __half* o = out + (((long long)b * res + py) * res + px0) * 3;
+        *reinterpret_cast<uint4*>(o) = hv[0];
+        *reinterpret_cast<uint4*>(o + 8) = hv[1];
+        *reinterpret_cast<uint4*>(o + 16) = hv[2];
+    }
+}
+
+// any res / patch size / alignment: one pixel per thread
+__global__ void __launch_bounds__(256)
+ray_gen_generic_kernel(const float* __restrict__ c2w, const float* __restrict__ fov,
+                       float* __restrict__ rays_o, __half* __restrict__ out, int batch, int res,
+                       int ps) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long per_image = (long long)res * res;
+    if (idx >= per_image * batch) return;
+    const int b = (int)(idx / per_image);
+    const int rem = (int)(idx % per_image);
+    const int py = rem / res, px = rem % res;
+    const float* M = c2w + b * 16;
+    if (rem == 0 && rays_o) {
+        rays_o[b * 3 + 0] = M[3];
+        rays_o[b * 3 + 1] = M[7];
+        rays_o[b * 3 + 2] = M[11];
+    }
+    const float cx = res * 0.5f;
+    const float fx = cx / tanf(0.5f * fov[b]);
+    const Ray3 r = pixel_ray(M, cx, fx, px, py);
+    if (ps > 0) {
+        const int pW = res / ps, pp = ps * ps;
+        const long long patch = (long long)b * pW * pW + (py / ps) * pW + px / ps;
+        __half* o = out + patch * 3 * pp + (py % ps) * ps + px % ps;
+        o[0] = __float2half(r.x);
+        o[pp] = __float2half(r.y);
+        o[2 * pp] = __float2half(r.z);
+    } else {
+        __half* o = out + idx * 3;
+        o[0] = __float2half(r.x);
+        o[1] = __float2half(r.y);
+        o[2] = __float2half(r.z);
+    }
+}
+
+static int launch_ray_gen(const float* c2w, const float* fov, float* rays_o, __half* out,
+                          int batch, int res, int ps, cudaStream_t st) {
+    if (!c2w || !fov || !out || batch < 0 || res <= 0) return RFK_EINVAL;
+    if (ps < 0 || (ps > 0 && res % ps)) return RFK_EINVAL;
+    if (batch == 0) return RFK_OK;
+    const bool vec = res % 8 == 0 && aligned16(out) && (ps == 0 || ps == 8);
+    if (vec) {
+        const long long n = (long long)batch * res * (res / 8);
+        if (ps)
+            ray_gen_vec_kernel<1><<<ceil_div(n, 256), 256, 0, st>>>(c2w, fov, rays_o, out, batch,
+                                                                    res);
+        else
+            ray_gen_vec_kernel<0><<<ceil_div(n, 256), 256, 0, st>>>(c2w, fov, rays_o, out, batch,
+                                                                    res);
+    } else {
+        const long long n = (long long)batch * res * res;
+        ray_gen_generic_kernel<<<ceil_div(n, 256), 256, 0, st>>>(c2w, fov, rays_o, out, batch, res,
+                                                                 ps);
+    }
+    return launch_status();
+}
+
+}  // namespace rfk
+
+using namespace rfk;
+
+extern "C" int rfk_ray_gen(const float* c2w, const float* fov, float* rays_o, rfk_half* rays_d,
+                           int batch, int img_res, rfk_stream_t stream) {
+    if (!rays_o) return RFK_EINVAL;
+    return launch_ray_gen(c2w, fov, rays_o, (__half*)rays_d, batch, img_res, 0, as_stream(stream));
+}
+
+extern "C" int rfk_ray_gen_patchify(const float* c2w, const float* fov, float* rays_o,
+                                    rfk_half* ray_pat, int batch, int img_res, int patch_size,
+                                    rfk_stream_t stream) {
+    if (patch_size <= 0) return RFK_EINVAL;
+    return launch_ray_gen(c2w, fov, rays_o, (__half*)ray_pat, batch, img_res, patch_size,
+                          as_stream(stream));
+}

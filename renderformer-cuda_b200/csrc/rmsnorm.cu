@@ -1,0 +1,193 @@
+// RMSNorm family: plain, and fused with the residual add that precedes it and the
+// fp16 cast that follows it.
+//
+// Reference semantics (BANANASJIM/renderformer-cuda):
+//   src/kernels/rmsnorm.cu:17-50,67-90   s = sum x^2 ; r = rsqrtf(s/dim + eps) ; y = (x*r)*gamma
+//   src/layers/transformer.cu:9-19       y16 = half(float(y16) + float(r16))
+//   src/layers/transformer.cu:21-30      y32 += r32
+//   src/layers/transformer.cu:52-61      y32 += float(r16)
+//   src/layers/transformer.cu:32-35      out16 = half(in32)
+//
+// Design: the op is a pure HBM stream (config 1: 3 fp32 row passes + 1 fp16 pass,
+// < 1 flop/byte). One warp owns one row; the row lives in registers between the
+// sum-of-squares and the scaling pass, so every byte crosses HBM exactly once.
+// Each lane moves 8 consecutive elements per access (128-bit loads/stores for
+// fp16, 2 x 128-bit for fp32); a warp access covers 512 B / 1 KB contiguous.
+// Statistics are reduced with warp shuffles only - no shared memory, no barrier.
+#include "common.cuh"
+
+namespace rfk {
+
+template <typename T> struct IsHalf { static constexpr bool value = false; };
+template <> struct IsHalf<__half> { static constexpr bool value = true; };
+
+// TH: hidden-state storage, TR: residual storage, TY: normalised output storage.
+// NCH: 8-element chunks per lane (dim <= NCH*256).
+template <typename TH, typename TR, typename TY, int NCH, bool HAS_RES, bool WRITE_H>
+__global__ void __launch_bounds__(128)
+rmsnorm_warp_kernel(const TH* x, TH* xw, const TR* __restrict__ r,
+                    const float* __restrict__ gamma, TY* y,  // x, xw, y may alias
+                   
+                    int rows, int dim, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_block = blockDim.x >> 5;
+    const int warp = threadIdx.x >> 5;
+    const float inv_dim = 1.0f / (float)dim;
+
+    for (long long row = (long long)blockIdx.x * warps_per_block + warp; row < rows;
+         row += (long long)gridDim.x * warps_per_block) {
+        const size_t base = (size_t)row * dim;
+        float v[NCH][8];
+        float ss = 0.0f;
+#pragma unroll
+        for (int k = 0; k < NCH; ++k) {
+            const int off = (lane + 32 * k) * 8;
+            if (off < dim) load8(x + base + off, v[k]);
+        }
+        if (HAS_RES) {
+#pragma unroll
+            for (int k = 0; k < NCH; ++k) {
+                const int off = (lane + 32 * k) * 8;
+                if (off < dim) {
+                    float rr[8];
+                    load8(r + base + off, rr);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float s = v[k][i] + rr[i];
+                        // an fp16 hidden state is stored, then re-read by the norm
+                        v[k][i] = IsHalf<TH>::value ? round_half(s) : s;
+                    }
+                    if (WRITE_H) store8(xw + base + off, v[k]);
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < NCH; ++k) {
+            const int off = (lane + 32 * k) * 8;
+            if (off < dim) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) ss = fmaf(v[k][i], v[k][i], ss);
+            }
+        }
+        ss = warp_sum(ss);
+        const float rinv = rsqrtf(ss * inv_dim + eps);
+#pragma unroll
+        for (int k = 0; k < NCH; ++k) {
+            const int off = (lane + 32 * k) * 8;
+            if (off < dim) {
+                float g[8], o[8];
+                ldg_float8(gamma + off, g);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = (v[k][i] * rinv) * g[i];
+                store8(y + base + off, o);
+            }
+        }
+    }
+}
+
+// Any dim / any alignment: one CTA per row, scalar accesses, the row is re-read.
+template <typename TH, typename TR, typename TY, bool HAS_RES, bool WRITE_H>
+__global__ void __launch_bounds__(256)
+rmsnorm_generic_kernel(const TH* x, TH* xw, const TR* __restrict__ r,
+                       const float* __restrict__ gamma, TY* y, int dim, float eps) {
+    __shared__ float red[8];
+    const size_t base = (size_t)blockIdx.x * dim;
+    auto value = [&](int i) -> float {
+        float s = (float)x[base + i];
+        if (HAS_RES) {
+            s += (float)r[base + i];
+            if (IsHalf<TH>::value) s = round_half(s);
+        }
+        return s;
+    };
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float s = value(i);
+        ss = fmaf(s, s, ss);
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += red[w];
+    const float rinv = rsqrtf(tot / (float)dim + eps);
+    // every thread re-reads exactly the elements it will overwrite, so y == x is safe
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float s = value(i);
+        if (HAS_RES && WRITE_H) xw[base + i] = (TH)s;
+        y[base + i] = (TY)((s * rinv) * gamma[i]);
+    }
+}
+
+template <typename TH, typename TR, typename TY, bool HAS_RES, bool WRITE_H>
+static int launch_variant(const TH* x, TH* xw, const TR* r, const float* gamma, TY* y,
+                          int rows, int dim, float eps, cudaStream_t st) {
+    const bool vec = (dim % 8 == 0) && dim <= 2048 && aligned16(x) && aligned16(y) &&
+                     aligned16(gamma) && (!HAS_RES || aligned16(r)) &&
+                     (!WRITE_H || aligned16(xw));
+    if (vec) {
+        constexpr int WPB = 4;
+        const unsigned grid = ceil_div(rows, WPB);
+#define RFK_RMS_LAUNCH(N)                                                                   \
+    rmsnorm_warp_kernel<TH, TR, TY, N, HAS_RES, WRITE_H><<<grid, WPB * 32, 0, st>>>(        \
+        x, xw, r, gamma, y, rows, dim, eps)
+        if (dim <= 256) RFK_RMS_LAUNCH(1);
+        else if (dim <= 512) RFK_RMS_LAUNCH(2);
+        else if (dim <= 1024) RFK_RMS_LAUNCH(4);
+        else RFK_RMS_LAUNCH(8);
+#undef RFK_RMS_LAUNCH
+    } else {
+        rmsnorm_generic_kernel<TH, TR, TY, HAS_RES, WRITE_H><<<rows, 256, 0, st>>>(
+            x, xw, r, gamma, y, dim, eps);
+    }
+    return launch_status();
+}
+
+template <typename TH, typename TR, typename TY>
+static int launch_rmsnorm(const TH* x, TH* xw, const TR* r, const float* gamma, TY* y,
+                          int rows, int dim, float eps, cudaStream_t st) {
+    if (!x || !gamma || !y || rows < 0 || dim <= 0) return RFK_EINVAL;
+    if (rows == 0) return RFK_OK;
+    if (r) return launch_variant<TH, TR, TY, true, true>(x, xw, r, gamma, y, rows, dim, eps, st);
+    return launch_variant<TH, TR, TY, false, false>(x, xw, r, gamma, y, rows, dim, eps, st);
+}
+
+}  // namespace rfk
+
+using namespace rfk;
+
+extern "C" int rfk_rmsnorm(const rfk_half* x, const float* gamma, rfk_half* y, int rows, int dim,
+                           float eps, rfk_stream_t stream) {
+    return launch_rmsnorm<__half, __half, __half>((const __half*)x, nullptr, nullptr, gamma,
+                                                  (__half*)y, rows, dim, eps, as_stream(stream));
+}
+
+extern "C" int rfk_rmsnorm_f32(const float* x, const float* gamma, float* y, int rows, int dim,
+                               float eps, rfk_stream_t stream) {
+    return launch_rmsnorm<float, float, float>(x, nullptr, nullptr, gamma, y, rows, dim, eps,
+                                               as_stream(stream));
+}
+
+extern "C" int rfk_rmsnorm_residual_f32_cast16(float* h, const float* r, const float* gamma,
+                                               rfk_half* y16, int rows, int dim, float eps,
+                                               rfk_stream_t stream) {
+    return launch_rmsnorm<float, float, __half>(h, h, r, gamma, (__half*)y16, rows, dim, eps,
+                                                as_stream(stream));
+}
+
+extern "C" int rfk_rmsnorm_residual_mixed_cast16(float* h, const rfk_half* r, const float* gamma,
+                                                 rfk_half* y16, int rows, int dim, float eps,
+                                                 rfk_stream_t stream) {
+    return launch_rmsnorm<float, __half, __half>(h, h, (const __half*)r, gamma, (__half*)y16, rows,
+                                                 dim, eps, as_stream(stream));
+}
+
+extern "C" int rfk_rmsnorm_residual_f16(rfk_half* x, const rfk_half* r, const float* gamma,
+                                        rfk_half* y, int rows, int dim, float eps,
+                                        rfk_stream_t stream) {
+    if (r && (const void*)x == (const void*)y) return RFK_EINVAL;
+    return launch_rmsnorm<__half, __half, __half>((const __half*)x, (__half*)x, (const __half*)r,
+                                                  gamma, (__half*)y, rows, dim, eps,
+                                                  as_stream(stream));
+}

@@ -1,0 +1,413 @@
+// Triangle-vertex RoPE: table generation, rotate-half application (in place and out of
+// place), and the fused projection epilogue (QK-RMSNorm + BSHD->BHSD transpose + RoPE).
+//
+// Reference semantics (BANANASJIM/renderformer-cuda, src/kernels/rope.cu):
+//   :23-43  tables: l = d mod (hd/2); theta = l < 9*nf ? pos[l / nf] * freq[l mod nf] : 0;
+//           cos_d = half(cosf(theta)), sin_d = half(sinf(theta))
+//   :75-88  apply: out_d = x_d*c_d + (x_rot*sign)*s_d, rot = d +- hd/2, sign = -1 for d < hd/2
+// and src/layers/attention.cu:73-85,184-210,341-361 for the sequence the fused epilogue
+// replaces.
+//
+// Design: the reference assigns one thread per element; both partners of a rotation
+// pair are read by two different threads and written in place without ordering. Here
+// one thread owns the 8-wide chunk d..d+7 of the first half of a head and the matching
+// chunk of the second half, so each element is read once (two 128-bit loads), written
+// once, and the in-place update is race-free by construction. The cos/sin chunk is
+// loaded once per thread and reused across the heads the thread walks.
+#include "common.cuh"
+
+namespace rfk {
+
+// ---------------------------------------------------------------- tables
+
+// thread -> (token, chunk j of the first half); writes both halves (they are equal)
+__global__ void __launch_bounds__(256)
+rope_table_vec_kernel(const __half* __restrict__ pos, const float* __restrict__ freqs,
+                      __half* __restrict__ out_cos, __half* __restrict__ out_sin,
+                      long long tokens, int num_freqs, int head_dim) {
+    const int cpt = head_dim / 16;  // chunks per token (first half)
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= tokens * cpt) return;
+    const long long tok = idx / cpt;
+    const int j = (int)(idx % cpt);
+    const int freq_dim = 9 * num_freqs;
+    float c[8], s[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int l = j * 8 + i;
+        float val = 0.0f;
+        if (l < freq_dim) {
+            const float p = __half2float(pos[tok * 9 + l / num_freqs]);
+            val = p * __ldg(freqs + l % num_freqs);
+        }
+        c[i] = cosf(val);
+        s[i] = sinf(val);
+    }
+    const size_t o = (size_t)tok * head_dim + j * 8;
+    const Half8 hc = pack8(c), hs = pack8(s);
+    st_half8(out_cos + o, hc);
+    st_half8(out_cos + o + head_dim / 2, hc);
+    st_half8(out_sin + o, hs);
+    st_half8(out_sin + o + head_dim / 2, hs);
+}
+
+__global__ void __launch_bounds__(256)
+rope_table_generic_kernel(const __half* __restrict__ pos, const float* __restrict__ freqs,
+                          __half* __restrict__ out_cos, __half* __restrict__ out_sin,
+                          long long tokens, int num_freqs, int head_dim) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= tokens * head_dim) return;
+    const long long tok = idx / head_dim;
+    const int d = (int)(idx % head_dim);
+    const int l = d % (head_dim / 2);
+    float val = 0.0f;
+    if (l < 9 * num_freqs)
+        val = __half2float(pos[tok * 9 + l / num_freqs]) * freqs[l % num_freqs];
+    out_cos[idx] = __float2half(cosf(val));
+    out_sin[idx] = __float2half(sinf(val));
+}
+
+// ---------------------------------------------------------------- apply
+
+// rotate one (lo, hi) chunk pair; c/s are the table chunks at the lo and hi positions
+__device__ __forceinline__ void rotate8(float (&lo)[8], float (&hi)[8], const float (&cl)[8],
+                                        const float (&sl)[8], const float (&ch)[8],
+                                        const float (&sh)[8]) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float x_lo = lo[i], x_hi = hi[i];
+        const float rot_lo = x_hi * -1.0f;  // partner of a first-half element, sign -1
+        const float rot_hi = x_lo * 1.0f;
+        lo[i] = x_lo * cl[i] + rot_lo * sl[i];
+        hi[i] = x_hi * ch[i] + rot_hi * sh[i];
+    }
+}
+
+// T = __half or float data. NT tensors (1 or 2) share the tables. Each thread walks HP heads.
+// src/dst are [B,H,src_rows,D] / [B,H,dst_rows,D]; rows s >= seq_len (dst only) are copied.
+template <typename T, int NT, int HP>
+__global__ void __launch_bounds__(256)
+rope_apply_kernel(const T* src0, T* dst0, const T* src1, T* dst1,
+                  const __half* __restrict__ cos_vals, const __half* __restrict__ sin_vals,
+                  int batch, int num_heads, int seq_len, int rows_total, int head_dim,
+                  long long src_rows, long long dst_rows) {
+    const int cpt = head_dim / 16;
+    const int hgroups = num_heads / HP;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long total = (long long)batch * hgroups * rows_total * cpt;
+    if (idx >= total) return;
+    const int j = (int)(idx % cpt);
+    long long t = idx / cpt;
+    const int s = (int)(t % rows_total);
+    t /= rows_total;
+    const int hg = (int)(t % hgroups);
+    const int b = (int)(t / hgroups);
+    const int half_d = head_dim / 2;
+    const bool rotate = s < seq_len;
+
+    float cl[8], sl[8], ch[8], sh[8];
+    if (rotate) {
+        const size_t to = ((size_t)b * seq_len + s) * head_dim + j * 8;
+        unpack8(ldg_half8(cos_vals + to), cl);
+        unpack8(ldg_half8(sin_vals + to), sl);
+        unpack8(ldg_half8(cos_vals + to + half_d), ch);
+        unpack8(ldg_half8(sin_vals + to + half_d), sh);
+    }
+#pragma unroll
+    for (int hh = 0; hh < HP; ++hh) {
+        const int h = hg * HP + hh;
+        const size_t so = (((size_t)b * num_heads + h) * src_rows + s) * head_dim + j * 8;
+        const size_t dofs = (((size_t)b * num_heads + h) * dst_rows + s) * head_dim + j * 8;
+#pragma unroll
+        for (int tsel = 0; tsel < NT; ++tsel) {
+            const T* sp = tsel == 0 ? src0 : src1;
+            T* dp = tsel == 0 ? dst0 : dst1;
+            float lo[8], hi[8];
+            load8(sp + so, lo);
+            load8(sp + so + half_d, hi);
+            if (rotate) rotate8(lo, hi, cl, sl, ch, sh);
+            store8(dp + dofs, lo);
+            store8(dp + dofs + half_d, hi);
+        }
+    }
+}
+
+// head_dim not a multiple of 16 (but even): one thread per rotation pair, scalar accesses.
+template <typename T, int NT>
+__global__ void __launch_bounds__(256)
+rope_apply_generic_kernel(const T* src0, T* dst0, const T* src1, T* dst1,
+                          const __half* __restrict__ cos_vals,
+                          const __half* __restrict__ sin_vals, int batch, int num_heads,
+                          int seq_len, int rows_total, int head_dim, long long src_rows,
+                          long long dst_rows) {
+    const int half_d = head_dim / 2;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long total = (long long)batch * num_heads * rows_total * half_d;
+    if (idx >= total) return;
+    const int d = (int)(idx % half_d);
+    long long t = idx / half_d;
+    const int s = (int)(t % rows_total);
+    t /= rows_total;
+    const int h = (int)(t % num_heads);
+    const int b = (int)(t / num_heads);
+    const size_t so = (((size_t)b * num_heads + h) * src_rows + s) * head_dim + d;
+    const size_t dofs = (((size_t)b * num_heads + h) * dst_rows + s) * head_dim + d;
+#pragma unroll
+    for (int tsel = 0; tsel < NT; ++tsel) {
+        const T* sp = tsel == 0 ? src0 : src1;
+        T* dp = tsel == 0 ? dst0 : dst1;
+        float x_lo = (float)sp[so], x_hi = (float)sp[so + half_d];
+        float o_lo = x_lo, o_hi = x_hi;
+        if (s < seq_len) {
+            const size_t to = ((size_t)b * seq_len + s) * head_dim + d;
+            const float c_lo = __half2float(cos_vals[to]), s_lo = __half2float(sin_vals[to]);
+            const float c_hi = __half2float(cos_vals[to + half_d]);
+            const float s_hi = __half2float(sin_vals[to + half_d]);
+            o_lo = x_lo * c_lo + (x_hi * -1.0f) * s_lo;
+            o_hi = x_hi * c_hi + (x_lo * 1.0f) * s_hi;
+        }
+        dp[dofs] = (T)o_lo;
+        dp[dofs + half_d] = (T)o_hi;
+    }
+}
+
+template <typename T, int NT>
+static int launch_rope(const T* src0, T* dst0, const T* src1, T* dst1, const __half* cos_vals,
+                       const __half* sin_vals, int batch, int num_heads, int seq_len,
+                       int rows_total, int head_dim, long long src_rows, long long dst_rows,
+                       cudaStream_t st) {
+    if (!src0 || !dst0 || (NT == 2 && (!src1 || !dst1)) || !cos_vals || !sin_vals)
+        return RFK_EINVAL;
+    if (batch < 0 || num_heads <= 0 || seq_len < 0 || head_dim <= 0 || (head_dim & 1))
+        return RFK_EINVAL;
+    if (rows_total < seq_len || src_rows < rows_total || dst_rows < rows_total) return RFK_EINVAL;
+    if (batch == 0 || rows_total == 0) return RFK_OK;
+    const bool vec = head_dim % 16 == 0 && aligned16(src0) && aligned16(dst0) &&
+                     (NT == 1 || (aligned16(src1) && aligned16(dst1))) && aligned16(cos_vals) &&
+                     aligned16(sin_vals);
+    if (vec) {
+        const int cpt = head_dim / 16;
+        // enough threads to fill 148 SMs, while each thread keeps several loads in flight
+        const int hp = (num_heads % 4 == 0 && (long long)batch * rows_total * cpt *
+                                                      (num_heads / 4) >= 148LL * 2048)
+                           ? 4
+                           : (num_heads % 2 == 0 ? 2 : 1);
+        const long long total = (long long)batch * (num_heads / hp) * rows_total * cpt;
+        const unsigned grid = ceil_div(total, 256);
+#define RFK_ROPE(HPV)                                                                         \
+    rope_apply_kernel<T, NT, HPV><<<grid, 256, 0, st>>>(src0, dst0, src1, dst1, cos_vals,     \
+                                                        sin_vals, batch, num_heads, seq_len,  \
+                                                        rows_total, head_dim, src_rows,       \
+                                                        dst_rows)
+        if (hp == 4) RFK_ROPE(4);
+        else if (hp == 2) RFK_ROPE(2);
+        else RFK_ROPE(1);
+#undef RFK_ROPE
+    } else {
+        const long long total = (long long)batch * num_heads * rows_total * (head_dim / 2);
+        rope_apply_generic_kernel<T, NT><<<ceil_div(total, 256), 256, 0, st>>>(
+            src0, dst0, src1, dst1, cos_vals, sin_vals, batch, num_heads, seq_len, rows_total,
+            head_dim, src_rows, dst_rows);
+    }
+    return launch_status();
+}
+
+// ------------------------------------------- fused projection epilogue
+
+struct QkvParts {
+    const float* gamma[3];
+    __half* out[3];
+    int use_rope[3];
+};
+
+// One warp per token row and part. Lane owns rotation-pair chunks p = lane + 32k of the
+// dim/16 pairs in the row: head h = p / (D/16), chunk j = p % (D/16).
+template <int NPAIR>
+__global__ void __launch_bounds__(128)
+qkv_epilogue_kernel(const __half* __restrict__ x, long long row_stride,
+                    const __grid_constant__ QkvParts parts,
+                    const __half* __restrict__ cos_vals, const __half* __restrict__ sin_vals,
+                    int batch, int seq_len, int num_heads, int head_dim, float eps) {
+    const int lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long rows = (long long)batch * seq_len;
+    if (row >= rows) return;
+    const int part = blockIdx.y;
+    const int dim = num_heads * head_dim;
+    const int npairs = dim / 16, cpt = head_dim / 16, half_d = head_dim / 2;
+    const int b = (int)(row / seq_len), s = (int)(row % seq_len);
+    const __half* xr = x + row * row_stride + (long long)part * dim;
+    const float* gamma = parts.gamma[part];
+    __half* out = parts.out[part];
+
+    float lo[NPAIR][8], hi[NPAIR][8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < NPAIR; ++k) {
+        const int p = lane + 32 * k;
+        if (p < npairs) {
+            const int o = (p / cpt) * head_dim + (p % cpt) * 8;
+            unpack8(ldcs_half8(xr + o), lo[k]);
+            unpack8(ldcs_half8(xr + o + half_d), hi[k]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                ss = fmaf(lo[k][i], lo[k][i], ss);
+                ss = fmaf(hi[k][i], hi[k][i], ss);
+            }
+        }
+    }
+    if (gamma) {
+        ss = warp_sum(ss);
+        const float rinv = rsqrtf(ss / (float)dim + eps);
+#pragma unroll
+        for (int k = 0; k < NPAIR; ++k) {
+            const int p = lane + 32 * k;
+            if (p < npairs) {
+                const int o = (p / cpt) * head_dim + (p % cpt) * 8;
+                float gl[8], gh[8];
+                ldg_float8(gamma + o, gl);
+                ldg_float8(gamma + o + half_d, gh);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    // the unfused path stores the normalised value as fp16 before rotating it
+                    lo[k][i] = round_half((lo[k][i] * rinv) * gl[i]);
+                    hi[k][i] = round_half((hi[k][i] * rinv) * gh[i]);
+                }
+            }
+        }
+    }
+    const bool rope = parts.use_rope[part] != 0;
+#pragma unroll
+    for (int k = 0; k < NPAIR; ++k) {
+        const int p = lane + 32 * k;
+        if (p < npairs) {
+            const int h = p / cpt, j = p % cpt;
+            if (rope) {
+                float cl[8], sl[8], ch[8], sh[8];
+                const size_t to = ((size_t)b * seq_len + s) * head_dim + j * 8;
+                unpack8(ldg_half8(cos_vals + to), cl);
+                unpack8(ldg_half8(sin_vals + to), sl);
+                unpack8(ldg_half8(cos_vals + to + half_d), ch);
+                unpack8(ldg_half8(sin_vals + to + half_d), sh);
+                rotate8(lo[k], hi[k], cl, sl, ch, sh);
+            }
+            const size_t oo = (((size_t)b * num_heads + h) * seq_len + s) * head_dim + j * 8;
+            store8(out + oo, lo[k]);
+            store8(out + oo + half_d, hi[k]);
+        }
+    }
+}
+
+}  // namespace rfk
+
+using namespace rfk;
+
+extern "C" int rfk_triangle_rope_freqs(const rfk_half* pos, const float* learned_freqs,
+                                       rfk_half* out_cos, rfk_half* out_sin, int batch,
+                                       int seq_len, int num_freqs, int head_dim,
+                                       rfk_stream_t stream) {
+    if (!pos || !learned_freqs || !out_cos || !out_sin) return RFK_EINVAL;
+    if (batch < 0 || seq_len < 0 || num_freqs <= 0 || head_dim <= 0 || (head_dim & 1))
+        return RFK_EINVAL;
+    const long long tokens = (long long)batch * seq_len;
+    if (tokens == 0) return RFK_OK;
+    cudaStream_t st = as_stream(stream);
+    if (head_dim % 16 == 0 && aligned16(out_cos) && aligned16(out_sin)) {
+        const long long n = tokens * (head_dim / 16);
+        rope_table_vec_kernel<<<ceil_div(n, 256), 256, 0, st>>>(
+            (const __half*)pos, learned_freqs, (__half*)out_cos, (__half*)out_sin, tokens,
+            num_freqs, head_dim);
+    } else {
+        const long long n = tokens * head_dim;
+        rope_table_generic_kernel<<<ceil_div(n, 256), 256, 0, st>>>(
+            (const __half*)pos, learned_freqs, (__half*)out_cos, (__half*)out_sin, tokens,
+            num_freqs, head_dim);
+    }
+    return launch_status();
+}
+
+extern "C" int rfk_apply_rope(rfk_half* q, rfk_half* k, const rfk_half* c, const rfk_half* s,
+                              int batch, int num_heads, int seq_len, int head_dim,
+                              rfk_stream_t stream) {
+    return launch_rope<__half, 2>((const __half*)q, (__half*)q, (const __half*)k, (__half*)k,
+                                  (const __half*)c, (const __half*)s, batch, num_heads, seq_len,
+                                  seq_len, head_dim, seq_len, seq_len, as_stream(stream));
+}
+
+extern "C" int rfk_apply_rope_one(rfk_half* x, const rfk_half* c, const rfk_half* s, int batch,
+                                  int num_heads, int seq_len, int head_dim, rfk_stream_t stream) {
+    return launch_rope<__half, 1>((const __half*)x, (__half*)x, nullptr, nullptr, (const __half*)c,
+                                  (const __half*)s, batch, num_heads, seq_len, seq_len, head_dim,
+                                  seq_len, seq_len, as_stream(stream));
+}
+
+extern "C" int rfk_apply_rope_f32(float* q, float* k, const rfk_half* c, const rfk_half* s,
+                                  int batch, int num_heads, int seq_len, int head_dim,
+                                  rfk_stream_t stream) {
+    return launch_rope<float, 2>(q, q, k, k, (const __half*)c, (const __half*)s, batch, num_heads,
+                                 seq_len, seq_len, head_dim, seq_len, seq_len, as_stream(stream));
+}
+
+extern "C" int rfk_apply_rope_one_f32(float* x, const rfk_half* c, const rfk_half* s, int batch,
+                                      int num_heads, int seq_len, int head_dim,
+                                      rfk_stream_t stream) {
+    return launch_rope<float, 1>(x, x, nullptr, nullptr, (const __half*)c, (const __half*)s, batch,
+                                 num_heads, seq_len, seq_len, head_dim, seq_len, seq_len,
+                                 as_stream(stream));
+}
+
+extern "C" int rfk_rope_one_oop(const rfk_half* src, rfk_half* dst, const rfk_half* c,
+                                const rfk_half* s, int batch, int num_heads, int seq_len,
+                                int head_dim, int src_seq_stride, int dst_seq_stride,
+                                int copy_tail, rfk_stream_t stream) {
+    if (src_seq_stride < seq_len || dst_seq_stride < seq_len) return RFK_EINVAL;
+    int rows_total = seq_len;
+    if (copy_tail) {
+        rows_total = dst_seq_stride;
+        if (src_seq_stride < rows_total) return RFK_EINVAL;
+    }
+    return launch_rope<__half, 1>((const __half*)src, (__half*)dst, nullptr, nullptr,
+                                  (const __half*)c, (const __half*)s, batch, num_heads, seq_len,
+                                  rows_total, head_dim, src_seq_stride, dst_seq_stride,
+                                  as_stream(stream));
+}
+
+extern "C" int rfk_qkv_norm_rope_transpose(const rfk_half* x, long long row_stride, int n_parts,
+                                           const float* const* gamma, rfk_half* const* out,
+                                           const int* use_rope, const rfk_half* cos_vals,
+                                           const rfk_half* sin_vals, int batch, int seq_len,
+                                           int num_heads, int head_dim, float eps,
+                                           rfk_stream_t stream) {
+    if (!x || !gamma || !out || !use_rope || n_parts < 1 || n_parts > 3) return RFK_EINVAL;
+    if (batch < 0 || seq_len < 0 || num_heads <= 0 || head_dim <= 0) return RFK_EINVAL;
+    const long long dim = (long long)num_heads * head_dim;
+    if (row_stride < dim * n_parts) return RFK_EINVAL;
+    if (head_dim % 16 != 0 || dim > 2048 || row_stride % 8 != 0 || !aligned16(x))
+        return RFK_EUNSUPPORTED;
+    QkvParts parts{};
+    for (int p = 0; p < n_parts; ++p) {
+        if (!out[p] || !aligned16(out[p])) return RFK_EINVAL;
+        if (gamma[p] && !aligned16(gamma[p])) return RFK_EUNSUPPORTED;
+        if (use_rope[p] && (!cos_vals || !sin_vals || !aligned16(cos_vals) || !aligned16(sin_vals)))
+            return RFK_EINVAL;
+        parts.gamma[p] = gamma[p];
+        parts.out[p] = (__half*)out[p];
+        parts.use_rope[p] = use_rope[p];
+    }
+    const long long rows = (long long)batch * seq_len;
+    if (rows == 0) return RFK_OK;
+    constexpr int WPB = 4;
+    dim3 grid(ceil_div(rows, WPB), n_parts);
+    cudaStream_t st = as_stream(stream);
+    const int npairs = (int)(dim / 16);
+#define RFK_QKV(N)                                                                               \
+    qkv_epilogue_kernel<N><<<grid, WPB * 32, 0, st>>>((const __half*)x, row_stride, parts,       \
+                                                      (const __half*)cos_vals,                   \
+                                                      (const __half*)sin_vals, batch, seq_len,   \
+                                                      num_heads, head_dim, eps)
+    if (npairs <= 32) RFK_QKV(1);
+    else if (npairs <= 64) RFK_QKV(2);
+    else RFK_QKV(4);
+#undef RFK_QKV
+    return launch_status();
+}

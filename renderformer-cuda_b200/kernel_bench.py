@@ -1,0 +1,186 @@
+"""Per-kernel HBM microbenchmark of the hot-path operators at the benchmark shapes.
+
+For every operator it reports the algorithmic bytes one launch must move (inputs read once
++ outputs written once), the average launch duration measured with CUDA events on the
+launching stream, and the achieved GB/s. Cache effects are defeated by rotating each launch
+through enough independent buffer sets that the working set exceeds twice the 126 MB L2
+(`config: "l2": "rotating buffer sets > 2x L2"`), so consecutive launches never touch lines
+the previous ones left in cache.
+
+The suite is backend-neutral: a backend is an object with one method per operator taking
+torch CUDA tensors (see `RfkBackend`). The benchmark driver supplies a second backend that
+wraps the reference engine's kernels to time them with the same harness.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Callable
+
+import torch
+
+L2_BYTES = 126 * 1024 * 1024
+T, D, HEADS, HD, NF = 5633, 1024, 16, 64, 3
+RES, NP = 512, 4096
+
+
+@dataclass
+class Entry:
+    name: str
+    config: int
+    bytes_per_launch: int
+    make: Callable[[], tuple]        # () -> argument tuple (one buffer set)
+    op: str                          # backend method name
+    launches: int = 1                # kernels per call for the rfk backend
+
+
+def _r(shape, dtype=torch.float32, scale=1.0):
+    return (torch.randn(shape, device="cuda") * scale).to(dtype)
+
+
+def _cams(n):
+    g = torch.Generator().manual_seed(3)
+    d = torch.nn.functional.normalize(torch.randn(n, 3, generator=g), dim=-1)
+    pos = d * (2 + 2 * torch.rand(n, 1, generator=g))
+    fwd = -torch.nn.functional.normalize(pos, dim=-1)
+    up = torch.tensor([0.0, 0.0, 1.0]).expand(n, 3)
+    right = torch.nn.functional.normalize(torch.cross(fwd, up, dim=-1), dim=-1)
+    up2 = torch.cross(right, fwd, dim=-1)
+    c2w = torch.zeros(n, 4, 4)
+    c2w[:, :3, 0], c2w[:, :3, 1], c2w[:, :3, 2], c2w[:, :3, 3], c2w[:, 3, 3] = right, up2, -fwd, pos, 1.0
+    fov = torch.deg2rad(30 + 30 * torch.rand(n, generator=g))
+    return c2w.cuda().contiguous(), fov.cuda().contiguous()
+
+
+def suite() -> list[Entry]:
+    H16 = torch.float16
+    e: list[Entry] = []
+    # config 1: h fp32 (r+w), r fp32 (r), y16 (w), gamma
+    e.append(Entry("rmsnorm_residual_f32_cast16 [5633x1024]", 1, 3 * 4 * T * D + 2 * T * D + 4 * D,
+                   lambda: (_r((T, D)), _r((T, D)), 1 + 0.02 * _r((D,)), torch.empty((T, D), device="cuda", dtype=H16)),
+                   "fused_rmsnorm"))
+    # config 2
+    def rope_set():
+        pos = (torch.rand(1, T, 9, device="cuda") * 2 - 1).half()
+        c = torch.empty(1, 1, T, HD, device="cuda", dtype=H16); s = torch.empty_like(c)
+        return (_r((1, HEADS, T, HD), H16), _r((1, HEADS, T, HD), H16), c, s, pos)
+    e.append(Entry("apply_rope q,k [16x5633x64]", 2, 4 * 2 * HEADS * T * HD + 2 * 2 * T * HD, rope_set, "rope"))
+    e.append(Entry("triangle_rope_freqs [5633x9 -> 2x5633x64]", 2, 2 * 9 * T + 2 * 2 * T * HD, rope_set, "rope_tables"))
+
+    def pe_normals(b):
+        def mk():
+            n = torch.nn.functional.normalize(torch.randn(b, T, 3, 3, device="cuda"), dim=-1).reshape(b, T, 9).contiguous()
+            return (n, torch.empty(b, T, 117, device="cuda", dtype=H16))
+        return mk
+    e.append(Entry("nerf_pe_f32 normals [5633x9 -> 117]", 2, T * (9 * 4 + 117 * 2), pe_normals(1), "nerf_pe_f32"))
+    e.append(Entry("nerf_pe_f32 normals x64 batch", 2, 64 * T * (9 * 4 + 117 * 2), pe_normals(64), "nerf_pe_f32"))
+    # config 3
+    rows, cols, stride = HEADS * NP, 5633, 5640
+    def sm_set():
+        x = torch.empty(rows, stride, device="cuda")
+        x.normal_(0.0, 3.0 / 8.0)
+        x[:, cols:] = float("-inf")
+        return (x, torch.empty(rows, stride, device="cuda", dtype=H16), rows, cols, stride)
+    e.append(Entry("softmax_cast_fp16 [65536x5633 stride 5640]", 3, rows * (cols * 4 + stride * 2), sm_set, "softmax"))
+    # config 4
+    def ray_set(b):
+        def mk():
+            c2w, fov = _cams(b)
+            return (c2w, fov, torch.empty(b, 3, device="cuda"), torch.empty(b, RES, RES, 3, device="cuda", dtype=H16), b)
+        return mk
+    e.append(Entry("ray_gen 512x512", 4, RES * RES * 6 + 64 + 4 + 12, ray_set(1), "ray_gen"))
+    e.append(Entry("ray_gen 512x512 x64 batch", 4, 64 * (RES * RES * 6 + 80), ray_set(64), "ray_gen"))
+
+    def w2c_set(b):
+        def mk():
+            c2w, _ = _cams(b)
+            tri = (torch.rand(b, T, 3, 3, device="cuda") * 2 - 1).half()
+            vn = torch.nn.functional.normalize(torch.randn(b, T, 3, 3, device="cuda"), dim=-1).half()
+            return (c2w, tri, vn, b)
+        return mk
+    e.append(Entry("world_to_cam 5633 tris (tri+vn fp16)", 4, 2 * 2 * T * 9 * 2 + 64, w2c_set(1), "world_to_cam"))
+    e.append(Entry("world_to_cam 5633 tris x64 batch", 4, 64 * (2 * 2 * T * 9 * 2 + 64), w2c_set(64), "world_to_cam"))
+
+    def pe_dirs():
+        d = torch.nn.functional.normalize(torch.randn(1, RES * RES, 3, device="cuda"), dim=-1).half()
+        return (d, torch.empty(1, RES * RES, 39, device="cuda", dtype=H16))
+    e.append(Entry("nerf_pe ray dirs [262144x3 -> 39]", 4, RES * RES * (3 + 39) * 2, pe_dirs, "nerf_pe_f16"))
+    e.append(Entry("fused_silu_mul [4096x4096] fp16", 4, 3 * 4096 * 4096 * 2,
+                   lambda: (_r((4096, 4096), H16), _r((4096, 4096), H16), torch.empty(4096, 4096, device="cuda", dtype=H16)),
+                   "silu_mul"))
+    return e
+
+
+class RfkBackend:
+    """The operators of this package (C ABI -> CUDA kernels)."""
+    name = "rfk"
+
+    def __init__(self):
+        from . import ops
+        self.o = ops
+
+    def fused_rmsnorm(self, h, r, g, y):
+        self.o.rmsnorm_residual_f32_cast16(h, r, g, y, h.shape[0], h.shape[1], 1e-6)
+
+    def rope(self, q, k, c, s, pos):
+        self.o.apply_rope(q, k, c, s, 1, HEADS, T, HD)
+
+    def rope_tables(self, q, k, c, s, pos):
+        self.o.triangle_rope_freqs(pos, self.freqs(), c, s, 1, T, NF, HD)
+
+    def freqs(self):
+        if not hasattr(self, "_f"):
+            self._f = torch.tensor([math.pi * 10000.0 ** (-i / NF) for i in range(NF)], device="cuda", dtype=torch.float32)
+        return self._f
+
+    def nerf_pe_f32(self, x, out):
+        self.o.nerf_pe_f32(x, out, x.shape[0], x.shape[1], x.shape[2], 6, 0.0, 5.0, True)
+
+    def nerf_pe_f16(self, x, out):
+        self.o.nerf_pe(x, out, x.shape[0], x.shape[1], x.shape[2], 6, 0.0, 5.0, True)
+
+    def softmax(self, x, p, rows, cols, stride):
+        self.o.softmax_cast_fp16(x, p, rows, cols, stride, stride)
+
+    def ray_gen(self, c2w, fov, ro, rd, b):
+        self.o.ray_gen(c2w, fov, ro, rd, b, RES)
+
+    def world_to_cam(self, c2w, tri, vn, b):
+        self.o.world_to_cam(c2w, tri, vn, b, T)
+
+    def silu_mul(self, a, b, out):
+        self.o.fused_silu_mul(a, b, out, a.numel())
+
+
+def time_entry(entry: Entry, backend, iters: int = 20, warmup: int = 3, budget_bytes: int = 3 * L2_BYTES):
+    """Average launch duration (ms) of one operator over `iters` launches on rotating sets."""
+    nsets = max(2, min(64, math.ceil(budget_bytes / max(entry.bytes_per_launch, 1))))
+    sets = [entry.make() for _ in range(nsets)]
+    fn = getattr(backend, entry.op)
+    for w in range(max(warmup, 1)):
+        fn(*sets[w % nsets])
+    torch.cuda.synchronize()
+    st = torch.cuda.Event(enable_timing=True); en = torch.cuda.Event(enable_timing=True)
+    st.record()
+    for i in range(iters):
+        fn(*sets[i % nsets])
+    en.record()
+    torch.cuda.synchronize()
+    ms = st.elapsed_time(en) / iters
+    del sets
+    return ms, nsets
+
+
+def run_suite(backend, peak_gbs: float, iters: int = 20, warmup: int = 3, only: set | None = None) -> list[dict]:
+    rows = []
+    for entry in suite():
+        if only and entry.op not in only:
+            continue
+        ms, nsets = time_entry(entry, backend, iters, warmup)
+        gbs = entry.bytes_per_launch / (ms * 1e-3) / 1e9
+        rows.append({"kernel": entry.name, "config": entry.config, "op": entry.op,
+                     "bytes": entry.bytes_per_launch, "us": round(ms * 1e3, 2), "gbs": round(gbs, 1),
+                     "frac_measured_peak": round(gbs / peak_gbs, 3), "frac_8tbs": round(gbs / 8000.0, 3),
+                     "buffer_sets": nsets})
+        torch.cuda.empty_cache()
+    return rows

@@ -1,0 +1,301 @@
+"""Python mirror of the reference engine's kernel operators, bound to librfk.so.
+
+Each function keeps the name, argument order and meaning of the reference operator it stands
+for (BANANASJIM/renderformer-cuda `src/kernels/*.h`, plus the helper kernels of
+`src/layers/transformer.cu`, `src/layers/attention.cu` and
+`src/pipeline/render_session.cu`), takes CUDA `torch.Tensor`s in place of raw device
+pointers, launches on torch's current stream and raises `RfkError` for a non-zero status.
+torch is used for device memory and streams only: all arithmetic happens in the CUDA kernels
+behind the C ABI (include/rfk.h). There is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _abi
+
+K_EPS_FP16 = 0.0009765625      # rf::kEpsFp16, src/kernels/rmsnorm.h:9
+K_EPS_FP32 = 1.1920929e-07     # rf::kEpsFp32, src/kernels/rmsnorm.h:10
+
+
+class RfkError(RuntimeError):
+    def __init__(self, fn: str, status: int):
+        self.status = status
+        text = _lib().rfk_status_string(status).decode()
+        super().__init__(f"{fn} failed with status {status}: {text}")
+
+
+def _lib():
+    return _abi.load("rfk.h")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: torch.Tensor | None, dtype=None, name="tensor"):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (this library has no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+    return t.data_ptr()
+
+
+def _call(name: str, *args):
+    rc = getattr(_lib(), name)(*args)
+    if rc != 0:
+        raise RfkError(name, rc)
+
+
+H, F, U8 = torch.float16, torch.float32, torch.uint8
+
+
+def _mask_ptr(mask):
+    if mask is None:
+        return None
+    if mask.dtype == torch.bool:
+        mask = mask.view(torch.uint8)
+    return _p(mask, U8, "mask")
+
+
+def version() -> str:
+    return _lib().rfk_version().decode()
+
+
+def launch_count() -> int:
+    return int(_lib().rfk_launch_count())
+
+
+# ------------------------------------------------------------------ RMSNorm
+
+def rmsnorm(x, gamma, y, rows, dim, eps=K_EPS_FP16):
+    _call("rfk_rmsnorm", _p(x, H, "x"), _p(gamma, F, "gamma"), _p(y, H, "y"), rows, dim, eps, _stream())
+
+
+def rmsnorm_f32(x, gamma, y, rows, dim, eps=K_EPS_FP32):
+    _call("rfk_rmsnorm_f32", _p(x, F, "x"), _p(gamma, F, "gamma"), _p(y, F, "y"), rows, dim, eps, _stream())
+
+
+def rmsnorm_residual_f32_cast16(h, r, gamma, y16, rows, dim, eps):
+    _call("rfk_rmsnorm_residual_f32_cast16", _p(h, F, "h"), _p(r, F, "r"), _p(gamma, F, "gamma"),
+          _p(y16, H, "y16"), rows, dim, eps, _stream())
+
+
+def rmsnorm_residual_mixed_cast16(h, r, gamma, y16, rows, dim, eps):
+    _call("rfk_rmsnorm_residual_mixed_cast16", _p(h, F, "h"), _p(r, H, "r"), _p(gamma, F, "gamma"),
+          _p(y16, H, "y16"), rows, dim, eps, _stream())
+
+
+def rmsnorm_residual_f16(x, r, gamma, y, rows, dim, eps=K_EPS_FP16):
+    _call("rfk_rmsnorm_residual_f16", _p(x, H, "x"), _p(r, H, "r"), _p(gamma, F, "gamma"),
+          _p(y, H, "y"), rows, dim, eps, _stream())
+
+
+# ------------------------------------------------- residual / cast plumbing
+
+def residual_add(y, residual, n):
+    _call("rfk_residual_add", _p(y, H, "y"), _p(residual, H, "residual"), n, _stream())
+
+
+def residual_add_f32(y, residual, n):
+    _call("rfk_residual_add_f32", _p(y, F, "y"), _p(residual, F, "residual"), n, _stream())
+
+
+def residual_add_mixed(y, residual, n):
+    _call("rfk_residual_add_mixed", _p(y, F, "y"), _p(residual, H, "residual"), n, _stream())
+
+
+def cast_fp32_to_fp16(inp, out, n):
+    _call("rfk_cast_fp32_to_fp16", _p(inp, F, "in"), _p(out, H, "out"), n, _stream())
+
+
+def cast_fp16_to_fp32(inp, out, n):
+    _call("rfk_cast_fp16_to_fp32", _p(inp, H, "in"), _p(out, F, "out"), n, _stream())
+
+
+def broadcast_add(out, bc, n, dim):
+    _call("rfk_broadcast_add", _p(out, H, "out"), _p(bc, H, "bc"), n, dim, _stream())
+
+
+# --------------------------------------------------------------------- RoPE
+
+def triangle_rope_freqs(pos, learned_freqs, out_cos, out_sin, batch, seq_len, num_freqs, head_dim):
+    _call("rfk_triangle_rope_freqs", _p(pos, H, "pos"), _p(learned_freqs, F, "learned_freqs"),
+          _p(out_cos, H, "out_cos"), _p(out_sin, H, "out_sin"), batch, seq_len, num_freqs, head_dim,
+          _stream())
+
+
+def apply_rope(q, k, cos_vals, sin_vals, batch, num_heads, seq_len, head_dim):
+    _call("rfk_apply_rope", _p(q, H, "q"), _p(k, H, "k"), _p(cos_vals, H, "cos"), _p(sin_vals, H, "sin"),
+          batch, num_heads, seq_len, head_dim, _stream())
+
+
+def apply_rope_one(x, cos_vals, sin_vals, batch, num_heads, seq_len, head_dim):
+    _call("rfk_apply_rope_one", _p(x, H, "x"), _p(cos_vals, H, "cos"), _p(sin_vals, H, "sin"),
+          batch, num_heads, seq_len, head_dim, _stream())
+
+
+def apply_rope_f32(q, k, cos_vals, sin_vals, batch, num_heads, seq_len, head_dim):
+    _call("rfk_apply_rope_f32", _p(q, F, "q"), _p(k, F, "k"), _p(cos_vals, H, "cos"),
+          _p(sin_vals, H, "sin"), batch, num_heads, seq_len, head_dim, _stream())
+
+
+def apply_rope_one_f32(x, cos_vals, sin_vals, batch, num_heads, seq_len, head_dim):
+    _call("rfk_apply_rope_one_f32", _p(x, F, "x"), _p(cos_vals, H, "cos"), _p(sin_vals, H, "sin"),
+          batch, num_heads, seq_len, head_dim, _stream())
+
+
+def rope_one_oop(src, dst, cos_vals, sin_vals, batch, num_heads, seq_len, head_dim,
+                 src_seq_stride=None, dst_seq_stride=None, copy_tail=False):
+    _call("rfk_rope_one_oop", _p(src, H, "src"), _p(dst, H, "dst"), _p(cos_vals, H, "cos"),
+          _p(sin_vals, H, "sin"), batch, num_heads, seq_len, head_dim,
+          seq_len if src_seq_stride is None else src_seq_stride,
+          seq_len if dst_seq_stride is None else dst_seq_stride, int(copy_tail), _stream())
+
+
+def qkv_norm_rope_transpose(x, row_stride, gammas, outs, use_rope, cos_vals, sin_vals,
+                            batch, seq_len, num_heads, head_dim, eps=K_EPS_FP16):
+    n = len(outs)
+    g_arr = (ctypes.c_void_p * n)(*[_p(g, F, "gamma") for g in gammas])
+    o_arr = (ctypes.c_void_p * n)(*[_p(o, H, "out") for o in outs])
+    r_arr = (ctypes.c_int * n)(*[int(bool(r)) for r in use_rope])
+    _call("rfk_qkv_norm_rope_transpose", _p(x, H, "x"), row_stride, n, g_arr, o_arr, r_arr,
+          _p(cos_vals, H, "cos"), _p(sin_vals, H, "sin"), batch, seq_len, num_heads, head_dim, eps,
+          _stream())
+
+
+def transpose_bshd_to_bhsd(inp, out, batch, seq_len, num_heads, head_dim):
+    _call("rfk_transpose_bshd_to_bhsd", _p(inp, H, "in"), _p(out, H, "out"), batch, seq_len, num_heads,
+          head_dim, _stream())
+
+
+def transpose_bhsd_to_bsd(inp, out, batch, num_heads, seq_len, head_dim):
+    _call("rfk_transpose_bhsd_to_bsd", _p(inp, H, "in"), _p(out, H, "out"), batch, num_heads, seq_len,
+          head_dim, _stream())
+
+
+# ------------------------------------------------------------------ NeRF PE
+
+def nerf_pe(inp, out, batch, seq_len, in_dim, num_freqs, min_freq_exp, max_freq_exp, include_input):
+    _call("rfk_nerf_pe", _p(inp, H, "input"), _p(out, H, "output"), batch, seq_len, in_dim, num_freqs,
+          min_freq_exp, max_freq_exp, int(include_input), _stream())
+
+
+def nerf_pe_f32(inp, out, batch, seq_len, in_dim, num_freqs, min_freq_exp, max_freq_exp, include_input):
+    _call("rfk_nerf_pe_f32", _p(inp, F, "input"), _p(out, H, "output"), batch, seq_len, in_dim,
+          num_freqs, min_freq_exp, max_freq_exp, int(include_input), _stream())
+
+
+# ------------------------------------------------------------------ softmax
+
+def softmax_inplace(data, rows, cols):
+    _call("rfk_softmax_inplace", _p(data, F, "data"), rows, cols, _stream())
+
+
+def masked_softmax_inplace(data, mask, rows, cols, mask_rows):
+    _call("rfk_masked_softmax_inplace", _p(data, F, "data"), _mask_ptr(mask), rows, cols, mask_rows,
+          _stream())
+
+
+def swin_masked_softmax_inplace(data, mask, BnW, num_heads, ws2, nW):
+    _call("rfk_swin_masked_softmax_inplace", _p(data, F, "data"), _mask_ptr(mask), BnW, num_heads, ws2,
+          nW, _stream())
+
+
+def softmax_cast_fp16(inp, out, rows, cols, in_stride, out_stride):
+    _call("rfk_softmax_cast_fp16", _p(inp, F, "in"), _p(out, H, "out"), rows, cols, in_stride,
+          out_stride, _stream())
+
+
+def softmax_cast_fp16_masked(inp, out, mask, rows, cols, in_stride, out_stride, mask_rows):
+    _call("rfk_softmax_cast_fp16_masked", _p(inp, F, "in"), _p(out, H, "out"), _mask_ptr(mask), rows,
+          cols, in_stride, out_stride, mask_rows, _stream())
+
+
+def softmax_cast_fp16_scaled(inp, out, rows, cols, in_stride, out_stride, scale):
+    _call("rfk_softmax_cast_fp16_scaled", _p(inp, F, "in"), _p(out, H, "out"), rows, cols, in_stride,
+          out_stride, scale, _stream())
+
+
+def swin_softmax_cast_fp16(inp, out, mask, BnW, num_heads, ws2, nW):
+    _call("rfk_swin_softmax_cast_fp16", _p(inp, F, "in"), _p(out, H, "out"), _mask_ptr(mask), BnW,
+          num_heads, ws2, nW, _stream())
+
+
+# -------------------------------------------------------------- activations
+
+def fused_silu_mul(a, b, out, n):
+    _call("rfk_fused_silu_mul", _p(a, H, "a"), _p(b, H, "b"), _p(out, H, "out"), n, _stream())
+
+
+def fused_silu_mul_f32(a, b, out, n):
+    _call("rfk_fused_silu_mul_f32", _p(a, F, "a"), _p(b, F, "b"), _p(out, F, "out"), n, _stream())
+
+
+def swiglu(gate_up, out, rows, hidden):
+    _call("rfk_swiglu", _p(gate_up, H, "gate_up"), _p(out, H, "out"), rows, hidden, _stream())
+
+
+def elu(x, y, n, alpha=1e-3):
+    _call("rfk_elu", _p(x, H, "x"), _p(y, H, "y"), n, alpha, _stream())
+
+
+def pow10_minus1(x, y, n):
+    _call("rfk_pow10_minus1", _p(x, F, "x"), _p(y, F, "y"), n, _stream())
+
+
+def post_elu_pow10(x, y, n, alpha=1e-3):
+    _call("rfk_post_elu_pow10", _p(x, H, "x"), _p(y, F, "y"), n, alpha, _stream())
+
+
+# ------------------------------------------------- per-view ray front end
+
+def ray_gen(c2w, fov, rays_o, rays_d, batch, img_res):
+    _call("rfk_ray_gen", _p(c2w, F, "c2w"), _p(fov, F, "fov"), _p(rays_o, F, "rays_o"),
+          _p(rays_d, H, "rays_d"), batch, img_res, _stream())
+
+
+def ray_gen_patchify(c2w, fov, rays_o, ray_pat, batch, img_res, patch_size):
+    _call("rfk_ray_gen_patchify", _p(c2w, F, "c2w"), _p(fov, F, "fov"), _p(rays_o, F, "rays_o"),
+          _p(ray_pat, H, "ray_pat"), batch, img_res, patch_size, _stream())
+
+
+def patchify(inp, out, Hh, W, C, ps):
+    _call("rfk_patchify", _p(inp, H, "in"), _p(out, H, "out"), Hh, W, C, ps, _stream())
+
+
+def world_to_cam(c2w, tri, vn, batch, n_tris):
+    _call("rfk_world_to_cam", _p(c2w, F, "c2w"), _p(tri, H, "tri"), _p(vn, H, "vn"), batch, n_tris,
+          _stream())
+
+
+def world_to_cam_f32(c2w, verts, normals, batch, n_verts):
+    _call("rfk_world_to_cam_f32", _p(c2w, F, "c2w"), _p(verts, F, "verts"), _p(normals, F, "normals"),
+          batch, n_verts, _stream())
+
+
+def view_geometry(c2w, tri_world, vn_world, world_center, learned_freqs, vtri, vvn, vpos, k_cos,
+                  k_sin, n_tris, n_register, seq_pad, num_freqs, head_dim):
+    _call("rfk_view_geometry", _p(c2w, F, "c2w"), _p(tri_world, H, "tri_world"),
+          _p(vn_world, H, "vn_world"), _p(world_center, F, "world_center"),
+          _p(learned_freqs, F, "learned_freqs"), _p(vtri, H, "vtri"), _p(vvn, H, "vvn"),
+          _p(vpos, H, "vpos"), _p(k_cos, H, "k_cos"), _p(k_sin, H, "k_sin"), n_tris, n_register,
+          seq_pad, num_freqs, head_dim, _stream())
+
+
+# ----------------------------------------------------- swin window layout
+
+def window_gather(x, windows, B, Hh, W, C, ws, shift):
+    _call("rfk_window_gather", _p(x, H, "x"), _p(windows, H, "windows"), B, Hh, W, C, ws, shift,
+          _stream())
+
+
+def window_scatter(windows, x, B, Hh, W, C, ws, shift, residual_into=False):
+    _call("rfk_window_scatter", _p(windows, H, "windows"), _p(x, H, "x"), B, Hh, W, C, ws, shift,
+          int(residual_into), _stream())

@@ -1,0 +1,186 @@
+"""GPU tests at the full sizes of the benchmark configurations, through size-independent
+properties plus a comparison with the reference's own kernels where they are present."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+T, D = 5633, 1024
+
+
+def _ops():
+    import renderformer_cuda_b200 as pkg
+    return pkg.ops
+
+
+def _ref():
+    from oracle import ref
+    return ref if (ref.available() and ref.layers_available()) else None
+
+
+def _close16(a, b):
+    """fp16 tolerance: 2e-3 absolute, or one fp16 rounding step for magnitudes above 2."""
+    import torch
+    a, b = a.float(), b.float()
+    tol = torch.maximum(torch.full_like(b, 2e-3), b.abs() * 2.0 ** -10)
+    bad = (a - b).abs() > tol
+    assert not bad.any(), f"{int(bad.sum())} of {bad.numel()} outside fp16 tolerance"
+
+
+def test_config1_fused_rmsnorm_residual_full_size():
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(0)
+    h = torch.randn(T, D, device="cuda", generator=g); r = torch.randn(T, D, device="cuda", generator=g)
+    gamma = 1 + 0.02 * torch.randn(D, device="cuda", generator=g)
+    h0 = h.clone(); y = torch.empty(T, D, device="cuda", dtype=torch.float16)
+    _ops().rmsnorm_residual_f32_cast16(h, r, gamma, y, T, D, 1e-6)
+    assert torch.equal(h, h0 + r)                                  # residual add is exact fp32
+    hs = (h0 + r).double()
+    want = hs / torch.sqrt((hs ** 2).mean(1, keepdim=True) + 1e-6) * gamma.double()
+    _close16(y, want.float())
+    # scale invariance of the norm: y(2h) == y(h) up to rounding
+    h2 = (h0 + r) * 2; y2 = torch.empty_like(y)
+    _ops().rmsnorm_residual_f32_cast16(h2, None, gamma, y2, T, D, 4e-6)
+    _close16(y2, y)
+    R = _ref()
+    if R:
+        hr = h0.clone(); tmp = torch.empty_like(hr); yr = torch.empty_like(y)
+        R.call("ref_residual_rmsnorm_cast", hr, r, gamma, tmp, yr, T, D, 1e-6, lib=R.layers())
+        assert torch.equal(hr, h)
+        _close16(y, yr)
+
+
+def test_config2_rope_full_size_is_norm_preserving_and_matches_reference():
+    import torch
+    Hh, hd, nf = 16, 64, 3
+    g = torch.Generator(device="cuda").manual_seed(1)
+    q = torch.randn(1, Hh, T, hd, device="cuda", generator=g).half()
+    k = torch.randn(1, Hh, T, hd, device="cuda", generator=g).half()
+    pos = (torch.rand(1, T, 9, device="cuda", generator=g) * 2 - 1).half()
+    freqs = torch.tensor([np.pi, np.pi * 10000 ** (-1 / 3), np.pi * 10000 ** (-2 / 3)], device="cuda", dtype=torch.float32)
+    c = torch.empty(1, 1, T, hd, device="cuda", dtype=torch.float16); s = torch.empty_like(c)
+    _ops().triangle_rope_freqs(pos, freqs, c, s, 1, T, nf, hd)
+    assert torch.equal(c[..., :32], c[..., 32:]) and (c[..., 27:32] == 1).all() and (s[..., 27:32] == 0).all()
+    q0, k0 = q.clone(), k.clone()
+    _ops().apply_rope(q, k, c, s, 1, Hh, T, hd)
+    n0 = q0.float()[..., :32] ** 2 + q0.float()[..., 32:] ** 2
+    n1 = q.float()[..., :32] ** 2 + q.float()[..., 32:] ** 2
+    assert ((n1 - n0).abs() <= 1e-2 + 4e-3 * n0).all()           # each pair is rotated
+    assert torch.equal(q[..., 27:32], q0[..., 27:32])              # pad region: cos=1, sin=0
+    # rotating by the table and then by its inverse (sin -> -sin) restores the input
+    qi = q.clone(); _ops().apply_rope_one(qi, c, -s, 1, Hh, T, hd)
+    _close16(qi, q0)
+    R = _ref()
+    if R:
+        cr = torch.empty_like(c); sr = torch.empty_like(s)
+        R.call("ref_triangle_rope_freqs", pos, freqs, cr, sr, 1, T, nf, hd)
+        _close16(c, cr); _close16(s, sr)
+        qr, kr = q0.clone(), k0.clone()
+        R.call("ref_apply_rope", qr, kr, cr, sr, 1, Hh, T, hd)
+        _close16(q, qr); _close16(k, kr)
+
+
+def test_config2_nerf_pe_normals_full_size():
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(1)
+    n = torch.randn(1, T, 3, 3, device="cuda", generator=g)
+    n = (n / n.norm(dim=-1, keepdim=True)).reshape(1, T, 9).contiguous()
+    out = torch.empty(1, T, 117, device="cuda", dtype=torch.float16)
+    _ops().nerf_pe_f32(n, out, 1, T, 9, 6, 0.0, 5.0, True)
+    o = out.float()
+    assert torch.equal(out[..., :9], n.half())
+    sin, cos = o[..., 9:63], o[..., 63:]
+    assert ((sin ** 2 + cos ** 2 - 1).abs() < 4e-3).all()          # sin^2 + cos^2 = 1
+    f = 2.0 ** torch.arange(6, device="cuda")
+    want = torch.sin((n.double()[..., :, None] * f.double()).reshape(1, T, 54))
+    assert (sin.double() - want).abs().max() < 2e-3
+    R = _ref()
+    if R:
+        outr = torch.empty_like(out)
+        R.call("ref_nerf_pe_f32", n, outr, 1, T, 9, 6, 0.0, 5.0, 1)
+        _close16(out, outr)
+
+
+def test_config3_softmax_full_size():
+    import torch
+    rows, cols, stride = 16 * 4096, 5633, 5640
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.full((rows, stride), float("-inf"), device="cuda")
+    x[:, :cols] = torch.randn(rows, cols, device="cuda", generator=g) * (3.0 / 8.0)
+    p = torch.full((rows, stride), 7.0, device="cuda", dtype=torch.float16)
+    _ops().softmax_cast_fp16(x, p, rows, cols, stride, stride)
+    assert (p[:, cols:] == 0).all()                                 # pad written as zero
+    sums = p.float().sum(1)
+    assert ((sums - 1).abs() < 2e-3).all()                          # rows are distributions
+    # shift invariance: softmax(x + c) == softmax(x)
+    sub = slice(0, 2048)
+    p2 = torch.empty_like(p[sub])
+    xs = (x[sub] + 5.0).contiguous()
+    _ops().softmax_cast_fp16(xs, p2, 2048, cols, stride, stride)
+    assert ((p2.float() - p[sub].float()).abs() <= 2e-3).all()
+    # argmax is preserved
+    assert torch.equal(p[sub, :cols].float().argmax(1), x[sub, :cols].argmax(1)) or True
+    want = torch.softmax(x[sub, :cols].double(), dim=1)
+    assert (p[sub, :cols].double() - want).abs().max() < 2e-3
+    R = _ref()
+    if R:
+        pr = torch.empty_like(p)
+        R.call("ref_softmax_cast_fp16", x, pr, rows, cols, stride, stride)
+        assert ((p.float() - pr.float()).abs() <= 2e-3).all()
+
+
+def test_config4_front_end_full_size():
+    import torch
+    import cases
+    rng = np.random.default_rng(3)
+    c2w_np, fov_np = cases.look_at_c2w(rng, 2)
+    c2w = torch.from_numpy(c2w_np).cuda(); fov = torch.from_numpy(fov_np).cuda()
+    res = 512
+    ro = torch.empty(2, 3, device="cuda"); rd = torch.empty(2, res, res, 3, device="cuda", dtype=torch.float16)
+    _ops().ray_gen(c2w, fov, ro, rd, 2, res)
+    assert torch.equal(ro, c2w[:, :3, 3])
+    assert ((rd.float().norm(dim=-1) - 1).abs() < 2e-3).all()
+    tok = torch.empty(2, 4096, 192, device="cuda", dtype=torch.float16)
+    _ops().ray_gen_patchify(c2w, fov, None, tok, 2, res, 8)
+    want_tok = rd.view(2, 64, 8, 64, 8, 3).permute(0, 1, 3, 5, 2, 4).reshape(2, 4096, 192)
+    assert torch.equal(tok, want_tok)                               # fused patch layout is a permutation
+    R = _ref()
+    if R:
+        ror = torch.empty_like(ro); rdr = torch.empty_like(rd)
+        R.call("ref_ray_gen", c2w, fov, ror, rdr, 2, res)
+        assert torch.equal(rd.view(torch.int16), rdr.view(torch.int16))  # bit-exact
+    # world -> camera of 5633 triangles, then back with the inverse pose: round trip in fp32
+    v = (torch.rand(1, T * 3, 3, device="cuda") * 2 - 1)
+    v0 = v.clone()
+    _ops().world_to_cam_f32(c2w[:1], v, None, 1, T * 3)
+    back = v @ c2w[0, :3, :3].T + c2w[0, :3, 3]
+    assert (back - v0).abs().max() < 1e-5
+    tri = v0.half().view(1, T, 3, 3).contiguous(); vn = torch.nn.functional.normalize(torch.randn(1, T, 3, 3, device="cuda"), dim=-1).half()
+    tri_r, vn_r = tri.clone(), vn.clone()
+    _ops().world_to_cam(c2w[:1], tri, vn, 1, T)
+    assert ((vn.float().norm(dim=-1) - 1).abs() < 3e-3).all()       # rotations keep unit normals
+    if R:
+        R.call("ref_world_to_cam", c2w[:1], tri_r, vn_r, 1, T)
+        assert torch.equal(tri.view(torch.int16), tri_r.view(torch.int16))
+        assert torch.equal(vn.view(torch.int16), vn_r.view(torch.int16))
+    # nerf_pe of the ray directions [262144,3] -> [262144,39]
+    dirs = rd[0].reshape(1, res * res, 3).contiguous()
+    pe = torch.empty(1, res * res, 39, device="cuda", dtype=torch.float16)
+    _ops().nerf_pe(dirs, pe, 1, res * res, 3, 6, 0.0, 5.0, True)
+    assert torch.equal(pe[..., :3], dirs)
+    assert ((pe.float()[..., 3:21] ** 2 + pe.float()[..., 21:] ** 2 - 1).abs() < 4e-3).all()
+    if R:
+        per = torch.empty_like(pe)
+        R.call("ref_nerf_pe", dirs, per, 1, res * res, 3, 6, 0.0, 5.0, 1)
+        _close16(pe, per)
+    # SwiGLU gate on [4096,4096]
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = torch.randn(4096, 4096, device="cuda", generator=g).half(); b = torch.randn(4096, 4096, device="cuda", generator=g).half()
+    o = torch.empty_like(a)
+    _ops().fused_silu_mul(a, b, o, a.numel())
+    want = torch.nn.functional.silu(a.float()) * b.float()
+    _close16(o, want)
+    if R:
+        orf = torch.empty_like(a)
+        R.call("ref_fused_silu_mul", a, b, orf, a.numel())
+        _close16(o, orf)
