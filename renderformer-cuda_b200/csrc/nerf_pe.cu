@@ -9,11 +9,14 @@
 // asynchronous launch.
 //
 // Design: output rows are 2*(in_dim*(2nf+1)) bytes (234 B for the 9-D normals, 78 B for
-// ray directions), never 16-byte multiples, so the output is treated as one flat fp16
-// array and each thread produces 8 consecutive elements with a single 128-bit store.
-// sin/cos arguments are reduced to [-pi, pi] with a two-constant Cody-Waite step and
-// evaluated on the SFU; accurate sinf/cosf would make the ray-direction case
-// (11 M outputs) instruction-bound at ~4x its HBM time.
+// ray directions), never 16-byte multiples, and the reference spends one thread, two
+// integer divisions and one sinf OR cosf per output element, which makes the op
+// instruction-bound (measured: 35 us for the 22 MB ray-direction case on B200 with that
+// structure). Here a CTA owns a tile of consecutive rows whose byte size is a multiple of
+// 16: each (row, d, k) item is evaluated once with a shared range reduction and one
+// sin+cos pair on the SFU, results are staged in shared memory in output order, and the
+// tile is then streamed to HBM with 128-bit stores. Index arithmetic uses multiply-high
+// reciprocals instead of divisions.
 #include "common.cuh"
 #include <cmath>
 
@@ -23,56 +26,100 @@ struct FreqTable {
     float f[32];
 };
 
-__device__ __forceinline__ float sincos_sel(float val, bool is_cos) {
+// n / d for n*d < 2^32 via one multiply-high (m = ceil(2^32 / d)); d == 1 handled apart.
+struct FastDiv {
+    unsigned m, d;
+    __host__ explicit FastDiv(unsigned dd = 1) : m(dd > 1 ? (unsigned)((0x100000000ULL + dd - 1) / dd) : 0), d(dd) {}
+    __device__ __forceinline__ unsigned div(unsigned n) const { return d == 1 ? n : __umulhi(n, m); }
+};
+
+// sin and cos of val: Cody-Waite reduction to [-pi, pi] with 2pi = hi + lo, then the SFU.
+__device__ __forceinline__ void sincos_fast(float val, float& s, float& c) {
     if (fabsf(val) < 8192.0f) {
-        // k = round(val / 2pi); r = val - k*2pi with 2pi split into hi + lo parts
         const float k = rintf(val * 0.15915494309189535f);
-        float r = fmaf(k, -6.2831854820251465f, val);   // 2pi rounded to fp32
-        r = fmaf(k, 1.7484555e-7f, r);                  // 2pi - fl(2pi) = -1.7484555e-7
-        return is_cos ? __cosf(r) : __sinf(r);
+        float r = fmaf(k, -6.2831854820251465f, val);  // 2pi rounded to fp32
+        r = fmaf(k, 1.7484555e-7f, r);                 // fl(2pi) - 2pi
+        __sincosf(r, &s, &c);
+    } else {
+        sincosf(val, &s, &c);
     }
-    return is_cos ? cosf(val) : sinf(val);
 }
+
+constexpr int kPeThreads = 256;
 
 template <typename TI>
-__device__ __forceinline__ float pe_element(const TI* __restrict__ in_row, int feat, int in_dim,
-                                            int num_freqs, int include_input,
-                                            const FreqTable& ft) {
-    int enc = feat;
-    if (include_input) {
-        if (feat < in_dim) return (float)in_row[feat];
-        enc -= in_dim;
+__global__ void __launch_bounds__(kPeThreads)
+nerf_pe_tile_kernel(const TI* __restrict__ input, __half* __restrict__ output, long long rows,
+                    int rows_per_block, int in_dim, int num_freqs, int include_input,
+                    const __grid_constant__ FreqTable ft, FastDiv div_per_row, FastDiv div_nf,
+                    FastDiv div_in, int vec_out) {
+    extern __shared__ __align__(16) __half s_out[];
+    const int per_row = in_dim * num_freqs;
+    const int off = include_input ? in_dim : 0;
+    const int out_dim = 2 * per_row + off;
+    const long long r0 = (long long)blockIdx.x * rows_per_block;
+    const int nrows = (int)min((long long)rows_per_block, rows - r0);
+    const TI* in = input + r0 * in_dim;
+
+    const unsigned items = (unsigned)nrows * per_row;
+    for (unsigned it = threadIdx.x; it < items; it += kPeThreads) {
+        const unsigned r = div_per_row.div(it);
+        const unsigned j = it - r * per_row;
+        const unsigned d = div_nf.div(j);
+        const unsigned k = j - d * num_freqs;
+        const float val = (float)in[r * in_dim + d] * ft.f[k];
+        float s, c;
+        sincos_fast(val, s, c);
+        __half* o = s_out + r * out_dim + off + j;
+        o[0] = __float2half(s);
+        o[per_row] = __float2half(c);
     }
-    const int half_dim = in_dim * num_freqs;
-    const bool is_cos = enc >= half_dim;
-    const int si = is_cos ? enc - half_dim : enc;
-    const int d = si / num_freqs, f = si - d * num_freqs;
-    const float val = (float)in_row[d] * ft.f[f];
-    return sincos_sel(val, is_cos);
+    if (include_input) {
+        const unsigned n = (unsigned)nrows * in_dim;
+        for (unsigned it = threadIdx.x; it < n; it += kPeThreads) {
+            const unsigned r = div_in.div(it);
+            const unsigned d = it - r * in_dim;
+            s_out[r * out_dim + d] = __float2half((float)in[it]);
+        }
+    }
+    __syncthreads();
+    const int n_out = nrows * out_dim;
+    __half* dst = output + r0 * out_dim;
+    if (vec_out) {
+        const int nvec = n_out / 8;
+        for (int v = threadIdx.x; v < nvec; v += kPeThreads)
+            reinterpret_cast<uint4*>(dst)[v] = reinterpret_cast<const uint4*>(s_out)[v];
+        for (int e = nvec * 8 + threadIdx.x; e < n_out; e += kPeThreads) dst[e] = s_out[e];
+    } else {
+        for (int e = threadIdx.x; e < n_out; e += kPeThreads) dst[e] = s_out[e];
+    }
 }
 
+// Rows too wide for a shared-memory tile: one thread per output element.
 template <typename TI>
 __global__ void __launch_bounds__(256)
-nerf_pe_kernel(const TI* __restrict__ input, __half* __restrict__ output, long long total,
-               int in_dim, int num_freqs, int out_dim, int include_input,
-               const __grid_constant__ FreqTable ft, int vec) {
-    const long long e0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
-    if (e0 >= total) return;
-    long long row = e0 / out_dim;
-    int feat = (int)(e0 - row * out_dim);
-    float o[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        o[i] = 0.0f;
-        if (e0 + i < total) o[i] = pe_element(input + row * in_dim, feat, in_dim, num_freqs,
-                                              include_input, ft);
-        if (++feat == out_dim) { feat = 0; ++row; }
-    }
-    if (vec && e0 + 8 <= total) {
-        st_half8(output + e0, pack8(o));
+nerf_pe_flat_kernel(const TI* __restrict__ input, __half* __restrict__ output, long long total,
+                    int in_dim, int num_freqs, int out_dim, int include_input,
+                    const __grid_constant__ FreqTable ft) {
+    const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= total) return;
+    const long long row = e / out_dim;
+    int feat = (int)(e - row * out_dim);
+    const TI* in_row = input + row * in_dim;
+    float o;
+    if (include_input && feat < in_dim) {
+        o = (float)in_row[feat];
     } else {
-        for (int i = 0; i < 8 && e0 + i < total; ++i) output[e0 + i] = __float2half(o[i]);
+        if (include_input) feat -= in_dim;
+        const int half_dim = in_dim * num_freqs;
+        const bool is_cos = feat >= half_dim;
+        const int si = is_cos ? feat - half_dim : feat;
+        const int d = si / num_freqs, f = si - d * num_freqs;
+        float s, c;
+        sincos_fast((float)in_row[d] * ft.f[f], s, c);
+        o = is_cos ? c : s;
     }
+    output[e] = __float2half(o);
 }
 
 template <typename TI>
@@ -82,18 +129,29 @@ static int launch_nerf_pe(const TI* input, __half* output, int batch, int seq_le
     if (!input || !output || batch < 0 || seq_len < 0 || in_dim <= 0 || num_freqs <= 0)
         return RFK_EINVAL;
     if (num_freqs > 32) return RFK_ETOOBIG;
-    const int out_dim = in_dim * num_freqs * 2 + (include_input ? in_dim : 0);
-    const long long total = (long long)batch * seq_len * out_dim;
-    if (total == 0) return RFK_OK;
+    const long long out_dim = (long long)in_dim * num_freqs * 2 + (include_input ? in_dim : 0);
+    const long long rows = (long long)batch * seq_len;
+    if (rows == 0) return RFK_OK;
     FreqTable ft{};
     for (int i = 0; i < num_freqs; ++i) {
         // same expression, in float, as the reference's host loop
         float e = min_exp + (max_exp - min_exp) * i / std::max(num_freqs - 1, 1);
         ft.f[i] = std::pow(2.0f, e);
     }
-    const int vec = aligned16(output);
-    nerf_pe_kernel<TI><<<ceil_div((total + 7) / 8, 256), 256, 0, st>>>(
-        input, output, total, in_dim, num_freqs, out_dim, include_input ? 1 : 0, ft, vec);
+    if (out_dim <= 3072) {
+        // tile rows: a multiple of 8 (so every tile starts 16-byte aligned), ~16 KB of output
+        int rpb = (int)std::max(8LL, std::min(256LL, (8192 / out_dim) & ~7LL));
+        const size_t smem = (size_t)rpb * out_dim * sizeof(__half);
+        const unsigned grid = ceil_div(rows, rpb);
+        nerf_pe_tile_kernel<TI><<<grid, kPeThreads, smem, st>>>(
+            input, output, rows, rpb, in_dim, num_freqs, include_input ? 1 : 0, ft,
+            FastDiv((unsigned)(in_dim * num_freqs)), FastDiv((unsigned)num_freqs),
+            FastDiv((unsigned)in_dim), aligned16(output) ? 1 : 0);
+    } else {
+        const long long total = rows * out_dim;
+        nerf_pe_flat_kernel<TI><<<ceil_div(total, 256), 256, 0, st>>>(
+            input, output, total, in_dim, num_freqs, (int)out_dim, include_input ? 1 : 0, ft);
+    }
     return launch_status();
 }
 

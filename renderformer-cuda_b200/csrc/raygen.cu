@@ -12,17 +12,16 @@
 // required to be bit-identical. What changes is the memory side: the reference issues
 // three 2-byte stores per thread at a 6-byte stride; here a thread computes 8 consecutive
 // pixels of a row and emits three 128-bit stores (48 contiguous bytes in pixel order, or
-// one 16-byte patch row per channel in token order).
+// one 16-byte patch row per channel in token order), and it reuses tanf and the per-column
+// divisions across 4 rows.
 #include "common.cuh"
 
 namespace rfk {
 
 struct Ray3 { float x, y, z; };
 
-__device__ __forceinline__ Ray3 pixel_ray(const float* __restrict__ M, float cx, float fx, int px,
-                                          int py) {
-    float x = (px + 0.5f - cx) / fx;
-    float y = -(py + 0.5f - cx) / fx;
+// x, y: camera-plane coordinates (px+0.5-cx)/fx and -(py+0.5-cx)/fx of the pixel
+__device__ __forceinline__ Ray3 rotate_normalize(const float* __restrict__ M, float x, float y) {
     float z = -1.0f;
     float dx = M[0] * x + M[1] * y + M[2] * z;
     float dy = M[4] * x + M[5] * y + M[6] * z;
@@ -32,18 +31,30 @@ __device__ __forceinline__ Ray3 pixel_ray(const float* __restrict__ M, float cx,
     return Ray3{dx, dy, dz};
 }
 
-// PATCH == 0: rays_d [B,res,res,3]; PATCH == 1: tokens [B,(res/8)^2,192], requires ps == 8
-template <int PATCH>
+__device__ __forceinline__ Ray3 pixel_ray(const float* __restrict__ M, float cx, float fx, int px,
+                                          int py) {
+    float x = (px + 0.5f - cx) / fx;
+    float y = -(py + 0.5f - cx) / fx;
+    return rotate_normalize(M, x, y);
+}
+
+
+// A thread owns an 8-pixel-wide, ROWS-tall strip: the 8 x-coordinates (8 IEEE divisions) and
+// tanf are computed once and reused for every row. ROWS = 4 keeps the kernel HBM-bound when
+// many views are batched; ROWS = 1 gives a single view 4x the threads and the shortest
+// critical path. PATCH == 0: rays_d [B,res,res,3]; PATCH == 1: tokens [B,(res/8)^2,192]
+// (requires ps == 8).
+template <int PATCH, int ROWS>
 __global__ void __launch_bounds__(256)
 ray_gen_vec_kernel(const float* __restrict__ c2w, const float* __restrict__ fov,
                    float* __restrict__ rays_o, __half* __restrict__ out, int batch, int res) {
     const int groups_per_row = res / 8;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long per_image = (long long)groups_per_row * res;
+    const long long per_image = (long long)groups_per_row * (res / ROWS);
     if (idx >= per_image * batch) return;
     const int b = (int)(idx / per_image);
     const int rem = (int)(idx % per_image);
-    const int py = rem / groups_per_row;
+    const int py0 = (rem / groups_per_row) * ROWS;
     const int px0 = (rem % groups_per_row) * 8;
     const float* M = c2w + b * 16;
     if (rem == 0 && rays_o) {
@@ -53,33 +64,41 @@ ray_gen_vec_kernel(const float* __restrict__ c2w, const float* __restrict__ fov,
     }
     const float cx = res * 0.5f;
     const float fx = cx / tanf(0.5f * fov[b]);
-    __align__(16) __half h[24];
+    float xs[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const Ray3 r = pixel_ray(M, cx, fx, px0 + i, py);
-        if (PATCH) {  // channel-major: 8 x-values, then 8 y-values, then 8 z-values
-            h[i] = __float2half(r.x);
-            h[8 + i] = __float2half(r.y);
-            h[16 + i] = __float2half(r.z);
-        } else {
-            h[3 * i] = __float2half(r.x);
-            h[3 * i + 1] = __float2half(r.y);
-            h[3 * i + 2] = __float2half(r.z);
+    for (int i = 0; i < 8; ++i) xs[i] = (px0 + i + 0.5f - cx) / fx;
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        const int py = py0 + r;
+        const float y = -(py + 0.5f - cx) / fx;
+        __align__(16) __half h[24];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const Ray3 d = rotate_normalize(M, xs[i], y);
+            if (PATCH) {  // channel-major: 8 x-values, then 8 y-values, then 8 z-values
+                h[i] = __float2half(d.x);
+                h[8 + i] = __float2half(d.y);
+                h[16 + i] = __float2half(d.z);
+            } else {
+                h[3 * i] = __float2half(d.x);
+                h[3 * i + 1] = __float2half(d.y);
+                h[3 * i + 2] = __float2half(d.z);
+            }
         }
-    }
-    const uint4* hv = reinterpret_cast<const uint4*>(h);
-    if (PATCH) {
-        const int pW = res / 8;
-        const long long patch = (long long)b * pW * pW + (py / 8) * pW + px0 / 8;
-        __half* o = out + patch * 192 + (py % 8) * 8;
-        *reinterpret_cast<uint4*>(o) = hv[0];
-        *reinterpret_cast<uint4*>(o + 64) = hv[1];
-        *reinterpret_cast<uint4*>(o + 128) = hv[2];
-    } else {
-        __half* o = out + (((long long)b * res + py) * res + px0) * 3;
-        *reinterpret_cast<uint4*>(o) = hv[0];
-        *reinterpret_cast<uint4*>(o + 8) = hv[1];
-        *reinterpret_cast<uint4*>(o + 16) = hv[2];
+        const uint4* hv = reinterpret_cast<const uint4*>(h);
+        if (PATCH) {
+            const int pW = res / 8;
+            const long long patch = (long long)b * pW * pW + (py / 8) * pW + px0 / 8;
+            __half* o = out + patch * 192 + (py % 8) * 8;
+            *reinterpret_cast<uint4*>(o) = hv[0];
+            *reinterpret_cast<uint4*>(o + 64) = hv[1];
+            *reinterpret_cast<uint4*>(o + 128) = hv[2];
+        } else {
+            __half* o = out + (((long long)b * res + py) * res + px0) * 3;
+            *reinterpret_cast<uint4*>(o) = hv[0];
+            *reinterpret_cast<uint4*>(o + 8) = hv[1];
+            *reinterpret_cast<uint4*>(o + 16) = hv[2];
+        }
     }
 }
 
@@ -125,13 +144,14 @@ static int launch_ray_gen(const float* c2w, const float* fov, float* rays_o, __h
     if (batch == 0) return RFK_OK;
     const bool vec = res % 8 == 0 && aligned16(out) && (ps == 0 || ps == 8);
     if (vec) {
-        const long long n = (long long)batch * res * (res / 8);
-        if (ps)
-            ray_gen_vec_kernel<1><<<ceil_div(n, 256), 256, 0, st>>>(c2w, fov, rays_o, out, batch,
-                                                                    res);
-        else
-            ray_gen_vec_kernel<0><<<ceil_div(n, 256), 256, 0, st>>>(c2w, fov, rays_o, out, batch,
-                                                                    res);
+        // 4-row strips once the strip threads alone fill every SM (148 x 2048 resident threads)
+        const bool strips = res % 4 == 0 && (long long)batch * res * (res / 8) >= 4LL * kNumSMs * 2048;
+        const long long n = (long long)batch * (res / (strips ? 4 : 1)) * (res / 8);
+        const unsigned grid = ceil_div(n, 256);
+        if (ps && strips) ray_gen_vec_kernel<1, 4><<<grid, 256, 0, st>>>(c2w, fov, rays_o, out, batch, res);
+        else if (ps) ray_gen_vec_kernel<1, 1><<<grid, 256, 0, st>>>(c2w, fov, rays_o, out, batch, res);
+        else if (strips) ray_gen_vec_kernel<0, 4><<<grid, 256, 0, st>>>(c2w, fov, rays_o, out, batch, res);
+        else ray_gen_vec_kernel<0, 1><<<grid, 256, 0, st>>>(c2w, fov, rays_o, out, batch, res);
     } else {
         const long long n = (long long)batch * res * res;
         ray_gen_generic_kernel<<<ceil_div(n, 256), 256, 0, st>>>(c2w, fov, rays_o, out, batch, res,

@@ -22,6 +22,7 @@ import torch
 L2_BYTES = 126 * 1024 * 1024
 T, D, HEADS, HD, NF = 5633, 1024, 16, 64, 3
 RES, NP = 512, 4096
+SOFTMAX_ROWS = HEADS * NP   # 65536 score rows; the CLI can shrink it for profiler captures
 
 
 @dataclass
@@ -59,12 +60,20 @@ def suite() -> list[Entry]:
     e.append(Entry("rmsnorm_residual_f32_cast16 [5633x1024]", 1, 3 * 4 * T * D + 2 * T * D + 4 * D,
                    lambda: (_r((T, D)), _r((T, D)), 1 + 0.02 * _r((D,)), torch.empty((T, D), device="cuda", dtype=H16)),
                    "fused_rmsnorm"))
+    e.append(Entry("rmsnorm_residual_f32_cast16 x8 batch [45064x1024]", 1, 8 * (3 * 4 * T * D + 2 * T * D) + 4 * D,
+                   lambda: (_r((8 * T, D)), _r((8 * T, D)), 1 + 0.02 * _r((D,)), torch.empty((8 * T, D), device="cuda", dtype=H16)),
+                   "fused_rmsnorm"))
     # config 2
     def rope_set():
         pos = (torch.rand(1, T, 9, device="cuda") * 2 - 1).half()
         c = torch.empty(1, 1, T, HD, device="cuda", dtype=H16); s = torch.empty_like(c)
         return (_r((1, HEADS, T, HD), H16), _r((1, HEADS, T, HD), H16), c, s, pos)
     e.append(Entry("apply_rope q,k [16x5633x64]", 2, 4 * 2 * HEADS * T * HD + 2 * 2 * T * HD, rope_set, "rope"))
+
+    def rope_set8():
+        c = torch.empty(8, 1, T, HD, device="cuda", dtype=H16).normal_(); s = torch.empty_like(c).normal_()
+        return (_r((8, HEADS, T, HD), H16), _r((8, HEADS, T, HD), H16), c, s, None)
+    e.append(Entry("apply_rope q,k x8 batch", 2, 8 * (4 * 2 * HEADS * T * HD + 2 * 2 * T * HD), rope_set8, "rope"))
     e.append(Entry("triangle_rope_freqs [5633x9 -> 2x5633x64]", 2, 2 * 9 * T + 2 * 2 * T * HD, rope_set, "rope_tables"))
 
     def pe_normals(b):
@@ -75,13 +84,13 @@ def suite() -> list[Entry]:
     e.append(Entry("nerf_pe_f32 normals [5633x9 -> 117]", 2, T * (9 * 4 + 117 * 2), pe_normals(1), "nerf_pe_f32"))
     e.append(Entry("nerf_pe_f32 normals x64 batch", 2, 64 * T * (9 * 4 + 117 * 2), pe_normals(64), "nerf_pe_f32"))
     # config 3
-    rows, cols, stride = HEADS * NP, 5633, 5640
+    rows, cols, stride = SOFTMAX_ROWS, 5633, 5640
     def sm_set():
         x = torch.empty(rows, stride, device="cuda")
         x.normal_(0.0, 3.0 / 8.0)
         x[:, cols:] = float("-inf")
         return (x, torch.empty(rows, stride, device="cuda", dtype=H16), rows, cols, stride)
-    e.append(Entry("softmax_cast_fp16 [65536x5633 stride 5640]", 3, rows * (cols * 4 + stride * 2), sm_set, "softmax"))
+    e.append(Entry(f"softmax_cast_fp16 [{rows}x5633 stride 5640]", 3, rows * (cols * 4 + stride * 2), sm_set, "softmax"))
     # config 4
     def ray_set(b):
         def mk():
@@ -123,7 +132,7 @@ class RfkBackend:
         self.o.rmsnorm_residual_f32_cast16(h, r, g, y, h.shape[0], h.shape[1], 1e-6)
 
     def rope(self, q, k, c, s, pos):
-        self.o.apply_rope(q, k, c, s, 1, HEADS, T, HD)
+        self.o.apply_rope(q, k, c, s, q.shape[0], HEADS, T, HD)
 
     def rope_tables(self, q, k, c, s, pos):
         self.o.triangle_rope_freqs(pos, self.freqs(), c, s, 1, T, NF, HD)
@@ -153,22 +162,45 @@ class RfkBackend:
 
 
 def time_entry(entry: Entry, backend, iters: int = 20, warmup: int = 3, budget_bytes: int = 3 * L2_BYTES):
-    """Average launch duration (ms) of one operator over `iters` launches on rotating sets."""
+    """Average launch duration (ms) of one operator over `iters` launches on rotating sets.
+
+    The launches are captured once into a CUDA graph and the graph is replayed between two
+    CUDA events, so the figure is device time (kernel + the few hundred ns between graph
+    nodes) and not the host's launch rate. Operators that cannot be captured (the
+    reference's nerf_pe wrappers allocate) are launched eagerly with one event pair per launch.
+    """
     nsets = max(2, min(64, math.ceil(budget_bytes / max(entry.bytes_per_launch, 1))))
     sets = [entry.make() for _ in range(nsets)]
     fn = getattr(backend, entry.op)
-    for w in range(max(warmup, 1)):
+    for w in range(max(warmup, 3)):
         fn(*sets[w % nsets])
     torch.cuda.synchronize()
-    st = torch.cuda.Event(enable_timing=True); en = torch.cuda.Event(enable_timing=True)
-    st.record()
-    for i in range(iters):
-        fn(*sets[i % nsets])
-    en.record()
-    torch.cuda.synchronize()
-    ms = st.elapsed_time(en) / iters
+    if entry.op in getattr(backend, "not_capturable", ()):
+        total = 0.0
+        for i in range(iters):
+            st = torch.cuda.Event(enable_timing=True); en = torch.cuda.Event(enable_timing=True)
+            st.record(); fn(*sets[i % nsets]); en.record()
+            torch.cuda.synchronize()
+            total += st.elapsed_time(en)
+        ms = total / iters
+        mode = "eager, event pair per launch"
+    else:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(iters):
+                fn(*sets[i % nsets])
+        graph.replay()  # warm replay
+        torch.cuda.synchronize()
+        st = torch.cuda.Event(enable_timing=True); en = torch.cuda.Event(enable_timing=True)
+        st.record()
+        graph.replay()
+        en.record()
+        torch.cuda.synchronize()
+        ms = st.elapsed_time(en) / iters
+        mode = "cuda graph replay"
+        del graph
     del sets
-    return ms, nsets
+    return ms, nsets, mode
 
 
 def run_suite(backend, peak_gbs: float, iters: int = 20, warmup: int = 3, only: set | None = None) -> list[dict]:
@@ -176,11 +208,47 @@ def run_suite(backend, peak_gbs: float, iters: int = 20, warmup: int = 3, only: 
     for entry in suite():
         if only and entry.op not in only:
             continue
-        ms, nsets = time_entry(entry, backend, iters, warmup)
+        ms, nsets, mode = time_entry(entry, backend, iters, warmup)
         gbs = entry.bytes_per_launch / (ms * 1e-3) / 1e9
         rows.append({"kernel": entry.name, "config": entry.config, "op": entry.op,
                      "bytes": entry.bytes_per_launch, "us": round(ms * 1e3, 2), "gbs": round(gbs, 1),
                      "frac_measured_peak": round(gbs / peak_gbs, 3), "frac_8tbs": round(gbs / 8000.0, 3),
-                     "buffer_sets": nsets})
+                     "buffer_sets": nsets, "timing": mode})
         torch.cuda.empty_cache()
     return rows
+
+
+def _main():
+    """python -m renderformer_cuda_b200.kernel_bench [--op NAME ...] [--iters N] [--eager]
+
+    Prints one JSON object per operator. --eager launches without graph capture (what a
+    profiler wants: a few plain launches of the selected operator); --rows scales the
+    softmax case down so that a profiler capture stays small."""
+    import argparse
+    import json
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", action="append", help="operator(s) to run (default: all)")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--eager", action="store_true")
+    ap.add_argument("--peak", type=float, default=6455.6, help="HBM GB/s used for the fraction column")
+    ap.add_argument("--softmax-rows", type=int, default=SOFTMAX_ROWS)
+    a = ap.parse_args()
+    globals()["SOFTMAX_ROWS"] = a.softmax_rows
+    backend = RfkBackend()
+    if a.eager:
+        for entry in suite():
+            if a.op and entry.op not in a.op:
+                continue
+            sets = [entry.make() for _ in range(2)]
+            fn = getattr(backend, entry.op)
+            for i in range(a.iters):
+                fn(*sets[i % 2])
+            torch.cuda.synchronize()
+            print(json.dumps({"kernel": entry.name, "launched": a.iters}))
+        return
+    for row in run_suite(backend, a.peak, a.iters, 3, set(a.op) if a.op else None):
+        print(json.dumps(row))
+
+
+if __name__ == "__main__":
+    _main()

@@ -406,7 +406,12 @@ for B, Hh, S, D, nf in [(2, 4, 33, 64, 3), (1, 8, 19, 128, 6), (1, 3, 11, 24, 1)
     for dt, tag in [(np.float16, "f16"), (np.float32, "f32")]:
         kind = "f16" if dt == np.float16 else "f32"
         case(name=f"apply_rope_{tag}_b{B}h{Hh}s{S}d{D}", make=_rope_make(B, Hh, S, D, dt, nf),
-             oracle=_rope_oracle, rfk=_rope_rfk, ref=_rope_ref, kinds=dict(q=kind, k=kind, one=kind))
+             # the reference updates in place with one thread per element and no ordering between
+             # the partner's load and this thread's store; with head_dim 24 a rotation pair can
+             # straddle a warp boundary and the race shows (observed on B200), so that shape is
+             # checked against the oracle only.
+             oracle=_rope_oracle, rfk=_rope_rfk, ref=_rope_ref if D % 64 == 0 else None,
+             kinds=dict(q=kind, k=kind, one=kind))
 
 
 def _oop_make(rng):
@@ -578,7 +583,10 @@ for rows, cols, ist, ost, masked, mr, tag in [
         (2, 9001, 9001, 9001, True, 2, "masked_long")]:
     case(name=f"softmax_cast_fp16_{tag}", make=_sm_make(rows, cols, ist, ost, masked, mr),
          oracle=lambda i: dict(p=O.softmax_cast_fp16(i["x"], i["cols"], i["out_stride"], i.get("mask"))),
-         rfk=_sm_rfk, ref=_sm_ref if cols >= 32 else None,  # the reference needs >= 1 full warp
+         # the reference needs >= 1 full warp, and its unmasked kernel issues float4 loads and
+         # half2 stores on every row: it faults (misaligned address) unless in_stride % 4 == 0
+         # and out_stride % 2 == 0. Those shapes are checked against the oracle only.
+         rfk=_sm_rfk, ref=_sm_ref if cols >= 32 and (masked or (ist % 4 == 0 and ost % 2 == 0)) else None,
          kinds=dict(p="f16"))
 
 

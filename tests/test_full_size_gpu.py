@@ -69,7 +69,14 @@ def test_config2_rope_full_size_is_norm_preserving_and_matches_reference():
     assert torch.equal(q[..., 27:32], q0[..., 27:32])              # pad region: cos=1, sin=0
     # rotating by the table and then by its inverse (sin -> -sin) restores the input
     qi = q.clone(); _ops().apply_rope_one(qi, c, -s, 1, Hh, T, hd)
-    _close16(qi, q0)
+    err = (qi.float() - q0.float()).abs()                          # two fp16 roundings + table rounding
+    assert (err <= 4e-3 + 3 * 2.0 ** -10 * q0.float().abs()).all()
+    # the rotation itself, from the stored fp16 tables, in fp32 (rope.cu:75-88 restated in torch)
+    def rot(x):
+        xf = x.float()
+        rh = torch.cat([-xf[..., 32:], xf[..., :32]], dim=-1)
+        return (xf * c.float() + rh * s.float()).half()
+    _close16(q, rot(q0)); _close16(k, rot(k0))
     R = _ref()
     if R:
         cr = torch.empty_like(c); sr = torch.empty_like(s)
@@ -77,7 +84,16 @@ def test_config2_rope_full_size_is_norm_preserving_and_matches_reference():
         _close16(c, cr); _close16(s, sr)
         qr, kr = q0.clone(), k0.clone()
         R.call("ref_apply_rope", qr, kr, cr, sr, 1, Hh, T, hd)
-        _close16(q, qr); _close16(k, kr)
+        # The reference rotates in place with one thread per element and no ordering between a
+        # thread's store and its partner's load (src/kernels/rope.cu:84-92): at this size a few
+        # hundred of the 5.8 M elements come out rotated from an already-updated partner. Where
+        # the two disagree, this library must be the one that matches the formula.
+        for mine, theirs, x0 in ((q, qr, q0), (k, kr, k0)):
+            tol = torch.maximum(torch.full_like(mine.float(), 2e-3), theirs.float().abs() * 2.0 ** -10)
+            bad = (mine.float() - theirs.float()).abs() > tol
+            assert bad.float().mean() < 1e-3, "more disagreement than a sporadic race explains"
+            want = rot(x0)
+            assert ((mine.float() - want.float()).abs()[bad] <= 2e-3 + 2.0 ** -10 * want.float().abs()[bad]).all()
 
 
 def test_config2_nerf_pe_normals_full_size():
@@ -119,7 +135,6 @@ def test_config3_softmax_full_size():
     _ops().softmax_cast_fp16(xs, p2, 2048, cols, stride, stride)
     assert ((p2.float() - p[sub].float()).abs() <= 2e-3).all()
     # argmax is preserved
-    assert torch.equal(p[sub, :cols].float().argmax(1), x[sub, :cols].argmax(1)) or True
     want = torch.softmax(x[sub, :cols].double(), dim=1)
     assert (p[sub, :cols].double() - want).abs().max() < 2e-3
     R = _ref()
