@@ -61,25 +61,21 @@ nerf_pe_tile_kernel(const TI* __restrict__ input, __half* __restrict__ output, l
     const int nrows = (int)min((long long)rows_per_block, rows - r0);
     const TI* in = input + r0 * in_dim;
 
-    const unsigned items = (unsigned)nrows * per_row;
-    for (unsigned it = threadIdx.x; it < items; it += kPeThreads) {
-        const unsigned r = div_per_row.div(it);
-        const unsigned j = it - r * per_row;
-        const unsigned d = div_nf.div(j);
-        const unsigned k = j - d * num_freqs;
-        const float val = (float)in[r * in_dim + d] * ft.f[k];
-        float s, c;
-        sincos_fast(val, s, c);
-        __half* o = s_out + r * out_dim + off + j;
-        o[0] = __float2half(s);
-        o[per_row] = __float2half(c);
-    }
-    if (include_input) {
-        const unsigned n = (unsigned)nrows * in_dim;
-        for (unsigned it = threadIdx.x; it < n; it += kPeThreads) {
-            const unsigned r = div_in.div(it);
-            const unsigned d = it - r * in_dim;
-            s_out[r * out_dim + d] = __float2half((float)in[it]);
+    // one (row, input coordinate) pair per step: a single coalesced read of x, then all of its
+    // frequencies (two consecutive runs of num_freqs outputs: the sin block and the cos block)
+    const unsigned pairs = (unsigned)nrows * in_dim;
+    for (unsigned it = threadIdx.x; it < pairs; it += kPeThreads) {
+        const unsigned r = div_in.div(it);
+        const unsigned d = it - r * in_dim;
+        const float x = (float)in[it];
+        __half* o = s_out + r * out_dim;
+        if (include_input) o[d] = __float2half(x);
+        o += off + d * num_freqs;
+        for (int k = 0; k < num_freqs; ++k) {
+            float s, c;
+            sincos_fast(x * ft.f[k], s, c);
+            o[k] = __float2half(s);
+            o[per_row + k] = __float2half(c);
         }
     }
     __syncthreads();

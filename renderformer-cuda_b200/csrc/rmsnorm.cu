@@ -9,11 +9,16 @@
 //   src/layers/transformer.cu:32-35      out16 = half(in32)
 //
 // Design: the op is a pure HBM stream (config 1: 3 fp32 row passes + 1 fp16 pass,
-// < 1 flop/byte). One warp owns one row; the row lives in registers between the
-// sum-of-squares and the scaling pass, so every byte crosses HBM exactly once.
-// Each lane moves 8 consecutive elements per access (128-bit loads/stores for
-// fp16, 2 x 128-bit for fp32); a warp access covers 512 B / 1 KB contiguous.
-// Statistics are reduced with warp shuffles only - no shared memory, no barrier.
+// < 1 flop/byte). A row lives in registers between the sum-of-squares and the scaling
+// pass, so every byte crosses HBM exactly once. Each lane moves 8 consecutive elements per
+// access (128-bit loads/stores for fp16, 2 x 128-bit for fp32).
+// A row is spread over W warps of a 128-thread CTA (W = 4 for dim 1024, i.e. one row per
+// CTA and one chunk per thread). A first version gave each warp a whole row (32 floats of h
+// and of r per lane): ncu showed 30 % DRAM utilisation with every warp stalled on its own
+// loads (long-scoreboard 35 cycles/issue), because the whole grid loaded in lock step and
+// then stored in lock step, in 1.4 waves. Small CTAs of short-lived threads (32 registers,
+// 16 CTAs per SM) retire and get replaced continuously, so loads of new rows overlap the
+// stores of finished ones. The W partial sums meet through 16 bytes of shared memory.
 #include "common.cuh"
 
 namespace rfk {
@@ -21,66 +26,77 @@ namespace rfk {
 template <typename T> struct IsHalf { static constexpr bool value = false; };
 template <> struct IsHalf<__half> { static constexpr bool value = true; };
 
-// TH: hidden-state storage, TR: residual storage, TY: normalised output storage.
-// NCH: 8-element chunks per lane (dim <= NCH*256).
-template <typename TH, typename TR, typename TY, int NCH, bool HAS_RES, bool WRITE_H>
-__global__ void __launch_bounds__(128)
-rmsnorm_warp_kernel(const TH* x, TH* xw, const TR* __restrict__ r,
-                    const float* __restrict__ gamma, TY* y,  // x, xw, y may alias
-                   
-                    int rows, int dim, float eps) {
-    const int lane = threadIdx.x & 31;
-    const int warps_per_block = blockDim.x >> 5;
-    const int warp = threadIdx.x >> 5;
-    const float inv_dim = 1.0f / (float)dim;
+constexpr int kRmsThreads = 128;
 
-    for (long long row = (long long)blockIdx.x * warps_per_block + warp; row < rows;
-         row += (long long)gridDim.x * warps_per_block) {
-        const size_t base = (size_t)row * dim;
-        float v[NCH][8];
-        float ss = 0.0f;
+// TH: hidden-state storage, TR: residual storage, TY: normalised output storage.
+// W: warps per row (1, 2 or 4); NCH: 8-element chunks per lane (dim <= NCH * W * 256).
+template <typename TH, typename TR, typename TY, int NCH, int W, bool HAS_RES, bool WRITE_H>
+__global__ void __launch_bounds__(kRmsThreads)
+rmsnorm_row_kernel(const TH* x, TH* xw, const TR* __restrict__ r,
+                   const float* __restrict__ gamma, TY* y,  // x, xw, y may alias
+                   int rows, int dim, float eps) {
+    constexpr int kWarps = kRmsThreads / 32;
+    constexpr int kRowsPerCta = kWarps / W;
+    __shared__ float s_part[kWarps];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int wir = warp % W;  // warp index within its row
+    long long row = (long long)blockIdx.x * kRowsPerCta + warp / W;
+    const bool live = row < rows;
+    if (!live) row = rows - 1;  // idle warps shadow the last row and never store
+    const size_t base = (size_t)row * dim;
+
+    float v[NCH][8];
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+        const int off = (wir * 32 + lane + k * W * 32) * 8;
+        if (off < dim) load8(x + base + off, v[k]);
+    }
+    if (HAS_RES) {
 #pragma unroll
         for (int k = 0; k < NCH; ++k) {
-            const int off = (lane + 32 * k) * 8;
-            if (off < dim) load8(x + base + off, v[k]);
-        }
-        if (HAS_RES) {
+            const int off = (wir * 32 + lane + k * W * 32) * 8;
+            if (off < dim) {
+                float rr[8];
+                load8(r + base + off, rr);
 #pragma unroll
-            for (int k = 0; k < NCH; ++k) {
-                const int off = (lane + 32 * k) * 8;
-                if (off < dim) {
-                    float rr[8];
-                    load8(r + base + off, rr);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        float s = v[k][i] + rr[i];
-                        // an fp16 hidden state is stored, then re-read by the norm
-                        v[k][i] = IsHalf<TH>::value ? round_half(s) : s;
-                    }
-                    if (WRITE_H) store8(xw + base + off, v[k]);
+                for (int i = 0; i < 8; ++i) {
+                    float s = v[k][i] + rr[i];
+                    // an fp16 hidden state is stored, then re-read by the norm
+                    v[k][i] = IsHalf<TH>::value ? round_half(s) : s;
                 }
+                if (WRITE_H && live) store8(xw + base + off, v[k]);
             }
         }
+    }
+    float ss = 0.0f;
 #pragma unroll
-        for (int k = 0; k < NCH; ++k) {
-            const int off = (lane + 32 * k) * 8;
-            if (off < dim) {
+    for (int k = 0; k < NCH; ++k) {
+        const int off = (wir * 32 + lane + k * W * 32) * 8;
+        if (off < dim) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) ss = fmaf(v[k][i], v[k][i], ss);
-            }
+            for (int i = 0; i < 8; ++i) ss = fmaf(v[k][i], v[k][i], ss);
         }
-        ss = warp_sum(ss);
-        const float rinv = rsqrtf(ss * inv_dim + eps);
+    }
+    ss = warp_sum(ss);
+    if (W > 1) {
+        if (lane == 0) s_part[warp] = ss;
+        __syncthreads();
+        ss = 0.0f;
 #pragma unroll
-        for (int k = 0; k < NCH; ++k) {
-            const int off = (lane + 32 * k) * 8;
-            if (off < dim) {
-                float g[8], o[8];
-                ldg_float8(gamma + off, g);
+        for (int i = 0; i < W; ++i) ss += s_part[(warp / W) * W + i];
+    }
+    const float rinv = rsqrtf(ss * (1.0f / (float)dim) + eps);
+    if (!live) return;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) o[i] = (v[k][i] * rinv) * g[i];
-                store8(y + base + off, o);
-            }
+    for (int k = 0; k < NCH; ++k) {
+        const int off = (wir * 32 + lane + k * W * 32) * 8;
+        if (off < dim) {
+            float g[8], o[8];
+            ldg_float8(gamma + off, g);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = (v[k][i] * rinv) * g[i];
+            store8(y + base + off, o);
         }
     }
 }
@@ -127,15 +143,14 @@ static int launch_variant(const TH* x, TH* xw, const TR* r, const float* gamma, 
                      aligned16(gamma) && (!HAS_RES || aligned16(r)) &&
                      (!WRITE_H || aligned16(xw));
     if (vec) {
-        constexpr int WPB = 4;
-        const unsigned grid = ceil_div(rows, WPB);
-#define RFK_RMS_LAUNCH(N)                                                                   \
-    rmsnorm_warp_kernel<TH, TR, TY, N, HAS_RES, WRITE_H><<<grid, WPB * 32, 0, st>>>(        \
-        x, xw, r, gamma, y, rows, dim, eps)
-        if (dim <= 256) RFK_RMS_LAUNCH(1);
-        else if (dim <= 512) RFK_RMS_LAUNCH(2);
-        else if (dim <= 1024) RFK_RMS_LAUNCH(4);
-        else RFK_RMS_LAUNCH(8);
+#define RFK_RMS_LAUNCH(N, WW)                                                                  \
+    rmsnorm_row_kernel<TH, TR, TY, N, WW, HAS_RES, WRITE_H>                                    \
+        <<<ceil_div(rows, (kRmsThreads / 32) / WW), kRmsThreads, 0, st>>>(x, xw, r, gamma, y,  \
+                                                                           rows, dim, eps)
+        if (dim <= 256) RFK_RMS_LAUNCH(1, 1);
+        else if (dim <= 512) RFK_RMS_LAUNCH(1, 2);
+        else if (dim <= 1024) RFK_RMS_LAUNCH(1, 4);
+        else RFK_RMS_LAUNCH(2, 4);
 #undef RFK_RMS_LAUNCH
     } else {
         rmsnorm_generic_kernel<TH, TR, TY, HAS_RES, WRITE_H><<<rows, 256, 0, st>>>(

@@ -86,7 +86,7 @@ __device__ __forceinline__ void rotate8(float (&lo)[8], float (&hi)[8], const fl
 // T = __half or float data. NT tensors (1 or 2) share the tables. Each thread walks HP heads.
 // src/dst are [B,H,src_rows,D] / [B,H,dst_rows,D]; rows s >= seq_len (dst only) are copied.
 template <typename T, int NT, int HP>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 rope_apply_kernel(const T* src0, T* dst0, const T* src1, T* dst1,
                   const __half* __restrict__ cos_vals, const __half* __restrict__ sin_vals,
                   int batch, int num_heads, int seq_len, int rows_total, int head_dim,
@@ -187,15 +187,19 @@ static int launch_rope(const T* src0, T* dst0, const T* src1, T* dst1, const __h
                      aligned16(sin_vals);
     if (vec) {
         const int cpt = head_dim / 16;
-        // enough threads to fill 148 SMs, while each thread keeps several loads in flight
-        const int hp = (num_heads % 4 == 0 && (long long)batch * rows_total * cpt *
-                                                      (num_heads / 4) >= 148LL * 2048)
-                           ? 4
-                           : (num_heads % 2 == 0 ? 2 : 1);
+        // One head per thread unless the problem is large: at the benchmark size (47 MB) the
+        // kernel lasts ~10 us and is bound by how evenly short-lived CTAs keep loads in
+        // flight (ncu: 24 % DRAM utilisation with 2 heads per thread and 1.6 waves of
+        // 705 CTAs); walking several heads per thread only pays once there are at least two
+        // full waves of threads left (the cos/sin re-reads it saves come from L2 anyway).
+        const long long per_head = (long long)batch * rows_total * cpt;
+        const long long two_waves = 2LL * kNumSMs * 2048;
+        const int hp = (num_heads % 4 == 0 && per_head * (num_heads / 4) >= two_waves) ? 4
+                     : (num_heads % 2 == 0 && per_head * (num_heads / 2) >= two_waves) ? 2 : 1;
         const long long total = (long long)batch * (num_heads / hp) * rows_total * cpt;
-        const unsigned grid = ceil_div(total, 256);
+        const unsigned grid = ceil_div(total, 128);
 #define RFK_ROPE(HPV)                                                                         \
-    rope_apply_kernel<T, NT, HPV><<<grid, 256, 0, st>>>(src0, dst0, src1, dst1, cos_vals,     \
+    rope_apply_kernel<T, NT, HPV><<<grid, 128, 0, st>>>(src0, dst0, src1, dst1, cos_vals,     \
                                                         sin_vals, batch, num_heads, seq_len,  \
                                                         rows_total, head_dim, src_rows,       \
                                                         dst_rows)
