@@ -143,13 +143,15 @@ int rfk_rope_one_oop(const rfk_half* src, rfk_half* dst,
  * transpose_bshd_to_bhsd x3 (+ memcpy x3) + apply_rope —
  * src/layers/attention.cu:73-85,184-210 (self), :341-361 (cross Q), :510-530 (swin).
  * Intermediate roundings match the unfused sequence (the normalised value is
- * rounded to fp16 before the rotation). gamma/out/use_rope are HOST arrays. */
+ * rounded to fp16 before the rotation). gamma/out/use_rope are HOST arrays.
+ * out_seq_stride: rows per head of the outputs (0 = seq_len); rows [seq_len, stride) are
+ * left untouched (a padded K/V cache zeroes them once). */
 int rfk_qkv_norm_rope_transpose(const rfk_half* x, long long row_stride, int n_parts,
                                 const float* const* gamma, rfk_half* const* out,
                                 const int* use_rope,
                                 const rfk_half* cos_vals, const rfk_half* sin_vals,
                                 int batch, int seq_len, int num_heads, int head_dim,
-                                float eps, rfk_stream_t stream);
+                                float eps, int out_seq_stride, rfk_stream_t stream);
 
 /* [B,S,H,D] -> [B,H,S,D] — replaces transpose_bshd_to_bhsd, src/layers/attention.cu:17-31 */
 int rfk_transpose_bshd_to_bhsd(const rfk_half* in, rfk_half* out,
@@ -202,6 +204,16 @@ int rfk_softmax_cast_fp16_masked(const float* in, rfk_half* out, const uint8_t* 
 int rfk_softmax_cast_fp16_scaled(const float* in, rfk_half* out, int rows, int cols,
                                  int in_stride, int out_stride, float scale,
                                  rfk_stream_t stream);
+/* softmax(scale * scores) written as fp16 OVER the score buffer: probability row r occupies
+ * the first `stride` halves of fp32 row r (row pitch 2*stride halves), columns
+ * [n_valid, stride) are zero. Saves the separate probability buffer the reference allocates
+ * per call (cudaMallocAsync of P_half, src/layers/attention.cu:148-149). Rows up to 8192
+ * columns (held in registers); longer rows return RFK_EUNSUPPORTED. */
+int rfk_softmax_probs_inplace(float* scores, int rows, int n_valid, int stride, float scale,
+                              rfk_stream_t stream);
+/* The same for swin window scores with the optional shift mask (row pitch 2*ws2 halves). */
+int rfk_swin_softmax_probs_inplace(float* scores, const uint8_t* mask, int BnW, int num_heads,
+                                   int ws2, int nW, rfk_stream_t stream);
 /* Swin window scores fp32 -> fp16 probabilities in one pass (mask may be NULL).
  * replaces swin_masked_softmax_inplace | softmax_inplace followed by fp32_to_fp16 —
  * src/layers/attention.cu:549-555 */
@@ -222,6 +234,9 @@ int rfk_fused_silu_mul_f32(const float* a, const float* b, float* out, long long
  * two GEMMs + fused_silu_mul of rf::ffn_swiglu, src/layers/transformer.cu:63-79. */
 int rfk_swiglu(const rfk_half* gate_up, rfk_half* out, int rows, int hidden,
                rfk_stream_t stream);
+/* The same, writing out over the gate half of each row (row pitch 2*hidden): the W2 GEMM
+ * then reads it with lda = 2*hidden and no separate activation buffer is needed. */
+int rfk_swiglu_inplace(rfk_half* gate_up, int rows, int hidden, rfk_stream_t stream);
 /* y = x > 0 ? x : alpha*(exp(x)-1), fp16, in place allowed — replaces rf::elu,
  * activations.h:16, activations.cu:38-50 */
 int rfk_elu(const rfk_half* x, rfk_half* y, long long n, float alpha, rfk_stream_t stream);

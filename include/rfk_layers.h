@@ -1,0 +1,285 @@
+/*
+ * rfk_layers.h — C ABI of librfk_layers.so: the launch / fusion boundaries around the
+ * rfk kernels (attention and transformer layers), the per-view render session with its
+ * CUDA-graph capture, and the hooks a multi-GPU view scheduler needs.
+ *
+ * The dense contractions stay library calls (cuBLAS GEMMs, as in the reference); every
+ * element-wise, normalisation, softmax, rotary and layout step between them is an rfk
+ * kernel (include/rfk.h), fused across the boundaries the reference leaves open.
+ *
+ * Conventions are those of rfk.h (int status, device pointers, stream last). Functions
+ * taking an rfk_ctx use its cuBLAS handle and workspace; one rfk_ctx per device and per
+ * host thread. Nothing here allocates on the launch path: all device memory is allocated
+ * by rfk_ctx_create / rfk_session_create or supplied by the caller, so every call made
+ * after creation can be captured in a CUDA graph.
+ *
+ * "replaces" comments name the reference interface (BANANASJIM/renderformer-cuda, paths
+ * relative to that project).
+ */
+#ifndef RFK_LAYERS_H
+#define RFK_LAYERS_H
+
+#include "rfk.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct rfk_ctx rfk_ctx;          /* per-device cuBLAS handle + workspace      */
+typedef struct rfk_session rfk_session;  /* per-device, per-scene render session      */
+
+/* Creates the context on the current CUDA device (allocates a 64 MiB cuBLAS workspace).
+ * replaces rf::CublasHandle — src/core/cuda_utils.h:50-59 */
+int rfk_ctx_create(rfk_ctx** out);
+int rfk_ctx_destroy(rfk_ctx* ctx);
+
+/* ------------------------------------------------------------- weight records */
+
+/* replaces rf::FFNWeights — src/layers/transformer.h:9-13. If w3 == w1 + hidden*dim (the
+ * two matrices stored back to back) the gate and up projections run as one GEMM. */
+typedef struct {
+    const rfk_half* w1;  /* [hidden, dim] */
+    const rfk_half* w2;  /* [dim, hidden] */
+    const rfk_half* w3;  /* [hidden, dim] */
+} rfk_ffn_weights;
+
+/* replaces rf::MHAWeights and rf::SwinAttnWeights (same fields) —
+ * src/layers/attention.h:23-30, 84-91 */
+typedef struct {
+    const rfk_half* in_proj_w;   /* [3*dim, dim] */
+    const rfk_half* in_proj_b;   /* [3*dim] or NULL */
+    const rfk_half* out_proj_w;  /* [dim, dim] */
+    const rfk_half* out_proj_b;  /* [dim] or NULL */
+    const float* q_norm_gamma;   /* [dim] or NULL */
+    const float* k_norm_gamma;   /* [dim] or NULL */
+} rfk_mha_weights;
+
+/* replaces rf::CrossAttnWeights — src/layers/attention.h:40-51 */
+typedef struct {
+    const rfk_half* q_proj_w;   const rfk_half* q_proj_b;
+    const rfk_half* k_proj_w;   const rfk_half* k_proj_b;
+    const rfk_half* v_proj_w;   const rfk_half* v_proj_b;
+    const rfk_half* out_proj_w; const rfk_half* out_proj_b;
+    const float* q_norm_gamma;  const float* k_norm_gamma;
+} rfk_cross_attn_weights;
+
+/* replaces rf::EncoderLayerWeights — src/layers/transformer.h:16-21 */
+typedef struct {
+    const float* query_norm_gamma;
+    rfk_mha_weights attn;
+    const float* ffn_norm_gamma;
+    rfk_ffn_weights ffn;
+} rfk_encoder_layer_weights;
+
+/* replaces rf::DecoderLayerWeights — src/layers/transformer.h:24-32 */
+typedef struct {
+    const float* query_norm_gamma;
+    const float* kv_norm_gamma;
+    rfk_cross_attn_weights cross_attn;
+    const float* self_attn_norm_gamma;
+    rfk_mha_weights self_attn;
+    const float* ffn_norm_gamma;
+    rfk_ffn_weights ffn;
+} rfk_decoder_layer_weights;
+
+/* ------------------------------------------------------------------- layers */
+
+/* Y[M,N] = X[M,K] W[N,K]^T (+ bias[N]); fp16 in/out, fp32 accumulation (cuBLAS).
+ * replaces rf::linear — src/layers/linear.h:9, linear.cu:7-25 */
+int rfk_linear(rfk_ctx* ctx, const rfk_half* X, const rfk_half* W, const rfk_half* bias,
+               rfk_half* Y, int M, int N, int K, rfk_stream_t stream);
+
+/* out[M,dim] = W2 (silu(W1 x) * (W3 x)); buf holds [M, 2*hidden] halves.
+ * One or two GEMMs into a gate|up buffer, the SwiGLU gate kernel, one GEMM.
+ * replaces rf::ffn_swiglu — src/layers/transformer.h:118, transformer.cu:63-79 */
+int rfk_ffn_swiglu(rfk_ctx* ctx, const rfk_ffn_weights* w, const rfk_half* x, rfk_half* out,
+                   rfk_half* buf, int M, int dim, int hidden, rfk_stream_t stream);
+
+/* Scaled dot-product attention on [B,H,S,D] fp16 tensors, scale 1/sqrt(D):
+ * batched GEMM into fp32 scores, rfk softmax (probabilities written as fp16 over the first
+ * half of each score row), batched GEMM. Sk must be a multiple of 8.
+ *   workspace: B*H*Sq*Sk floats.
+ *   n_keys: keys that take part in the softmax (<= Sk); keys [n_keys, Sk) get probability 0.
+ *           n_keys == Sk reproduces the reference, which attends its zero pad keys.
+ *   o_bshd != 0: O is written as [B,Sq,H*D] (saves the transpose that follows).
+ * replaces the cuBLAS + softmax_cast_fp16 path of rf::sdpa — src/layers/attention.cu:112-165
+ * (the reference's first choice, cuDNN fused SDPA, attention.cu:97-110, computes the same
+ * function without materialising the scores). mask must be NULL or [B,Sk] bytes. */
+int rfk_sdpa(rfk_ctx* ctx, const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,
+             float* workspace, const uint8_t* mask, int B, int H, int Sq, int Sk, int n_keys,
+             int D, int o_bshd, rfk_stream_t stream);
+
+/* K/V projections of the (normalised) context, K-RMSNorm, [B,H,Sk_pad,D] layout with rows
+ * [Sk, Sk_pad) zeroed. proj_buf: 2*B*Sk*dim halves.
+ * replaces rf::precompute_cross_kv + the per-head padding copies —
+ * src/layers/attention.cu:302-324, src/pipeline/render_session.cu:395-414 */
+int rfk_precompute_cross_kv(rfk_ctx* ctx, const rfk_cross_attn_weights* w,
+                            const rfk_half* ctx_normed, rfk_half* K_out, rfk_half* V_out,
+                            rfk_half* proj_buf, int B, int Sk, int Sk_pad, int kv_dim, int dim,
+                            int num_heads, rfk_stream_t stream);
+
+/* Cross-attention of q_in [B*Sq, q_dim] against cached K/V [B,H,Sk,D] (Sk a multiple of 8).
+ * proj_buf: (2*B*Sq*dim + B*H*Sk*D) halves; score_buf: B*H*Sq*Sk floats.
+ * Fusions: Q-RMSNorm + transpose + RoPE in one kernel; cached-K copy + RoPE in one kernel;
+ * softmax writes fp16 in place; the PV GEMM writes [B,Sq,dim] directly.
+ * replaces rf::cross_attention_cached — src/layers/attention.h:70-82, attention.cu:326-373 */
+int rfk_cross_attention_cached(rfk_ctx* ctx, const rfk_cross_attn_weights* w,
+                               const rfk_half* q_in, rfk_half* out, rfk_half* proj_buf,
+                               float* score_buf, const rfk_half* K_cached,
+                               const rfk_half* V_cached, int B, int Sq, int Sk, int n_keys,
+                               int q_dim, int dim, int num_heads,
+                               const rfk_half* q_rope_cos, const rfk_half* q_rope_sin,
+                               const rfk_half* k_rope_cos, const rfk_half* k_rope_sin,
+                               rfk_stream_t stream);
+
+/* Shifted-window self-attention on an [B,H,W,dim] token map.
+ *   window_buf: B*H*W*dim halves; qkv_buf: 3*B*H*W*dim halves; scratch: 3*B*H*W*dim halves;
+ *   score_buf: B*nW*heads*ws^4 floats; shift_mask [nW, ws^2, ws^2] bytes (used when shift > 0).
+ * If residual_x != NULL the result is added into residual_x (fp16 residual add fused with the
+ * window reverse + un-shift) and `out` is not written; otherwise out receives the result.
+ * replaces rf::swin_self_attention (+ residual_add) — src/layers/attention.h:95-102,
+ * attention.cu:476-576, src/layers/transformer.cu:183-188 */
+int rfk_swin_self_attention(rfk_ctx* ctx, const rfk_mha_weights* w, const rfk_half* x,
+                            rfk_half* out, rfk_half* residual_x, rfk_half* window_buf,
+                            rfk_half* qkv_buf, float* score_buf, rfk_half* scratch, int B, int H,
+                            int W, int dim, int num_heads, int window_size, int shift_size,
+                            const uint8_t* shift_mask, rfk_stream_t stream);
+
+/* Self-attention with packed QKV projection on [B,S,dim] (encoder). score_buf:
+ * B*H*S*S_pad floats (S_pad = S rounded up to 8); qkv_buf: B*S*3*dim halves + 3*B*H*S_pad*D.
+ * replaces rf::self_attention — src/layers/attention.h:32-37, attention.cu:170-231 */
+int rfk_self_attention(rfk_ctx* ctx, const rfk_mha_weights* w, const rfk_half* x, rfk_half* out,
+                       rfk_half* qkv_buf, float* score_buf, int B, int S, int dim, int num_heads,
+                       const rfk_half* rope_cos, const rfk_half* rope_sin, rfk_stream_t stream);
+
+/* One decoder layer with cached cross-attention K/V, in place on x [B*Sq, dim] fp16.
+ * Buffer minimums (halves unless noted), Mq = B*Sq:
+ *   temp Mq*dim; proj_buf max(2*Mq*dim + B*heads*Sk*hd, 3*Mq*dim); qkv_buf Mq*max(3*dim, 2*ffn);
+ *   ffn_buf Mq*max(dim, ffn); window_buf Mq*dim; cross_score_buf B*heads*Sq*Sk floats;
+ *   self_score_buf B*nW*heads*ws^4 floats.
+ * pending_residual: if non-NULL, a sub-layer output of the PREVIOUS layer that has not been
+ * added to x yet; it is added by this layer's first fused residual+RMSNorm kernel.
+ * On return *pending_out (if pending_out != NULL) names this layer's FFN output, not yet
+ * added to x (the caller passes it to the next layer, or adds it with rfk_residual_add);
+ * with pending_out == NULL the layer adds it itself and x is complete.
+ * replaces rf::decoder_layer_forward_cached — src/layers/transformer.h:88-103,
+ * transformer.cu:151-194 */
+int rfk_decoder_layer_forward_cached(rfk_ctx* ctx, const rfk_decoder_layer_weights* w,
+                                     rfk_half* x, const rfk_half* pending_residual,
+                                     const rfk_half** pending_out, rfk_half* temp,
+                                     rfk_half* proj_buf, rfk_half* qkv_buf, rfk_half* ffn_buf,
+                                     rfk_half* window_buf, float* cross_score_buf,
+                                     float* self_score_buf, const rfk_half* K_cached,
+                                     const rfk_half* V_cached, int B, int Sq, int Sk, int n_keys,
+                                     int dim, int num_heads, int ffn_hidden, int patch_h,
+                                     int patch_w, int window_size, int shift_size,
+                                     const uint8_t* shift_mask, const rfk_half* q_rope_cos,
+                                     const rfk_half* q_rope_sin, const rfk_half* k_rope_cos,
+                                     const rfk_half* k_rope_sin, rfk_stream_t stream);
+
+/* One encoder layer with an fp32 hidden state and fp16 sub-layers, in place on x [B*S, dim].
+ * temp: B*S*dim halves; qkv_buf: as rfk_self_attention, at least B*S*2*ffn halves;
+ * ffn_buf: B*S*max(dim, ffn) halves; score_buf: as rfk_self_attention.
+ * Same pending-residual protocol as the decoder layer (fp16 sub-layer output added to the
+ * fp32 hidden state by the next fused residual+RMSNorm+cast kernel).
+ * replaces rf::encoder_layer_forward_mixed — src/layers/transformer.h:48-57,
+ * transformer.cu:196-224 */
+int rfk_encoder_layer_forward_mixed(rfk_ctx* ctx, const rfk_encoder_layer_weights* w, float* x,
+                                    const rfk_half* pending_residual,
+                                    const rfk_half** pending_out, rfk_half* temp,
+                                    rfk_half* qkv_buf, rfk_half* ffn_buf, float* score_buf, int B,
+                                    int S, int dim, int num_heads, int ffn_hidden,
+                                    const rfk_half* rope_cos, const rfk_half* rope_sin,
+                                    rfk_stream_t stream);
+
+/* ------------------------------------------------------------ render session */
+
+#define RFK_MAX_LAYERS 32
+
+/* Model record (device pointers): the fields of rf::RenderFormerModel
+ * (src/model/renderformer.h:12-44) without the DPT head, with runtime shapes in place of
+ * the compile-time rf::Config (src/model/config.h:6-43). */
+typedef struct {
+    int dim, num_heads, ffn_hidden, num_register_tokens;
+    int enc_layers, dec_layers;
+    int rope_num_freqs;          /* frequencies per coordinate: 9*nf <= head_dim/2 */
+    int patch_size, window_size, shift_size;
+    int texture_channels;        /* 13 */
+    int vn_pe_num_freqs;         /* 6  */
+    const rfk_half* tri_token;   /* [dim] */
+    const rfk_half* reg_tokens;  /* [num_register_tokens, dim] */
+    const rfk_half* tex_enc_w;   const rfk_half* tex_enc_b;  const float* tex_enc_norm;
+    const rfk_half* vn_proj_w;   const rfk_half* vn_proj_b;  const float* vn_enc_norm;
+    const float* enc_rope_freqs;
+    const rfk_half* ray_map_patch_token;
+    const rfk_half* ray_enc_w;   const rfk_half* ray_enc_b;  const float* ray_enc_norm;
+    const float* vt_rope_freqs;
+    rfk_encoder_layer_weights enc[RFK_MAX_LAYERS];
+    rfk_decoder_layer_weights dec[RFK_MAX_LAYERS];
+} rfk_model;
+
+enum {
+    RFK_SESSION_PAD_KEYS_ATTEND = 1,  /* reproduce the reference: zero pad keys take part in the
+                                         cross-attention softmax (render_session.cu:229-230) */
+    RFK_SESSION_NO_GRAPH        = 2   /* launch eagerly instead of replaying a CUDA graph */
+};
+
+/* Bytes of the scene state of an n_tris scene: the encoder's cross-attention K/V cache
+ * [dec_layers][2][heads][Se_pad][head_dim] fp16 followed by the fp16 triangles, the fp16
+ * vertex normals and the fp32 scene centre. This is the blob a view scheduler broadcasts. */
+size_t rfk_scene_state_bytes(const rfk_model* model, int n_tris);
+
+/* Creates a session on the current device for `n_tris` triangles at img_res x img_res.
+ * scene_state: caller-owned device buffer of rfk_scene_state_bytes() bytes (filled either by
+ * rfk_session_encode_scene on this device or by a broadcast from the device that ran it).
+ * Allocates every per-view buffer; runs nothing.
+ * replaces the allocation half of rf::RenderSession::create — src/pipeline/render_session.cu:258-295,418-462 */
+int rfk_session_create(const rfk_model* model, int n_tris, int img_res, void* scene_state,
+                       int flags, rfk_session** out);
+int rfk_session_destroy(rfk_session* s);
+
+/* Scene preprocessing, 12-layer encoder and K/V cache build into the scene state.
+ * tri, vn: [n_tris,3,3] fp32 world space; tex: [n_tris, texture_channels] fp16 (first texel
+ * of each channel; the last 3 channels are log-encoded here). Synchronises at the end.
+ * replaces the compute half of rf::RenderSession::create — render_session.cu:296-416 */
+int rfk_session_encode_scene(rfk_session* s, const float* tri, const float* vn,
+                             const rfk_half* tex);
+
+/* Builds the per-session constants (query RoPE tables, shift mask), runs one warm-up view and
+ * captures the per-view CUDA graph. Call after the scene state is complete on this device.
+ * replaces render_session.cu:430-495 */
+int rfk_session_finalize(rfk_session* s);
+
+/* Renders one view asynchronously on the session's stream: copies c2w (16 floats, row-major,
+ * HOST) and fov (radians) into pinned staging memory and launches the captured graph.
+ * The session has two frame slots (pinned camera, graph instance, result buffer each), so the
+ * call returns at once unless the frame submitted two calls ago is still running or
+ * downloading: the host can stay one frame ahead of the device.
+ * replaces rf::RenderSession::render_frame_async — render_session.cu:515-527 */
+int rfk_session_render_frame(rfk_session* s, const float* h_c2w, float fov_rad);
+/* Blocks until the last submitted frame is done; *ms (optional) receives its device time.
+ * replaces rf::RenderSession::get_frame_result — render_session.cu:539-548 */
+int rfk_session_wait(rfk_session* s, float* ms);
+/* Device pointer and shape of the last frame's result: the decoder's final token map
+ * [(img_res/patch)^2, dim] fp16 (the DPT image head is outside this library). */
+int rfk_session_result(rfk_session* s, const rfk_half** tokens, int* n_tokens, int* dim);
+/* Device pointers of the 4 decoder feature taps a DPT head consumes (layers at 1/4, 1/2, 3/4
+ * and the end of the stack; render_session.cu:235-238). */
+int rfk_session_feature_taps(rfk_session* s, const rfk_half** taps /* HOST array of 4 */);
+/* Copies the last frame's token map to HOST memory (waits for the frame).
+ * replaces rf::RenderSession::download_frame_hwc — render_session.cu:550-559 */
+int rfk_session_download(rfk_session* s, rfk_half* h_out, size_t bytes);
+/* Queues the device->host copy of the last submitted frame's token map on the session's copy
+ * stream (h_out should be pinned); it runs as soon as that frame is done, overlapping the
+ * next frame. rfk_session_drain waits for every submitted frame and copy. */
+int rfk_session_download_async(rfk_session* s, rfk_half* h_out, size_t bytes);
+int rfk_session_drain(rfk_session* s);
+/* Number of nodes in the captured per-view graph (0 when running eagerly). */
+int rfk_session_graph_nodes(rfk_session* s);
+/* Kernels of librfk.so launched per view (counted while the graph was captured). */
+int rfk_session_kernels_per_view(rfk_session* s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RFK_LAYERS_H */

@@ -129,4 +129,20 @@ void ref_decoder_layer_forward_cached(void* h, const RefDecoderLayerW* w, half* 
                                      qs, kc, ks, S(s));
 }
 
+// src/layers/transformer.cu:196-224 (fp32 hidden state, fp16 sub-layers), flat weight arguments
+void ref_encoder_layer_forward_mixed(void* h, const float* query_norm, const half* in_proj_w,
+                                     const half* out_proj_w, const float* q_norm, const float* k_norm,
+                                     const float* ffn_norm, const half* w1, const half* w2, const half* w3,
+                                     float* x, half* temp, half* qkv_buf, half* ffn_buf, float* score_buf,
+                                     int B, int S_, int dim, int heads, int ffn_hidden, const half* rc,
+                                     const half* rs, void* s) {
+    rf::EncoderLayerWeights w{};
+    w.query_norm_gamma = query_norm;
+    w.attn = rf::MHAWeights{in_proj_w, nullptr, out_proj_w, nullptr, q_norm, k_norm};
+    w.ffn_norm_gamma = ffn_norm;
+    w.ffn = rf::FFNWeights{w1, w2, w3};
+    rf::encoder_layer_forward_mixed((cublasHandle_t)h, w, x, temp, qkv_buf, ffn_buf, score_buf, nullptr, B, S_,
+                                    dim, heads, ffn_hidden, rc, rs, S(s));
+}
+
 }  // extern "C"

@@ -4,6 +4,7 @@
 
 Produces, next to this file:
     librfk.so         the kernel library behind include/rfk.h (CUDA runtime only)
+    librfk_layers.so  layer boundaries, render session (include/rfk_layers.h; cuBLAS + librfk.so)
 
 nvcc cross-compiles without a GPU, so this also runs on a CPU-only machine.
 """
@@ -27,6 +28,8 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC,-O3,-Wall,-Wno-unused-function",
     "--expt-relaxed-constexpr",
 ]
+
+LAYER_SOURCES = ["layers.cu", "session.cu"]
 
 KERNEL_SOURCES = [
     "abi.cu", "rmsnorm.cu", "softmax.cu", "rope.cu", "layout.cu",
@@ -84,6 +87,10 @@ def build_library(name: str, sources: list[str], extra: list[str], force: bool,
 
 def build_all(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> dict[str, Path]:
     libs = {"rfk": build_library("rfk", KERNEL_SOURCES, [], force, verbose, ptxas_info)}
+    # layer boundaries + session: cuBLAS for the GEMMs, librfk.so (same directory) for everything else
+    libs["rfk_layers"] = build_library(
+        "rfk_layers", LAYER_SOURCES,
+        ["-lcublas", f"-L{PKG}", "-lrfk", "-Xlinker", "-rpath=$ORIGIN"], force, verbose, ptxas_info)
     return libs
 
 

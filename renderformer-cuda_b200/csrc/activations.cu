@@ -42,8 +42,8 @@ silu_mul_kernel(const T* a, const T* __restrict__ b, T* out, long long n, int ve
 
 // gate_up [rows, 2*hidden] -> out [rows, hidden]
 __global__ void __launch_bounds__(256)
-swiglu_kernel(const __half* __restrict__ gate_up, __half* __restrict__ out, long long rows,
-              int hidden, int vec) {
+swiglu_kernel(const __half* gate_up, __half* out, long long rows, int hidden,
+              long long out_pitch, int vec) {  // out may alias the gate half of gate_up
     const int cpr = (hidden + 7) / 8;
     const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= rows * cpr) return;
@@ -51,7 +51,7 @@ swiglu_kernel(const __half* __restrict__ gate_up, __half* __restrict__ out, long
     const int j0 = (int)(c % cpr) * 8;
     const __half* g = gate_up + row * 2 * hidden + j0;
     const __half* u = g + hidden;
-    __half* o = out + row * hidden + j0;
+    __half* o = out + row * out_pitch + j0;
     if (vec) {
         float fg[8], fu[8];
         unpack8(ldcs_half8(g), fg);
@@ -132,7 +132,18 @@ extern "C" int rfk_swiglu(const rfk_half* gate_up, rfk_half* out, int rows, int 
     const int vec = hidden % 8 == 0 && aligned16(gate_up) && aligned16(out);
     const long long chunks = (long long)rows * ((hidden + 7) / 8);
     swiglu_kernel<<<ceil_div(chunks, 256), 256, 0, as_stream(stream)>>>(
-        (const __half*)gate_up, (__half*)out, rows, hidden, vec);
+        (const __half*)gate_up, (__half*)out, rows, hidden, hidden, vec);
+    return launch_status();
+}
+
+extern "C" int rfk_swiglu_inplace(rfk_half* gate_up, int rows, int hidden, rfk_stream_t stream) {
+    if (!gate_up || rows < 0 || hidden <= 0) return RFK_EINVAL;
+    if (rows == 0) return RFK_OK;
+    const int vec = hidden % 8 == 0 && aligned16(gate_up);
+    const long long chunks = (long long)rows * ((hidden + 7) / 8);
+    // every thread overwrites exactly the gate elements it has just read
+    swiglu_kernel<<<ceil_div(chunks, 256), 256, 0, as_stream(stream)>>>(
+        (const __half*)gate_up, (__half*)gate_up, rows, hidden, 2LL * hidden, vec);
     return launch_status();
 }
 

@@ -1,0 +1,334 @@
+// Attention / transformer layer boundaries: cuBLAS GEMMs joined by the rfk kernels.
+//
+// Reference call sequences (BANANASJIM/renderformer-cuda):
+//   src/layers/linear.cu:7-25            linear
+//   src/layers/transformer.cu:63-79      ffn_swiglu           (2 GEMMs + gate + GEMM)
+//   src/layers/attention.cu:112-165      sdpa, cuBLAS path    (GEMM, softmax, GEMM)
+//   src/layers/attention.cu:170-231      self_attention
+//   src/layers/attention.cu:302-373      precompute_cross_kv, cross_attention_cached
+//   src/layers/attention.cu:476-576      swin_self_attention
+//   src/layers/transformer.cu:151-224    decoder_layer_forward_cached, encoder_layer_forward_mixed
+//
+// What is re-cut here (launches per decoder layer: ~36 in the reference, 21 here):
+//   - residual add + RMSNorm (+ fp16 cast) is one kernel; the FFN residual of a layer is
+//     deferred into the first norm of the next layer;
+//   - QK-RMSNorm + [B,S,H,D]->[B,H,S,D] + RoPE (+ QKV de-interleave) is one kernel;
+//   - the cached K is rotated out of place (no device-to-device copy first);
+//   - softmax writes fp16 probabilities over its own fp32 score rows (no P buffer, no cast);
+//   - the PV GEMM of the cross-attention writes [B,Sq,H*D] directly (no transpose back);
+//   - w1 and w3 run as one GEMM when stored back to back; the gate overwrites its own input;
+//   - cyclic shift + window partition, and window reverse + un-shift + residual add, are one
+//     kernel each.
+#include "layers_internal.h"
+
+#include <algorithm>
+#include <cmath>
+
+using namespace rfk_layers;
+
+#define TRY(expr)                       \
+    do {                                \
+        int rc_ = (expr);               \
+        if (rc_ != RFK_OK) return rc_;  \
+    } while (0)
+
+static int blas_status(cublasStatus_t s) {
+    if (s == CUBLAS_STATUS_SUCCESS) return RFK_OK;
+    return 1000 + (int)s;  // distinct from cudaError_t values used by the kernels
+}
+
+// C[M,N] (ldc) = alpha * A[M,K] (lda) * B[N,K]^T (ldb), row-major fp16, fp32 accumulation
+static int gemm_nt(rfk_ctx* ctx, cudaStream_t st, int M, int N, int K, float alpha, const __half* A,
+                   int lda, const __half* B, int ldb, __half* C, int ldc) {
+    if (M == 0 || N == 0) return RFK_OK;
+    TRY(blas_status(cublasSetStream(ctx->blas, st)));
+    const float beta = 0.0f;
+    return blas_status(cublasGemmEx(ctx->blas, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha, B,
+                                    CUDA_R_16F, ldb, A, CUDA_R_16F, lda, &beta, C, CUDA_R_16F, ldc,
+                                    CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT));
+}
+
+extern "C" int rfk_ctx_create(rfk_ctx** out) {
+    if (!out) return RFK_EINVAL;
+    rfk_ctx* c = new rfk_ctx();
+    cudaError_t e = cudaGetDevice(&c->device);
+    if (e != cudaSuccess) { delete c; return (int)e; }
+    cublasStatus_t s = cublasCreate(&c->blas);
+    if (s != CUBLAS_STATUS_SUCCESS) { delete c; return blas_status(s); }
+    c->ws_bytes = 64ull << 20;
+    e = cudaMalloc(&c->ws, c->ws_bytes);
+    if (e != cudaSuccess) { cublasDestroy(c->blas); delete c; return (int)e; }
+    // an explicit workspace keeps cuBLAS from allocating while a graph is being captured
+    s = cublasSetWorkspace(c->blas, c->ws, c->ws_bytes);
+    if (s != CUBLAS_STATUS_SUCCESS) { cudaFree(c->ws); cublasDestroy(c->blas); delete c; return blas_status(s); }
+    *out = c;
+    return RFK_OK;
+}
+
+extern "C" int rfk_ctx_destroy(rfk_ctx* ctx) {
+    if (!ctx) return RFK_OK;
+    cublasDestroy(ctx->blas);
+    cudaFree(ctx->ws);
+    delete ctx;
+    return RFK_OK;
+}
+
+extern "C" int rfk_linear(rfk_ctx* ctx, const rfk_half* X, const rfk_half* W, const rfk_half* bias,
+                          rfk_half* Y, int M, int N, int K, rfk_stream_t stream) {
+    if (!ctx || !X || !W || !Y || M < 0 || N <= 0 || K <= 0) return RFK_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    TRY(gemm_nt(ctx, st, M, N, K, 1.0f, (const __half*)X, K, (const __half*)W, K, (__half*)Y, N));
+    if (bias) TRY(rfk_broadcast_add(Y, bias, (long long)M * N, N, stream));
+    return RFK_OK;
+}
+
+extern "C" int rfk_ffn_swiglu(rfk_ctx* ctx, const rfk_ffn_weights* w, const rfk_half* x,
+                              rfk_half* out, rfk_half* buf, int M, int dim, int hidden,
+                              rfk_stream_t stream) {
+    if (!ctx || !w || !w->w1 || !w->w2 || !w->w3 || !x || !out || !buf) return RFK_EINVAL;
+    if (M < 0 || dim <= 0 || hidden <= 0) return RFK_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    __half* gu = (__half*)buf;  // [M, 2*hidden]: gate | up per row
+    if (w->w3 == w->w1 + (size_t)hidden * dim) {
+        TRY(gemm_nt(ctx, st, M, 2 * hidden, dim, 1.0f, (const __half*)x, dim, (const __half*)w->w1,
+                    dim, gu, 2 * hidden));
+    } else {
+        TRY(gemm_nt(ctx, st, M, hidden, dim, 1.0f, (const __half*)x, dim, (const __half*)w->w1, dim,
+                    gu, 2 * hidden));
+        TRY(gemm_nt(ctx, st, M, hidden, dim, 1.0f, (const __half*)x, dim, (const __half*)w->w3, dim,
+                    gu + hidden, 2 * hidden));
+    }
+    TRY(rfk_swiglu_inplace(buf, M, hidden, stream));  // activation over the gate half, pitch 2*hidden
+    return gemm_nt(ctx, st, M, dim, hidden, 1.0f, gu, 2 * hidden, (const __half*)w->w2, hidden,
+                   (__half*)out, dim);
+}
+
+extern "C" int rfk_sdpa(rfk_ctx* ctx, const rfk_half* Q, const rfk_half* K, const rfk_half* V,
+                        rfk_half* O, float* workspace, const uint8_t* mask, int B, int H, int Sq,
+                        int Sk, int n_keys, int D, int o_bshd, rfk_stream_t stream) {
+    if (!ctx || !Q || !K || !V || !O || !workspace) return RFK_EINVAL;
+    if (B < 0 || H <= 0 || Sq < 0 || Sk <= 0 || D <= 0 || n_keys <= 0 || n_keys > Sk) return RFK_EINVAL;
+    if (mask) return RFK_EUNSUPPORTED;
+    if (B == 0 || Sq == 0) return RFK_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    TRY(blas_status(cublasSetStream(ctx->blas, st)));
+    const int ld = (Sk + 7) & ~7;  // score row pitch in floats; P row pitch is 2*ld halves
+    const int BH = B * H;
+    const float scale = 1.0f / sqrtf((float)D), zero = 0.0f, one = 1.0f;
+    // scores[bh] (Sq x Sk, pitch ld) = scale * Q[bh] K[bh]^T
+    TRY(blas_status(cublasGemmStridedBatchedEx(
+        ctx->blas, CUBLAS_OP_T, CUBLAS_OP_N, Sk, Sq, D, &scale, K, CUDA_R_16F, D, (long long)Sk * D,
+        Q, CUDA_R_16F, D, (long long)Sq * D, &zero, workspace, CUDA_R_32F, ld, (long long)Sq * ld, BH,
+        CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT)));
+    TRY(rfk_softmax_probs_inplace(workspace, BH * Sq, n_keys, ld, 1.0f, stream));
+    const __half* P = reinterpret_cast<const __half*>(workspace);
+    // O[bh] (Sq x D) = P[bh] (Sq x Sk, pitch 2*ld) V[bh] (Sk x D); only the n_keys live columns
+    // of P are multiplied (the rest are zero), rounded up to the GEMM's preferred multiple of 8
+    const int kk = std::min(Sk, (n_keys + 7) & ~7);
+    if (!o_bshd) {
+        return blas_status(cublasGemmStridedBatchedEx(
+            ctx->blas, CUBLAS_OP_N, CUBLAS_OP_N, D, Sq, kk, &one, V, CUDA_R_16F, D, (long long)Sk * D,
+            P, CUDA_R_16F, 2 * ld, 2LL * Sq * ld, &zero, O, CUDA_R_16F, D, (long long)Sq * D, BH,
+            CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT));
+    }
+    // [B,Sq,H*D]: head h of batch b starts at b*Sq*H*D + h*D with row pitch H*D
+    for (int b = 0; b < B; ++b) {
+        TRY(blas_status(cublasGemmStridedBatchedEx(
+            ctx->blas, CUBLAS_OP_N, CUBLAS_OP_N, D, Sq, kk, &one,
+            (const __half*)V + (size_t)b * H * Sk * D, CUDA_R_16F, D, (long long)Sk * D,
+            P + (size_t)b * H * 2 * Sq * ld, CUDA_R_16F, 2 * ld, 2LL * Sq * ld, &zero,
+            (__half*)O + (size_t)b * Sq * H * D, CUDA_R_16F, H * D, (long long)D, H,
+            CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT)));
+    }
+    return RFK_OK;
+}
+
+// Q/K/V epilogue of a projection: fused kernel when the shape allows, else the unfused steps.
+static int project_epilogue(const rfk_half* x, long long row_stride, int n_parts,
+                            const float* const* gamma, rfk_half* const* out, const int* use_rope,
+                            const rfk_half* cosv, const rfk_half* sinv, int B, int S, int H, int D,
+                            int out_seq_stride, rfk_half* tmp, rfk_stream_t stream) {
+    int rc = rfk_qkv_norm_rope_transpose(x, row_stride, n_parts, gamma, out, use_rope, cosv, sinv, B,
+                                         S, H, D, kEpsFp16, out_seq_stride, stream);
+    if (rc != RFK_EUNSUPPORTED) return rc;
+    // unfused: needs a contiguous copy of each part in tmp [B*S, H*D]
+    if (!tmp || (out_seq_stride && out_seq_stride != S)) return RFK_EUNSUPPORTED;
+    const int dim = H * D;
+    const long long M = (long long)B * S;
+    for (int p = 0; p < n_parts; ++p) {
+        cudaError_t e = cudaMemcpy2DAsync(tmp, (size_t)dim * 2, x + (size_t)p * dim, (size_t)row_stride * 2,
+                                          (size_t)dim * 2, (size_t)M, cudaMemcpyDeviceToDevice,
+                                          (cudaStream_t)stream);
+        if (e != cudaSuccess) return (int)e;
+        if (gamma[p]) TRY(rfk_rmsnorm(tmp, gamma[p], tmp, (int)M, dim, kEpsFp16, stream));
+        TRY(rfk_transpose_bshd_to_bhsd(tmp, out[p], B, S, H, D, stream));
+        if (use_rope[p]) TRY(rfk_apply_rope_one(out[p], cosv, sinv, B, H, S, D, stream));
+    }
+    return RFK_OK;
+}
+
+extern "C" int rfk_precompute_cross_kv(rfk_ctx* ctx, const rfk_cross_attn_weights* w,
+                                       const rfk_half* ctx_normed, rfk_half* K_out, rfk_half* V_out,
+                                       rfk_half* proj_buf, int B, int Sk, int Sk_pad, int kv_dim,
+                                       int dim, int num_heads, rfk_stream_t stream) {
+    if (!ctx || !w || !ctx_normed || !K_out || !V_out || !proj_buf) return RFK_EINVAL;
+    if (B <= 0 || Sk <= 0 || Sk_pad < Sk || dim <= 0 || num_heads <= 0 || dim % num_heads) return RFK_EINVAL;
+    const int Mk = B * Sk, hd = dim / num_heads;
+    rfk_half* Kp = proj_buf;
+    rfk_half* Vp = proj_buf + (size_t)Mk * dim;
+    TRY(rfk_linear(ctx, ctx_normed, w->k_proj_w, w->k_proj_b, Kp, Mk, dim, kv_dim, stream));
+    TRY(rfk_linear(ctx, ctx_normed, w->v_proj_w, w->v_proj_b, Vp, Mk, dim, kv_dim, stream));
+    if (Sk_pad != Sk) {
+        const size_t bytes = (size_t)B * num_heads * Sk_pad * hd * 2;
+        cudaError_t e = cudaMemsetAsync(K_out, 0, bytes, (cudaStream_t)stream);
+        if (e == cudaSuccess) e = cudaMemsetAsync(V_out, 0, bytes, (cudaStream_t)stream);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const float* g[1] = {w->k_norm_gamma};
+    rfk_half* o[1] = {K_out};
+    const int no_rope[1] = {0};
+    // K and V cannot share a launch: they live in two separate [Mk, dim] projections
+    TRY(project_epilogue(Kp, dim, 1, g, o, no_rope, nullptr, nullptr, B, Sk, num_heads, hd, Sk_pad,
+                         nullptr, stream));
+    g[0] = nullptr; o[0] = V_out;
+    return project_epilogue(Vp, dim, 1, g, o, no_rope, nullptr, nullptr, B, Sk, num_heads, hd, Sk_pad,
+                            nullptr, stream);
+}
+
+extern "C" int rfk_cross_attention_cached(rfk_ctx* ctx, const rfk_cross_attn_weights* w,
+                                          const rfk_half* q_in, rfk_half* out, rfk_half* proj_buf,
+                                          float* score_buf, const rfk_half* K_cached,
+                                          const rfk_half* V_cached, int B, int Sq, int Sk, int n_keys,
+                                          int q_dim, int dim, int num_heads,
+                                          const rfk_half* q_rope_cos, const rfk_half* q_rope_sin,
+                                          const rfk_half* k_rope_cos, const rfk_half* k_rope_sin,
+                                          rfk_stream_t stream) {
+    if (!ctx || !w || !q_in || !out || !proj_buf || !score_buf || !K_cached || !V_cached) return RFK_EINVAL;
+    if (B <= 0 || Sq <= 0 || Sk <= 0 || dim <= 0 || num_heads <= 0 || dim % num_heads) return RFK_EINVAL;
+    const int Mq = B * Sq, hd = dim / num_heads;
+    rfk_half* Q = proj_buf;                          // [Mq, dim] projection, later the attention output
+    rfk_half* Q_bhsd = proj_buf + (size_t)Mq * dim;  // [B,H,Sq,hd]
+    rfk_half* K_rot = Q_bhsd + (size_t)Mq * dim;     // [B,H,Sk,hd]
+    TRY(rfk_linear(ctx, q_in, w->q_proj_w, w->q_proj_b, Q, Mq, dim, q_dim, stream));
+    const float* g[1] = {w->q_norm_gamma};
+    rfk_half* o[1] = {Q_bhsd};
+    const int rope[1] = {q_rope_cos != nullptr};
+    TRY(project_epilogue(Q, dim, 1, g, o, rope, q_rope_cos, q_rope_sin, B, Sq, num_heads, hd, 0, K_rot, stream));
+    const rfk_half* K_use = K_cached;
+    if (k_rope_cos) {
+        TRY(rfk_rope_one_oop(K_cached, K_rot, k_rope_cos, k_rope_sin, B, num_heads, Sk, hd, Sk, Sk, 0, stream));
+        K_use = K_rot;
+    }
+    TRY(rfk_sdpa(ctx, Q_bhsd, K_use, V_cached, Q /* [B,Sq,dim] */, score_buf, nullptr, B, num_heads, Sq,
+                 Sk, n_keys, hd, 1, stream));
+    return rfk_linear(ctx, Q, w->out_proj_w, w->out_proj_b, out, Mq, q_dim, dim, stream);
+}
+
+extern "C" int rfk_swin_self_attention(rfk_ctx* ctx, const rfk_mha_weights* w, const rfk_half* x,
+                                       rfk_half* out, rfk_half* residual_x, rfk_half* window_buf,
+                                       rfk_half* qkv_buf, float* score_buf, rfk_half* scratch, int B,
+                                       int H, int W, int dim, int num_heads, int window_size,
+                                       int shift_size, const uint8_t* shift_mask, rfk_stream_t stream) {
+    if (!ctx || !w || !x || (!out && !residual_x) || !window_buf || !qkv_buf || !score_buf || !scratch)
+        return RFK_EINVAL;
+    if (B <= 0 || H <= 0 || W <= 0 || window_size <= 0 || H % window_size || W % window_size) return RFK_EINVAL;
+    if (dim <= 0 || num_heads <= 0 || dim % num_heads) return RFK_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int ws = window_size, ws2 = ws * ws, nW = (H / ws) * (W / ws), hd = dim / num_heads;
+    const int BnW = B * nW, M = BnW * ws2, BH = BnW * num_heads;
+    TRY(rfk_window_gather(x, window_buf, B, H, W, dim, ws, shift_size, stream));
+    TRY(rfk_linear(ctx, window_buf, w->in_proj_w, w->in_proj_b, qkv_buf, M, 3 * dim, dim, stream));
+    rfk_half* Qt = scratch;
+    rfk_half* Kt = scratch + (size_t)M * dim;
+    rfk_half* Vt = scratch + (size_t)2 * M * dim;
+    const float* g[3] = {w->q_norm_gamma, w->k_norm_gamma, nullptr};
+    rfk_half* o[3] = {Qt, Kt, Vt};
+    const int no_rope[3] = {0, 0, 0};
+    TRY(project_epilogue(qkv_buf, 3LL * dim, 3, g, o, no_rope, nullptr, nullptr, BnW, ws2, num_heads, hd, 0,
+                         window_buf, stream));
+    TRY(blas_status(cublasSetStream(ctx->blas, st)));
+    const float scale = 1.0f / sqrtf((float)hd), zero = 0.0f, one = 1.0f;
+    const long long sQ = (long long)ws2 * hd, sS = (long long)ws2 * ws2;
+    TRY(blas_status(cublasGemmStridedBatchedEx(ctx->blas, CUBLAS_OP_T, CUBLAS_OP_N, ws2, ws2, hd, &scale, Kt,
+                                               CUDA_R_16F, hd, sQ, Qt, CUDA_R_16F, hd, sQ, &zero, score_buf,
+                                               CUDA_R_32F, ws2, sS, BH, CUBLAS_COMPUTE_32F,
+                                               CUBLAS_GEMM_DEFAULT)));
+    TRY(rfk_swin_softmax_probs_inplace(score_buf, (shift_mask && shift_size > 0) ? shift_mask : nullptr, BnW,
+                                       num_heads, ws2, nW, stream));
+    // O (over Q) = P V ; P pitch is 2*ws2 halves inside the score rows
+    TRY(blas_status(cublasGemmStridedBatchedEx(
+        ctx->blas, CUBLAS_OP_N, CUBLAS_OP_N, hd, ws2, ws2, &one, Vt, CUDA_R_16F, hd, sQ,
+        reinterpret_cast<const __half*>(score_buf), CUDA_R_16F, 2 * ws2, 2 * sS, &zero, Qt, CUDA_R_16F, hd,
+        sQ, BH, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT)));
+    TRY(rfk_transpose_bhsd_to_bsd(Qt, window_buf, BnW, num_heads, ws2, hd, stream));
+    TRY(rfk_linear(ctx, window_buf, w->out_proj_w, w->out_proj_b, qkv_buf, M, dim, dim, stream));
+    if (residual_x) return rfk_window_scatter(qkv_buf, residual_x, B, H, W, dim, ws, shift_size, 1, stream);
+    return rfk_window_scatter(qkv_buf, out, B, H, W, dim, ws, shift_size, 0, stream);
+}
+
+extern "C" int rfk_self_attention(rfk_ctx* ctx, const rfk_mha_weights* w, const rfk_half* x,
+                                  rfk_half* out, rfk_half* qkv_buf, float* score_buf, int B, int S,
+                                  int dim, int num_heads, const rfk_half* rope_cos,
+                                  const rfk_half* rope_sin, rfk_stream_t stream) {
+    if (!ctx || !w || !x || !out || !qkv_buf || !score_buf) return RFK_EINVAL;
+    if (B <= 0 || S <= 0 || dim <= 0 || num_heads <= 0 || dim % num_heads) return RFK_EINVAL;
+    const int M = B * S, hd = dim / num_heads;
+    TRY(rfk_linear(ctx, x, w->in_proj_w, w->in_proj_b, qkv_buf, M, 3 * dim, dim, stream));
+    rfk_half* Qb = qkv_buf + (size_t)M * 3 * dim;
+    rfk_half* Kb = Qb + (size_t)M * dim;
+    rfk_half* Vb = Kb + (size_t)M * dim;
+    const float* g[3] = {w->q_norm_gamma, w->k_norm_gamma, nullptr};
+    rfk_half* o[3] = {Qb, Kb, Vb};
+    const int rope[3] = {rope_cos != nullptr, rope_cos != nullptr, 0};
+    TRY(project_epilogue(qkv_buf, 3LL * dim, 3, g, o, rope, rope_cos, rope_sin, B, S, num_heads, hd, 0, nullptr,
+                         stream));
+    // attention output lands in the (dead) front of qkv_buf as [B,S,dim]
+    TRY(rfk_sdpa(ctx, Qb, Kb, Vb, qkv_buf, score_buf, nullptr, B, num_heads, S, S, S, hd, 1, stream));
+    return rfk_linear(ctx, qkv_buf, w->out_proj_w, w->out_proj_b, out, M, dim, dim, stream);
+}
+
+extern "C" int rfk_decoder_layer_forward_cached(
+    rfk_ctx* ctx, const rfk_decoder_layer_weights* w, rfk_half* x, const rfk_half* pending_residual,
+    const rfk_half** pending_out, rfk_half* temp, rfk_half* proj_buf, rfk_half* qkv_buf, rfk_half* ffn_buf,
+    rfk_half* window_buf, float* cross_score_buf, float* self_score_buf, const rfk_half* K_cached,
+    const rfk_half* V_cached, int B, int Sq, int Sk, int n_keys, int dim, int num_heads, int ffn_hidden,
+    int patch_h, int patch_w, int window_size, int shift_size, const uint8_t* shift_mask,
+    const rfk_half* q_rope_cos, const rfk_half* q_rope_sin, const rfk_half* k_rope_cos,
+    const rfk_half* k_rope_sin, rfk_stream_t stream) {
+    if (!ctx || !w || !x || !temp || !proj_buf || !qkv_buf || !ffn_buf || !window_buf) return RFK_EINVAL;
+    if (Sq != patch_h * patch_w) return RFK_EINVAL;
+    const int Mq = B * Sq;
+    // 1) (deferred FFN residual of the previous layer +) pre-norm -> cached cross-attention
+    TRY(rfk_rmsnorm_residual_f16(x, pending_residual, w->query_norm_gamma, temp, Mq, dim, kEpsFp16, stream));
+    rfk_half* cross_out = qkv_buf;
+    TRY(rfk_cross_attention_cached(ctx, &w->cross_attn, temp, cross_out, proj_buf, cross_score_buf, K_cached,
+                                   V_cached, B, Sq, Sk, n_keys, dim, dim, num_heads, q_rope_cos, q_rope_sin,
+                                   k_rope_cos, k_rope_sin, stream));
+    // 2) residual + pre-norm in one kernel -> swin attention, whose window scatter adds into x
+    TRY(rfk_rmsnorm_residual_f16(x, cross_out, w->self_attn_norm_gamma, temp, Mq, dim, kEpsFp16, stream));
+    TRY(rfk_swin_self_attention(ctx, &w->self_attn, temp, nullptr, x, window_buf, qkv_buf, self_score_buf,
+                                proj_buf, B, patch_h, patch_w, dim, num_heads, window_size, shift_size,
+                                shift_mask, stream));
+    // 3) pre-norm -> FFN; its residual is left to the next layer's first kernel when asked
+    TRY(rfk_rmsnorm(x, w->ffn_norm_gamma, temp, Mq, dim, kEpsFp16, stream));
+    TRY(rfk_ffn_swiglu(ctx, &w->ffn, temp, ffn_buf, qkv_buf, Mq, dim, ffn_hidden, stream));
+    if (pending_out) { *pending_out = ffn_buf; return RFK_OK; }
+    return rfk_residual_add(x, ffn_buf, (long long)Mq * dim, stream);
+}
+
+extern "C" int rfk_encoder_layer_forward_mixed(
+    rfk_ctx* ctx, const rfk_encoder_layer_weights* w, float* x, const rfk_half* pending_residual,
+    const rfk_half** pending_out, rfk_half* temp, rfk_half* qkv_buf, rfk_half* ffn_buf, float* score_buf,
+    int B, int S, int dim, int num_heads, int ffn_hidden, const rfk_half* rope_cos, const rfk_half* rope_sin,
+    rfk_stream_t stream) {
+    if (!ctx || !w || !x || !temp || !qkv_buf || !ffn_buf || !score_buf) return RFK_EINVAL;
+    const int M = B * S;
+    // fp32 hidden (+= fp16 sub-layer output) -> fp32 norm -> fp16, one kernel instead of three
+    TRY(rfk_rmsnorm_residual_mixed_cast16(x, pending_residual, w->query_norm_gamma, temp, M, dim, kEpsFp32, stream));
+    TRY(rfk_self_attention(ctx, &w->attn, temp, ffn_buf, qkv_buf, score_buf, B, S, dim, num_heads, rope_cos,
+                           rope_sin, stream));
+    TRY(rfk_rmsnorm_residual_mixed_cast16(x, ffn_buf, w->ffn_norm_gamma, temp, M, dim, kEpsFp32, stream));
+    TRY(rfk_ffn_swiglu(ctx, &w->ffn, temp, ffn_buf, qkv_buf, M, dim, ffn_hidden, stream));
+    if (pending_out) { *pending_out = ffn_buf; return RFK_OK; }
+    return rfk_residual_add_mixed(x, ffn_buf, (long long)M * dim, stream);
+}

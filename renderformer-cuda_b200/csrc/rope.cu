@@ -231,7 +231,8 @@ __global__ void __launch_bounds__(128)
 qkv_epilogue_kernel(const __half* __restrict__ x, long long row_stride,
                     const __grid_constant__ QkvParts parts,
                     const __half* __restrict__ cos_vals, const __half* __restrict__ sin_vals,
-                    int batch, int seq_len, int num_heads, int head_dim, float eps) {
+                    int batch, int seq_len, int num_heads, int head_dim, float eps,
+                    long long out_seq_stride) {
     const int lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const long long rows = (long long)batch * seq_len;
@@ -295,7 +296,7 @@ qkv_epilogue_kernel(const __half* __restrict__ x, long long row_stride,
                 unpack8(ldg_half8(sin_vals + to + half_d), sh);
                 rotate8(lo[k], hi[k], cl, sl, ch, sh);
             }
-            const size_t oo = (((size_t)b * num_heads + h) * seq_len + s) * head_dim + j * 8;
+            const size_t oo = (((size_t)b * num_heads + h) * out_seq_stride + s) * head_dim + j * 8;
             store8(out + oo, lo[k]);
             store8(out + oo + half_d, hi[k]);
         }
@@ -381,8 +382,10 @@ extern "C" int rfk_qkv_norm_rope_transpose(const rfk_half* x, long long row_stri
                                            const int* use_rope, const rfk_half* cos_vals,
                                            const rfk_half* sin_vals, int batch, int seq_len,
                                            int num_heads, int head_dim, float eps,
-                                           rfk_stream_t stream) {
+                                           int out_seq_stride, rfk_stream_t stream) {
     if (!x || !gamma || !out || !use_rope || n_parts < 1 || n_parts > 3) return RFK_EINVAL;
+    if (out_seq_stride == 0) out_seq_stride = seq_len;
+    if (out_seq_stride < seq_len) return RFK_EINVAL;
     if (batch < 0 || seq_len < 0 || num_heads <= 0 || head_dim <= 0) return RFK_EINVAL;
     const long long dim = (long long)num_heads * head_dim;
     if (row_stride < dim * n_parts) return RFK_EINVAL;
@@ -408,7 +411,7 @@ extern "C" int rfk_qkv_norm_rope_transpose(const rfk_half* x, long long row_stri
     qkv_epilogue_kernel<N><<<grid, WPB * 32, 0, st>>>((const __half*)x, row_stride, parts,       \
                                                       (const __half*)cos_vals,                   \
                                                       (const __half*)sin_vals, batch, seq_len,   \
-                                                      num_heads, head_dim, eps)
+                                                      num_heads, head_dim, eps, out_seq_stride)
     if (npairs <= 32) RFK_QKV(1);
     else if (npairs <= 64) RFK_QKV(2);
     else RFK_QKV(4);

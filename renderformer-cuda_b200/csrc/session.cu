@@ -1,0 +1,495 @@
+// Per-scene render session: scene encoding (once), per-view front end + decoder stack
+// captured as a CUDA graph, double-buffered frame slots so the host can stay one frame
+// ahead of the device.
+//
+// Reference: src/pipeline/render_session.cu (BANANASJIM/renderformer-cuda)
+//   :177-254  render_view            (the captured per-view work)
+//   :258-416  create: preprocessing, encoder, K/V cache
+//   :418-495  create: buffers, constants, warm-up, graph capture
+//   :501-559  render_frame / async API / download
+// Differences that matter:
+//   - the per-view geometry front end is one kernel (rfk_view_geometry) instead of three
+//     device-to-device copies and three launches; rays are generated directly as patch tokens;
+//   - nothing inside the captured region allocates (the reference's DPT head and attention
+//     fall-back call cudaMallocAsync while capturing);
+//   - two frame slots (pinned camera + result buffer + graph instance each): frame i+1 can be
+//     submitted while frame i renders and frame i-1 downloads;
+//   - the query RoPE tables are built from all-zero positions in the reference
+//     (render_session.cu:446-454), i.e. cos = 1 and sin = 0 exactly; rotating by them returns
+//     the input bit for bit, so the query rotation is skipped;
+//   - the DPT convolution head and the image post-process are outside this library: the frame
+//     result is the decoder's final token map plus the four feature taps a DPT head reads.
+#include "layers_internal.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+using namespace rfk_layers;
+
+#define TRY(expr)                       \
+    do {                                \
+        int rc_ = (expr);               \
+        if (rc_ != RFK_OK) return rc_;  \
+    } while (0)
+#define TRY_CUDA(expr)                          \
+    do {                                        \
+        cudaError_t e_ = (expr);                \
+        if (e_ != cudaSuccess) return (int)e_;  \
+    } while (0)
+
+namespace {
+
+constexpr int kSlots = 2;
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct StateLayout {
+    size_t kv_layer_bytes;  // one K (or V) cache of one layer: [heads, Se_pad, hd] fp16
+    size_t kv_off, tri_off, vn_off, center_off, total;
+};
+
+StateLayout state_layout(const rfk_model& m, int n_tris) {
+    const int Se_pad = (m.num_register_tokens + n_tris + 7) & ~7;
+    StateLayout L{};
+    L.kv_layer_bytes = (size_t)Se_pad * m.dim * sizeof(__half);
+    L.kv_off = 0;
+    L.tri_off = align_up(L.kv_off + 2 * (size_t)m.dec_layers * L.kv_layer_bytes, 256);
+    L.vn_off = align_up(L.tri_off + (size_t)n_tris * 9 * sizeof(__half), 256);
+    L.center_off = align_up(L.vn_off + (size_t)n_tris * 9 * sizeof(__half), 256);
+    L.total = align_up(L.center_off + 3 * sizeof(float), 256);
+    return L;
+}
+
+// last `last_n` channels of each row: v <- half(log10f(float(v) + 1))   (render_session.cu:33-38)
+__global__ void log_encode_kernel(__half* data, int N, int C, int last_n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N * last_n) return;
+    const int n = i / last_n, idx = n * C + (C - last_n) + (i % last_n);
+    data[idx] = __float2half(log10f(__half2float(data[idx]) + 1.0f));
+}
+
+// out = a + b + float(c[i % dim])   (render_session.cu:39-43)
+__global__ void add3_bc_kernel(float* out, const float* a, const float* b, const __half* c, long long n, int dim) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = a[i] + b[i] + __half2float(c[i % dim]);
+}
+
+inline unsigned blocks_for(long long n) { return (unsigned)((n + 255) / 256); }
+
+// swin shift mask [nWin, ws2, ws2]: 1 where both tokens come from the same pre-shift region
+// (render_session.cu:99-116)
+std::vector<uint8_t> make_shift_mask(int pH, int pW, int ws, int shift) {
+    const int nH = pH / ws, nW = pW / ws, ws2 = ws * ws;
+    std::vector<int> reg((size_t)pH * pW);
+    for (int i = 0; i < pH; ++i)
+        for (int j = 0; j < pW; ++j) reg[(size_t)i * pW + j] = ((i + shift) % pH / ws) * nW + ((j + shift) % pW / ws);
+    std::vector<uint8_t> mask((size_t)nH * nW * ws2 * ws2, 1);
+    for (int wi = 0; wi < nH; ++wi)
+        for (int wj = 0; wj < nW; ++wj) {
+            const int wid = wi * nW + wj;
+            for (int a = 0; a < ws2; ++a) {
+                const int ra = reg[(size_t)(wi * ws + a / ws) * pW + wj * ws + a % ws];
+                for (int b = 0; b < ws2; ++b) {
+                    const int rb = reg[(size_t)(wi * ws + b / ws) * pW + wj * ws + b % ws];
+                    mask[((size_t)wid * ws2 + a) * ws2 + b] = (ra == rb);
+                }
+            }
+        }
+    return mask;
+}
+
+}  // namespace
+
+struct rfk_session {
+    rfk_model m{};
+    int N = 0, res = 0, Se = 0, Se_pad = 0, pH = 0, pW = 0, nP = 0, hd = 0, flags = 0;
+    rfk_ctx* ctx = nullptr;
+    cudaStream_t stream = nullptr, copy_stream = nullptr;
+    StateLayout L{};
+    char* state = nullptr;  // caller-owned scene state
+    std::vector<void*> owned;  // device allocations of this session
+
+    // per-view buffers
+    float* cam_gpu = nullptr;  // [16 c2w | 1 fov | pad]
+    float* id_c2w = nullptr;
+    rfk_half *vtri = nullptr, *vvn = nullptr, *vpos = nullptr, *k_cos = nullptr, *k_sin = nullptr;
+    rfk_half *ray_pat = nullptr, *rtok = nullptr;
+    rfk_half *temp = nullptr, *proj = nullptr, *qkv = nullptr, *ffn = nullptr, *win = nullptr;
+    float *score = nullptr, *self_score = nullptr;
+    uint8_t* shift_mask = nullptr;
+    rfk_half* dft[4] = {nullptr, nullptr, nullptr, nullptr};
+    rfk_half* result[kSlots] = {nullptr, nullptr};
+
+    // frame slots
+    float* pin_cam[kSlots] = {nullptr, nullptr};  // pinned [16 c2w | fov]
+    cudaGraph_t graph[kSlots] = {nullptr, nullptr};
+    cudaGraphExec_t exec[kSlots] = {nullptr, nullptr};
+    cudaEvent_t ev_start[kSlots]{}, ev_done[kSlots]{}, ev_dl[kSlots]{};
+    bool dl_pending[kSlots] = {false, false};
+    long long frames = 0;  // frames submitted so far
+    int graph_nodes = 0, kernels_per_view = 0;
+    bool finalized = false;
+
+    rfk_half* kvK(int layer) const { return (rfk_half*)(state + L.kv_off + (size_t)(2 * layer) * L.kv_layer_bytes); }
+    rfk_half* kvV(int layer) const { return (rfk_half*)(state + L.kv_off + (size_t)(2 * layer + 1) * L.kv_layer_bytes); }
+    rfk_half* tri16() const { return (rfk_half*)(state + L.tri_off); }
+    rfk_half* vn16() const { return (rfk_half*)(state + L.vn_off); }
+    float* center() const { return (float*)(state + L.center_off); }
+
+    template <typename T> int alloc(T** p, size_t count) {
+        void* d = nullptr;
+        cudaError_t e = cudaMalloc(&d, std::max<size_t>(count * sizeof(T), 256));
+        if (e != cudaSuccess) return (int)e;
+        owned.push_back(d);
+        *p = (T*)d;
+        return RFK_OK;
+    }
+
+    int render_view(const float* pinned_cam, rfk_half* result_out);
+};
+
+// The per-view work; everything here is captured into the graph.
+int rfk_session::render_view(const float* pinned_cam, rfk_half* result_out) {
+    rfk_stream_t s = (rfk_stream_t)stream;
+    const int dim = m.dim, nr = m.num_register_tokens, ps = m.patch_size;
+    TRY_CUDA(cudaMemcpyAsync(cam_gpu, pinned_cam, 17 * sizeof(float), cudaMemcpyHostToDevice, stream));
+    // world -> camera of triangles and normals, register-token positions, K RoPE tables
+    TRY(rfk_view_geometry(cam_gpu, tri16(), vn16(), center(), m.vt_rope_freqs, vtri, vvn, vpos, k_cos, k_sin, N, nr,
+                          Se_pad, m.rope_num_freqs, hd, s));
+    // camera-space rays (identity pose, as the reference does) written straight as patch tokens
+    TRY(rfk_ray_gen_patchify(id_c2w, cam_gpu + 16, nullptr, ray_pat, 1, res, ps, s));
+    TRY(rfk_linear(ctx, ray_pat, m.ray_enc_w, m.ray_enc_b, rtok, nP, dim, 3 * ps * ps, s));
+    TRY(rfk_rmsnorm(rtok, m.ray_enc_norm, rtok, nP, dim, kEpsFp16, s));
+    TRY(rfk_broadcast_add(rtok, m.ray_map_patch_token, (long long)nP * dim, dim, s));
+
+    const int n_keys = (flags & RFK_SESSION_PAD_KEYS_ATTEND) ? Se_pad : Se;
+    const rfk_half* pending = nullptr;
+    const int L4 = std::max(1, m.dec_layers / 4);
+    for (int i = 0; i < m.dec_layers; ++i) {
+        const int shift = (i % 2 == 1) ? m.shift_size : 0;
+        const bool tap = ((i + 1) % L4 == 0) && ((i + 1) / L4 <= 4);
+        const bool last = i == m.dec_layers - 1;
+        const rfk_half* next_pending = nullptr;
+        // a tapped (or the last) layer finishes x itself; the others leave their FFN residual
+        // to the first kernel of the next layer
+        TRY(rfk_decoder_layer_forward_cached(ctx, &m.dec[i], rtok, pending, (tap || last) ? nullptr : &next_pending,
+                                             temp, proj, qkv, ffn, win, score, self_score, kvK(i), kvV(i), 1, nP,
+                                             Se_pad, n_keys, dim, m.num_heads, m.ffn_hidden, pH, pW, m.window_size,
+                                             shift, shift > 0 ? shift_mask : nullptr, nullptr, nullptr, k_cos, k_sin, s));
+        pending = next_pending;
+        if (tap)
+            TRY_CUDA(cudaMemcpyAsync(dft[(i + 1) / L4 - 1], rtok, (size_t)nP * dim * sizeof(rfk_half),
+                                     cudaMemcpyDeviceToDevice, stream));
+    }
+    TRY_CUDA(cudaMemcpyAsync(result_out, rtok, (size_t)nP * dim * sizeof(rfk_half), cudaMemcpyDeviceToDevice, stream));
+    return RFK_OK;
+}
+
+extern "C" size_t rfk_scene_state_bytes(const rfk_model* model, int n_tris) {
+    if (!model || n_tris <= 0) return 0;
+    return state_layout(*model, n_tris).total;
+}
+
+static int check_model(const rfk_model* m) {
+    if (!m) return RFK_EINVAL;
+    if (m->dim <= 0 || m->num_heads <= 0 || m->dim % m->num_heads || m->ffn_hidden <= 0) return RFK_EINVAL;
+    if (m->enc_layers < 0 || m->enc_layers > RFK_MAX_LAYERS || m->dec_layers <= 0 || m->dec_layers > RFK_MAX_LAYERS)
+        return RFK_EINVAL;
+    const int hd = m->dim / m->num_heads;
+    if (m->rope_num_freqs <= 0 || 9 * m->rope_num_freqs > hd / 2 || hd % 16) return RFK_EINVAL;
+    if (m->patch_size <= 0 || m->window_size <= 0 || m->shift_size < 0 || m->shift_size >= m->window_size)
+        return RFK_EINVAL;
+    return RFK_OK;
+}
+
+extern "C" int rfk_session_create(const rfk_model* model, int n_tris, int img_res, void* scene_state, int flags,
+                                  rfk_session** out) {
+    if (!out || !scene_state || n_tris <= 0 || img_res <= 0) return RFK_EINVAL;
+    TRY(check_model(model));
+    if (img_res % model->patch_size || (img_res / model->patch_size) % model->window_size) return RFK_EINVAL;
+    rfk_session* d = new rfk_session();
+    d->m = *model;
+    d->N = n_tris; d->res = img_res; d->flags = flags;
+    d->Se = model->num_register_tokens + n_tris;
+    d->Se_pad = (d->Se + 7) & ~7;
+    d->pH = d->pW = img_res / model->patch_size;
+    d->nP = d->pH * d->pW;
+    d->hd = model->dim / model->num_heads;
+    d->L = state_layout(*model, n_tris);
+    d->state = (char*)scene_state;
+    const int dim = model->dim, nh = model->num_heads, ffn = model->ffn_hidden, nP = d->nP, Se_pad = d->Se_pad;
+    const int ws = model->window_size, nWin = (d->pH / ws) * (d->pW / ws);
+    int rc = rfk_ctx_create(&d->ctx);
+    auto fail = [&](int code) { rfk_session_destroy(d); return code; };
+    if (rc) return fail(rc);
+    if (cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking) != cudaSuccess) return fail((int)cudaGetLastError());
+    if (cudaStreamCreateWithFlags(&d->copy_stream, cudaStreamNonBlocking) != cudaSuccess) return fail((int)cudaGetLastError());
+    for (int k = 0; k < kSlots; ++k) {
+        if (cudaEventCreate(&d->ev_start[k]) != cudaSuccess || cudaEventCreate(&d->ev_done[k]) != cudaSuccess ||
+            cudaEventCreateWithFlags(&d->ev_dl[k], cudaEventDisableTiming) != cudaSuccess)
+            return fail((int)cudaGetLastError());
+        if (cudaHostAlloc((void**)&d->pin_cam[k], 32 * sizeof(float), cudaHostAllocDefault) != cudaSuccess)
+            return fail((int)cudaGetLastError());
+    }
+#define ALLOC(ptr, count)                    \
+    if ((rc = d->alloc(&d->ptr, (count)))) return fail(rc)
+    ALLOC(cam_gpu, 32);
+    ALLOC(id_c2w, 16);
+    ALLOC(vtri, (size_t)n_tris * 9);
+    ALLOC(vvn, (size_t)n_tris * 9);
+    ALLOC(vpos, (size_t)Se_pad * 9);
+    ALLOC(k_cos, (size_t)Se_pad * d->hd);
+    ALLOC(k_sin, (size_t)Se_pad * d->hd);
+    ALLOC(ray_pat, (size_t)nP * 3 * model->patch_size * model->patch_size);
+    ALLOC(rtok, (size_t)nP * dim);
+    ALLOC(temp, (size_t)nP * dim);
+    ALLOC(proj, std::max((size_t)2 * nP * dim + (size_t)nh * Se_pad * d->hd, (size_t)3 * nP * dim));
+    ALLOC(qkv, (size_t)nP * std::max(3 * dim, 2 * ffn));
+    ALLOC(ffn, (size_t)nP * std::max(dim, ffn));
+    ALLOC(win, (size_t)nP * dim);
+    ALLOC(score, (size_t)nh * nP * Se_pad);
+    ALLOC(self_score, (size_t)nWin * nh * ws * ws * ws * ws);
+    ALLOC(shift_mask, (size_t)nWin * ws * ws * ws * ws);
+    for (int j = 0; j < 4; ++j) ALLOC(dft[j], (size_t)nP * dim);
+    for (int k = 0; k < kSlots; ++k) ALLOC(result[k], (size_t)nP * dim);
+#undef ALLOC
+    const float id[16] = {1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1};
+    if (cudaMemcpy(d->id_c2w, id, sizeof(id), cudaMemcpyHostToDevice) != cudaSuccess) return fail((int)cudaGetLastError());
+    *out = d;
+    return RFK_OK;
+}
+
+extern "C" int rfk_session_destroy(rfk_session* d) {
+    if (!d) return RFK_OK;
+    if (d->stream) cudaStreamSynchronize(d->stream);
+    if (d->copy_stream) cudaStreamSynchronize(d->copy_stream);
+    for (int k = 0; k < kSlots; ++k) {
+        if (d->exec[k]) cudaGraphExecDestroy(d->exec[k]);
+        if (d->graph[k]) cudaGraphDestroy(d->graph[k]);
+        if (d->pin_cam[k]) cudaFreeHost(d->pin_cam[k]);
+        if (d->ev_start[k]) cudaEventDestroy(d->ev_start[k]);
+        if (d->ev_done[k]) cudaEventDestroy(d->ev_done[k]);
+        if (d->ev_dl[k]) cudaEventDestroy(d->ev_dl[k]);
+    }
+    for (void* p : d->owned) cudaFree(p);
+    if (d->stream) cudaStreamDestroy(d->stream);
+    if (d->copy_stream) cudaStreamDestroy(d->copy_stream);
+    rfk_ctx_destroy(d->ctx);
+    delete d;
+    return RFK_OK;
+}
+
+// Scratch allocations of the one-time scene encoding (freed on every exit path).
+struct Scratch {
+    std::vector<void*> ptrs;
+    ~Scratch() { for (void* p : ptrs) cudaFree(p); }
+    template <typename T> int get(T** p, size_t count) {
+        void* d = nullptr;
+        cudaError_t e = cudaMalloc(&d, std::max<size_t>(count * sizeof(T), 256));
+        if (e != cudaSuccess) return (int)e;
+        ptrs.push_back(d);
+        *p = (T*)d;
+        return RFK_OK;
+    }
+};
+
+extern "C" int rfk_session_encode_scene(rfk_session* d, const float* tri, const float* vn, const rfk_half* tex) {
+    if (!d || !tri || !vn || !tex) return RFK_EINVAL;
+    const rfk_model& m = d->m;
+    const int N = d->N, Se = d->Se, Se_pad = d->Se_pad, dim = m.dim, nh = m.num_heads, hd = d->hd, nr = m.num_register_tokens;
+    const int ffn = m.ffn_hidden, C = m.texture_channels;
+    const int vn_pe_dim = 9 + 9 * m.vn_pe_num_freqs * 2;
+    cudaStream_t st = d->stream;
+    rfk_stream_t s = (rfk_stream_t)st;
+    Scratch sc;
+
+    // texture: log-encode the last 3 channels (render_session.cu:297-299)
+    rfk_half* tex_buf; TRY(sc.get(&tex_buf, (size_t)N * C));
+    TRY_CUDA(cudaMemcpyAsync(tex_buf, tex, (size_t)N * C * sizeof(rfk_half), cudaMemcpyDeviceToDevice, st));
+    log_encode_kernel<<<blocks_for((long long)N * 3), 256, 0, st>>>((__half*)tex_buf, N, C, 3);
+    // fp16 copies of the geometry kept for every view (render_session.cu:301-304)
+    TRY(rfk_cast_fp32_to_fp16(tri, d->tri16(), (long long)N * 9, s));
+    TRY(rfk_cast_fp32_to_fp16(vn, d->vn16(), (long long)N * 9, s));
+    // world-space centroid, on the host in double as the reference does (render_session.cu:62-70)
+    std::vector<__half> h_tri((size_t)N * 9);
+    TRY_CUDA(cudaMemcpyAsync(h_tri.data(), d->tri16(), h_tri.size() * sizeof(__half), cudaMemcpyDeviceToHost, st));
+    TRY_CUDA(cudaStreamSynchronize(st));
+    double mean[9] = {};
+    for (int i = 0; i < N; ++i)
+        for (int k = 0; k < 9; ++k) mean[k] += __half2float(h_tri[(size_t)i * 9 + k]);
+    float c[3];
+    for (int j = 0; j < 3; ++j) c[j] = (float)(((mean[j] + mean[3 + j] + mean[6 + j]) / N) / 3.0);
+    TRY_CUDA(cudaMemcpyAsync(d->center(), c, sizeof(c), cudaMemcpyHostToDevice, st));
+
+    // normals: NeRF PE -> linear -> fp32 RMSNorm (render_session.cu:310-318)
+    rfk_half *vn_pe, *emb16; float *vn_n, *tex_n, *seq;
+    TRY(sc.get(&vn_pe, (size_t)N * vn_pe_dim));
+    TRY(sc.get(&emb16, (size_t)N * dim));
+    TRY(sc.get(&vn_n, (size_t)N * dim));
+    TRY(sc.get(&tex_n, (size_t)N * dim));
+    TRY(sc.get(&seq, (size_t)Se * dim));
+    TRY(rfk_nerf_pe_f32(vn, vn_pe, 1, N, 9, m.vn_pe_num_freqs, 0.0f, (float)(m.vn_pe_num_freqs - 1), 1, s));
+    TRY(rfk_linear(d->ctx, vn_pe, m.vn_proj_w, m.vn_proj_b, emb16, N, dim, vn_pe_dim, s));
+    TRY(rfk_cast_fp16_to_fp32(emb16, vn_n, (long long)N * dim, s));
+    TRY(rfk_rmsnorm_f32(vn_n, m.vn_enc_norm, vn_n, N, dim, kEpsFp16, s));
+    // texture: linear -> fp32 RMSNorm (render_session.cu:321-327)
+    TRY(rfk_linear(d->ctx, tex_buf, m.tex_enc_w, m.tex_enc_b, emb16, N, dim, C, s));
+    TRY(rfk_cast_fp16_to_fp32(emb16, tex_n, (long long)N * dim, s));
+    TRY(rfk_rmsnorm_f32(tex_n, m.tex_enc_norm, tex_n, N, dim, kEpsFp16, s));
+    // sequence = [register tokens | texture + normal + triangle token] in fp32 (render_session.cu:330-339)
+    TRY(rfk_cast_fp16_to_fp32(m.reg_tokens, seq, (long long)nr * dim, s));
+    add3_bc_kernel<<<blocks_for((long long)N * dim), 256, 0, st>>>(seq + (size_t)nr * dim, tex_n, vn_n,
+                                                                   (const __half*)m.tri_token, (long long)N * dim, dim);
+    // encoder positions: world centroid for the register tokens, then the triangles (render_session.cu:91-97,342-350)
+    rfk_half *enc_pos, *enc_cos, *enc_sin;
+    TRY(sc.get(&enc_pos, (size_t)Se * 9));
+    TRY(sc.get(&enc_cos, (size_t)Se * hd));
+    TRY(sc.get(&enc_sin, (size_t)Se * hd));
+    std::vector<__half> h_reg((size_t)nr * 9);
+    for (int r = 0; r < nr; ++r)
+        for (int k = 0; k < 9; ++k) h_reg[(size_t)r * 9 + k] = __float2half(c[k % 3]);
+    TRY_CUDA(cudaMemcpyAsync(enc_pos, h_reg.data(), h_reg.size() * sizeof(__half), cudaMemcpyHostToDevice, st));
+    TRY_CUDA(cudaMemcpyAsync(enc_pos + (size_t)nr * 9, d->tri16(), (size_t)N * 9 * sizeof(rfk_half), cudaMemcpyDeviceToDevice, st));
+    TRY(rfk_triangle_rope_freqs(enc_pos, m.enc_rope_freqs, enc_cos, enc_sin, 1, Se,
+                                m.rope_num_freqs, hd, s));
+    TRY_CUDA(cudaStreamSynchronize(st));  // h_reg goes out of use
+
+    // encoder (render_session.cu:356-371)
+    rfk_half *temp, *qkvb, *ffnb; float* score;
+    TRY(sc.get(&temp, (size_t)Se * dim));
+    TRY(sc.get(&qkvb, (size_t)Se * std::max(6 * dim, 2 * ffn)));
+    TRY(sc.get(&ffnb, (size_t)Se * std::max(dim, ffn)));
+    TRY(sc.get(&score, (size_t)nh * Se * Se_pad));
+    const rfk_half* pending = nullptr;
+    for (int i = 0; i < m.enc_layers; ++i) {
+        const rfk_half* next = nullptr;
+        TRY(rfk_encoder_layer_forward_mixed(d->ctx, &m.enc[i], seq, pending, i + 1 < m.enc_layers ? &next : nullptr,
+                                            temp, qkvb, ffnb, score, 1, Se, dim, nh, ffn,
+                                            enc_cos, enc_sin, s));
+        pending = next;
+    }
+    // context in fp16, then per decoder layer: kv-norm, K/V projections, padded head-major cache
+    // (render_session.cu:377-416)
+    rfk_half *ctx16, *ctx_normed, *kv_proj;
+    TRY(sc.get(&ctx16, (size_t)Se * dim));
+    TRY(sc.get(&ctx_normed, (size_t)Se * dim));
+    TRY(sc.get(&kv_proj, (size_t)2 * Se * dim));
+    TRY(rfk_cast_fp32_to_fp16(seq, ctx16, (long long)Se * dim, s));
+    for (int i = 0; i < m.dec_layers; ++i) {
+        TRY(rfk_rmsnorm(ctx16, m.dec[i].kv_norm_gamma, ctx_normed, Se, dim, kEpsFp16, s));
+        TRY(rfk_precompute_cross_kv(d->ctx, &m.dec[i].cross_attn, ctx_normed, d->kvK(i),
+                                    d->kvV(i), kv_proj, 1, Se, Se_pad, dim, dim, nh, s));
+    }
+    TRY_CUDA(cudaStreamSynchronize(st));
+    TRY_CUDA(cudaGetLastError());
+    return RFK_OK;
+}
+
+extern "C" int rfk_session_finalize(rfk_session* d) {
+    if (!d) return RFK_EINVAL;
+    if (d->finalized) return RFK_OK;
+    const rfk_model& m = d->m;
+    std::vector<uint8_t> mask = make_shift_mask(d->pH, d->pW, m.window_size, m.shift_size);
+    TRY_CUDA(cudaMemcpy(d->shift_mask, mask.data(), mask.size(), cudaMemcpyHostToDevice));
+    // warm-up view (also lets cuBLAS pick and load its kernels before capture)
+    float cam[17] = {1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 3, 0, 0, 0, 1, 0.7f};
+    for (int k = 0; k < kSlots; ++k) memcpy(d->pin_cam[k], cam, sizeof(cam));
+    TRY(d->render_view(d->pin_cam[0], d->result[0]));
+    TRY_CUDA(cudaStreamSynchronize(d->stream));
+    if (!(d->flags & RFK_SESSION_NO_GRAPH)) {
+        for (int k = 0; k < kSlots; ++k) {
+            const unsigned long long n0 = rfk_launch_count();
+            TRY_CUDA(cudaStreamBeginCapture(d->stream, cudaStreamCaptureModeThreadLocal));
+            int rc = d->render_view(d->pin_cam[k], d->result[k]);
+            cudaError_t e = cudaStreamEndCapture(d->stream, &d->graph[k]);
+            if (rc != RFK_OK) return rc;
+            TRY_CUDA(e);
+            d->kernels_per_view = (int)(rfk_launch_count() - n0);
+            TRY_CUDA(cudaGraphInstantiate(&d->exec[k], d->graph[k], 0));
+            size_t nodes = 0;
+            TRY_CUDA(cudaGraphGetNodes(d->graph[k], nullptr, &nodes));
+            d->graph_nodes = (int)nodes;
+        }
+    } else {
+        const unsigned long long n0 = rfk_launch_count();
+        TRY(d->render_view(d->pin_cam[0], d->result[0]));
+        d->kernels_per_view = (int)(rfk_launch_count() - n0);
+        TRY_CUDA(cudaStreamSynchronize(d->stream));
+    }
+    d->finalized = true;
+    return RFK_OK;
+}
+
+extern "C" int rfk_session_render_frame(rfk_session* d, const float* h_c2w, float fov_rad) {
+    if (!d || !h_c2w || !d->finalized) return RFK_EINVAL;
+    const int k = (int)(d->frames % kSlots);
+    // the slot's previous frame (two frames ago) must have left the device, and its download
+    // must have finished, before its pinned camera and result buffer are reused
+    if (d->frames >= kSlots) TRY_CUDA(cudaEventSynchronize(d->ev_done[k]));
+    if (d->dl_pending[k]) {
+        TRY_CUDA(cudaEventSynchronize(d->ev_dl[k]));
+        d->dl_pending[k] = false;
+    }
+    memcpy(d->pin_cam[k], h_c2w, 16 * sizeof(float));
+    d->pin_cam[k][16] = fov_rad;
+    TRY_CUDA(cudaEventRecord(d->ev_start[k], d->stream));
+    if (d->exec[k]) TRY_CUDA(cudaGraphLaunch(d->exec[k], d->stream));
+    else TRY(d->render_view(d->pin_cam[k], d->result[k]));
+    TRY_CUDA(cudaEventRecord(d->ev_done[k], d->stream));
+    d->frames++;
+    return RFK_OK;
+}
+
+extern "C" int rfk_session_wait(rfk_session* d, float* ms) {
+    if (!d || d->frames == 0) return RFK_EINVAL;
+    const int k = (int)((d->frames - 1) % kSlots);
+    TRY_CUDA(cudaEventSynchronize(d->ev_done[k]));
+    if (ms) TRY_CUDA(cudaEventElapsedTime(ms, d->ev_start[k], d->ev_done[k]));
+    return RFK_OK;
+}
+
+extern "C" int rfk_session_result(rfk_session* d, const rfk_half** tokens, int* n_tokens, int* dim) {
+    if (!d || d->frames == 0) return RFK_EINVAL;
+    if (tokens) *tokens = d->result[(d->frames - 1) % kSlots];
+    if (n_tokens) *n_tokens = d->nP;
+    if (dim) *dim = d->m.dim;
+    return RFK_OK;
+}
+
+extern "C" int rfk_session_feature_taps(rfk_session* d, const rfk_half** taps) {
+    if (!d || !taps) return RFK_EINVAL;
+    for (int j = 0; j < 4; ++j) taps[j] = d->dft[j];
+    return RFK_OK;
+}
+
+extern "C" int rfk_session_download_async(rfk_session* d, rfk_half* h_out, size_t bytes) {
+    if (!d || !h_out || d->frames == 0) return RFK_EINVAL;
+    const size_t need = (size_t)d->nP * d->m.dim * sizeof(rfk_half);
+    if (bytes < need) return RFK_EINVAL;
+    const int k = (int)((d->frames - 1) % kSlots);
+    TRY_CUDA(cudaStreamWaitEvent(d->copy_stream, d->ev_done[k], 0));
+    TRY_CUDA(cudaMemcpyAsync(h_out, d->result[k], need, cudaMemcpyDeviceToHost, d->copy_stream));
+    TRY_CUDA(cudaEventRecord(d->ev_dl[k], d->copy_stream));
+    d->dl_pending[k] = true;
+    return RFK_OK;
+}
+
+extern "C" int rfk_session_drain(rfk_session* d) {
+    if (!d) return RFK_EINVAL;
+    TRY_CUDA(cudaStreamSynchronize(d->stream));
+    TRY_CUDA(cudaStreamSynchronize(d->copy_stream));
+    for (int k = 0; k < kSlots; ++k) d->dl_pending[k] = false;
+    return RFK_OK;
+}
+
+extern "C" int rfk_session_download(rfk_session* d, rfk_half* h_out, size_t bytes) {
+    TRY(rfk_session_download_async(d, h_out, bytes));
+    TRY_CUDA(cudaStreamSynchronize(d->copy_stream));
+    d->dl_pending[(d->frames - 1) % kSlots] = false;
+    return RFK_OK;
+}
+
+extern "C" int rfk_session_graph_nodes(rfk_session* d) { return d ? d->graph_nodes : 0; }
+extern "C" int rfk_session_kernels_per_view(rfk_session* d) { return d ? d->kernels_per_view : 0; }

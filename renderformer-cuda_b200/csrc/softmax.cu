@@ -51,15 +51,15 @@ __device__ __forceinline__ void store_out(float* p, float v) { *p = v; }
 template <typename TOut, int NCH, int MASK>
 __global__ void __launch_bounds__(256)
 softmax_row_kernel(const float* in, TOut* out, const uint8_t* __restrict__ mask, MaskMap mm,
-                   int cols, long long in_stride, long long out_stride, float scale_log2e,
-                   int vec_in, int vec_out, int vec_mask) {
+                   int cols, long long in_stride, long long out_stride, long long out_pitch,
+                   float scale_log2e, int vec_in, int vec_out, int vec_mask) {
     __shared__ float s_max[8];
     __shared__ float s_sum[8];
     const int tid = threadIdx.x;
     const int nthreads = blockDim.x;
     const long long row = blockIdx.x;
     const float* ri = in + row * in_stride;
-    TOut* ro = out + row * out_stride;
+    TOut* ro = out + row * out_pitch;  // out_stride: columns to fill, out_pitch: row pitch
     const uint8_t* rm = nullptr;
     if (MASK != MASK_NONE) rm = mask + mask_row_of(mm, row) * (long long)cols;
 
@@ -138,13 +138,13 @@ template <typename TOut, int G, int NCH, int MASK>
 __global__ void __launch_bounds__(256)
 softmax_small_kernel(const float* in, TOut* out, const uint8_t* __restrict__ mask, MaskMap mm,
                      long long rows, int cols, long long in_stride, long long out_stride,
-                     float scale_log2e, int vec_in, int vec_out) {
+                     long long out_pitch, float scale_log2e, int vec_in, int vec_out) {
     const long long gid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / G;
     const int gl = threadIdx.x % G;
     const bool live = gid < rows;
     const long long row = live ? gid : rows - 1;  // idle groups shadow the last row, never store
     const float* ri = in + row * in_stride;
-    TOut* ro = out + row * out_stride;
+    TOut* ro = out + row * out_pitch;  // out_stride: columns to fill, out_pitch: row pitch
     const uint8_t* rm = nullptr;
     if (MASK != MASK_NONE) rm = mask + mask_row_of(mm, row) * (long long)cols;
 
@@ -216,13 +216,14 @@ softmax_small_kernel(const float* in, TOut* out, const uint8_t* __restrict__ mas
 template <typename TOut, int MASK>
 __global__ void __launch_bounds__(1024)
 softmax_long_kernel(const float* in, TOut* out, const uint8_t* __restrict__ mask, MaskMap mm,
-                    int cols, long long in_stride, long long out_stride, float scale_log2e) {
+                    int cols, long long in_stride, long long out_stride, long long out_pitch,
+                    float scale_log2e) {
     __shared__ float s_red[32];
     __shared__ float s_bcast;
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, nwarps = blockDim.x >> 5;
     const long long row = blockIdx.x;
     const float* ri = in + row * in_stride;
-    TOut* ro = out + row * out_stride;
+    TOut* ro = out + row * out_pitch;  // out_stride: columns to fill, out_pitch: row pitch
     const uint8_t* rm = nullptr;
     if (MASK != MASK_NONE) rm = mask + mask_row_of(mm, row) * (long long)cols;
     auto value = [&](int j) -> float {
@@ -267,8 +268,11 @@ softmax_long_kernel(const float* in, TOut* out, const uint8_t* __restrict__ mask
 template <typename TOut, int MASK>
 static int launch_softmax(const float* in, TOut* out, const uint8_t* mask, MaskMap mm,
                           long long rows, int cols, long long in_stride, long long out_stride,
-                          float scale, cudaStream_t st) {
-    if (!in || !out || rows < 0 || cols <= 0 || in_stride < cols || out_stride < cols)
+                          float scale, cudaStream_t st, long long out_pitch = 0,
+                          bool registers_only = false) {
+    if (out_pitch == 0) out_pitch = out_stride;
+    if (!in || !out || rows < 0 || cols <= 0 || in_stride < cols || out_stride < cols ||
+        (out_pitch != 0 && out_pitch < out_stride))
         return RFK_EINVAL;
     if (MASK != MASK_NONE && !mask) return RFK_EINVAL;
     if (!(scale > 0.0f)) return RFK_EINVAL;
@@ -281,10 +285,10 @@ static int launch_softmax(const float* in, TOut* out, const uint8_t* mask, MaskM
     if (span <= 256) {
         const int vec_in = aligned16(in) && (in_stride % 4 == 0);
         const int vec_out = ((reinterpret_cast<uintptr_t>(out) % (4 * osz)) == 0) &&
-                            (out_stride % 4 == 0);
+                            (out_pitch % 4 == 0);
 #define RFK_SM_SMALL(G, N)                                                                    \
     softmax_small_kernel<TOut, G, N, MASK><<<ceil_div(rows * G, 256), 256, 0, st>>>(          \
-        in, out, mask, mm, rows, cols, in_stride, out_stride, sl2, vec_in, vec_out)
+        in, out, mask, mm, rows, cols, in_stride, out_stride, out_pitch, sl2, vec_in, vec_out)
         if (span <= 32) RFK_SM_SMALL(8, 1);
         else if (span <= 64) RFK_SM_SMALL(16, 1);
         else if (span <= 128) RFK_SM_SMALL(32, 1);
@@ -294,14 +298,14 @@ static int launch_softmax(const float* in, TOut* out, const uint8_t* mask, MaskM
     }
     if (span <= 8192) {
         const int vec_in = aligned16(in) && (in_stride % 4 == 0);
-        const int vec_out = aligned16(out) && ((out_stride * osz) % 16 == 0);
+        const int vec_out = aligned16(out) && ((out_pitch * osz) % 16 == 0);
         const int vec_mask = MASK != MASK_NONE && aligned8(mask) && (cols % 8 == 0);
         const int chunks = (int)((span + 7) / 8);
         const int threads = chunks <= 128 ? 128 : 256;
         const int nch = (chunks + threads - 1) / threads;
 #define RFK_SM_ROW(N)                                                                         \
     softmax_row_kernel<TOut, N, MASK><<<(unsigned)rows, threads, 0, st>>>(                    \
-        in, out, mask, mm, cols, in_stride, out_stride, sl2, vec_in, vec_out, vec_mask)
+        in, out, mask, mm, cols, in_stride, out_stride, out_pitch, sl2, vec_in, vec_out, vec_mask)
         switch (nch) {
             case 1: RFK_SM_ROW(1); break;
             case 2: RFK_SM_ROW(2); break;
@@ -311,8 +315,9 @@ static int launch_softmax(const float* in, TOut* out, const uint8_t* mask, MaskM
 #undef RFK_SM_ROW
         return launch_status();
     }
-    softmax_long_kernel<TOut, MASK><<<(unsigned)rows, 1024, 0, st>>>(in, out, mask, mm, cols,
-                                                                     in_stride, out_stride, sl2);
+    if (registers_only) return RFK_EUNSUPPORTED;  // the streaming tier re-reads its input
+    softmax_long_kernel<TOut, MASK><<<(unsigned)rows, 1024, 0, st>>>(
+        in, out, mask, mm, cols, in_stride, out_stride, out_pitch, sl2);
     return launch_status();
 }
 
@@ -377,4 +382,27 @@ extern "C" int rfk_swin_softmax_cast_fp16(const float* in, rfk_half* out, const 
     // the unfused pair fills masked scores with -FLT_MAX before the softmax, keep that rule
     return launch_softmax<__half, MASK_FILL>(in, (__half*)out, mask, mm, rows, ws2, ws2, ws2, 1.0f,
                                              as_stream(stream));
+}
+
+extern "C" int rfk_softmax_probs_inplace(float* scores, int rows, int n_valid, int stride,
+                                         float scale, rfk_stream_t stream) {
+    if (stride < n_valid) return RFK_EINVAL;
+    // fp16 row r lives in the first half of fp32 row r: pitch = 2*stride halves. Safe because
+    // the register tiers read a whole row before they store any of it.
+    return launch_softmax<__half, MASK_NONE>(scores, reinterpret_cast<__half*>(scores), nullptr,
+                                             MaskMap{}, rows, n_valid, stride, stride, scale,
+                                             as_stream(stream), 2LL * stride, true);
+}
+
+extern "C" int rfk_swin_softmax_probs_inplace(float* scores, const uint8_t* mask, int BnW,
+                                              int num_heads, int ws2, int nW, rfk_stream_t stream) {
+    if (BnW < 0 || num_heads <= 0 || ws2 <= 0 || nW <= 0) return RFK_EINVAL;
+    const long long rows = (long long)BnW * num_heads * ws2;
+    __half* out = reinterpret_cast<__half*>(scores);
+    if (!mask)
+        return launch_softmax<__half, MASK_NONE>(scores, out, nullptr, MaskMap{}, rows, ws2, ws2, ws2,
+                                                 1.0f, as_stream(stream), 2LL * ws2, true);
+    MaskMap mm{1, 0, ws2, num_heads, nW};
+    return launch_softmax<__half, MASK_FILL>(scores, out, mask, mm, rows, ws2, ws2, ws2, 1.0f,
+                                             as_stream(stream), 2LL * ws2, true);
 }

@@ -160,14 +160,14 @@ def rope_one_oop(src, dst, cos_vals, sin_vals, batch, num_heads, seq_len, head_d
 
 
 def qkv_norm_rope_transpose(x, row_stride, gammas, outs, use_rope, cos_vals, sin_vals,
-                            batch, seq_len, num_heads, head_dim, eps=K_EPS_FP16):
+                            batch, seq_len, num_heads, head_dim, eps=K_EPS_FP16, out_seq_stride=0):
     n = len(outs)
     g_arr = (ctypes.c_void_p * n)(*[_p(g, F, "gamma") for g in gammas])
     o_arr = (ctypes.c_void_p * n)(*[_p(o, H, "out") for o in outs])
     r_arr = (ctypes.c_int * n)(*[int(bool(r)) for r in use_rope])
     _call("rfk_qkv_norm_rope_transpose", _p(x, H, "x"), row_stride, n, g_arr, o_arr, r_arr,
           _p(cos_vals, H, "cos"), _p(sin_vals, H, "sin"), batch, seq_len, num_heads, head_dim, eps,
-          _stream())
+          out_seq_stride, _stream())
 
 
 def transpose_bshd_to_bhsd(inp, out, batch, seq_len, num_heads, head_dim):
@@ -223,6 +223,15 @@ def softmax_cast_fp16_scaled(inp, out, rows, cols, in_stride, out_stride, scale)
           out_stride, scale, _stream())
 
 
+def softmax_probs_inplace(scores, rows, n_valid, stride, scale=1.0):
+    _call("rfk_softmax_probs_inplace", _p(scores, F, "scores"), rows, n_valid, stride, scale, _stream())
+
+
+def swin_softmax_probs_inplace(scores, mask, BnW, num_heads, ws2, nW):
+    _call("rfk_swin_softmax_probs_inplace", _p(scores, F, "scores"), _mask_ptr(mask), BnW, num_heads,
+          ws2, nW, _stream())
+
+
 def swin_softmax_cast_fp16(inp, out, mask, BnW, num_heads, ws2, nW):
     _call("rfk_swin_softmax_cast_fp16", _p(inp, F, "in"), _p(out, H, "out"), _mask_ptr(mask), BnW,
           num_heads, ws2, nW, _stream())
@@ -240,6 +249,10 @@ def fused_silu_mul_f32(a, b, out, n):
 
 def swiglu(gate_up, out, rows, hidden):
     _call("rfk_swiglu", _p(gate_up, H, "gate_up"), _p(out, H, "out"), rows, hidden, _stream())
+
+
+def swiglu_inplace(gate_up, rows, hidden):
+    _call("rfk_swiglu_inplace", _p(gate_up, H, "gate_up"), rows, hidden, _stream())
 
 
 def elu(x, y, n, alpha=1e-3):

@@ -1,0 +1,343 @@
+"""Python side of the layer library (include/rfk_layers.h): weight records, the per-scene
+render session and the multi-GPU view scheduler.
+
+torch supplies device memory, streams and (for the scheduler) `torch.distributed`; all
+compute happens behind the C ABI in librfk_layers.so / librfk.so.
+
+    model   = Model.random(seed=4)                    # renderformer-v1.1-swin-large shapes
+    session = RenderSession(model, n_tris=5633, img_res=512)
+    session.encode_scene(tri, vn, tex); session.finalize()
+    session.render_frame(c2w, fov); tokens = session.download()
+
+    sched = ViewScheduler(model, scene, img_res=512)  # one process per GPU (torchrun)
+    sched.render(c2ws, fovs, out=pinned_host_buffer)
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _abi
+
+VP = ctypes.c_void_p
+MAX_LAYERS = 32
+
+
+class FfnW(ctypes.Structure):
+    _fields_ = [("w1", VP), ("w2", VP), ("w3", VP)]
+
+
+class MhaW(ctypes.Structure):
+    _fields_ = [(n, VP) for n in ("in_proj_w", "in_proj_b", "out_proj_w", "out_proj_b", "q_norm_gamma", "k_norm_gamma")]
+
+
+class CrossW(ctypes.Structure):
+    _fields_ = [(n, VP) for n in ("q_proj_w", "q_proj_b", "k_proj_w", "k_proj_b", "v_proj_w", "v_proj_b",
+                                  "out_proj_w", "out_proj_b", "q_norm_gamma", "k_norm_gamma")]
+
+
+class EncLayerW(ctypes.Structure):
+    _fields_ = [("query_norm_gamma", VP), ("attn", MhaW), ("ffn_norm_gamma", VP), ("ffn", FfnW)]
+
+
+class DecLayerW(ctypes.Structure):
+    _fields_ = [("query_norm_gamma", VP), ("kv_norm_gamma", VP), ("cross_attn", CrossW),
+                ("self_attn_norm_gamma", VP), ("self_attn", MhaW), ("ffn_norm_gamma", VP), ("ffn", FfnW)]
+
+
+class ModelW(ctypes.Structure):
+    _fields_ = ([(n, ctypes.c_int) for n in ("dim", "num_heads", "ffn_hidden", "num_register_tokens", "enc_layers",
+                                             "dec_layers", "rope_num_freqs", "patch_size", "window_size", "shift_size",
+                                             "texture_channels", "vn_pe_num_freqs")]
+                + [(n, VP) for n in ("tri_token", "reg_tokens", "tex_enc_w", "tex_enc_b", "tex_enc_norm", "vn_proj_w",
+                                     "vn_proj_b", "vn_enc_norm", "enc_rope_freqs", "ray_map_patch_token", "ray_enc_w",
+                                     "ray_enc_b", "ray_enc_norm", "vt_rope_freqs")]
+                + [("enc", EncLayerW * MAX_LAYERS), ("dec", DecLayerW * MAX_LAYERS)])
+
+
+RFK_SESSION_PAD_KEYS_ATTEND = 1
+RFK_SESSION_NO_GRAPH = 2
+
+
+def _lib():
+    return _abi.load("rfk_layers.h")
+
+
+class RfkLayersError(RuntimeError):
+    pass
+
+
+def _check(name, rc):
+    if rc != 0:
+        text = _abi.load("rfk.h").rfk_status_string(rc).decode() if rc < 1000 else f"cuBLAS status {rc - 1000}"
+        raise RfkLayersError(f"{name} failed with status {rc}: {text}")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+class Model:
+    """Device weights + the C record that points at them. Shapes follow the reference's
+    RenderFormerModel (src/model/renderformer.h:12-44) with runtime dimensions."""
+
+    def __init__(self, dim=1024, num_heads=16, ffn_hidden=4096, num_register_tokens=32, enc_layers=12, dec_layers=12,
+                 patch_size=8, window_size=8, shift_size=4, texture_channels=13, vn_pe_num_freqs=6, device="cuda"):
+        self.dim, self.num_heads, self.ffn_hidden = dim, num_heads, ffn_hidden
+        self.head_dim = dim // num_heads
+        # frequencies per coordinate: as many as fit, 9*nf <= head_dim/2, at most 6 (src/model/config.h:28)
+        self.rope_num_freqs = max(1, min(6, (self.head_dim // 2) // 9))
+        self.num_register_tokens, self.enc_layers, self.dec_layers = num_register_tokens, enc_layers, dec_layers
+        self.patch_size, self.window_size, self.shift_size = patch_size, window_size, shift_size
+        self.texture_channels, self.vn_pe_num_freqs = texture_channels, vn_pe_num_freqs
+        self.device = device
+        self.t: dict[str, torch.Tensor] = {}
+        self.c = ModelW()
+
+    # -- construction -------------------------------------------------------------------
+    @classmethod
+    def random(cls, seed=4, weight_std=0.02, **kw) -> "Model":
+        """Random-init weights of the given architecture: N(0, weight_std) matrices, gains
+        N(1, 0.02), geometric rotary frequencies (stand-ins for the learned ones)."""
+        m = cls(**kw)
+        g = torch.Generator(device=m.device).manual_seed(seed)
+        dim, ffn = m.dim, m.ffn_hidden
+
+        def W(*shape):
+            return (torch.randn(*shape, device=m.device, generator=g) * weight_std).half().contiguous()
+
+        def G(n):
+            return (1 + 0.02 * torch.randn(n, device=m.device, generator=g)).float().contiguous()
+
+        t = m.t
+        t["tri_token"], t["reg_tokens"] = W(dim), W(m.num_register_tokens, dim)
+        t["tex_enc_w"], t["tex_enc_b"], t["tex_enc_norm"] = W(dim, m.texture_channels), W(dim), G(dim)
+        vn_pe = 9 + 9 * m.vn_pe_num_freqs * 2
+        t["vn_proj_w"], t["vn_proj_b"], t["vn_enc_norm"] = W(dim, vn_pe), W(dim), G(dim)
+        nf = m.rope_num_freqs
+        freqs = torch.tensor([math.pi * 10000.0 ** (-i / nf) for i in range(nf)], device=m.device, dtype=torch.float32)
+        t["enc_rope_freqs"], t["vt_rope_freqs"] = freqs.clone(), freqs.clone()
+        t["ray_map_patch_token"] = W(dim)
+        t["ray_enc_w"], t["ray_enc_b"], t["ray_enc_norm"] = W(dim, 3 * m.patch_size ** 2), W(dim), G(dim)
+        for i in range(m.enc_layers):
+            p = f"enc{i}."
+            t[p + "query_norm"], t[p + "ffn_norm"] = G(dim), G(dim)
+            t[p + "in_proj_w"], t[p + "out_proj_w"] = W(3 * dim, dim), W(dim, dim)
+            t[p + "q_norm"], t[p + "k_norm"] = G(dim), G(dim)
+            t[p + "w13"], t[p + "w2"] = W(2 * ffn, dim), W(dim, ffn)   # w1 and w3 stored back to back
+        for i in range(m.dec_layers):
+            p = f"dec{i}."
+            for n in ("query_norm", "kv_norm", "self_attn_norm", "ffn_norm", "cq_norm", "ck_norm", "sq_norm", "sk_norm"):
+                t[p + n] = G(dim)
+            for n in ("q_proj_w", "k_proj_w", "v_proj_w", "cross_out_w", "swin_out_w"):
+                t[p + n] = W(dim, dim)
+            t[p + "swin_in_w"] = W(3 * dim, dim)
+            t[p + "w13"], t[p + "w2"] = W(2 * ffn, dim), W(dim, ffn)
+        m._fill_record()
+        return m
+
+    def _fill_record(self):
+        c, t = self.c, self.t
+        for n in ("dim", "num_heads", "ffn_hidden", "num_register_tokens", "enc_layers", "dec_layers", "rope_num_freqs",
+                  "patch_size", "window_size", "shift_size", "texture_channels", "vn_pe_num_freqs"):
+            setattr(c, n, getattr(self, n))
+        for n in ("tri_token", "reg_tokens", "tex_enc_w", "tex_enc_b", "tex_enc_norm", "vn_proj_w", "vn_proj_b",
+                  "vn_enc_norm", "enc_rope_freqs", "ray_map_patch_token", "ray_enc_w", "ray_enc_b", "ray_enc_norm",
+                  "vt_rope_freqs"):
+            setattr(c, n, t[n].data_ptr())
+        half_w13 = self.ffn_hidden * self.dim * 2  # bytes of w1
+        for i in range(self.enc_layers):
+            p, e = f"enc{i}.", c.enc[i]
+            e.query_norm_gamma, e.ffn_norm_gamma = t[p + "query_norm"].data_ptr(), t[p + "ffn_norm"].data_ptr()
+            e.attn = self.mha_record(t[p + "in_proj_w"], t[p + "out_proj_w"], t[p + "q_norm"], t[p + "k_norm"])
+            e.ffn = FfnW(t[p + "w13"].data_ptr(), t[p + "w2"].data_ptr(), t[p + "w13"].data_ptr() + half_w13)
+        for i in range(self.dec_layers):
+            c.dec[i] = self.decoder_record(i)
+
+    @staticmethod
+    def mha_record(in_w, out_w, qn, kn) -> MhaW:
+        return MhaW(in_w.data_ptr(), None, out_w.data_ptr(), None, _ptr(qn), _ptr(kn))
+
+    def decoder_record(self, i) -> DecLayerW:
+        t, p = self.t, f"dec{i}."
+        d = DecLayerW()
+        d.query_norm_gamma, d.kv_norm_gamma = t[p + "query_norm"].data_ptr(), t[p + "kv_norm"].data_ptr()
+        d.cross_attn = CrossW(t[p + "q_proj_w"].data_ptr(), None, t[p + "k_proj_w"].data_ptr(), None,
+                              t[p + "v_proj_w"].data_ptr(), None, t[p + "cross_out_w"].data_ptr(), None,
+                              t[p + "cq_norm"].data_ptr(), t[p + "ck_norm"].data_ptr())
+        d.self_attn_norm_gamma = t[p + "self_attn_norm"].data_ptr()
+        d.self_attn = self.mha_record(t[p + "swin_in_w"], t[p + "swin_out_w"], t[p + "sq_norm"], t[p + "sk_norm"])
+        d.ffn_norm_gamma = t[p + "ffn_norm"].data_ptr()
+        w13 = t[p + "w13"]
+        d.ffn = FfnW(w13.data_ptr(), t[p + "w2"].data_ptr(), w13.data_ptr() + self.ffn_hidden * self.dim * 2)
+        return d
+
+    def num_params(self) -> int:
+        return sum(v.numel() for v in self.t.values())
+
+
+class Ctx:
+    """One cuBLAS context per device (rfk_ctx)."""
+
+    def __init__(self):
+        self.h = VP()
+        _check("rfk_ctx_create", _lib().rfk_ctx_create(ctypes.byref(self.h)))
+
+    def close(self):
+        if self.h:
+            _lib().rfk_ctx_destroy(self.h)
+            self.h = VP()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class RenderSession:
+    """Mirror of the reference's RenderSession (src/pipeline/render_session.h:10-39): create
+    for a scene, then render_frame / wait / download per camera view."""
+
+    def __init__(self, model: Model, n_tris: int, img_res: int = 512, scene_state: torch.Tensor | None = None,
+                 pad_keys_attend: bool = False, use_graph: bool = True):
+        self.model, self.n_tris, self.img_res = model, n_tris, img_res
+        lib = _lib()
+        lib.rfk_scene_state_bytes.restype = ctypes.c_size_t
+        nbytes = lib.rfk_scene_state_bytes(ctypes.byref(model.c), n_tris)
+        if nbytes == 0:
+            raise RfkLayersError("invalid model or triangle count")
+        if scene_state is None:
+            scene_state = torch.zeros(nbytes, dtype=torch.uint8, device=model.device)
+        if scene_state.numel() < nbytes or not scene_state.is_cuda:
+            raise ValueError("scene_state must be a CUDA byte tensor of rfk_scene_state_bytes() bytes")
+        self.scene_state = scene_state
+        flags = (RFK_SESSION_PAD_KEYS_ATTEND if pad_keys_attend else 0) | (0 if use_graph else RFK_SESSION_NO_GRAPH)
+        self.h = VP()
+        _check("rfk_session_create", lib.rfk_session_create(ctypes.byref(model.c), n_tris, img_res,
+                                                            scene_state.data_ptr(), flags, ctypes.byref(self.h)))
+        self.n_tokens = (img_res // model.patch_size) ** 2
+        self.result_bytes = self.n_tokens * model.dim * 2
+
+    def encode_scene(self, tri: torch.Tensor, vn: torch.Tensor, tex: torch.Tensor):
+        """tri, vn [N,3,3] fp32 (world space), tex [N, texture_channels] fp16. Runs the scene
+        preprocessing, the encoder and the K/V cache build into the scene state."""
+        assert tri.dtype == torch.float32 and vn.dtype == torch.float32 and tex.dtype == torch.float16
+        tri, vn, tex = tri.contiguous(), vn.contiguous(), tex.contiguous()
+        torch.cuda.synchronize()
+        _check("rfk_session_encode_scene", _lib().rfk_session_encode_scene(self.h, tri.data_ptr(), vn.data_ptr(),
+                                                                           tex.data_ptr()))
+
+    def finalize(self):
+        torch.cuda.synchronize()
+        _check("rfk_session_finalize", _lib().rfk_session_finalize(self.h))
+
+    def render_frame(self, c2w, fov_rad: float):
+        """c2w: 16 floats (row-major 4x4, host: list / numpy / CPU tensor)."""
+        arr = (ctypes.c_float * 16)(*[float(v) for v in (c2w.reshape(-1).tolist() if hasattr(c2w, "reshape") else c2w)])
+        _check("rfk_session_render_frame", _lib().rfk_session_render_frame(self.h, arr, ctypes.c_float(fov_rad)))
+
+    def render_frame_raw(self, c2w_ptr: int, fov_rad: float):
+        """Same with a raw host pointer to 16 floats (no per-call conversion)."""
+        _check("rfk_session_render_frame", _lib().rfk_session_render_frame(self.h, VP(c2w_ptr), ctypes.c_float(fov_rad)))
+
+    def wait(self) -> float:
+        ms = ctypes.c_float()
+        _check("rfk_session_wait", _lib().rfk_session_wait(self.h, ctypes.byref(ms)))
+        return ms.value
+
+    def result_tensor(self) -> torch.Tensor:
+        """The last frame's token map [n_tokens, dim] fp16 as a device tensor (via the host)."""
+        return self.download().to(self.model.device)
+
+    def download(self, host: torch.Tensor | None = None) -> torch.Tensor:
+        if host is None:
+            host = torch.empty(self.n_tokens, self.model.dim, dtype=torch.float16).pin_memory()
+        _check("rfk_session_download", _lib().rfk_session_download(self.h, host.data_ptr(), host.numel() * 2))
+        return host
+
+    def download_async(self, host: torch.Tensor):
+        _check("rfk_session_download_async", _lib().rfk_session_download_async(self.h, host.data_ptr(), host.numel() * 2))
+
+    def drain(self):
+        _check("rfk_session_drain", _lib().rfk_session_drain(self.h))
+
+    @property
+    def graph_nodes(self) -> int:
+        return _lib().rfk_session_graph_nodes(self.h)
+
+    @property
+    def kernels_per_view(self) -> int:
+        return _lib().rfk_session_kernels_per_view(self.h)
+
+    def close(self):
+        if self.h:
+            _lib().rfk_session_destroy(self.h)
+            self.h = VP()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def shard_views(n_views: int, rank: int, world: int) -> list[int]:
+    """Static round-robin: view v is rendered by rank v mod world."""
+    return list(range(rank, n_views, world))
+
+
+class ViewScheduler:
+    """Data-parallel view scheduler: one process per GPU. Rank 0 encodes the scene; the scene
+    state (cross-attention K/V cache + fp16 geometry) is broadcast once over NCCL into every
+    GPU's own memory; each rank then renders its share of the camera views from its local
+    copy through its own captured graph. No collective runs on the per-view path."""
+
+    def __init__(self, model: Model, n_tris: int, img_res: int = 512, process_group=None, pad_keys_attend=False):
+        import torch.distributed as dist
+        self.dist = dist if (dist.is_available() and dist.is_initialized()) else None
+        self.group = process_group
+        self.rank = self.dist.get_rank(process_group) if self.dist else 0
+        self.world = self.dist.get_world_size(process_group) if self.dist else 1
+        self.session = RenderSession(model, n_tris, img_res, pad_keys_attend=pad_keys_attend)
+        self.broadcast_ms = 0.0
+
+    def load_scene(self, tri=None, vn=None, tex=None, src: int = 0):
+        """Rank `src` passes the scene tensors and runs the encoder; every rank receives the
+        scene state. Returns the broadcast time in ms (device events, this rank)."""
+        if self.rank == src:
+            self.session.encode_scene(tri, vn, tex)
+        if self.dist and self.world > 1:
+            st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            st.record()
+            self.dist.broadcast(self.session.scene_state, src=src, group=self.group)
+            en.record()
+            torch.cuda.synchronize()
+            self.broadcast_ms = st.elapsed_time(en)
+        self.session.finalize()
+        return self.broadcast_ms
+
+    def my_views(self, n_views: int) -> list[int]:
+        return shard_views(n_views, self.rank, self.world)
+
+    def render(self, c2ws: torch.Tensor, fovs: torch.Tensor, out: torch.Tensor | None = None) -> list[int]:
+        """c2ws [V,4,4] fp32 and fovs [V] fp32 (radians) on the HOST. Renders this rank's views;
+        if `out` (pinned host [n_local, n_tokens, dim] fp16) is given, each frame is downloaded
+        into it while the next one renders. Returns the view ids rendered here."""
+        mine = self.my_views(c2ws.shape[0])
+        c2ws = c2ws.contiguous()
+        base, stride = c2ws.data_ptr(), 16 * 4
+        fl = fovs.tolist()
+        for j, v in enumerate(mine):
+            self.session.render_frame_raw(base + v * stride, fl[v])
+            if out is not None:
+                self.session.download_async(out[j])
+        self.session.drain()
+        return mine
