@@ -274,6 +274,11 @@ int rfk_session_download(rfk_session* s, rfk_half* h_out, size_t bytes);
  * next frame. rfk_session_drain waits for every submitted frame and copy. */
 int rfk_session_download_async(rfk_session* s, rfk_half* h_out, size_t bytes);
 int rfk_session_drain(rfk_session* s);
+/* Timing marks: mark_begin records a CUDA event on the session's render stream; mark_end
+ * records a second one, waits for it (and for the copy stream) and returns the device time
+ * between the two in *ms. Brackets a batch of rfk_session_render_frame calls. */
+int rfk_session_mark_begin(rfk_session* s);
+int rfk_session_mark_end(rfk_session* s, float* ms);
 /* Number of nodes in the captured per-view graph (0 when running eagerly). */
 int rfk_session_graph_nodes(rfk_session* s);
 /* Kernels of librfk.so launched per view (counted while the graph was captured). */

@@ -68,8 +68,8 @@ def _conv(a):
         return ctypes.c_int(a)
     if isinstance(a, float):
         return ctypes.c_float(a)
-    if isinstance(a, (ctypes.Structure, ctypes._Pointer, ctypes.c_void_p)):
-        return a
+    if isinstance(a, (ctypes.Structure, ctypes._Pointer, ctypes.c_void_p)) or type(a).__name__ == "CArgObject":
+        return a  # ctypes.byref(struct) arrives as a CArgObject
     raise TypeError(type(a))
 
 

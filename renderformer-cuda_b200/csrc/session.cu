@@ -128,6 +128,7 @@ struct rfk_session {
     cudaGraphExec_t exec[kSlots] = {nullptr, nullptr};
     cudaEvent_t ev_start[kSlots]{}, ev_done[kSlots]{}, ev_dl[kSlots]{};
     bool dl_pending[kSlots] = {false, false};
+    cudaEvent_t ev_mark0 = nullptr, ev_mark1 = nullptr;
     long long frames = 0;  // frames submitted so far
     int graph_nodes = 0, kernels_per_view = 0;
     bool finalized = false;
@@ -273,6 +274,8 @@ extern "C" int rfk_session_destroy(rfk_session* d) {
         if (d->ev_done[k]) cudaEventDestroy(d->ev_done[k]);
         if (d->ev_dl[k]) cudaEventDestroy(d->ev_dl[k]);
     }
+    if (d->ev_mark0) cudaEventDestroy(d->ev_mark0);
+    if (d->ev_mark1) cudaEventDestroy(d->ev_mark1);
     for (void* p : d->owned) cudaFree(p);
     if (d->stream) cudaStreamDestroy(d->stream);
     if (d->copy_stream) cudaStreamDestroy(d->copy_stream);
@@ -488,6 +491,31 @@ extern "C" int rfk_session_download(rfk_session* d, rfk_half* h_out, size_t byte
     TRY(rfk_session_download_async(d, h_out, bytes));
     TRY_CUDA(cudaStreamSynchronize(d->copy_stream));
     d->dl_pending[(d->frames - 1) % kSlots] = false;
+    return RFK_OK;
+}
+
+extern "C" int rfk_session_mark_begin(rfk_session* d) {
+    if (!d) return RFK_EINVAL;
+    if (!d->ev_mark0) {
+        TRY_CUDA(cudaEventCreate(&d->ev_mark0));
+        TRY_CUDA(cudaEventCreate(&d->ev_mark1));
+    }
+    TRY_CUDA(cudaEventRecord(d->ev_mark0, d->stream));
+    return RFK_OK;
+}
+
+extern "C" int rfk_session_mark_end(rfk_session* d, float* ms) {
+    if (!d || !d->ev_mark0) return RFK_EINVAL;
+    // downloads are part of the bracketed work: the end mark waits for the copy stream too
+    cudaEvent_t dl = nullptr;
+    TRY_CUDA(cudaEventCreateWithFlags(&dl, cudaEventDisableTiming));
+    cudaError_t e = cudaEventRecord(dl, d->copy_stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(d->stream, dl, 0);
+    cudaEventDestroy(dl);
+    TRY_CUDA(e);
+    TRY_CUDA(cudaEventRecord(d->ev_mark1, d->stream));
+    TRY_CUDA(cudaEventSynchronize(d->ev_mark1));
+    if (ms) TRY_CUDA(cudaEventElapsedTime(ms, d->ev_mark0, d->ev_mark1));
     return RFK_OK;
 }
 

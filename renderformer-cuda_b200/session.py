@@ -268,6 +268,14 @@ class RenderSession:
     def drain(self):
         _check("rfk_session_drain", _lib().rfk_session_drain(self.h))
 
+    def mark_begin(self):
+        _check("rfk_session_mark_begin", _lib().rfk_session_mark_begin(self.h))
+
+    def mark_end(self) -> float:
+        ms = ctypes.c_float()
+        _check("rfk_session_mark_end", _lib().rfk_session_mark_end(self.h, ctypes.byref(ms)))
+        return ms.value
+
     @property
     def graph_nodes(self) -> int:
         return _lib().rfk_session_graph_nodes(self.h)
