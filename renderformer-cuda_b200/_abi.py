@@ -68,12 +68,13 @@ def parse_header(path: Path) -> dict[str, tuple]:
     return out
 
 
-def declared_symbols() -> dict[str, dict[str, tuple]]:
-    """{header file name: {symbol: signature}} for all headers under include/."""
-    return {h.name: parse_header(h) for h in sorted(INCLUDE.glob("*.h"))}
-
-
 _HEADER_LIB = {"rfk.h": "librfk.so", "rfk_layers.h": "librfk_layers.so"}
+
+
+def declared_symbols() -> dict[str, dict[str, tuple]]:
+    """{header file name: {symbol: signature}} for the C-ABI headers under include/
+    (rfk_compat.h is a C++ convenience layer over rfk.h and declares no symbols of its own)."""
+    return {name: parse_header(INCLUDE / name) for name in sorted(_HEADER_LIB) if (INCLUDE / name).exists()}
 _loaded: dict[str, ctypes.CDLL] = {}
 
 

@@ -58,3 +58,47 @@ def test_python_mirror_refuses_cpu_tensors():
     g = torch.ones(64)
     with pytest.raises(ValueError, match="CUDA tensor"):
         pkg.ops.rmsnorm(x, g, x, 2, 64)
+
+
+def test_compat_header_compiles_and_links_reference_style_code(tmp_path):
+    """Host code written against the reference's rf:: kernel interface builds against
+    include/rfk_compat.h and links librfk.so (compile + link only, nothing runs)."""
+    import shutil
+    import subprocess
+    from pathlib import Path
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    root = Path(__file__).resolve().parent.parent
+    src = tmp_path / "caller.cu"
+    src.write_text(r'''
+#include <rfk_compat.h>
+// call sites in the style of src/layers/attention.cu:193-194,210 and src/pipeline/render_session.cu:194-208,249-253
+void reference_style_caller(half* q, half* k, const float* g, const half* c, const half* s, float* scores, half* p,
+                            const bool* mask, float* c2w, float* fov, float* ro, half* rd, half* tri, half* vn,
+                            float* out32, float* x32, const half* r16, cudaStream_t st) {
+    rf::rmsnorm(q, g, q, 4096, 1024, rf::kEpsFp16, st);
+    rf::rmsnorm_f32(x32, g, x32, 16, 1024);
+    rf::apply_rope(q, k, c, s, 1, 16, 4096, 64, st);
+    rf::apply_rope_one(q, c, s, 1, 16, 4096, 64, st);
+    rf::triangle_rope_freqs(q, g, q, k, 1, 5672, 3, 64, st);
+    rf::softmax_cast_fp16(scores, p, 65536, 5633, 5640, 5640, st);
+    rf::softmax_cast_fp16_masked(scores, p, mask, 16, 64, 64, 64, 1, st);
+    rf::swin_masked_softmax_inplace(scores, mask, 64, 16, 64, 64, st);
+    rf::softmax_inplace(scores, 16, 64);
+    rf::fused_silu_mul(q, k, q, 4096 * 4096, st);
+    rf::nerf_pe_f32(x32, p, 1, 5633, 9, 6, 0, 5, true, st);
+    rf::ray_gen(c2w, fov, ro, rd, 1, 512, st);
+    rf::world_to_cam(c2w, tri, vn, 1, 5633, st);
+    rf::elu(p, p, 786432, 1e-3f, st);
+    rf::pow10_minus1(out32, out32, 786432, st);
+    rf::residual_add(q, k, 4096 * 1024, st);
+    rf::residual_add_mixed(x32, r16, 1024, st);
+    rf::cast_fp32_to_fp16(x32, q, 1024, st);
+}
+''')
+    pkg_dir = root / "renderformer-cuda_b200"
+    out = tmp_path / "libcaller.so"
+    cmd = [nvcc, "-std=c++17", "-DRFK_COMPAT_CHECK", "-gencode", "arch=compute_100a,code=sm_100a", "-shared",
+           "-Xcompiler", "-fPIC", f"-I{root / 'include'}", str(src), "-o", str(out), f"-L{pkg_dir}", "-lrfk"]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    assert proc.returncode == 0, proc.stderr
+    assert out.exists()
