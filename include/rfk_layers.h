@@ -109,6 +109,20 @@ int rfk_sdpa(rfk_ctx* ctx, const rfk_half* Q, const rfk_half* K, const rfk_half*
              float* workspace, const uint8_t* mask, int B, int H, int Sq, int Sk, int n_keys,
              int D, int o_bshd, rfk_stream_t stream);
 
+/* rfk_sdpa for callers that cannot allocate device memory (code running inside a CUDA stream
+ * capture, stream host callbacks, plug-in hosts with a fixed memory budget): the fp32 score
+ * matrix lives in a 32 MiB array inside the library instead of a caller-supplied workspace,
+ * so B*H*Sq*roundup8(Sk) must not exceed 8 Mi (8388608) floats; larger shapes return
+ * RFK_ETOOBIG. The call allocates and frees nothing. The first call on each device looks up
+ * the array's device address (cudaGetSymbolAddress, with that device current) and should
+ * therefore be made before any stream capture begins; later calls only launch. All calls on
+ * a device share the one array: it keeps the previous call's contents (no call depends on
+ * them), and two calls whose work overlaps on the GPU (different streams) race on it.
+ * This entry point has no counterpart in the reference, whose attention allocates per call. */
+int rfk_sdpa_static(rfk_ctx* ctx, const rfk_half* Q, const rfk_half* K, const rfk_half* V,
+                    rfk_half* O, int B, int H, int Sq, int Sk, int n_keys, int D, int o_bshd,
+                    rfk_stream_t stream);
+
 /* K/V projections of the (normalised) context, K-RMSNorm, [B,H,Sk_pad,D] layout with rows
  * [Sk, Sk_pad) zeroed. proj_buf: 2*B*Sk*dim halves.
  * replaces rf::precompute_cross_kv + the per-head padding copies —

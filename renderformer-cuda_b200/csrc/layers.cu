@@ -332,3 +332,41 @@ extern "C" int rfk_encoder_layer_forward_mixed(
     if (pending_out) { *pending_out = ffn_buf; return RFK_OK; }
     return rfk_residual_add_mixed(x, ffn_buf, (long long)M * dim, stream);
 }
+
+// ------------------------------------------------------------------------------------------
+// rfk_sdpa without a caller-supplied score buffer.
+//
+// Some callers of this library are not in a position to allocate device memory: code that
+// runs between cudaStreamBeginCapture and cudaStreamEndCapture (cudaMalloc is not permitted
+// there), host callbacks enqueued on a stream, and plug-in hosts that hand the library a fixed
+// set of tensors and forbid it to grow the process's memory. For them the fp32 score matrix of
+// the attention lives in the library itself: a file-scope __device__ array of fixed size that
+// every GPU that loads this library holds until the process exits.
+constexpr size_t kStaticScoreFloats = 8u << 20;  // 8 Mi floats = 32 MiB
+static __device__ __align__(256) float g_static_scores[kStaticScoreFloats];
+// In host code the array's name is only a handle for the symbol, not a device address: the
+// address is looked up once per device, with that device current, and cached here.
+constexpr int kMaxDevices = 64;
+static float* g_static_scores_addr[kMaxDevices] = {};
+
+extern "C" int rfk_sdpa_static(rfk_ctx* ctx, const rfk_half* Q, const rfk_half* K, const rfk_half* V,
+                               rfk_half* O, int B, int H, int Sq, int Sk, int n_keys, int D, int o_bshd,
+                               rfk_stream_t stream) {
+    if (B < 0 || H <= 0 || Sq < 0 || Sk <= 0) return RFK_EINVAL;
+    const size_t ld = ((size_t)Sk + 7) & ~(size_t)7;
+    const size_t need = (size_t)B * H * Sq * ld;
+    if (need > kStaticScoreFloats) return RFK_ETOOBIG;  // B*H*Sq*roundup8(Sk) floats must fit in 32 MiB
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return RFK_EUNSUPPORTED;
+    if (!g_static_scores_addr[dev]) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_static_scores);
+        if (e != cudaSuccess) return (int)e;
+        g_static_scores_addr[dev] = p;
+    }
+    // Nothing in the array has to be cleared first: the score GEMM overwrites (beta = 0) every
+    // element the softmax reads, and the softmax writes every element the second GEMM reads.
+    return rfk_sdpa(ctx, Q, K, V, O, g_static_scores_addr[dev], nullptr, B, H, Sq, Sk, n_keys, D, o_bshd, stream);
+}
