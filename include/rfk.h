@@ -220,6 +220,17 @@ int rfk_swin_softmax_probs_inplace(float* scores, const uint8_t* mask, int BnW, 
 int rfk_swin_softmax_cast_fp16(const float* in, rfk_half* out, const uint8_t* mask,
                                int BnW, int num_heads, int ws2, int nW, rfk_stream_t stream);
 
+/* ---------------------------------------------------------------- attention */
+
+/* O = softmax(scale * Q K^T) V without materialising the scores. Q [B,H,Sq,D], K,V [B,H,Sk,D],
+ * fp16, fp32 accumulation; the first n_keys (<= Sk) keys of every head take part. O is written
+ * [B,H,Sq,D] or, with o_bshd != 0, [B,Sq,H*D]. D = 64 or 128 (RFK_EUNSUPPORTED otherwise).
+ * replaces the contraction behind rf::sdpa — src/layers/attention.cu:89-166 (cuDNN fused
+ * attention or GEMM -> softmax_cast_fp16 -> GEMM in the reference) */
+int rfk_flash_attention(const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,
+                        int B, int H, int Sq, int Sk, int n_keys, int D, int o_bshd, float scale,
+                        rfk_stream_t stream);
+
 /* -------------------------------------------------------------- activations */
 
 /* out = half(silu(a) * b), out may alias a — replaces rf::fused_silu_mul,

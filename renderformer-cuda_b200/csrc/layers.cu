@@ -143,6 +143,16 @@ extern "C" int rfk_sdpa(rfk_ctx* ctx, const rfk_half* Q, const rfk_half* K, cons
     return RFK_OK;
 }
 
+// Attention core: the fused kernel (no score matrix) for the head sizes it implements, the
+// materialised GEMM -> softmax -> GEMM sequence (score_buf) for any other.
+static int attention_core(rfk_ctx* ctx, const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,
+                          float* score_buf, int B, int H, int Sq, int Sk, int n_keys, int D, int o_bshd,
+                          rfk_stream_t stream) {
+    int rc = rfk_flash_attention(Q, K, V, O, B, H, Sq, Sk, n_keys, D, o_bshd, 1.0f / sqrtf((float)D), stream);
+    if (rc != RFK_EUNSUPPORTED) return rc;
+    return rfk_sdpa(ctx, Q, K, V, O, score_buf, nullptr, B, H, Sq, Sk, n_keys, D, o_bshd, stream);
+}
+
 // Q/K/V epilogue of a projection: fused kernel when the shape allows, else the unfused steps.
 static int project_epilogue(const rfk_half* x, long long row_stride, int n_parts,
                             const float* const* gamma, rfk_half* const* out, const int* use_rope,
@@ -219,8 +229,8 @@ extern "C" int rfk_cross_attention_cached(rfk_ctx* ctx, const rfk_cross_attn_wei
         TRY(rfk_rope_one_oop(K_cached, K_rot, k_rope_cos, k_rope_sin, B, num_heads, Sk, hd, Sk, Sk, 0, stream));
         K_use = K_rot;
     }
-    TRY(rfk_sdpa(ctx, Q_bhsd, K_use, V_cached, Q /* [B,Sq,dim] */, score_buf, nullptr, B, num_heads, Sq,
-                 Sk, n_keys, hd, 1, stream));
+    TRY(attention_core(ctx, Q_bhsd, K_use, V_cached, Q /* [B,Sq,dim] */, score_buf, B, num_heads, Sq, Sk, n_keys,
+                       hd, 1, stream));
     return rfk_linear(ctx, Q, w->out_proj_w, w->out_proj_b, out, Mq, q_dim, dim, stream);
 }
 
@@ -283,7 +293,7 @@ extern "C" int rfk_self_attention(rfk_ctx* ctx, const rfk_mha_weights* w, const 
     TRY(project_epilogue(qkv_buf, 3LL * dim, 3, g, o, rope, rope_cos, rope_sin, B, S, num_heads, hd, 0, nullptr,
                          stream));
     // attention output lands in the (dead) front of qkv_buf as [B,S,dim]
-    TRY(rfk_sdpa(ctx, Qb, Kb, Vb, qkv_buf, score_buf, nullptr, B, num_heads, S, S, S, hd, 1, stream));
+    TRY(attention_core(ctx, Qb, Kb, Vb, qkv_buf, score_buf, B, num_heads, S, S, S, hd, 1, stream));
     return rfk_linear(ctx, qkv_buf, w->out_proj_w, w->out_proj_b, out, M, dim, dim, stream);
 }
 

@@ -237,6 +237,13 @@ def swin_softmax_cast_fp16(inp, out, mask, BnW, num_heads, ws2, nW):
           num_heads, ws2, nW, _stream())
 
 
+# ---------------------------------------------------------------- attention
+
+def flash_attention(q, k, v, o, B, Hh, Sq, Sk, n_keys, D, o_bshd=False, scale=None):
+    _call("rfk_flash_attention", _p(q, H, "q"), _p(k, H, "k"), _p(v, H, "v"), _p(o, H, "o"), B, Hh, Sq, Sk, n_keys, D,
+          int(o_bshd), float(scale if scale is not None else D ** -0.5), _stream())
+
+
 # -------------------------------------------------------------- activations
 
 def fused_silu_mul(a, b, out, n):

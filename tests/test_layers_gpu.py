@@ -417,3 +417,43 @@ def test_scheduler_single_rank_renders_all_views(small):
         assert torch.equal(sched.session.download(), out[v])
     assert session.shard_views(10, 1, 4) == [1, 5, 9]
     sched.session.close()
+
+
+@pytest.mark.parametrize("B,Hh,Sq,Sk,n_keys,D", [
+    (1, 4, 256, 72, 72, 64), (1, 4, 256, 72, 65, 64), (2, 3, 300, 200, 193, 128), (1, 2, 77, 77, 77, 64),
+    (1, 1, 1, 5, 3, 64), (1, 2, 130, 64, 64, 128)])
+def test_flash_attention_matches_fp32_attention(B, Hh, Sq, Sk, n_keys, D):
+    """Fused attention (no score matrix) against torch fp32 attention over the first n_keys keys,
+    both output layouts, ragged query and key counts, both head sizes."""
+    pkg, _, _ = _mods()
+    g = torch.Generator(device="cuda").manual_seed(Sq * 31 + Sk)
+    Q = torch.randn(B, Hh, Sq, D, device="cuda", generator=g).half()
+    K = torch.randn(B, Hh, Sk, D, device="cuda", generator=g).half()
+    V = torch.randn(B, Hh, Sk, D, device="cuda", generator=g).half()
+    O = torch.full_like(Q, 7.0)
+    pkg.ops.flash_attention(Q, K, V, O, B, Hh, Sq, Sk, n_keys, D)
+    want = torch.nn.functional.scaled_dot_product_attention(Q.float(), K[:, :, :n_keys].float(), V[:, :, :n_keys].float())
+    _close(O, want, "flash attention", atol=4e-3, rtol=4e-3, mean_tol=5e-4)
+    O2 = torch.full((B, Sq, Hh * D), 7.0, device="cuda", dtype=H16)
+    pkg.ops.flash_attention(Q, K, V, O2, B, Hh, Sq, Sk, n_keys, D, o_bshd=True)
+    torch.cuda.synchronize()
+    assert torch.equal(O2.view(B, Sq, Hh, D).permute(0, 2, 1, 3), O)
+
+
+def test_flash_attention_full_size_matches_materialised_path(ctx):
+    """16 heads x 4096 queries x 5672 keys (5665 live): the fused kernel against rfk_sdpa
+    (GEMM -> softmax -> GEMM through a 1.5 GB score matrix), and shift invariance in Q scale."""
+    pkg, L, _ = _mods()
+    Hh, Sq, Sk, nk, D = 16, 4096, 5672, 5665, 64
+    g = torch.Generator(device="cuda").manual_seed(7)
+    Q = torch.randn(1, Hh, Sq, D, device="cuda", generator=g).half()
+    K = torch.randn(1, Hh, Sk, D, device="cuda", generator=g).half(); K[:, :, nk:] = 0
+    V = torch.randn(1, Hh, Sk, D, device="cuda", generator=g).half(); V[:, :, nk:] = 0
+    O = torch.empty(1, Sq, Hh * D, device="cuda", dtype=H16); Om = torch.empty_like(O)
+    pkg.ops.flash_attention(Q, K, V, O, 1, Hh, Sq, Sk, nk, D, o_bshd=True)
+    ws = torch.empty(Hh * Sq * Sk, device="cuda")
+    assert L.rfk_sdpa(ctx.h, _p(Q), _p(K), _p(V), _p(Om), _p(ws), VP(0), 1, Hh, Sq, Sk, nk, D, 1, _s()) == 0
+    torch.cuda.synchronize()
+    _close(O, Om, "fused vs materialised attention", atol=3e-3, rtol=3e-3, mean_tol=3e-4)
+    # rows are convex combinations of V rows
+    assert O.float().abs().max() <= V.float().abs().max() + 1e-3
