@@ -436,20 +436,31 @@ def run_kernels(args, backend, rank, world, peak, peak_src):
     }
 
 
-def softmax_roofline(peak, peak_src, n_tris, nr, heads, n_tokens, iters=12):
-    """Dominant rfk kernel of a view: the cross-attention softmax, fp32 scores -> fp16
-    probabilities written over the score rows. Timed live with CUDA events (graph replay of
-    `iters` launches on rotating buffers), at the exact shape the session launches."""
+def measured_tensor_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["bf16_tflops"]), "measured cuBLAS bf16 burst (MEASURED_PEAKS.json)"
+    return 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
+
+
+def attention_roofline(n_tris, nr, heads, n_tokens, head_dim, iters=12):
+    """Dominant rfk kernel of a view: the fused cross-attention (58 % of the view's device
+    time). A contraction, so its bound is the tensor pipe: achieved = 4*H*Sq*n_keys*D flop per
+    launch / average launch duration, timed live with CUDA events (graph replay of `iters`
+    launches, K/V/Q rotated over two buffer sets), at the exact shape the session launches."""
     import torch
     import renderformer_cuda_b200 as pkg
     Se = nr + n_tris; Se_pad = (Se + 7) & ~7
-    rows = heads * n_tokens
-    bufs = [torch.empty(rows, Se_pad, device="cuda").normal_(0, 0.375) for _ in range(2)]
-    fn = lambda i: pkg.ops.softmax_probs_inplace(bufs[i % 2], rows, Se, Se_pad, 1.0)
+    sets = []
+    for _ in range(2):
+        q = torch.randn(1, heads, n_tokens, head_dim, device="cuda").half()
+        k = torch.randn(1, heads, Se_pad, head_dim, device="cuda").half()
+        v = torch.randn(1, heads, Se_pad, head_dim, device="cuda").half()
+        sets.append((q, k, v, torch.empty(1, n_tokens, heads * head_dim, device="cuda", dtype=torch.float16)))
+    fn = lambda i: pkg.ops.flash_attention(*sets[i % 2], 1, heads, n_tokens, Se_pad, Se, head_dim, o_bshd=True)
     for i in range(3):
         fn(i)
-    # the kernel overwrites its input with fp16: refill between launches would be timed, so the
-    # scores are left as they are (any fp32 bit pattern costs the same to read)
     g = torch.cuda.CUDAGraph()
     with torch.cuda.graph(g):
         for i in range(iters):
@@ -460,17 +471,15 @@ def softmax_roofline(peak, peak_src, n_tris, nr, heads, n_tokens, iters=12):
     st.record(); g.replay(); en.record()
     torch.cuda.synchronize()
     ms = st.elapsed_time(en) / iters
-    bytes_alg = rows * (Se * 4 + Se_pad * 2)
-    gbs = bytes_alg / (ms * 1e-3) / 1e9
-    del bufs
+    flop = 4.0 * heads * n_tokens * Se * head_dim
+    tf = flop / (ms * 1e-3) / 1e12
+    peak, src = measured_tensor_peak()
+    alg_bytes = 2 * (2 * heads * n_tokens * head_dim + 2 * heads * Se_pad * head_dim)
+    del sets
     torch.cuda.empty_cache()
-    # ncu (profiles/softmax_row_kernel_*.md): dram bytes read+written of this kernel are within 1 % of
-    # the algorithmic bytes at a proportionally smaller row count; scaled here to a full launch
-    return {"bound": "hbm", "kernel": f"softmax_row_kernel<half,3,0> in place [{rows}x{Se} pitch {Se_pad}]",
-            "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(gbs / peak, 3),
-            "peak_source": peak_src, "frac_of_8tbs_nominal": round(gbs / 8000.0, 3),
-            "us_per_launch": round(ms * 1e3, 1), "algorithmic_bytes": bytes_alg,
-            "traffic": int(bytes_alg * 1.002), "traffic_note": "ncu dram read+write, scaled from an 8192-row capture"}
+    return {"bound": "tensor", "kernel": f"flash_attention_kernel<{head_dim}> [{heads}x{n_tokens} queries x {Se} keys]",
+            "achieved": round(tf, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(tf / peak, 3), "peak_source": src,
+            "us_per_launch": round(ms * 1e3, 1), "flop_per_launch": flop, "algorithmic_bytes": alg_bytes, "traffic": None}
 
 
 def run_views(args, rank, world, peak, peak_src):
@@ -543,7 +552,7 @@ def run_views(args, rank, world, peak, peak_src):
                                "heads, FFN 4096, 12 layers, fp16) per 512x512 view over a 5633-triangle scene, 64 look-at "
                                "cameras; encoder K/V cache computed once on rank 0 and NCCL-broadcast; views sharded "
                                "round-robin, one view per GPU per step; DPT head not included",
-                   "l2": "per-view working set (1.5 GB of scores + 0.43 GB of decoder weights) exceeds the 126 MB L2",
+                   "l2": "per-view working set (0.43 GB of decoder weights + 0.28 GB K/V cache + activations) exceeds the 126 MB L2",
                    "impl": args.impl, "params": model.num_params(), "n_tris": N_TRIS, "img_res": IMG_RES,
                    "parallelism": f"view-sharded dp{world}"},
         "e2e": {"value": round(world * args.steps / (ms_e2e * 1e-3), 3), "unit": "views/s",
@@ -561,7 +570,8 @@ def run_views(args, rank, world, peak, peak_src):
         line["graph_nodes_per_view"] = ses.graph_nodes
         line["rfk_kernels_per_view"] = ses.kernels_per_view
         line["gpu_launches"] = ses.kernels_per_view * args.steps
-        line["roofline"] = softmax_roofline(peak, peak_src, N_TRIS, model.num_register_tokens, model.num_heads, ses.n_tokens)
+        line["roofline"] = attention_roofline(N_TRIS, model.num_register_tokens, model.num_heads, ses.n_tokens,
+                                              model.head_dim)
     ses.close()
     return line
 

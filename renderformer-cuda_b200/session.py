@@ -322,6 +322,8 @@ class ViewScheduler:
         if self.rank == src:
             self.session.encode_scene(tri, vn, tex)
         if self.dist and self.world > 1:
+            # a 4-byte collective first: communicator set-up is not part of the broadcast's cost
+            self.dist.broadcast(torch.zeros(1, device=self.session.scene_state.device), src=src, group=self.group)
             st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             st.record()
