@@ -231,6 +231,18 @@ int rfk_flash_attention(const rfk_half* Q, const rfk_half* K, const rfk_half* V,
                         int B, int H, int Sq, int Sk, int n_keys, int D, int o_bshd, float scale,
                         rfk_stream_t stream);
 
+/* Which kernel serves rfk_flash_attention at D = 64: 0 automatic, 1 the mma.sync kernel, 2 the
+ * tcgen05 / tensor-memory kernel. Process-wide; D = 128 always takes the mma.sync kernel.
+ * No reference counterpart (the reference leaves the choice to cuDNN's heuristics,
+ * src/layers/attention.cu:100-140). */
+int rfk_flash_attention_set_path(int path);
+
+/* Reads (and with clear != 0 resets) the current device's error word of the tcgen05 kernel:
+ * 0 none, 1 a bounded wait ran out (the CTA freed its tensor memory and returned; its output rows
+ * are undefined), 2 shared memory window not 1024-byte aligned. Synchronises the device.
+ * No reference counterpart. */
+int rfk_flash_attention_error(int* code, int clear);
+
 /* -------------------------------------------------------------- activations */
 
 /* out = half(silu(a) * b), out may alias a — replaces rf::fused_silu_mul,

@@ -277,6 +277,11 @@ static int launch_flash(const __half* Q, const __half* K, const __half* V, __hal
     return launch_status();
 }
 
+// attention_tc.cu
+extern int g_attn_path;
+int launch_attention_tc(const __half* Q, const __half* K, const __half* V, __half* O, int B, int H, int Sq, int Sk,
+                        int n_keys, int o_bshd, float scale, cudaStream_t st);
+
 }  // namespace rfk
 
 using namespace rfk;
@@ -291,6 +296,9 @@ extern "C" int rfk_flash_attention(const rfk_half* Q, const rfk_half* K, const r
     if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O)) return RFK_EUNSUPPORTED;
     cudaStream_t st = as_stream(stream);
     const long long kvs = (long long)Sk * D;
+    if (D == 64 && g_attn_path == 2)
+        return launch_attention_tc((const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, B, H, Sq, Sk, n_keys,
+                                   o_bshd, scale, st);
     if (D == 64)
         return launch_flash<64>((const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, B, H, Sq, Sk, n_keys, kvs,
                                 o_bshd, scale, st);

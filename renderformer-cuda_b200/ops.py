@@ -244,6 +244,19 @@ def flash_attention(q, k, v, o, B, Hh, Sq, Sk, n_keys, D, o_bshd=False, scale=No
           int(o_bshd), float(scale if scale is not None else D ** -0.5), _stream())
 
 
+def flash_attention_set_path(path):
+    """0 automatic, 1 mma.sync kernel, 2 tcgen05 kernel (head_dim 64)."""
+    _call("rfk_flash_attention_set_path", int(path))
+
+
+def flash_attention_error(clear=True):
+    """Error word of the tcgen05 attention kernel on the current device (0 = none)."""
+    import ctypes
+    code = ctypes.c_int(-1)
+    _call("rfk_flash_attention_error", ctypes.byref(code), int(clear))
+    return code.value
+
+
 # -------------------------------------------------------------- activations
 
 def fused_silu_mul(a, b, out, n):

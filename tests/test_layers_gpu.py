@@ -457,3 +457,55 @@ def test_flash_attention_full_size_matches_materialised_path(ctx):
     _close(O, Om, "fused vs materialised attention", atol=3e-3, rtol=3e-3, mean_tol=3e-4)
     # rows are convex combinations of V rows
     assert O.float().abs().max() <= V.float().abs().max() + 1e-3
+
+
+@pytest.fixture
+def tc_path():
+    """Routes rfk_flash_attention (D = 64) to the tcgen05 kernel for one test and checks its error word."""
+    pkg, _, _ = _mods()
+    pkg.ops.flash_attention_error(clear=True)
+    pkg.ops.flash_attention_set_path(2)
+    yield pkg
+    pkg.ops.flash_attention_set_path(0)
+    torch.cuda.synchronize()
+    assert pkg.ops.flash_attention_error(clear=True) == 0
+
+
+@pytest.mark.parametrize("B,Hh,Sq,Sk,n_keys", [
+    (1, 1, 128, 128, 128), (1, 1, 128, 128, 100), (1, 4, 256, 72, 65), (1, 2, 77, 77, 77), (1, 1, 1, 5, 3),
+    (2, 3, 300, 1000, 993), (1, 2, 130, 384, 384)])
+def test_tcgen05_attention_matches_fp32_attention(tc_path, B, Hh, Sq, Sk, n_keys):
+    """tcgen05 / tensor-memory kernel against torch fp32 attention: one and many key tiles, ragged query
+    and key counts, masked tail keys, both output layouts; tolerance 4e-3 abs + 4e-3 rel (fp16 output,
+    fp16 probabilities), mean error 5e-4."""
+    pkg, D = tc_path, 64
+    g = torch.Generator(device="cuda").manual_seed(Sq * 31 + Sk)
+    Q = torch.randn(B, Hh, Sq, D, device="cuda", generator=g).half()
+    K = torch.randn(B, Hh, Sk, D, device="cuda", generator=g).half()
+    V = torch.randn(B, Hh, Sk, D, device="cuda", generator=g).half()
+    O = torch.full_like(Q, 7.0)
+    pkg.ops.flash_attention(Q, K, V, O, B, Hh, Sq, Sk, n_keys, D)
+    want = torch.nn.functional.scaled_dot_product_attention(Q.float(), K[:, :, :n_keys].float(), V[:, :, :n_keys].float())
+    _close(O, want, "tcgen05 attention", atol=4e-3, rtol=4e-3, mean_tol=5e-4)
+    O2 = torch.full((B, Sq, Hh * D), 7.0, device="cuda", dtype=H16)
+    pkg.ops.flash_attention(Q, K, V, O2, B, Hh, Sq, Sk, n_keys, D, o_bshd=True)
+    torch.cuda.synchronize()
+    assert torch.equal(O2.view(B, Sq, Hh, D).permute(0, 2, 1, 3), O)
+
+
+def test_tcgen05_attention_full_size_matches_mma_sync_kernel(tc_path):
+    """16 heads x 4096 queries x 5672 keys (5665 live): the two fused kernels agree on peaked rows
+    (scaled scores with standard deviation 4, so the running maximum moves often and by a lot)."""
+    pkg = tc_path
+    Hh, Sq, Sk, nk, D = 16, 4096, 5672, 5665, 64
+    g = torch.Generator(device="cuda").manual_seed(11)
+    Q = (torch.randn(1, Hh, Sq, D, device="cuda", generator=g) * 2).half()
+    K = (torch.randn(1, Hh, Sk, D, device="cuda", generator=g) * 2).half()
+    V = torch.randn(1, Hh, Sk, D, device="cuda", generator=g).half()
+    O = torch.empty(1, Sq, Hh * D, device="cuda", dtype=H16); Om = torch.empty_like(O)
+    pkg.ops.flash_attention(Q, K, V, O, 1, Hh, Sq, Sk, nk, D, o_bshd=True)
+    pkg.ops.flash_attention_set_path(1)
+    pkg.ops.flash_attention(Q, K, V, Om, 1, Hh, Sq, Sk, nk, D, o_bshd=True)
+    torch.cuda.synchronize()
+    assert torch.isfinite(O.float()).all()
+    _close(O, Om, "tcgen05 vs mma.sync attention", atol=4e-3, rtol=4e-3, mean_tol=3e-4)
