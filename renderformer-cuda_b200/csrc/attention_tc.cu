@@ -37,10 +37,11 @@ constexpr int kStages = 6;
 constexpr int kQBytes = BM * HD * 2;           // 16 KB
 constexpr int kKBytes = BN * HD * 2;           // 8 KB; a stage is K then V
 constexpr int kStageBytes = 2 * kKBytes;
-constexpr int kTmemCols = 256;                 // S0 at +0, S1 at +64, O at +128
+constexpr int kSBufs = 3;                      // score buffers in tensor memory
+constexpr int kTmemCols = 256;                 // S0, S1, S2 at +0, +64, +128; O at +192
 
 struct __align__(8) Ctrl {
-    uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[2], p_full[2], pv_done[2];
+    uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[kSBufs], p_full[kSBufs], pv_done[2];
     uint32_t tmem_base;
     int abort;
 };
@@ -55,6 +56,38 @@ enum : int { kErrTimeout = 1, kErrSmemAlign = 2 };
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// 32 raw scores (columns col0 .. col0+31 of the tile) -> 32 probabilities exp2(s * c - mc), packed
+// two fp16 per word into pk[0..16); their fp32 sums are added to acc0 / acc1 (two lanes each).
+// Packed fp32x2 multiply-adds and adds halve the instruction count around the exponentials.
+template <bool MASKED>
+__device__ __forceinline__ void exp_half(const uint32_t (&v)[32], uint32_t* pk, int col0, int n_valid, float c, float mc,
+                                         float2& acc0, float2& acc1) {
+    const float2 c2 = make_float2(c, c), nm2 = make_float2(-mc, -mc);
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+        const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), c2, nm2);
+        const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])), c2, nm2);
+        float2 p0 = make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
+        float2 p1 = make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
+        if (MASKED) {  // last tile: keys at or beyond n_keys contribute nothing
+            if (col0 + i >= n_valid) p0.x = 0.0f;
+            if (col0 + i + 1 >= n_valid) p0.y = 0.0f;
+            if (col0 + i + 2 >= n_valid) p1.x = 0.0f;
+            if (col0 + i + 3 >= n_valid) p1.y = 0.0f;
+        }
+        acc0 = __fadd2_rn(acc0, p0);
+        acc1 = __fadd2_rn(acc1, p1);
+        pk[i >> 1] = pack_half2(p0.x, p0.y);
+        pk[(i >> 1) + 1] = pack_half2(p1.x, p1.y);
+    }
 }
 
 __global__ void __launch_bounds__(kThreads, 2)
@@ -79,8 +112,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (tid == 0) {
         tc::mbar_init(&ctrl->q_full, 1);
         for (int s = 0; s < kStages; ++s) { tc::mbar_init(&ctrl->kv_full[s], 1); tc::mbar_init(&ctrl->kv_empty[s], 1); }
-        tc::mbar_init(&ctrl->s_full[0], 1); tc::mbar_init(&ctrl->s_full[1], 1);
-        tc::mbar_init(&ctrl->p_full[0], 4); tc::mbar_init(&ctrl->p_full[1], 4);
+        for (int b = 0; b < kSBufs; ++b) { tc::mbar_init(&ctrl->s_full[b], 1); tc::mbar_init(&ctrl->p_full[b], 4); }
         tc::mbar_init(&ctrl->pv_done[0], 1); tc::mbar_init(&ctrl->pv_done[1], 1);
         ctrl->abort = 0;
         tc::fence_barrier_init();
@@ -93,7 +125,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem = ctrl->tmem_base;
-    const uint32_t tmem_O = tmem + 128;
+    const uint32_t tmem_O = tmem + kSBufs * 64;
 
     if (warp == 4) {
         // ------------------------------------------------------------ producer (one thread)
@@ -116,37 +148,43 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (lane == 0) {
             constexpr uint32_t idesc_qk = tc::umma_idesc_f16(BM, BN, 0);  // B = K tile, K-major
             constexpr uint32_t idesc_pv = tc::umma_idesc_f16(BM, HD, 1);  // B = V tile, MN-major
-            auto issue_qk = [&](int j) {  // S[j & 1] = Q K(j)^T
-                const uint32_t kt = sKV + (j % kStages) * kStageBytes;
+            // tile j: score buffer j % kSBufs (its use number j / kSBufs gives the barrier phase), ring stage j % kStages
+            auto issue_qk = [&](int buf, int stage) {  // S[buf] = Q K(stage)^T
+                const uint32_t kt = sKV + stage * kStageBytes;
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks)  // 16 head-dim elements = 32 bytes along a row
-                    tc::umma_f16(tmem + (j & 1) * 64, tc::umma_desc_sw128(sQ + ks * 32), tc::umma_desc_sw128(kt + ks * 32),
+                    tc::umma_f16(tmem + buf * 64, tc::umma_desc_sw128(sQ + ks * 32), tc::umma_desc_sw128(kt + ks * 32),
                                  idesc_qk, ks > 0);
-                tc::umma_commit(&ctrl->s_full[j & 1]);
+                tc::umma_commit(&ctrl->s_full[buf]);
             };
             bool ok = tc::mbar_wait(&ctrl->q_full, 0, abort_flag);
-            for (int j = 0; ok && j < 2 && j < n_tiles; ++j) {
+            for (int j = 0; ok && j < kSBufs && j < n_tiles; ++j) {
                 ok = tc::mbar_wait(&ctrl->kv_full[j], 0, abort_flag);
-                if (ok) { tc::tc_fence_after(); issue_qk(j); }
+                if (ok) { tc::tc_fence_after(); issue_qk(j, j); }
             }
+            // running indices: buffer / stage of tile j, stage of tile j + kSBufs, and the phase parities that go with them
+            int buf = 0, buf_par = 0, st = 0, st3 = kSBufs % kStages, st3_par = (kSBufs / kStages) & 1;
             for (int j = 0; ok && j < n_tiles; ++j) {
-                ok = tc::mbar_wait(&ctrl->p_full[j & 1], (j >> 1) & 1, abort_flag);
+                ok = tc::mbar_wait(&ctrl->p_full[buf], buf_par, abort_flag);
                 if (!ok) break;
                 tc::tc_fence_after();
-                const uint32_t vt = sKV + (j % kStages) * kStageBytes + kKBytes;
+                const uint32_t vt = sKV + st * kStageBytes + kKBytes;
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks)  // P: 16 keys = 8 columns; V: 16 keys = 16 rows of 128 bytes
-                    tc::umma_f16_ts(tmem_O, tmem + (j & 1) * 64 + ks * 8, tc::umma_desc_sw128(vt + ks * 2048), idesc_pv,
+                    tc::umma_f16_ts(tmem_O, tmem + buf * 64 + ks * 8, tc::umma_desc_sw128(vt + ks * 2048), idesc_pv,
                                     (j > 0) || (ks > 0));
-                tc::umma_commit(&ctrl->kv_empty[j % kStages]);
+                tc::umma_commit(&ctrl->kv_empty[st]);
                 tc::umma_commit(&ctrl->pv_done[j & 1]);
-                if (j + 2 < n_tiles) {
-                    // products of one thread execute in issue order: S(j+2) overwrites the buffer only after P(j) was read
-                    ok = tc::mbar_wait(&ctrl->kv_full[(j + 2) % kStages], ((j + 2) / kStages) & 1, abort_flag);
+                if (j + kSBufs < n_tiles) {
+                    // products of one thread execute in issue order: S(j+3) overwrites the buffer only after P(j) was read
+                    ok = tc::mbar_wait(&ctrl->kv_full[st3], st3_par, abort_flag);
                     if (!ok) break;
                     tc::tc_fence_after();
-                    issue_qk(j + 2);
+                    issue_qk(buf, st3);
                 }
+                if (++buf == kSBufs) { buf = 0; buf_par ^= 1; }
+                if (++st == kStages) st = 0;
+                if (++st3 == kStages) { st3 = 0; st3_par ^= 1; }
             }
         }
         __syncwarp();
@@ -159,24 +197,35 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const uint32_t lane_off = (uint32_t)(warp * 32) << 16;      // a warp reaches lanes [32 * (warp % 4), +32)
         const uint32_t tO = tmem_O + lane_off;
         float m_run = -INFINITY, l_run = 0.0f;
-        bool ok = true;
-        uint32_t va[32], vb[32];
-        for (int j = 0; j < n_tiles; ++j) {
-            const uint32_t tS = tmem + lane_off + (j & 1) * 64;
-            // s_full of tile j also tells that every earlier product, P V of tile j - 2 included, is complete
-            ok = __all_sync(kFull, tc::mbar_wait(&ctrl->s_full[j & 1], (j >> 1) & 1, abort_flag));
-            if (!ok) break;
+        uint32_t va[32], vb[32], pk[32];
+        // The scores of tile j + 1 are fetched from tensor memory while tile j is exponentiated.
+        bool ok = __all_sync(kFull, tc::mbar_wait(&ctrl->s_full[0], 0, abort_flag));
+        if (ok) {
             tc::tc_fence_after();
-            tc::tmem_ld32(tS, va);
-            tc::tmem_ld32(tS + 32, vb);
+            tc::tmem_ld32(tmem + lane_off, va);
+            tc::tmem_ld32(tmem + lane_off + 32, vb);
+        }
+        int buf = 0, buf_par = 0;  // score buffer of tile j and the phase parity of its barriers
+        for (int j = 0; ok && j < n_tiles; ++j) {
+            const int nbuf = buf + 1 == kSBufs ? 0 : buf + 1, nbuf_par = buf + 1 == kSBufs ? buf_par ^ 1 : buf_par;
+            const uint32_t tS = tmem + lane_off + buf * 64, tS_next = tmem + lane_off + nbuf * 64;
+            const bool more = j + 1 < n_tiles;
             tc::tc_wait_ld(va);
             tc::tc_wait_ld(vb);
             const int n_valid = min(BN, n_keys - j * BN);  // real keys among this tile's 64 columns
-            float m_tile = -INFINITY;
+            float m_tile;
             if (n_valid == BN) {
+                float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) m_tile = fmaxf(m_tile, fmaxf(__uint_as_float(va[i]), __uint_as_float(vb[i])));
+                for (int i = 0; i < 32; i += 4) {
+                    m0 = fmax3(m0, __uint_as_float(va[i]), __uint_as_float(va[i + 1]));
+                    m1 = fmax3(m1, __uint_as_float(va[i + 2]), __uint_as_float(va[i + 3]));
+                    m2 = fmax3(m2, __uint_as_float(vb[i]), __uint_as_float(vb[i + 1]));
+                    m3 = fmax3(m3, __uint_as_float(vb[i + 2]), __uint_as_float(vb[i + 3]));
+                }
+                m_tile = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
             } else {
+                m_tile = -INFINITY;
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     if (i < n_valid) m_tile = fmaxf(m_tile, __uint_as_float(va[i]));
@@ -189,54 +238,49 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const float m_new = move ? m_tile : m_run;
             const float alpha = move ? fast_exp2((m_run - m_new) * scale_log2e) : 1.0f;  // first tile: 0
             const float mc = m_new * scale_log2e;
-            // P = exp2(scale * log2e * (S - max)), two fp16 per 32-bit column: keys 2i, 2i+1 in column i
-            float sum0 = 0.0f, sum1 = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                float p0 = fast_exp2(fmaf(__uint_as_float(va[i]), scale_log2e, -mc));
-                float p1 = fast_exp2(fmaf(__uint_as_float(va[i + 1]), scale_log2e, -mc));
-                float p2 = fast_exp2(fmaf(__uint_as_float(vb[i]), scale_log2e, -mc));
-                float p3 = fast_exp2(fmaf(__uint_as_float(vb[i + 1]), scale_log2e, -mc));
-                if (n_valid != BN) {  // last tile: keys at or beyond n_keys contribute nothing
-                    if (i >= n_valid) p0 = 0.0f;
-                    if (i + 1 >= n_valid) p1 = 0.0f;
-                    if (32 + i >= n_valid) p2 = 0.0f;
-                    if (33 + i >= n_valid) p3 = 0.0f;
-                }
-                sum0 += p0 + p1;
-                sum1 += p2 + p3;
-                va[i >> 1] = pack_half2(p0, p1);         // va[0..16): keys 0..31 (element i/2 <= i: already consumed)
-                vb[i >> 1] = pack_half2(p2, p3);         // vb[0..16): keys 32..63
-            }
-#pragma unroll
-            for (int i = 0; i < 16; ++i) va[16 + i] = vb[i];  // va = the 32 columns of P
-            if (j > 0 && __any_sync(kFull, move)) {  // rescale this warp's 32 rows of O
-                // O belongs to the tensor core until the previous tile's P V is done
+            if (j > 0 && __any_sync(kFull, move)) {  // rescale this warp's 32 rows of O (pk is free here)
+                // O belongs to the tensor core until the previous tile's P V is done. Having seen s_full of tile j,
+                // P V of tile j - 3 (the previous phase of this barrier) is known complete: the parity is unambiguous.
                 ok = __all_sync(kFull, tc::mbar_wait(&ctrl->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag));
                 if (!ok) break;
                 tc::tc_fence_after();
 #pragma unroll
                 for (int hc = 0; hc < 2; ++hc) {
-                    tc::tmem_ld32(tO + hc * 32, vb);
-                    tc::tc_wait_ld(vb);
+                    tc::tmem_ld32(tO + hc * 32, pk);
+                    tc::tc_wait_ld(pk);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) vb[i] = __float_as_uint(__uint_as_float(vb[i]) * alpha);
-                    tc::tmem_st32(tO + hc * 32, vb);
+                    for (int i = 0; i < 32; ++i) pk[i] = __float_as_uint(__uint_as_float(pk[i]) * alpha);
+                    tc::tmem_st32(tO + hc * 32, pk);
                 }
             }
-            l_run = l_run * alpha + (sum0 + sum1);
+            // P = exp2(scale * log2e * (S - max)), two fp16 per 32-bit column: keys 2i, 2i+1 in column i
+            float2 acc0 = make_float2(0.0f, 0.0f), acc1 = make_float2(0.0f, 0.0f);
+            if (n_valid == BN) exp_half<false>(va, pk, 0, n_valid, scale_log2e, mc, acc0, acc1);
+            else exp_half<true>(va, pk, 0, n_valid, scale_log2e, mc, acc0, acc1);
+            if (more) {
+                ok = __all_sync(kFull, tc::mbar_wait(&ctrl->s_full[nbuf], nbuf_par, abort_flag));
+                if (!ok) break;
+                tc::tc_fence_after();
+                tc::tmem_ld32(tS_next, va);
+            }
+            if (n_valid == BN) exp_half<false>(vb, pk + 16, 32, n_valid, scale_log2e, mc, acc0, acc1);
+            else exp_half<true>(vb, pk + 16, 32, n_valid, scale_log2e, mc, acc0, acc1);
+            if (more) tc::tmem_ld32(tS_next + 32, vb);
+            l_run = l_run * alpha + ((acc0.x + acc0.y) + (acc1.x + acc1.y));
             m_run = m_new;
-            tc::tmem_st32(tS, va);    // P over the first 32 columns of this thread's own lane of S
+            tc::tmem_st32(tS, pk);    // P over the first 32 columns of this thread's own lane of S
             tc::tc_wait_st();
             tc::tc_fence_before();    // the writes of P and O come before the arrival
             __syncwarp();
-            if (lane == 0) tc::mbar_arrive(&ctrl->p_full[j & 1]);
+            if (lane == 0) tc::mbar_arrive(&ctrl->p_full[buf]);
+            buf = nbuf;
+            buf_par = nbuf_par;
         }
+        tc::tc_wait_ld();  // an aborted loop may leave loads in flight
         // ---- epilogue: O / l -> fp16 -> global, one 128-byte row per thread
-        if (ok) {
-            const int jl = n_tiles - 1;
+        // last but one first: that keeps each wait within one phase of its barrier (see the rescale above)
+        for (int jl = max(n_tiles - 2, 0); ok && jl < n_tiles; ++jl)
             ok = __all_sync(kFull, tc::mbar_wait(&ctrl->pv_done[jl & 1], (jl >> 1) & 1, abort_flag));
-        }
         if (ok) {
             tc::tc_fence_after();
             const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
