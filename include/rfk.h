@@ -231,8 +231,9 @@ int rfk_flash_attention(const rfk_half* Q, const rfk_half* K, const rfk_half* V,
                         int B, int H, int Sq, int Sk, int n_keys, int D, int o_bshd, float scale,
                         rfk_stream_t stream);
 
-/* Which kernel serves rfk_flash_attention at D = 64: 0 automatic, 1 the mma.sync kernel, 2 the
- * tcgen05 / tensor-memory kernel. Process-wide; D = 128 always takes the mma.sync kernel.
+/* Which kernel serves rfk_flash_attention at D = 64: 0 automatic (the tcgen05 / tensor-memory
+ * kernel; the mma.sync kernel only if the driver cannot encode tensor maps), 1 the mma.sync kernel,
+ * 2 the tcgen05 kernel or RFK_EUNSUPPORTED. Process-wide; D = 128 always takes the mma.sync kernel.
  * No reference counterpart (the reference leaves the choice to cuDNN's heuristics,
  * src/layers/attention.cu:100-140). */
 int rfk_flash_attention_set_path(int path);

@@ -32,7 +32,7 @@ __device__ int g_attn_tc_error = 0;  // first time-out / failure code seen by an
 namespace tcattn {
 
 constexpr int BM = 128, BN = 64, HD = 64;
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;
 constexpr int kStages = 6;
 constexpr int kQBytes = BM * HD * 2;           // 16 KB
 constexpr int kKBytes = BN * HD * 2;           // 8 KB; a stage is K then V
@@ -41,7 +41,7 @@ constexpr int kSBufs = 3;                      // score buffers in tensor memory
 constexpr int kTmemCols = 256;                 // S0, S1, S2 at +0, +64, +128; O at +192
 
 struct __align__(8) Ctrl {
-    uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[kSBufs], p_full[kSBufs], pv_done[2];
+    uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[kSBufs], p_full[kSBufs], pv_done[kSBufs];
     uint32_t tmem_base;
     int abort;
 };
@@ -64,19 +64,40 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     return d;
 }
 
+// 2^x for two values on the FMA pipes (no special-function unit): x = n + f with n = round(x),
+// 2^f from a degree-4 polynomial on [-0.5, 0.5] (relative error 2.6e-6, far below the fp16 rounding
+// of the result), and n added into the exponent field. Inputs below -125 give a value near 2^-125.
+__device__ __forceinline__ float2 exp2_poly(float2 x) {
+    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: x + kMagic holds round(x) in its low mantissa bits
+    x.x = fmaxf(x.x, -125.0f);
+    x.y = fmaxf(x.y, -125.0f);
+    const float2 t = __fadd2_rn(x, make_float2(kMagic, kMagic));
+    const float2 n = __fadd2_rn(t, make_float2(-kMagic, -kMagic));
+    const float2 f = __ffma2_rn(n, make_float2(-1.0f, -1.0f), x);
+    float2 p = __ffma2_rn(f, make_float2(0.009570092f, 0.009570092f), make_float2(0.05591786f, 0.05591786f));
+    p = __ffma2_rn(p, f, make_float2(0.24024744f, 0.24024744f));
+    p = __ffma2_rn(p, f, make_float2(0.6931218f, 0.6931218f));
+    p = __ffma2_rn(p, f, make_float2(0.9999993f, 0.9999993f));
+    return make_float2(__uint_as_float(__float_as_uint(p.x) + (__float_as_uint(t.x) << 23)),
+                       __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(t.y) << 23)));
+}
+
 // 32 raw scores (columns col0 .. col0+31 of the tile) -> 32 probabilities exp2(s * c - mc), packed
 // two fp16 per word into pk[0..16); their fp32 sums are added to acc0 / acc1 (two lanes each).
-// Packed fp32x2 multiply-adds and adds halve the instruction count around the exponentials.
+// Packed fp32x2 multiply-adds and adds halve the instruction count around the exponentials. The
+// special-function unit (16 exponentials per clock and SM) is the scarcest resource of this kernel,
+// so of every four pairs, those selected by kPolyMask take the polynomial path instead.
+constexpr int kPolyMask = 0x0;
 template <bool MASKED>
-__device__ __forceinline__ void exp_half(const uint32_t (&v)[32], uint32_t* pk, int col0, int n_valid, float c, float mc,
-                                         float2& acc0, float2& acc1) {
+__device__ __forceinline__ void exp_half(const uint32_t (&v)[32], uint32_t* pk /* may alias v */, int col0, int n_valid, float c,
+                                         float mc, float2& acc0, float2& acc1) {
     const float2 c2 = make_float2(c, c), nm2 = make_float2(-mc, -mc);
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
         const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), c2, nm2);
         const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])), c2, nm2);
-        float2 p0 = make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
-        float2 p1 = make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
+        float2 p0 = ((kPolyMask >> ((i >> 1) & 3)) & 1) ? exp2_poly(x0) : make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
+        float2 p1 = ((kPolyMask >> (((i >> 1) + 1) & 3)) & 1) ? exp2_poly(x1) : make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
         if (MASKED) {  // last tile: keys at or beyond n_keys contribute nothing
             if (col0 + i >= n_valid) p0.x = 0.0f;
             if (col0 + i + 1 >= n_valid) p0.y = 0.0f;
@@ -112,8 +133,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (tid == 0) {
         tc::mbar_init(&ctrl->q_full, 1);
         for (int s = 0; s < kStages; ++s) { tc::mbar_init(&ctrl->kv_full[s], 1); tc::mbar_init(&ctrl->kv_empty[s], 1); }
-        for (int b = 0; b < kSBufs; ++b) { tc::mbar_init(&ctrl->s_full[b], 1); tc::mbar_init(&ctrl->p_full[b], 4); }
-        tc::mbar_init(&ctrl->pv_done[0], 1); tc::mbar_init(&ctrl->pv_done[1], 1);
+        for (int b = 0; b < kSBufs; ++b) {
+            tc::mbar_init(&ctrl->s_full[b], 1); tc::mbar_init(&ctrl->p_full[b], 4); tc::mbar_init(&ctrl->pv_done[b], 1);
+        }
         ctrl->abort = 0;
         tc::fence_barrier_init();
     }
@@ -144,47 +166,48 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         __syncwarp();
     } else if (warp == 5) {
-        // ------------------------------------------------------------ MMA issuer (one thread)
+        // ------------------------------------------------------------ issuer of O += P V (one thread)
+        // tile j: score buffer j % kSBufs (its use number j / kSBufs gives the barrier phase), ring stage j % kStages
         if (lane == 0) {
-            constexpr uint32_t idesc_qk = tc::umma_idesc_f16(BM, BN, 0);  // B = K tile, K-major
             constexpr uint32_t idesc_pv = tc::umma_idesc_f16(BM, HD, 1);  // B = V tile, MN-major
-            // tile j: score buffer j % kSBufs (its use number j / kSBufs gives the barrier phase), ring stage j % kStages
-            auto issue_qk = [&](int buf, int stage) {  // S[buf] = Q K(stage)^T
-                const uint32_t kt = sKV + stage * kStageBytes;
-#pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks)  // 16 head-dim elements = 32 bytes along a row
-                    tc::umma_f16(tmem + buf * 64, tc::umma_desc_sw128(sQ + ks * 32), tc::umma_desc_sw128(kt + ks * 32),
-                                 idesc_qk, ks > 0);
-                tc::umma_commit(&ctrl->s_full[buf]);
-            };
-            bool ok = tc::mbar_wait(&ctrl->q_full, 0, abort_flag);
-            for (int j = 0; ok && j < kSBufs && j < n_tiles; ++j) {
-                ok = tc::mbar_wait(&ctrl->kv_full[j], 0, abort_flag);
-                if (ok) { tc::tc_fence_after(); issue_qk(j, j); }
-            }
-            // running indices: buffer / stage of tile j, stage of tile j + kSBufs, and the phase parities that go with them
-            int buf = 0, buf_par = 0, st = 0, st3 = kSBufs % kStages, st3_par = (kSBufs / kStages) & 1;
+            const uint32_t v_lo = tc::umma_desc_lo(sKV + kKBytes);
+            bool ok = true;
+            int buf = 0, buf_par = 0, st = 0;
             for (int j = 0; ok && j < n_tiles; ++j) {
                 ok = tc::mbar_wait(&ctrl->p_full[buf], buf_par, abort_flag);
                 if (!ok) break;
                 tc::tc_fence_after();
-                const uint32_t vt = sKV + st * kStageBytes + kKBytes;
+                const uint32_t p_tmem = tmem + buf * 64, vt_lo = v_lo + st * (kStageBytes >> 4);
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks)  // P: 16 keys = 8 columns; V: 16 keys = 16 rows of 128 bytes
-                    tc::umma_f16_ts(tmem_O, tmem + buf * 64 + ks * 8, tc::umma_desc_sw128(vt + ks * 2048), idesc_pv,
-                                    (j > 0) || (ks > 0));
-                tc::umma_commit(&ctrl->kv_empty[st]);
-                tc::umma_commit(&ctrl->pv_done[j & 1]);
-                if (j + kSBufs < n_tiles) {
-                    // products of one thread execute in issue order: S(j+3) overwrites the buffer only after P(j) was read
-                    ok = tc::mbar_wait(&ctrl->kv_full[st3], st3_par, abort_flag);
-                    if (!ok) break;
-                    tc::tc_fence_after();
-                    issue_qk(buf, st3);
-                }
+                    tc::umma_f16_ts_lo(tmem_O, p_tmem + ks * 8, vt_lo + ks * (2048 >> 4), idesc_pv, (j > 0) || (ks > 0));
+                tc::umma_commit(&ctrl->kv_empty[st]);  // K of this stage was consumed before its scores could be read
+                tc::umma_commit(&ctrl->pv_done[buf]);
                 if (++buf == kSBufs) { buf = 0; buf_par ^= 1; }
                 if (++st == kStages) st = 0;
-                if (++st3 == kStages) { st3 = 0; st3_par ^= 1; }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 6) {
+        // ------------------------------------------------------------ issuer of S = Q K^T (one thread)
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = tc::umma_idesc_f16(BM, BN, 0);  // B = K tile, K-major
+            const uint32_t q_lo = tc::umma_desc_lo(sQ), k_lo = tc::umma_desc_lo(sKV);
+            bool ok = tc::mbar_wait(&ctrl->q_full, 0, abort_flag);
+            int buf = 0, buf_par = 0, st = 0, st_par = 0;
+            for (int j = 0; ok && j < n_tiles; ++j) {
+                ok = tc::mbar_wait(&ctrl->kv_full[st], st_par, abort_flag);
+                // the buffer still holds P of tile j - kSBufs until that tile's P V is complete
+                if (ok && j >= kSBufs) ok = tc::mbar_wait(&ctrl->pv_done[buf], buf_par ^ 1, abort_flag);
+                if (!ok) break;
+                tc::tc_fence_after();
+                const uint32_t kt_lo = k_lo + st * (kStageBytes >> 4);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks)  // 16 head-dim elements = 32 bytes along a row
+                    tc::umma_f16_lo(tmem + buf * 64, q_lo + ks * 2, kt_lo + ks * 2, idesc_qk, ks > 0);
+                tc::umma_commit(&ctrl->s_full[buf]);
+                if (++buf == kSBufs) { buf = 0; buf_par ^= 1; }
+                if (++st == kStages) { st = 0; st_par ^= 1; }
             }
         }
         __syncwarp();
@@ -197,19 +220,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const uint32_t lane_off = (uint32_t)(warp * 32) << 16;      // a warp reaches lanes [32 * (warp % 4), +32)
         const uint32_t tO = tmem_O + lane_off;
         float m_run = -INFINITY, l_run = 0.0f;
-        uint32_t va[32], vb[32], pk[32];
-        // The scores of tile j + 1 are fetched from tensor memory while tile j is exponentiated.
-        bool ok = __all_sync(kFull, tc::mbar_wait(&ctrl->s_full[0], 0, abort_flag));
-        if (ok) {
-            tc::tc_fence_after();
-            tc::tmem_ld32(tmem + lane_off, va);
-            tc::tmem_ld32(tmem + lane_off + 32, vb);
-        }
+        uint32_t va[32], vb[32];
+        bool ok = true;
         int buf = 0, buf_par = 0;  // score buffer of tile j and the phase parity of its barriers
-        for (int j = 0; ok && j < n_tiles; ++j) {
-            const int nbuf = buf + 1 == kSBufs ? 0 : buf + 1, nbuf_par = buf + 1 == kSBufs ? buf_par ^ 1 : buf_par;
-            const uint32_t tS = tmem + lane_off + buf * 64, tS_next = tmem + lane_off + nbuf * 64;
-            const bool more = j + 1 < n_tiles;
+        for (int j = 0; j < n_tiles; ++j) {
+            const uint32_t tS = tmem + lane_off + buf * 64;
+            ok = tc::mbar_wait_warp(&ctrl->s_full[buf], buf_par, abort_flag);
+            if (!ok) break;
+            tc::tc_fence_after();
+            tc::tmem_ld32(tS, va);
+            tc::tmem_ld32(tS + 32, vb);
             tc::tc_wait_ld(va);
             tc::tc_wait_ld(vb);
             const int n_valid = min(BN, n_keys - j * BN);  // real keys among this tile's 64 columns
@@ -238,49 +258,48 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const float m_new = move ? m_tile : m_run;
             const float alpha = move ? fast_exp2((m_run - m_new) * scale_log2e) : 1.0f;  // first tile: 0
             const float mc = m_new * scale_log2e;
-            if (j > 0 && __any_sync(kFull, move)) {  // rescale this warp's 32 rows of O (pk is free here)
+            // P = exp2(scale * log2e * (S - max)), two fp16 per 32-bit column: keys 2i, 2i+1 in column i.
+            // The packed words overwrite the scores they came from: va[0..16) and vb[0..16).
+            float2 acc0 = make_float2(0.0f, 0.0f), acc1 = make_float2(0.0f, 0.0f);
+            if (n_valid == BN) {
+                exp_half<false>(va, va, 0, n_valid, scale_log2e, mc, acc0, acc1);
+                exp_half<false>(vb, vb, 32, n_valid, scale_log2e, mc, acc0, acc1);
+            } else {
+                exp_half<true>(va, va, 0, n_valid, scale_log2e, mc, acc0, acc1);
+                exp_half<true>(vb, vb, 32, n_valid, scale_log2e, mc, acc0, acc1);
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) va[16 + i] = vb[i];  // va = the 32 columns of P
+            if (j > 0 && __any_sync(kFull, move)) {  // rescale this warp's 32 rows of O (vb is free here)
                 // O belongs to the tensor core until the previous tile's P V is done. Having seen s_full of tile j,
-                // P V of tile j - 3 (the previous phase of this barrier) is known complete: the parity is unambiguous.
-                ok = __all_sync(kFull, tc::mbar_wait(&ctrl->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag));
+                // P V of tile j - 4 (the previous phase of this barrier) is known complete: the parity is unambiguous.
+                const int pbuf = buf == 0 ? kSBufs - 1 : buf - 1, pbuf_par = buf == 0 ? buf_par ^ 1 : buf_par;  // of tile j - 1
+                ok = tc::mbar_wait_warp(&ctrl->pv_done[pbuf], pbuf_par, abort_flag);
                 if (!ok) break;
                 tc::tc_fence_after();
 #pragma unroll
                 for (int hc = 0; hc < 2; ++hc) {
-                    tc::tmem_ld32(tO + hc * 32, pk);
-                    tc::tc_wait_ld(pk);
+                    tc::tmem_ld32(tO + hc * 32, vb);
+                    tc::tc_wait_ld(vb);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) pk[i] = __float_as_uint(__uint_as_float(pk[i]) * alpha);
-                    tc::tmem_st32(tO + hc * 32, pk);
+                    for (int i = 0; i < 32; ++i) vb[i] = __float_as_uint(__uint_as_float(vb[i]) * alpha);
+                    tc::tmem_st32(tO + hc * 32, vb);
                 }
             }
-            // P = exp2(scale * log2e * (S - max)), two fp16 per 32-bit column: keys 2i, 2i+1 in column i
-            float2 acc0 = make_float2(0.0f, 0.0f), acc1 = make_float2(0.0f, 0.0f);
-            if (n_valid == BN) exp_half<false>(va, pk, 0, n_valid, scale_log2e, mc, acc0, acc1);
-            else exp_half<true>(va, pk, 0, n_valid, scale_log2e, mc, acc0, acc1);
-            if (more) {
-                ok = __all_sync(kFull, tc::mbar_wait(&ctrl->s_full[nbuf], nbuf_par, abort_flag));
-                if (!ok) break;
-                tc::tc_fence_after();
-                tc::tmem_ld32(tS_next, va);
-            }
-            if (n_valid == BN) exp_half<false>(vb, pk + 16, 32, n_valid, scale_log2e, mc, acc0, acc1);
-            else exp_half<true>(vb, pk + 16, 32, n_valid, scale_log2e, mc, acc0, acc1);
-            if (more) tc::tmem_ld32(tS_next + 32, vb);
             l_run = l_run * alpha + ((acc0.x + acc0.y) + (acc1.x + acc1.y));
             m_run = m_new;
-            tc::tmem_st32(tS, pk);    // P over the first 32 columns of this thread's own lane of S
+            tc::tmem_st32(tS, va);    // P over the first 32 columns of this thread's own lane of S
             tc::tc_wait_st();
             tc::tc_fence_before();    // the writes of P and O come before the arrival
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&ctrl->p_full[buf]);
-            buf = nbuf;
-            buf_par = nbuf_par;
+            if (++buf == kSBufs) { buf = 0; buf_par ^= 1; }
         }
-        tc::tc_wait_ld();  // an aborted loop may leave loads in flight
         // ---- epilogue: O / l -> fp16 -> global, one 128-byte row per thread
-        // last but one first: that keeps each wait within one phase of its barrier (see the rescale above)
-        for (int jl = max(n_tiles - 2, 0); ok && jl < n_tiles; ++jl)
-            ok = __all_sync(kFull, tc::mbar_wait(&ctrl->pv_done[jl & 1], (jl >> 1) & 1, abort_flag));
+        if (ok) {  // buf / buf_par have moved on to tile n_tiles: step back to the last tile
+            const int lbuf = buf == 0 ? kSBufs - 1 : buf - 1, lbuf_par = buf == 0 ? buf_par ^ 1 : buf_par;
+            ok = tc::mbar_wait_warp(&ctrl->pv_done[lbuf], lbuf_par, abort_flag);
+        }
         if (ok) {
             tc::tc_fence_after();
             const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;

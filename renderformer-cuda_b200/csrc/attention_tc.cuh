@@ -17,13 +17,16 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_addr(bar)) : "memory");
 }
+// One poll: returns at once if the phase with this parity is complete, otherwise the thread may
+// sleep until it completes or until the suspend-time hint (nanoseconds) runs out.
+constexpr uint32_t kSuspendHintNs = 20000;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity), "r"(kSuspendHintNs) : "memory");
     return ok != 0;
 }
 __device__ __forceinline__ uint64_t global_timer_ns() {
@@ -34,19 +37,26 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // Bounded wait: gives up after kWaitLimitNs of wall time (and in any case after kSpinLimit polls),
 // or as soon as another thread of the CTA has raised *abort.
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000 * 1000;
-constexpr uint32_t kSpinLimit = 1u << 26;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
-    if (mbar_try_wait(bar, parity)) return true;
+constexpr uint32_t kSpinLimit = 1u << 22;
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort) {
     const uint64_t t0 = global_timer_ns();
     for (uint32_t it = 0; it < kSpinLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 15u) == 15u) {
-            if (*abort) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) break;
-        }
+        if (*abort) return false;
+        if (global_timer_ns() - t0 > kWaitLimitNs) break;
     }
     *abort = 1;
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+    if (mbar_try_wait(bar, parity)) return true;  // complete, or completed while this thread slept
+    return mbar_wait_slow(bar, parity, abort);
+}
+// The same for a whole warp: lane 0 polls, the others take its answer.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort);
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 // make generic-proxy writes to shared memory (st.shared, cp.async) visible to the tensor core's async proxy
@@ -118,6 +128,29 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// The same two products with the descriptors given as 32-bit halves (the high half of a 128-byte-swizzle
+// descriptor is a constant, the low half is (address >> 4) | 1 << 16), so that the issuing thread only
+// does one integer add per instruction.
+constexpr uint32_t kDescHiSw128 = (uint32_t)(((64ull << 32) | (1ull << 46) | (2ull << 61)) >> 32);
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t saddr) { return ((saddr >> 4) & 0x3fffu) | (1u << 16); }
+__device__ __forceinline__ void umma_f16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %5};\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128) : "memory");
+}
+__device__ __forceinline__ void umma_f16_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHiSw128) : "memory");
 }
 
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets lane (base lane + t)
