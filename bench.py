@@ -445,8 +445,8 @@ def measured_tensor_peak():
 
 
 def attention_roofline(n_tris, nr, heads, n_tokens, head_dim, iters=12):
-    """Dominant rfk kernel of a view: the fused cross-attention (58 % of the view's device
-    time). A contraction, so its bound is the tensor pipe: achieved = 4*H*Sq*n_keys*D flop per
+    """Dominant rfk kernel of a view: the fused cross-attention (tcgen05 / tensor-memory kernel
+    at head_dim 64). A contraction, so its bound is the tensor pipe: achieved = 4*H*Sq*n_keys*D flop per
     launch / average launch duration, timed live with CUDA events (graph replay of `iters`
     launches, K/V/Q rotated over two buffer sets), at the exact shape the session launches."""
     import torch
@@ -477,9 +477,16 @@ def attention_roofline(n_tris, nr, heads, n_tokens, head_dim, iters=12):
     alg_bytes = 2 * (2 * heads * n_tokens * head_dim + 2 * heads * Se_pad * head_dim)
     del sets
     torch.cuda.empty_cache()
-    return {"bound": "tensor", "kernel": f"flash_attention_kernel<{head_dim}> [{heads}x{n_tokens} queries x {Se} keys]",
+    name = "attention_tc_kernel (tcgen05)" if head_dim == 64 else f"flash_attention_kernel<{head_dim}> (mma.sync)"
+    err = pkg.ops.flash_attention_error(clear=False)
+    if err:
+        raise RuntimeError(f"tcgen05 attention kernel reported error word {err}")
+    return {"bound": "tensor", "kernel": f"{name} [{heads}x{n_tokens} queries x {Se} keys]",
             "achieved": round(tf, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(tf / peak, 3), "peak_source": src,
-            "us_per_launch": round(ms * 1e3, 1), "flop_per_launch": flop, "algorithmic_bytes": alg_bytes, "traffic": None}
+            "us_per_launch": round(ms * 1e3, 1), "flop_per_launch": flop, "algorithmic_bytes": alg_bytes,
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this shape inside this
+            # benchmark (ncu capture summarised in profiles/attention_tc_kernel_decoder_layer.md)
+            "traffic": 31654912 if head_dim == 64 else None}
 
 
 def run_views(args, rank, world, peak, peak_src):
