@@ -42,8 +42,11 @@ __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, vola
     const uint64_t t0 = global_timer_ns();
     for (uint32_t it = 0; it < kSpinLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (*abort) return false;
-        if (global_timer_ns() - t0 > kWaitLimitNs) break;
+        if ((it & 63u) == 63u) {
+            if (*abort) return false;
+            if (global_timer_ns() - t0 > kWaitLimitNs) break;
+        }
+        __nanosleep(32);
     }
     *abort = 1;
     return false;
