@@ -244,6 +244,18 @@ int rfk_flash_attention_set_path(int path);
  * No reference counterpart. */
 int rfk_flash_attention_error(int* code, int clear);
 
+/* Swin window attention core in one kernel: per (window, head) O = softmax(scale * Q K^T [masked]) V.
+ * Q, K, V [BnW, heads, 64, 64] fp16; O [BnW * 64, heads * 64] fp16 (token-major, what the output
+ * projection reads); mask [nW, 64, 64] bytes or NULL, byte 0 = pair masked out (score replaced by
+ * -FLT_MAX before the softmax), window index = bw % nW. window_tokens = 64 and head_dim = 64 only
+ * (RFK_EUNSUPPORTED otherwise: callers then use the GEMM -> rfk_swin_softmax_probs_inplace -> GEMM path).
+ * replaces the batched GEMM -> swin_masked_softmax_inplace | softmax_inplace -> fp32_to_fp16 ->
+ * batched GEMM -> transpose_bhsd_to_bsd sequence of rf::swin_self_attention —
+ * src/layers/attention.cu:542-566 */
+int rfk_window_attention(const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,
+                         const uint8_t* mask, int BnW, int num_heads, int window_tokens, int head_dim,
+                         int nW, float scale, rfk_stream_t stream);
+
 /* -------------------------------------------------------------- activations */
 
 /* out = half(silu(a) * b), out may alias a — replaces rf::fused_silu_mul,

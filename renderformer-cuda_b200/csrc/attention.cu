@@ -277,6 +277,135 @@ static int launch_flash(const __half* Q, const __half* K, const __half* V, __hal
     return launch_status();
 }
 
+// ------------------------------------------------------------------ swin window attention
+// One CTA = one (window, head): 64 queries x 64 keys x head_dim 64, everything in one pass:
+// S = scale Q K^T (mma.sync), optional shifted-window mask, row softmax in registers, P rounded to
+// fp16 after normalisation (what the unfused GEMM -> softmax -> GEMM sequence does), O = P V, and
+// the output written straight into the [windows * 64, heads * 64] token-major layout the output
+// projection reads. Four warps, 16 query rows each; Q, K, V are 8 KB contiguous tiles.
+constexpr int kWinTokens = 64, kWinThreads = 128;
+
+__global__ void __launch_bounds__(kWinThreads)
+window_attention_kernel(const __half* __restrict__ Q, const __half* __restrict__ K, const __half* __restrict__ V,
+                        __half* __restrict__ O, const uint8_t* __restrict__ mask, int heads, int nW, float scale_log2e) {
+    constexpr int HD = 64;
+    __shared__ __align__(128) __half sQ[kWinTokens * HD];
+    __shared__ __align__(128) __half sK[kWinTokens * HD];
+    __shared__ __align__(128) __half sV[kWinTokens * HD];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, tig = lane & 3;
+    const long long bh = blockIdx.x;
+    const int bw = (int)(bh / heads), h = (int)(bh % heads);
+    const __half* Qh = Q + bh * (kWinTokens * HD);
+    const __half* Kh = K + bh * (kWinTokens * HD);
+    const __half* Vh = V + bh * (kWinTokens * HD);
+    for (int i = tid; i < kWinTokens * 8; i += kWinThreads) {
+        const int r = i >> 3, c = i & 7;
+        cp_async16(tile_ptr<HD>(sQ, r, c), Qh + r * HD + c * 8, 16);
+        cp_async16(tile_ptr<HD>(sK, r, c), Kh + r * HD + c * 8, 16);
+        cp_async16(tile_ptr<HD>(sV, r, c), Vh + r * HD + c * 8, 16);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+
+    unsigned qf[4][4];
+    {
+        const int r = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) ldmatrix_x4(qf[ks], tile_ptr<HD>(sQ, r, ks * 2 + (lane >> 4)));
+    }
+    float s[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+            unsigned kb[4];
+            const int key = np * 16 + (lane & 7) + 8 * (lane >> 4);
+            ldmatrix_x4(kb, tile_ptr<HD>(sK, key, ks * 2 + ((lane >> 3) & 1)));
+            mma_16816(s[2 * np], qf[ks], kb[0], kb[1]);
+            mma_16816(s[2 * np + 1], qf[ks], kb[2], kb[3]);
+        }
+    }
+    // scores in the exponent's units; masked-out pairs get -FLT_MAX (a fully masked row ends up uniform)
+    const int q_lo = warp * 16 + g;  // this thread's rows: q_lo (regs 0, 1) and q_lo + 8 (regs 2, 3)
+    const uint8_t* m0 = mask ? mask + ((long long)(bw % nW) * kWinTokens + q_lo) * kWinTokens : nullptr;
+    const uint8_t* m1 = mask ? m0 + 8 * kWinTokens : nullptr;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        const int c = n * 8 + 2 * tig;
+        s[n][0] *= scale_log2e; s[n][1] *= scale_log2e; s[n][2] *= scale_log2e; s[n][3] *= scale_log2e;
+        if (mask) {
+            const unsigned a = *reinterpret_cast<const unsigned short*>(m0 + c);
+            const unsigned b = *reinterpret_cast<const unsigned short*>(m1 + c);
+            if ((a & 0xffu) == 0) s[n][0] = -FLT_MAX;
+            if ((a >> 8) == 0) s[n][1] = -FLT_MAX;
+            if ((b & 0xffu) == 0) s[n][2] = -FLT_MAX;
+            if ((b >> 8) == 0) s[n][3] = -FLT_MAX;
+        }
+        mx[0] = fmaxf(mx[0], fmaxf(s[n][0], s[n][1]));
+        mx[1] = fmaxf(mx[1], fmaxf(s[n][2], s[n][3]));
+    }
+    float rs[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    }
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        s[n][0] = fast_exp2(s[n][0] - mx[0]); s[n][1] = fast_exp2(s[n][1] - mx[0]);
+        s[n][2] = fast_exp2(s[n][2] - mx[1]); s[n][3] = fast_exp2(s[n][3] - mx[1]);
+        rs[0] += s[n][0] + s[n][1];
+        rs[1] += s[n][2] + s[n][3];
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
+        rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
+        rs[r] = 1.0f / rs[r];
+    }
+    unsigned pf[4][4];  // normalised P as A fragments: 4 k-steps of 16 keys
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        pf[n >> 1][(n & 1) * 2 + 0] = pack_half2(s[n][0] * rs[0], s[n][1] * rs[0]);
+        pf[n >> 1][(n & 1) * 2 + 1] = pack_half2(s[n][2] * rs[1], s[n][3] * rs[1]);
+    }
+    float o_acc[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) o_acc[n][0] = o_acc[n][1] = o_acc[n][2] = o_acc[n][3] = 0.0f;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+            unsigned vb[4];
+            const int key = ks * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+            ldmatrix_x4_trans(vb, tile_ptr<HD>(sV, key, np * 2 + (lane >> 4)));
+            mma_16816(o_acc[2 * np], pf[ks], vb[0], vb[1]);
+            mma_16816(o_acc[2 * np + 1], pf[ks], vb[2], vb[3]);
+        }
+    }
+    // stage this warp's 16 output rows over its own rows of sQ (only this warp read them), then 128-bit stores
+    __syncwarp();
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+        const int col = n * 8 + 2 * tig;
+        *reinterpret_cast<unsigned*>(tile_ptr<HD>(sQ, q_lo, col >> 3) + (col & 7)) = pack_half2(o_acc[n][0], o_acc[n][1]);
+        *reinterpret_cast<unsigned*>(tile_ptr<HD>(sQ, q_lo + 8, col >> 3) + (col & 7)) = pack_half2(o_acc[n][2], o_acc[n][3]);
+    }
+    __syncwarp();
+    const long long dim = (long long)heads * HD;
+#pragma unroll
+    for (int i = lane; i < 16 * 8; i += 32) {
+        const int r = warp * 16 + (i >> 3), c = i & 7;
+        *reinterpret_cast<uint4*>(O + ((long long)bw * kWinTokens + r) * dim + h * HD + c * 8) =
+            *reinterpret_cast<const uint4*>(tile_ptr<HD>(sQ, r, c));
+    }
+}
+
 // attention_tc.cu
 extern int g_attn_path;
 int launch_attention_tc(const __half* Q, const __half* K, const __half* V, __half* O, int B, int H, int Sq, int Sk,
@@ -308,4 +437,20 @@ extern "C" int rfk_flash_attention(const rfk_half* Q, const rfk_half* K, const r
         return launch_flash<128>((const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, B, H, Sq, Sk, n_keys, kvs,
                                  o_bshd, scale, st);
     return RFK_EUNSUPPORTED;
+}
+
+extern "C" int rfk_window_attention(const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,
+                                    const uint8_t* mask, int BnW, int num_heads, int window_tokens, int head_dim, int nW,
+                                    float scale, rfk_stream_t stream) {
+    if (!Q || !K || !V || !O || BnW < 0 || num_heads <= 0 || nW <= 0) return RFK_EINVAL;
+    if (window_tokens != kWinTokens || head_dim != 64) return RFK_EUNSUPPORTED;
+    if (BnW == 0) return RFK_OK;
+    if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O)) return RFK_EUNSUPPORTED;
+    if (mask && (reinterpret_cast<uintptr_t>(mask) & 1u)) return RFK_EUNSUPPORTED;
+    const long long ctas = (long long)BnW * num_heads;
+    if (ctas > 0x7fffffffLL) return RFK_EUNSUPPORTED;
+    window_attention_kernel<<<(unsigned)ctas, kWinThreads, 0, as_stream(stream)>>>(
+        (const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, mask, num_heads, nW,
+        scale * 1.4426950408889634f);
+    return launch_status();
 }

@@ -256,15 +256,21 @@ extern "C" int rfk_swin_self_attention(rfk_ctx* ctx, const rfk_mha_weights* w, c
     const int no_rope[3] = {0, 0, 0};
     TRY(project_epilogue(qkv_buf, 3LL * dim, 3, g, o, no_rope, nullptr, nullptr, BnW, ws2, num_heads, hd, 0,
                          window_buf, stream));
-    TRY(blas_status(cublasSetStream(ctx->blas, st)));
     const float scale = 1.0f / sqrtf((float)hd), zero = 0.0f, one = 1.0f;
+    const uint8_t* win_mask = (shift_mask && shift_size > 0) ? shift_mask : nullptr;
+    if (ws2 == 64 && hd == 64) {  // the whole window attention in one kernel, output already token-major
+        TRY(rfk_window_attention(Qt, Kt, Vt, window_buf, win_mask, BnW, num_heads, ws2, hd, nW, scale, stream));
+        TRY(rfk_linear(ctx, window_buf, w->out_proj_w, w->out_proj_b, qkv_buf, M, dim, dim, stream));
+        if (residual_x) return rfk_window_scatter(qkv_buf, residual_x, B, H, W, dim, ws, shift_size, 1, stream);
+        return rfk_window_scatter(qkv_buf, out, B, H, W, dim, ws, shift_size, 0, stream);
+    }
+    TRY(blas_status(cublasSetStream(ctx->blas, st)));
     const long long sQ = (long long)ws2 * hd, sS = (long long)ws2 * ws2;
     TRY(blas_status(cublasGemmStridedBatchedEx(ctx->blas, CUBLAS_OP_T, CUBLAS_OP_N, ws2, ws2, hd, &scale, Kt,
                                                CUDA_R_16F, hd, sQ, Qt, CUDA_R_16F, hd, sQ, &zero, score_buf,
                                                CUDA_R_32F, ws2, sS, BH, CUBLAS_COMPUTE_32F,
                                                CUBLAS_GEMM_DEFAULT)));
-    TRY(rfk_swin_softmax_probs_inplace(score_buf, (shift_mask && shift_size > 0) ? shift_mask : nullptr, BnW,
-                                       num_heads, ws2, nW, stream));
+    TRY(rfk_swin_softmax_probs_inplace(score_buf, win_mask, BnW, num_heads, ws2, nW, stream));
     // O (over Q) = P V ; P pitch is 2*ws2 halves inside the score rows
     TRY(blas_status(cublasGemmStridedBatchedEx(
         ctx->blas, CUBLAS_OP_N, CUBLAS_OP_N, hd, ws2, ws2, &one, Vt, CUDA_R_16F, hd, sQ,

@@ -244,6 +244,11 @@ def flash_attention(q, k, v, o, B, Hh, Sq, Sk, n_keys, D, o_bshd=False, scale=No
           int(o_bshd), float(scale if scale is not None else D ** -0.5), _stream())
 
 
+def window_attention(q, k, v, o, mask, BnW, Hh, nW, window_tokens=64, head_dim=64, scale=None):
+    _call("rfk_window_attention", _p(q, H, "q"), _p(k, H, "k"), _p(v, H, "v"), _p(o, H, "o"), _mask_ptr(mask), BnW, Hh,
+          window_tokens, head_dim, nW, float(scale if scale is not None else head_dim ** -0.5), _stream())
+
+
 def flash_attention_set_path(path):
     """0 automatic, 1 mma.sync kernel, 2 tcgen05 kernel (head_dim 64)."""
     _call("rfk_flash_attention_set_path", int(path))

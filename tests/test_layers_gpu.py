@@ -509,3 +509,31 @@ def test_tcgen05_attention_full_size_matches_mma_sync_kernel(tc_path):
     torch.cuda.synchronize()
     assert torch.isfinite(O.float()).all()
     _close(O, Om, "tcgen05 vs mma.sync attention", atol=4e-3, rtol=4e-3, mean_tol=3e-4)
+
+
+@pytest.mark.parametrize("masked", [False, True])
+def test_window_attention_matches_fp32_attention(masked):
+    """Fused swin window attention (64 tokens x 64 keys per window and head) against torch fp32: plain, and with a
+    byte mask that includes one fully masked row (which must come out as the plain average of V, as filling the
+    scores with -FLT_MAX gives). Tolerance 3e-3 abs + 3e-3 rel: fp16 probabilities and fp16 output."""
+    pkg, _, _ = _mods()
+    BnW, Hh, nW = 12, 3, 4
+    g = torch.Generator(device="cuda").manual_seed(5)
+    Q = torch.randn(BnW, Hh, 64, 64, device="cuda", generator=g).half()
+    K = torch.randn(BnW, Hh, 64, 64, device="cuda", generator=g).half()
+    V = torch.randn(BnW, Hh, 64, 64, device="cuda", generator=g).half()
+    mask = None
+    scores = (Q.float() @ K.float().transpose(-1, -2)) * 0.125
+    if masked:
+        mask = (torch.rand(nW, 64, 64, device="cuda", generator=g) > 0.4).to(torch.uint8)
+        mask[1, 7, :] = 0
+        mfull = mask.repeat(BnW // nW, 1, 1)[:, None].bool()           # window index = bw % nW
+        scores = torch.where(mfull, scores, torch.full_like(scores, -3.0e38))
+    want = (torch.softmax(scores, dim=-1) @ V.float())                  # [BnW, Hh, 64, 64]
+    O = torch.full((BnW * 64, Hh * 64), 7.0, device="cuda", dtype=H16)
+    pkg.ops.window_attention(Q, K, V, O, mask, BnW, Hh, nW)
+    torch.cuda.synchronize()
+    got = O.view(BnW, 64, Hh, 64).permute(0, 2, 1, 3)
+    _close(got, want, "window attention", atol=3e-3, rtol=3e-3, mean_tol=3e-4)
+    if masked:
+        assert torch.allclose(got[1, :, 7].float(), V[1].float().mean(dim=1), atol=3e-3)
