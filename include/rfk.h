@@ -83,6 +83,20 @@ int rfk_rmsnorm_residual_f16(rfk_half* x, const rfk_half* r, const float* gamma,
                              rfk_half* y, int rows, int dim, float eps,
                              rfk_stream_t stream);
 
+/* The same with one operand in swin window order, for the two norms around the window attention of a
+ * decoder layer over a [B, H, W] token grid (window_size x window_size windows of the grid shifted by
+ * -shift_size). windowed_operand = 1: y is written in window order, i.e. residual add + norm + cyclic
+ * shift + window partition in one pass — replaces residual_add -> rmsnorm (src/layers/transformer.cu:
+ * 9-19, 179-182) -> cyclic_shift -> window_partition (src/layers/attention.cu:495-506).
+ * windowed_operand = 2: r is read in window order, i.e. window reverse + shift back + residual add +
+ * norm — replaces window_reverse -> cyclic_shift (src/layers/attention.cu:568-575) -> residual_add ->
+ * rmsnorm. r must not be NULL; y must alias neither x nor r. dim % 8 == 0 and dim <= 2048
+ * (RFK_EUNSUPPORTED otherwise). */
+int rfk_rmsnorm_residual_f16_windows(rfk_half* x, const rfk_half* r, const float* gamma,
+                                     rfk_half* y, int B, int H, int W, int dim, int window_size,
+                                     int shift_size, int windowed_operand, float eps,
+                                     rfk_stream_t stream);
+
 /* ----------------------------------------------- residual / cast plumbing */
 
 /* y = half(float(y) + float(r)) — replaces rf::residual_add, src/layers/transformer.cu:9-19 */

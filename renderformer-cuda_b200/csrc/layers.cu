@@ -234,19 +234,13 @@ extern "C" int rfk_cross_attention_cached(rfk_ctx* ctx, const rfk_cross_attn_wei
     return rfk_linear(ctx, Q, w->out_proj_w, w->out_proj_b, out, Mq, q_dim, dim, stream);
 }
 
-extern "C" int rfk_swin_self_attention(rfk_ctx* ctx, const rfk_mha_weights* w, const rfk_half* x,
-                                       rfk_half* out, rfk_half* residual_x, rfk_half* window_buf,
-                                       rfk_half* qkv_buf, float* score_buf, rfk_half* scratch, int B,
-                                       int H, int W, int dim, int num_heads, int window_size,
-                                       int shift_size, const uint8_t* shift_mask, rfk_stream_t stream) {
-    if (!ctx || !w || !x || (!out && !residual_x) || !window_buf || !qkv_buf || !score_buf || !scratch)
-        return RFK_EINVAL;
-    if (B <= 0 || H <= 0 || W <= 0 || window_size <= 0 || H % window_size || W % window_size) return RFK_EINVAL;
-    if (dim <= 0 || num_heads <= 0 || dim % num_heads) return RFK_EINVAL;
+// Window attention over tokens that are already in window order: window_buf [BnW * ws2, dim] in,
+// qkv_buf [BnW * ws2, dim] out (still in window order); window_buf and scratch are overwritten.
+static int swin_core(rfk_ctx* ctx, const rfk_mha_weights* w, rfk_half* window_buf, rfk_half* qkv_buf,
+                     float* score_buf, rfk_half* scratch, int BnW, int nW, int ws2, int dim, int num_heads,
+                     const uint8_t* win_mask, rfk_stream_t stream) {
     cudaStream_t st = (cudaStream_t)stream;
-    const int ws = window_size, ws2 = ws * ws, nW = (H / ws) * (W / ws), hd = dim / num_heads;
-    const int BnW = B * nW, M = BnW * ws2, BH = BnW * num_heads;
-    TRY(rfk_window_gather(x, window_buf, B, H, W, dim, ws, shift_size, stream));
+    const int hd = dim / num_heads, M = BnW * ws2, BH = BnW * num_heads;
     TRY(rfk_linear(ctx, window_buf, w->in_proj_w, w->in_proj_b, qkv_buf, M, 3 * dim, dim, stream));
     rfk_half* Qt = scratch;
     rfk_half* Kt = scratch + (size_t)M * dim;
@@ -257,13 +251,11 @@ extern "C" int rfk_swin_self_attention(rfk_ctx* ctx, const rfk_mha_weights* w, c
     TRY(project_epilogue(qkv_buf, 3LL * dim, 3, g, o, no_rope, nullptr, nullptr, BnW, ws2, num_heads, hd, 0,
                          window_buf, stream));
     const float scale = 1.0f / sqrtf((float)hd), zero = 0.0f, one = 1.0f;
-    const uint8_t* win_mask = (shift_mask && shift_size > 0) ? shift_mask : nullptr;
     if (ws2 == 64 && hd == 64) {  // the whole window attention in one kernel, output already token-major
         TRY(rfk_window_attention(Qt, Kt, Vt, window_buf, win_mask, BnW, num_heads, ws2, hd, nW, scale, stream));
-        TRY(rfk_linear(ctx, window_buf, w->out_proj_w, w->out_proj_b, qkv_buf, M, dim, dim, stream));
-        if (residual_x) return rfk_window_scatter(qkv_buf, residual_x, B, H, W, dim, ws, shift_size, 1, stream);
-        return rfk_window_scatter(qkv_buf, out, B, H, W, dim, ws, shift_size, 0, stream);
+        return rfk_linear(ctx, window_buf, w->out_proj_w, w->out_proj_b, qkv_buf, M, dim, dim, stream);
     }
+    if (!score_buf) return RFK_EINVAL;
     TRY(blas_status(cublasSetStream(ctx->blas, st)));
     const long long sQ = (long long)ws2 * hd, sS = (long long)ws2 * ws2;
     TRY(blas_status(cublasGemmStridedBatchedEx(ctx->blas, CUBLAS_OP_T, CUBLAS_OP_N, ws2, ws2, hd, &scale, Kt,
@@ -277,7 +269,22 @@ extern "C" int rfk_swin_self_attention(rfk_ctx* ctx, const rfk_mha_weights* w, c
         reinterpret_cast<const __half*>(score_buf), CUDA_R_16F, 2 * ws2, 2 * sS, &zero, Qt, CUDA_R_16F, hd,
         sQ, BH, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT)));
     TRY(rfk_transpose_bhsd_to_bsd(Qt, window_buf, BnW, num_heads, ws2, hd, stream));
-    TRY(rfk_linear(ctx, window_buf, w->out_proj_w, w->out_proj_b, qkv_buf, M, dim, dim, stream));
+    return rfk_linear(ctx, window_buf, w->out_proj_w, w->out_proj_b, qkv_buf, M, dim, dim, stream);
+}
+
+extern "C" int rfk_swin_self_attention(rfk_ctx* ctx, const rfk_mha_weights* w, const rfk_half* x,
+                                       rfk_half* out, rfk_half* residual_x, rfk_half* window_buf,
+                                       rfk_half* qkv_buf, float* score_buf, rfk_half* scratch, int B,
+                                       int H, int W, int dim, int num_heads, int window_size,
+                                       int shift_size, const uint8_t* shift_mask, rfk_stream_t stream) {
+    if (!ctx || !w || !x || (!out && !residual_x) || !window_buf || !qkv_buf || !score_buf || !scratch)
+        return RFK_EINVAL;
+    if (B <= 0 || H <= 0 || W <= 0 || window_size <= 0 || H % window_size || W % window_size) return RFK_EINVAL;
+    if (dim <= 0 || num_heads <= 0 || dim % num_heads) return RFK_EINVAL;
+    const int ws = window_size, ws2 = ws * ws, nW = (H / ws) * (W / ws);
+    TRY(rfk_window_gather(x, window_buf, B, H, W, dim, ws, shift_size, stream));
+    TRY(swin_core(ctx, w, window_buf, qkv_buf, score_buf, scratch, B * nW, nW, ws2, dim, num_heads,
+                  (shift_mask && shift_size > 0) ? shift_mask : nullptr, stream));
     if (residual_x) return rfk_window_scatter(qkv_buf, residual_x, B, H, W, dim, ws, shift_size, 1, stream);
     return rfk_window_scatter(qkv_buf, out, B, H, W, dim, ws, shift_size, 0, stream);
 }
@@ -320,13 +327,30 @@ extern "C" int rfk_decoder_layer_forward_cached(
     TRY(rfk_cross_attention_cached(ctx, &w->cross_attn, temp, cross_out, proj_buf, cross_score_buf, K_cached,
                                    V_cached, B, Sq, Sk, n_keys, dim, dim, num_heads, q_rope_cos, q_rope_sin,
                                    k_rope_cos, k_rope_sin, stream));
-    // 2) residual + pre-norm in one kernel -> swin attention, whose window scatter adds into x
-    TRY(rfk_rmsnorm_residual_f16(x, cross_out, w->self_attn_norm_gamma, temp, Mq, dim, kEpsFp16, stream));
-    TRY(rfk_swin_self_attention(ctx, &w->self_attn, temp, nullptr, x, window_buf, qkv_buf, self_score_buf,
-                                proj_buf, B, patch_h, patch_w, dim, num_heads, window_size, shift_size,
-                                shift_mask, stream));
-    // 3) pre-norm -> FFN; its residual is left to the next layer's first kernel when asked
-    TRY(rfk_rmsnorm(x, w->ffn_norm_gamma, temp, Mq, dim, kEpsFp16, stream));
+    // 2) residual + pre-norm -> swin attention -> residual + pre-norm of the FFN. When the fused norm can take an
+    //    operand in window order, the cyclic shift / window partition and their inverse cost no launch: the first norm
+    //    writes the windows, the second reads the attention output out of them.
+    const bool win_ok = window_size > 0 && patch_h % window_size == 0 && patch_w % window_size == 0 &&
+                        num_heads > 0 && dim % num_heads == 0 && dim % 8 == 0 && dim <= 2048;
+    int rc = win_ok ? rfk_rmsnorm_residual_f16_windows(x, cross_out, w->self_attn_norm_gamma, window_buf, B, patch_h,
+                                                       patch_w, dim, window_size, shift_size, 1, kEpsFp16, stream)
+                    : RFK_EUNSUPPORTED;
+    if (rc == RFK_OK) {
+        const int ws2 = window_size * window_size, nW = (patch_h / window_size) * (patch_w / window_size);
+        TRY(swin_core(ctx, &w->self_attn, window_buf, qkv_buf, self_score_buf, proj_buf, B * nW, nW, ws2, dim, num_heads,
+                      (shift_mask && shift_size > 0) ? shift_mask : nullptr, stream));
+        TRY(rfk_rmsnorm_residual_f16_windows(x, qkv_buf, w->ffn_norm_gamma, temp, B, patch_h, patch_w, dim, window_size,
+                                             shift_size, 2, kEpsFp16, stream));
+    } else if (rc == RFK_EUNSUPPORTED) {
+        TRY(rfk_rmsnorm_residual_f16(x, cross_out, w->self_attn_norm_gamma, temp, Mq, dim, kEpsFp16, stream));
+        TRY(rfk_swin_self_attention(ctx, &w->self_attn, temp, nullptr, x, window_buf, qkv_buf, self_score_buf,
+                                    proj_buf, B, patch_h, patch_w, dim, num_heads, window_size, shift_size,
+                                    shift_mask, stream));
+        TRY(rfk_rmsnorm(x, w->ffn_norm_gamma, temp, Mq, dim, kEpsFp16, stream));
+    } else {
+        return rc;
+    }
+    // 3) FFN; its residual is left to the next layer's first kernel when asked
     TRY(rfk_ffn_swiglu(ctx, &w->ffn, temp, ffn_buf, qkv_buf, Mq, dim, ffn_hidden, stream));
     if (pending_out) { *pending_out = ffn_buf; return RFK_OK; }
     return rfk_residual_add(x, ffn_buf, (long long)Mq * dim, stream);

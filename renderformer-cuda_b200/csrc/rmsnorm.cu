@@ -28,13 +28,30 @@ template <> struct IsHalf<__half> { static constexpr bool value = true; };
 
 constexpr int kRmsThreads = 128;
 
+// Token (b, h, w) of a [B, H, W] grid -> its row in swin window order (windows of ws x ws over the
+// grid shifted by -shift, as the reference's cyclic shift + window_partition produce).
+struct WinRows {
+    int H, W, ws, shift;
+    __device__ __forceinline__ long long operator()(long long token) const {
+        const int w = (int)(token % W);
+        const long long t = token / W;
+        const int h = (int)(t % H);
+        const long long b = t / H;
+        const int hs = (h + shift) % H, wsft = (w + shift) % W;  // position in the shifted grid
+        const int nWw = W / ws, nW = (H / ws) * nWw;
+        const int win = (hs / ws) * nWw + wsft / ws, local = (hs % ws) * ws + wsft % ws;
+        return (b * nW + win) * (long long)(ws * ws) + local;
+    }
+};
+
 // TH: hidden-state storage, TR: residual storage, TY: normalised output storage.
+// MAP: 0 all operands in token order; 1 y is written in window order; 2 r is read in window order.
 // W: warps per row (1, 2 or 4); NCH: 8-element chunks per lane (dim <= NCH * W * 256).
-template <typename TH, typename TR, typename TY, int NCH, int W, bool HAS_RES, bool WRITE_H>
+template <typename TH, typename TR, typename TY, int NCH, int W, bool HAS_RES, bool WRITE_H, int MAP = 0>
 __global__ void __launch_bounds__(kRmsThreads)
 rmsnorm_row_kernel(const TH* x, TH* xw, const TR* __restrict__ r,
                    const float* __restrict__ gamma, TY* y,  // x, xw, y may alias
-                   int rows, int dim, float eps) {
+                   int rows, int dim, float eps, WinRows wr = WinRows{}) {
     constexpr int kWarps = kRmsThreads / 32;
     constexpr int kRowsPerCta = kWarps / W;
     __shared__ float s_part[kWarps];
@@ -45,6 +62,8 @@ rmsnorm_row_kernel(const TH* x, TH* xw, const TR* __restrict__ r,
     const bool live = row < rows;
     if (!live) row = rows - 1;  // idle warps shadow the last row and never store
     const size_t base = (size_t)row * dim;
+    const size_t rbase = MAP == 2 ? (size_t)wr(row) * dim : base;
+    const size_t ybase = MAP == 1 ? (size_t)wr(row) * dim : base;
 
     float v[NCH][8];
 #pragma unroll
@@ -58,7 +77,7 @@ rmsnorm_row_kernel(const TH* x, TH* xw, const TR* __restrict__ r,
             const int off = (wir * 32 + lane + k * W * 32) * 8;
             if (off < dim) {
                 float rr[8];
-                load8(r + base + off, rr);
+                load8(r + rbase + off, rr);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     float s = v[k][i] + rr[i];
@@ -96,7 +115,7 @@ rmsnorm_row_kernel(const TH* x, TH* xw, const TR* __restrict__ r,
             ldg_float8(gamma + off, g);
 #pragma unroll
             for (int i = 0; i < 8; ++i) o[i] = (v[k][i] * rinv) * g[i];
-            store8(y + base + off, o);
+            store8(y + ybase + off, o);
         }
     }
 }
@@ -196,6 +215,38 @@ extern "C" int rfk_rmsnorm_residual_mixed_cast16(float* h, const rfk_half* r, co
                                                  rfk_stream_t stream) {
     return launch_rmsnorm<float, __half, __half>(h, h, (const __half*)r, gamma, (__half*)y16, rows,
                                                  dim, eps, as_stream(stream));
+}
+
+extern "C" int rfk_rmsnorm_residual_f16_windows(rfk_half* x, const rfk_half* r, const float* gamma,
+                                                rfk_half* y, int B, int H, int W, int dim,
+                                                int window_size, int shift_size, int windowed_operand,
+                                                float eps, rfk_stream_t stream) {
+    if (!x || !r || !gamma || !y || B < 0 || H <= 0 || W <= 0 || dim <= 0) return RFK_EINVAL;
+    if (window_size <= 0 || H % window_size || W % window_size || shift_size < 0) return RFK_EINVAL;
+    if (windowed_operand != 1 && windowed_operand != 2) return RFK_EINVAL;
+    if ((const void*)x == (const void*)y || (const void*)r == (const void*)y) return RFK_EINVAL;
+    if (dim % 8 != 0 || dim > 2048 || !aligned16(x) || !aligned16(y) || !aligned16(gamma) || !aligned16(r))
+        return RFK_EUNSUPPORTED;
+    const long long rows_ll = (long long)B * H * W;
+    if (rows_ll > 0x7fffffffLL) return RFK_EUNSUPPORTED;
+    const int rows = (int)rows_ll;
+    if (rows == 0) return RFK_OK;
+    const WinRows wr{H, W, window_size, shift_size};
+    cudaStream_t st = as_stream(stream);
+    __half* xh = (__half*)x;
+#define RFK_RMS_WIN(N, WW, M)                                                                               \
+    rmsnorm_row_kernel<__half, __half, __half, N, WW, true, true, M>                                        \
+        <<<ceil_div(rows, (kRmsThreads / 32) / WW), kRmsThreads, 0, st>>>(xh, xh, (const __half*)r, gamma,   \
+                                                                           (__half*)y, rows, dim, eps, wr)
+#define RFK_RMS_WIN_DIM(M)                          \
+    if (dim <= 256) RFK_RMS_WIN(1, 1, M);           \
+    else if (dim <= 512) RFK_RMS_WIN(1, 2, M);      \
+    else if (dim <= 1024) RFK_RMS_WIN(1, 4, M);     \
+    else RFK_RMS_WIN(2, 4, M)
+    if (windowed_operand == 1) { RFK_RMS_WIN_DIM(1); } else { RFK_RMS_WIN_DIM(2); }
+#undef RFK_RMS_WIN_DIM
+#undef RFK_RMS_WIN
+    return launch_status();
 }
 
 extern "C" int rfk_rmsnorm_residual_f16(rfk_half* x, const rfk_half* r, const float* gamma,

@@ -92,6 +92,12 @@ def rmsnorm_residual_mixed_cast16(h, r, gamma, y16, rows, dim, eps):
           _p(y16, H, "y16"), rows, dim, eps, _stream())
 
 
+def rmsnorm_residual_f16_windows(x, r, gamma, y, B, Hh, W, dim, ws, shift, windowed_operand, eps=K_EPS_FP16):
+    """windowed_operand 1: y written in swin window order; 2: r read in window order."""
+    _call("rfk_rmsnorm_residual_f16_windows", _p(x, H, "x"), _p(r, H, "r"), _p(gamma, F, "gamma"), _p(y, H, "y"),
+          B, Hh, W, dim, ws, shift, windowed_operand, eps, _stream())
+
+
 def rmsnorm_residual_f16(x, r, gamma, y, rows, dim, eps=K_EPS_FP16):
     _call("rfk_rmsnorm_residual_f16", _p(x, H, "x"), _p(r, H, "r"), _p(gamma, F, "gamma"),
           _p(y, H, "y"), rows, dim, eps, _stream())

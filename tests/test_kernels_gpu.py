@@ -88,3 +88,34 @@ def test_kernels_run_on_a_side_stream_and_in_a_graph():
     torch.cuda.synchronize()
     assert torch.equal(y, want)
     assert torch.isfinite(pe_out.float()).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,Hh,W,dim,ws,shift", [(1, 16, 16, 256, 8, 0), (1, 16, 16, 256, 8, 4), (2, 8, 24, 1024, 4, 3),
+                                                 (1, 64, 64, 1024, 8, 4), (1, 8, 8, 2048, 8, 1)])
+def test_rmsnorm_residual_with_window_ordered_operand_equals_the_separate_kernels(B, Hh, W, dim, ws, shift):
+    """The fused norm that writes its output in swin window order (or reads its residual out of it) is bit-identical
+    to residual+norm followed by window_gather, and to window_scatter(+residual) followed by the norm."""
+    import torch
+    import renderformer_cuda_b200 as pkg
+    ops = pkg.ops
+    rows = B * Hh * W
+    g = torch.Generator(device="cuda").manual_seed(rows + dim + shift)
+    x0 = torch.randn(rows, dim, device="cuda", generator=g).half()
+    r = torch.randn(rows, dim, device="cuda", generator=g).half()
+    gamma = torch.rand(dim, device="cuda", generator=g) + 0.5
+    # (1) y in window order
+    xa, xb = x0.clone(), x0.clone()
+    ya, tmp, yb = torch.empty_like(x0), torch.empty_like(x0), torch.empty_like(x0)
+    ops.rmsnorm_residual_f16(xa, r, gamma, tmp, rows, dim)
+    ops.window_gather(tmp, ya, B, Hh, W, dim, ws, shift)
+    ops.rmsnorm_residual_f16_windows(xb, r, gamma, yb, B, Hh, W, dim, ws, shift, 1)
+    torch.cuda.synchronize()
+    assert torch.equal(xa, xb) and torch.equal(ya, yb)
+    # (2) r in window order
+    xa, xb = x0.clone(), x0.clone()
+    ops.window_scatter(r, xa, B, Hh, W, dim, ws, shift, residual_into=True)
+    ops.rmsnorm(xa, gamma, ya, rows, dim)
+    ops.rmsnorm_residual_f16_windows(xb, r, gamma, yb, B, Hh, W, dim, ws, shift, 2)
+    torch.cuda.synchronize()
+    assert torch.equal(xa, xb) and torch.equal(ya, yb)
