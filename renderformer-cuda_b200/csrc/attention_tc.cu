@@ -87,23 +87,42 @@ __device__ __forceinline__ float2 exp2_poly(float2 x) {
 // Packed fp32x2 multiply-adds and adds halve the instruction count around the exponentials. The
 // special-function unit (16 exponentials per clock and SM) is the scarcest resource of this kernel,
 // so of every four pairs, those selected by kPolyMask take the polynomial path instead.
-constexpr int kPolyMask = 0x0;
+constexpr int kPolyMask = 0x1;
 template <bool MASKED>
-__device__ __forceinline__ void exp_half(const uint32_t (&v)[32], uint32_t* pk /* may alias v */, int col0, int n_valid, float c,
+__device__ __forceinline__ void exp_half(uint32_t (&v)[32], uint32_t* pk /* may alias v */, int col0, int n_valid, float c,
                                          float mc, float2& acc0, float2& acc1) {
     const float2 c2 = make_float2(c, c), nm2 = make_float2(-mc, -mc);
+    // three passes over the registers, each a run of independent instructions: exponents, exponentials
+    // (back to back, so that one warp alone can keep the special-function unit busy), then sums and packing
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+        const float2 x = __ffma2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), c2, nm2);
+        v[i] = __float_as_uint(x.x);
+        v[i + 1] = __float_as_uint(x.y);
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        if ((kPolyMask >> ((i >> 1) & 3)) & 1) continue;  // this pair takes the polynomial path below
+        float p = fast_exp2(__uint_as_float(v[i]));
+        if (MASKED && col0 + i >= n_valid) p = 0.0f;  // last tile: keys at or beyond n_keys contribute nothing
+        v[i] = __float_as_uint(p);
+    }
+    if (kPolyMask) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            if ((kPolyMask >> ((i >> 1) & 3)) & 1) {
+                float2 p = exp2_poly(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
+                if (MASKED && col0 + i >= n_valid) p.x = 0.0f;
+                if (MASKED && col0 + i + 1 >= n_valid) p.y = 0.0f;
+                v[i] = __float_as_uint(p.x);
+                v[i + 1] = __float_as_uint(p.y);
+            }
+        }
+    }
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
-        const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), c2, nm2);
-        const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])), c2, nm2);
-        float2 p0 = ((kPolyMask >> ((i >> 1) & 3)) & 1) ? exp2_poly(x0) : make_float2(fast_exp2(x0.x), fast_exp2(x0.y));
-        float2 p1 = ((kPolyMask >> (((i >> 1) + 1) & 3)) & 1) ? exp2_poly(x1) : make_float2(fast_exp2(x1.x), fast_exp2(x1.y));
-        if (MASKED) {  // last tile: keys at or beyond n_keys contribute nothing
-            if (col0 + i >= n_valid) p0.x = 0.0f;
-            if (col0 + i + 1 >= n_valid) p0.y = 0.0f;
-            if (col0 + i + 2 >= n_valid) p1.x = 0.0f;
-            if (col0 + i + 3 >= n_valid) p1.y = 0.0f;
-        }
+        const float2 p0 = make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+        const float2 p1 = make_float2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
         acc0 = __fadd2_rn(acc0, p0);
         acc1 = __fadd2_rn(acc1, p1);
         pk[i >> 1] = pack_half2(p0.x, p0.y);
@@ -256,8 +275,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             // the probabilities of this row are scaled by up to 2^threshold, which cancels in O / l.
             const bool move = (m_tile - m_run) * scale_log2e > kRescaleThreshold;  // first tile: m_run = -inf
             const float m_new = move ? m_tile : m_run;
-            const float alpha = move ? fast_exp2((m_run - m_new) * scale_log2e) : 1.0f;  // first tile: 0
             const float mc = m_new * scale_log2e;
+            const bool any_move = __any_sync(kFull, move);  // rare after the first tiles: keeps alpha off the common path
+            float alpha = 1.0f;
+            if (any_move && move) alpha = fast_exp2((m_run - m_new) * scale_log2e);  // first tile: 0
             // P = exp2(scale * log2e * (S - max)), two fp16 per 32-bit column: keys 2i, 2i+1 in column i.
             // The packed words overwrite the scores they came from: va[0..16) and vb[0..16).
             float2 acc0 = make_float2(0.0f, 0.0f), acc1 = make_float2(0.0f, 0.0f);
@@ -270,7 +291,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
 #pragma unroll
             for (int i = 0; i < 16; ++i) va[16 + i] = vb[i];  // va = the 32 columns of P
-            if (j > 0 && __any_sync(kFull, move)) {  // rescale this warp's 32 rows of O (vb is free here)
+            if (j > 0 && any_move) {  // rescale this warp's 32 rows of O (vb is free here)
                 // O belongs to the tensor core until the previous tile's P V is done. Having seen s_full of tile j,
                 // P V of tile j - 4 (the previous phase of this barrier) is known complete: the parity is unambiguous.
                 const int pbuf = buf == 0 ? kSBufs - 1 : buf - 1, pbuf_par = buf == 0 ? buf_par ^ 1 : buf_par;  // of tile j - 1
@@ -286,7 +307,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     tc::tmem_st32(tO + hc * 32, vb);
                 }
             }
-            l_run = l_run * alpha + ((acc0.x + acc0.y) + (acc1.x + acc1.y));
+            l_run = (any_move ? l_run * alpha : l_run) + ((acc0.x + acc0.y) + (acc1.x + acc1.y));
             m_run = m_new;
             tc::tmem_st32(tS, va);    // P over the first 32 columns of this thread's own lane of S
             tc::tc_wait_st();
