@@ -133,7 +133,10 @@ int rfk_precompute_cross_kv(rfk_ctx* ctx, const rfk_cross_attn_weights* w,
                             int num_heads, rfk_stream_t stream);
 
 /* Cross-attention of q_in [B*Sq, q_dim] against cached K/V [B,H,Sk,D] (Sk a multiple of 8).
- * proj_buf: (2*B*Sq*dim + B*H*Sk*D) halves; score_buf: B*H*Sq*Sk floats.
+ * proj_buf: (2*B*Sq*dim + B*H*Sk*D) halves; score_buf: B*H*Sq*Sk floats, or NULL when the head
+ * size is 64 or 128 (rfk_flash_attention then serves the attention and no score matrix exists;
+ * with NULL any other head size returns RFK_EINVAL). The same holds for every score buffer below;
+ * the swin score buffer may be NULL for 64-token windows of 64-wide heads.
  * Fusions: Q-RMSNorm + transpose + RoPE in one kernel; cached-K copy + RoPE in one kernel;
  * softmax writes fp16 in place; the PV GEMM writes [B,Sq,dim] directly.
  * replaces rf::cross_attention_cached — src/layers/attention.h:70-82, attention.cu:326-373 */

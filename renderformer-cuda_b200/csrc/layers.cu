@@ -150,6 +150,7 @@ static int attention_core(rfk_ctx* ctx, const rfk_half* Q, const rfk_half* K, co
                           rfk_stream_t stream) {
     int rc = rfk_flash_attention(Q, K, V, O, B, H, Sq, Sk, n_keys, D, o_bshd, 1.0f / sqrtf((float)D), stream);
     if (rc != RFK_EUNSUPPORTED) return rc;
+    if (!score_buf) return RFK_EINVAL;  // the materialised path needs its score matrix
     return rfk_sdpa(ctx, Q, K, V, O, score_buf, nullptr, B, H, Sq, Sk, n_keys, D, o_bshd, stream);
 }
 
@@ -213,7 +214,7 @@ extern "C" int rfk_cross_attention_cached(rfk_ctx* ctx, const rfk_cross_attn_wei
                                           const rfk_half* q_rope_cos, const rfk_half* q_rope_sin,
                                           const rfk_half* k_rope_cos, const rfk_half* k_rope_sin,
                                           rfk_stream_t stream) {
-    if (!ctx || !w || !q_in || !out || !proj_buf || !score_buf || !K_cached || !V_cached) return RFK_EINVAL;
+    if (!ctx || !w || !q_in || !out || !proj_buf || !K_cached || !V_cached) return RFK_EINVAL;
     if (B <= 0 || Sq <= 0 || Sk <= 0 || dim <= 0 || num_heads <= 0 || dim % num_heads) return RFK_EINVAL;
     const int Mq = B * Sq, hd = dim / num_heads;
     rfk_half* Q = proj_buf;                          // [Mq, dim] projection, later the attention output
@@ -277,7 +278,7 @@ extern "C" int rfk_swin_self_attention(rfk_ctx* ctx, const rfk_mha_weights* w, c
                                        rfk_half* qkv_buf, float* score_buf, rfk_half* scratch, int B,
                                        int H, int W, int dim, int num_heads, int window_size,
                                        int shift_size, const uint8_t* shift_mask, rfk_stream_t stream) {
-    if (!ctx || !w || !x || (!out && !residual_x) || !window_buf || !qkv_buf || !score_buf || !scratch)
+    if (!ctx || !w || !x || (!out && !residual_x) || !window_buf || !qkv_buf || !scratch)
         return RFK_EINVAL;
     if (B <= 0 || H <= 0 || W <= 0 || window_size <= 0 || H % window_size || W % window_size) return RFK_EINVAL;
     if (dim <= 0 || num_heads <= 0 || dim % num_heads) return RFK_EINVAL;
@@ -293,7 +294,7 @@ extern "C" int rfk_self_attention(rfk_ctx* ctx, const rfk_mha_weights* w, const 
                                   rfk_half* out, rfk_half* qkv_buf, float* score_buf, int B, int S,
                                   int dim, int num_heads, const rfk_half* rope_cos,
                                   const rfk_half* rope_sin, rfk_stream_t stream) {
-    if (!ctx || !w || !x || !out || !qkv_buf || !score_buf) return RFK_EINVAL;
+    if (!ctx || !w || !x || !out || !qkv_buf) return RFK_EINVAL;
     if (B <= 0 || S <= 0 || dim <= 0 || num_heads <= 0 || dim % num_heads) return RFK_EINVAL;
     const int M = B * S, hd = dim / num_heads;
     TRY(rfk_linear(ctx, x, w->in_proj_w, w->in_proj_b, qkv_buf, M, 3 * dim, dim, stream));
@@ -361,7 +362,7 @@ extern "C" int rfk_encoder_layer_forward_mixed(
     const rfk_half** pending_out, rfk_half* temp, rfk_half* qkv_buf, rfk_half* ffn_buf, float* score_buf,
     int B, int S, int dim, int num_heads, int ffn_hidden, const rfk_half* rope_cos, const rfk_half* rope_sin,
     rfk_stream_t stream) {
-    if (!ctx || !w || !x || !temp || !qkv_buf || !ffn_buf || !score_buf) return RFK_EINVAL;
+    if (!ctx || !w || !x || !temp || !qkv_buf || !ffn_buf) return RFK_EINVAL;
     const int M = B * S;
     // fp32 hidden (+= fp16 sub-layer output) -> fp32 norm -> fp16, one kernel instead of three
     TRY(rfk_rmsnorm_residual_mixed_cast16(x, pending_residual, w->query_norm_gamma, temp, M, dim, kEpsFp32, stream));

@@ -106,7 +106,7 @@ struct rfk_session {
     rfk_model m{};
     int N = 0, res = 0, Se = 0, Se_pad = 0, pH = 0, pW = 0, nP = 0, hd = 0, flags = 0;
     rfk_ctx* ctx = nullptr;
-    cudaStream_t stream = nullptr, copy_stream = nullptr;
+    cudaStream_t stream = nullptr, copy_stream = nullptr, side_stream = nullptr;
     StateLayout L{};
     char* state = nullptr;  // caller-owned scene state
     std::vector<void*> owned;  // device allocations of this session
@@ -117,7 +117,9 @@ struct rfk_session {
     rfk_half *vtri = nullptr, *vvn = nullptr, *vpos = nullptr, *k_cos = nullptr, *k_sin = nullptr;
     rfk_half *ray_pat = nullptr, *rtok = nullptr;
     rfk_half *temp = nullptr, *proj = nullptr, *qkv = nullptr, *ffn = nullptr, *win = nullptr;
-    float *score = nullptr, *self_score = nullptr;
+    float *score = nullptr, *self_score = nullptr;  // only allocated when a materialised attention path can be taken
+    rfk_half* k_rot = nullptr;  // [dec_layers][heads][Se_pad][hd]: this view's rotated keys of every layer
+    cudaEvent_t ev_fork = nullptr, ev_rot[RFK_MAX_LAYERS]{};
     uint8_t* shift_mask = nullptr;
     rfk_half* dft[4] = {nullptr, nullptr, nullptr, nullptr};
     rfk_half* result[kSlots] = {nullptr, nullptr};
@@ -134,6 +136,7 @@ struct rfk_session {
     bool finalized = false;
 
     rfk_half* kvK(int layer) const { return (rfk_half*)(state + L.kv_off + (size_t)(2 * layer) * L.kv_layer_bytes); }
+    rfk_half* kRot(int layer) const { return k_rot + (size_t)layer * m.num_heads * Se_pad * hd; }
     rfk_half* kvV(int layer) const { return (rfk_half*)(state + L.kv_off + (size_t)(2 * layer + 1) * L.kv_layer_bytes); }
     rfk_half* tri16() const { return (rfk_half*)(state + L.tri_off); }
     rfk_half* vn16() const { return (rfk_half*)(state + L.vn_off); }
@@ -159,6 +162,17 @@ int rfk_session::render_view(const float* pinned_cam, rfk_half* result_out) {
     // world -> camera of triangles and normals, register-token positions, K RoPE tables
     TRY(rfk_view_geometry(cam_gpu, tri16(), vn16(), center(), m.vt_rope_freqs, vtri, vvn, vpos, k_cos, k_sin, N, nr,
                           Se_pad, m.rope_num_freqs, hd, s));
+    // The rotation of the cached keys by this view's tables is the same for every query and independent of the
+    // layers' data flow, so all layers' keys are rotated on a second stream (a parallel branch of the graph) while
+    // the front end and the first layers run; layer i waits for its own buffer only. These launches are bound by
+    // memory bandwidth, the kernels they overlap with are not.
+    TRY_CUDA(cudaEventRecord(ev_fork, stream));
+    TRY_CUDA(cudaStreamWaitEvent(side_stream, ev_fork, 0));
+    for (int i = 0; i < m.dec_layers; ++i) {
+        TRY(rfk_rope_one_oop(kvK(i), kRot(i), k_cos, k_sin, 1, m.num_heads, Se_pad, hd, Se_pad, Se_pad, 0,
+                             (rfk_stream_t)side_stream));
+        TRY_CUDA(cudaEventRecord(ev_rot[i], side_stream));
+    }
     // camera-space rays (identity pose, as the reference does) written straight as patch tokens
     TRY(rfk_ray_gen_patchify(id_c2w, cam_gpu + 16, nullptr, ray_pat, 1, res, ps, s));
     TRY(rfk_linear(ctx, ray_pat, m.ray_enc_w, m.ray_enc_b, rtok, nP, dim, 3 * ps * ps, s));
@@ -175,10 +189,11 @@ int rfk_session::render_view(const float* pinned_cam, rfk_half* result_out) {
         const rfk_half* next_pending = nullptr;
         // a tapped (or the last) layer finishes x itself; the others leave their FFN residual
         // to the first kernel of the next layer
+        TRY_CUDA(cudaStreamWaitEvent(stream, ev_rot[i], 0));
         TRY(rfk_decoder_layer_forward_cached(ctx, &m.dec[i], rtok, pending, (tap || last) ? nullptr : &next_pending,
-                                             temp, proj, qkv, ffn, win, score, self_score, kvK(i), kvV(i), 1, nP,
+                                             temp, proj, qkv, ffn, win, score, self_score, kRot(i), kvV(i), 1, nP,
                                              Se_pad, n_keys, dim, m.num_heads, m.ffn_hidden, pH, pW, m.window_size,
-                                             shift, shift > 0 ? shift_mask : nullptr, nullptr, nullptr, k_cos, k_sin, s));
+                                             shift, shift > 0 ? shift_mask : nullptr, nullptr, nullptr, nullptr, nullptr, s));
         pending = next_pending;
         if (tap)
             TRY_CUDA(cudaMemcpyAsync(dft[(i + 1) / L4 - 1], rtok, (size_t)nP * dim * sizeof(rfk_half),
@@ -227,6 +242,10 @@ extern "C" int rfk_session_create(const rfk_model* model, int n_tris, int img_re
     if (rc) return fail(rc);
     if (cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking) != cudaSuccess) return fail((int)cudaGetLastError());
     if (cudaStreamCreateWithFlags(&d->copy_stream, cudaStreamNonBlocking) != cudaSuccess) return fail((int)cudaGetLastError());
+    if (cudaStreamCreateWithFlags(&d->side_stream, cudaStreamNonBlocking) != cudaSuccess) return fail((int)cudaGetLastError());
+    if (cudaEventCreateWithFlags(&d->ev_fork, cudaEventDisableTiming) != cudaSuccess) return fail((int)cudaGetLastError());
+    for (int i = 0; i < model->dec_layers; ++i)
+        if (cudaEventCreateWithFlags(&d->ev_rot[i], cudaEventDisableTiming) != cudaSuccess) return fail((int)cudaGetLastError());
     for (int k = 0; k < kSlots; ++k) {
         if (cudaEventCreate(&d->ev_start[k]) != cudaSuccess || cudaEventCreate(&d->ev_done[k]) != cudaSuccess ||
             cudaEventCreateWithFlags(&d->ev_dl[k], cudaEventDisableTiming) != cudaSuccess)
@@ -250,8 +269,10 @@ extern "C" int rfk_session_create(const rfk_model* model, int n_tris, int img_re
     ALLOC(qkv, (size_t)nP * std::max(3 * dim, 2 * ffn));
     ALLOC(ffn, (size_t)nP * std::max(dim, ffn));
     ALLOC(win, (size_t)nP * dim);
-    ALLOC(score, (size_t)nh * nP * Se_pad);
-    ALLOC(self_score, (size_t)nWin * nh * ws * ws * ws * ws);
+    ALLOC(k_rot, (size_t)model->dec_layers * nh * Se_pad * d->hd);
+    const bool fused_attention = d->hd == 64 || d->hd == 128;  // rfk_flash_attention serves these
+    if (!fused_attention) ALLOC(score, (size_t)nh * nP * Se_pad);
+    if (!(ws * ws == 64 && d->hd == 64)) ALLOC(self_score, (size_t)nWin * nh * ws * ws * ws * ws);
     ALLOC(shift_mask, (size_t)nWin * ws * ws * ws * ws);
     for (int j = 0; j < 4; ++j) ALLOC(dft[j], (size_t)nP * dim);
     for (int k = 0; k < kSlots; ++k) ALLOC(result[k], (size_t)nP * dim);
@@ -266,6 +287,10 @@ extern "C" int rfk_session_destroy(rfk_session* d) {
     if (!d) return RFK_OK;
     if (d->stream) cudaStreamSynchronize(d->stream);
     if (d->copy_stream) cudaStreamSynchronize(d->copy_stream);
+    if (d->side_stream) cudaStreamSynchronize(d->side_stream);
+    if (d->ev_fork) cudaEventDestroy(d->ev_fork);
+    for (int i = 0; i < RFK_MAX_LAYERS; ++i)
+        if (d->ev_rot[i]) cudaEventDestroy(d->ev_rot[i]);
     for (int k = 0; k < kSlots; ++k) {
         if (d->exec[k]) cudaGraphExecDestroy(d->exec[k]);
         if (d->graph[k]) cudaGraphDestroy(d->graph[k]);
@@ -279,6 +304,7 @@ extern "C" int rfk_session_destroy(rfk_session* d) {
     for (void* p : d->owned) cudaFree(p);
     if (d->stream) cudaStreamDestroy(d->stream);
     if (d->copy_stream) cudaStreamDestroy(d->copy_stream);
+    if (d->side_stream) cudaStreamDestroy(d->side_stream);
     rfk_ctx_destroy(d->ctx);
     delete d;
     return RFK_OK;
@@ -364,7 +390,8 @@ extern "C" int rfk_session_encode_scene(rfk_session* d, const float* tri, const 
     TRY(sc.get(&temp, (size_t)Se * dim));
     TRY(sc.get(&qkvb, (size_t)Se * std::max(6 * dim, 2 * ffn)));
     TRY(sc.get(&ffnb, (size_t)Se * std::max(dim, ffn)));
-    TRY(sc.get(&score, (size_t)nh * Se * Se_pad));
+    score = nullptr;
+    if (!(hd == 64 || hd == 128)) TRY(sc.get(&score, (size_t)nh * Se * Se_pad));
     const rfk_half* pending = nullptr;
     for (int i = 0; i < m.enc_layers; ++i) {
         const rfk_half* next = nullptr;
