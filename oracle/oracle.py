@@ -193,6 +193,24 @@ def softmax_inplace(data, mask=None, swin=None):
     return data
 
 
+# ---------------------------------------------------------------- attention
+
+
+def sdpa(Q, K, V, n_keys=None, mask=None, o_bshd=False, scale=None):
+    """Q [B,H,Sq,D], K,V [B,H,Sk,D] fp16 -> O fp16 ([B,H,Sq,D] or [B,Sq,H*D]); mask [nW,Sq,Sk] bytes (0 = masked out)."""
+    Q, K, V = _c(Q, f16), _c(K, f16), _c(V, f16)
+    B, Hh, Sq, D = Q.shape; Sk = K.shape[2]
+    n_keys = Sk if n_keys is None else n_keys
+    nW = 1
+    if mask is not None:
+        mask = _c(mask, np.uint8); nW = mask.shape[0]
+        assert mask.shape == (nW, Sq, Sk) and n_keys == Sk
+    out = np.empty((B, Sq, Hh * D) if o_bshd else (B, Hh, Sq, D), f16)
+    lib().oracle_sdpa(_ptr(Q), _ptr(K), _ptr(V), _ptr(out), I(B), I(Hh), I(Sq), I(Sk), I(n_keys), I(D),
+                      Fl(scale if scale is not None else D ** -0.5), _ptr(mask), I(nW), I(int(o_bshd)))
+    return out
+
+
 # -------------------------------------------------------------- activations
 
 

@@ -294,6 +294,53 @@ void oracle_softmax_inplace(float* data, const uint8_t* mask, int swin, int mask
     }
 }
 
+/* ---------------------------------------------------------------- attention */
+
+/* Scaled dot-product attention as the reference's cuBLAS path composes it
+ * (src/layers/attention.cu:112-165): S = scale * Q K^T accumulated in fp32 over fp16 operands
+ * (:142-153, scale folded into the GEMM alpha :114,144), row softmax with the probabilities rounded
+ * to fp16 (softmax_cast_fp16, src/kernels/softmax.cu:190-235), O = P V accumulated in fp32 and
+ * rounded to fp16 (:155-165). Q [B,H,Sq,D], K,V [B,H,Sk,D]; O is [B,H,Sq,D], or [B,Sq,H*D] with o_bshd
+ * (what transpose_bhsd_to_bsd makes of it, src/layers/attention.cu:34-45). Only the first n_keys
+ * keys take part (n_keys = Sk is the reference).
+ * With a mask ([nW][Sq][Sk] bytes, window of batch entry b = b % nW, 0 = pair masked out) this is
+ * the core of swin_self_attention (src/layers/attention.cu:542-566): masked scores are replaced by
+ * -FLT_MAX before an ordinary softmax (swin_masked_softmax_inplace, src/kernels/softmax.cu:108-153),
+ * then fp32_to_fp16 (:555), then P V. */
+void oracle_sdpa(const f16* Q, const f16* K, const f16* V, f16* O, int B, int H, int Sq, int Sk,
+                 int n_keys, int D, float scale, const uint8_t* mask, int nW, int o_bshd) {
+    const long rows = (long)B * H * Sq;
+    PAR_FOR
+    for (long row = 0; row < rows; ++row) {
+        const int q = (int)(row % Sq);
+        const long bh = row / Sq;
+        const int h = (int)(bh % H), b = (int)(bh / H);
+        const f16* qr = Q + row * D;
+        const f16* Kh = K + bh * (long)Sk * D;
+        const f16* Vh = V + bh * (long)Sk * D;
+        const uint8_t* mr = mask ? mask + ((long)(b % nW) * Sq + q) * Sk : 0;
+        float s[n_keys];
+        float m = -FLT_MAX;
+        for (int j = 0; j < n_keys; ++j) {
+            double acc = 0.0;
+            for (int d = 0; d < D; ++d) acc += (double)(float)qr[d] * (double)(float)Kh[(long)j * D + d];
+            float x = (float)acc * scale;
+            if (mr && !mr[j]) x = -FLT_MAX;
+            s[j] = x;
+            if (x > m) m = x;
+        }
+        double l = 0.0;
+        for (int j = 0; j < n_keys; ++j) { s[j] = expf(s[j] - m); l += s[j]; }
+        const float inv = 1.0f / (float)l;
+        f16* orow = o_bshd ? O + (((long)b * Sq + q) * H + h) * D : O + row * D;
+        for (int d = 0; d < D; ++d) {
+            double acc = 0.0;
+            for (int j = 0; j < n_keys; ++j) acc += (double)(float)(f16)(s[j] * inv) * (double)(float)Vh[(long)j * D + d];
+            orow[d] = (f16)(float)acc;
+        }
+    }
+}
+
 /* -------------------------------------------------------------- activations */
 
 /* src/kernels/activations.cu:10-13 */

@@ -984,5 +984,115 @@ case(name="patchify_24x16x3", make=lambda rng: dict(x=normal(rng, (24, 16, 3), n
      oracle_kinds=dict(o="exact"))
 
 
+# ------------------------------------------------- fused attention (no score matrix)
+
+def _attn_make(B, Hh, Sq, Sk, D, n_keys):
+    def make(rng):
+        K = normal(rng, (B, Hh, Sk, D), np.float16); V = normal(rng, (B, Hh, Sk, D), np.float16)
+        K[:, :, n_keys:] = 0; V[:, :, n_keys:] = 0  # pad keys as the K/V cache builder leaves them
+        return dict(Q=normal(rng, (B, Hh, Sq, D), np.float16), K=K, V=V, n_keys=n_keys)
+    return make
+
+
+def _attn_oracle(i):
+    return dict(o=O.sdpa(i["Q"], i["K"], i["V"], n_keys=i["n_keys"]),
+                o_bshd=O.sdpa(i["Q"], i["K"], i["V"], n_keys=i["n_keys"], o_bshd=True))
+
+
+def _attn_rfk(i):
+    import torch
+    Q, K, V = _t(i["Q"]), _t(i["K"]), _t(i["V"]); B, Hh, Sq, D = Q.shape; Sk = K.shape[2]
+    o = _empty(Q.shape, torch.float16); ob = _empty((B, Sq, Hh * D), torch.float16)
+    _ops().flash_attention(Q, K, V, o, B, Hh, Sq, Sk, i["n_keys"], D)
+    _ops().flash_attention(Q, K, V, ob, B, Hh, Sq, Sk, i["n_keys"], D, o_bshd=True)
+    torch.cuda.synchronize()
+    assert _ops().flash_attention_error() == 0
+    return dict(o=_n(o), o_bshd=_n(ob))
+
+
+def _attn_ref(i):
+    """rf::sdpa (cuDNN fused kernel when it takes the shape, else cuBLAS + softmax_cast_fp16); it attends all Sk keys."""
+    import torch
+    R = _ref()
+    Q, K, V = _t(i["Q"]), _t(i["K"]), _t(i["V"]); B, Hh, Sq, D = Q.shape; Sk = K.shape[2]
+    o = _empty(Q.shape, torch.float16); ws = _empty((B * Hh * Sq * Sk,), torch.float32)
+    h = R.cublas_create()
+    R.call("ref_sdpa", R.Raw(h), Q, K, V, o, ws, None, B, Hh, Sq, Sk, D, lib=R.layers())
+    torch.cuda.synchronize()
+    R.cublas_destroy(h)
+    ob = o.permute(0, 2, 1, 3).contiguous().view(B, Sq, Hh * D)
+    return dict(o=_n(o), o_bshd=_n(ob))
+
+
+for B, Hh, Sq, Sk, D, nk in [(1, 2, 128, 128, 64, 128), (1, 3, 200, 328, 64, 328), (2, 2, 77, 200, 64, 193),
+                             (1, 2, 130, 72, 128, 72), (1, 1, 5, 40, 64, 33)]:
+    case(name=f"flash_attention_b{B}h{Hh}_{Sq}x{Sk}_d{D}_k{nk}", make=_attn_make(B, Hh, Sq, Sk, D, nk),
+         oracle=_attn_oracle, rfk=_attn_rfk, ref=_attn_ref if nk == Sk else None, kinds=dict(o="f16", o_bshd="f16"))
+
+
+def _winattn_make(BnW, Hh, nW, masked):
+    def make(rng):
+        m = None
+        if masked:
+            m = (rng.uniform(size=(nW, 64, 64)) > 0.4).astype(np.uint8)
+            m[nW - 1, 5, :] = 0  # one fully masked row: the -FLT_MAX fill makes it the plain mean of V
+        return dict(Q=normal(rng, (BnW, Hh, 64, 64), np.float16), K=normal(rng, (BnW, Hh, 64, 64), np.float16),
+                    V=normal(rng, (BnW, Hh, 64, 64), np.float16), mask=m, nW=nW)
+    return make
+
+
+def _winattn_rfk(i):
+    import torch
+    Q, K, V = _t(i["Q"]), _t(i["K"]), _t(i["V"]); BnW, Hh = Q.shape[:2]
+    o = _empty((BnW * 64, Hh * 64), torch.float16)
+    _ops().window_attention(Q, K, V, o, None if i["mask"] is None else _t(i["mask"]), BnW, Hh, i["nW"])
+    return dict(o=_n(o))
+
+
+for BnW, Hh, nW, masked in [(4, 2, 4, False), (8, 3, 4, True)]:
+    case(name=f"window_attention_{BnW}x{Hh}_{'masked' if masked else 'plain'}", make=_winattn_make(BnW, Hh, nW, masked),
+         oracle=lambda i: dict(o=O.sdpa(i["Q"], i["K"], i["V"], mask=i["mask"], o_bshd=True).reshape(-1, i["Q"].shape[1] * 64)),
+         rfk=_winattn_rfk, kinds=dict(o="f16"))
+
+
+# ---------------------------- residual + RMSNorm with one operand in swin window order
+
+def _normwin_make(B, Hh, W, C, ws, sh):
+    def make(rng):
+        return dict(x=normal(rng, (B, Hh, W, C), np.float16), r=normal(rng, (B, Hh, W, C), np.float16),
+                    gamma=normal(rng, (C,), np.float32, 0.1, 1.0), ws=ws, shift=sh)
+    return make
+
+
+def _normwin_oracle(i):
+    x, r, ws, sh = i["x"], i["r"], i["ws"], i["shift"]; B, Hh, W, C = x.shape
+    to_win = lambda a: O.window_partition(O.cyclic_shift(a, -sh, -sh) if sh > 0 else a, ws)
+    # (1) x += r; y = norm(x); y leaves in window order
+    x1, y1 = O.rmsnorm_residual_f16(x.reshape(-1, C), r.reshape(-1, C), i["gamma"], 2.0 ** -10)
+    y1w = to_win(y1.reshape(B, Hh, W, C)).reshape(-1, C)
+    # (2) r arrives in window order: x += unwindow(r); y = norm(x)
+    rev = O.window_reverse(r.reshape(-1, ws * ws, C), B, Hh, W, ws)
+    back = O.cyclic_shift(rev, sh, sh) if sh > 0 else rev
+    x2, y2 = O.rmsnorm_residual_f16(x.reshape(-1, C), back.reshape(-1, C), i["gamma"], 2.0 ** -10)
+    return dict(x1=x1, y1=y1w, x2=x2, y2=y2)
+
+
+def _normwin_rfk(i):
+    import torch
+    x, r, g = _t(i["x"]), _t(i["r"]), _t(i["gamma"]); B, Hh, W, C = x.shape
+    out = {}
+    for which in (1, 2):
+        xx = x.clone().view(-1, C); y = torch.empty_like(xx)
+        _ops().rmsnorm_residual_f16_windows(xx, r.view(-1, C), g, y, B, Hh, W, C, i["ws"], i["shift"], which)
+        out[f"x{which}"] = _n(xx); out[f"y{which}"] = _n(y)
+    return out
+
+
+for B, Hh, W, C, ws, sh in [(1, 16, 16, 256, 8, 4), (2, 8, 16, 64, 4, 0), (1, 8, 8, 1024, 4, 3)]:
+    k = dict(x1="exact", y1="f16", x2="exact", y2="f16")
+    case(name=f"rmsnorm_windows_b{B}_{Hh}x{W}x{C}_ws{ws}_s{sh}", make=_normwin_make(B, Hh, W, C, ws, sh),
+         oracle=_normwin_oracle, rfk=_normwin_rfk, kinds=k)
+
+
 BY_NAME = {c.name: c for c in CASES}
 assert len(BY_NAME) == len(CASES), "duplicate case names"
