@@ -69,6 +69,36 @@ world_to_cam_kernel(const float* __restrict__ c2w, T* tri, T* vn, int n_verts) {
     }
 }
 
+// fp16, many vertices: a thread owns 8 consecutive vertices of the flat [batch * n_verts] list = 48
+// contiguous bytes = three 128-bit accesses per array (the one-vertex kernel above issues 6-byte ones and
+// is bound by load latency). A thread whose vertices straddle two batch entries looks the camera up per vertex.
+__global__ void __launch_bounds__(256)
+world_to_cam_vec8_kernel(const float* __restrict__ c2w, __half* tri, __half* vn, int n_verts, long long n_groups) {
+    const long long gidx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gidx >= n_groups) return;
+    const long long v0 = gidx * 8;
+    const int b0 = (int)(v0 / n_verts), b1 = (int)((v0 + 7) / n_verts);
+    CamRT c = load_cam(c2w + (size_t)b0 * 16);
+    auto transform = [&](__half* arr, bool translate) {
+        uint4* p = reinterpret_cast<uint4*>(arr + v0 * 3);
+        __align__(16) __half h[24];
+        uint4* hv = reinterpret_cast<uint4*>(h);
+        hv[0] = p[0]; hv[1] = p[1]; hv[2] = p[2];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (b1 != b0) c = load_cam(c2w + (size_t)((v0 + i) / n_verts) * 16);
+            float vx = __half2float(h[3 * i]), vy = __half2float(h[3 * i + 1]), vz = __half2float(h[3 * i + 2]);
+            if (translate) { vx = vx - c.tx; vy = vy - c.ty; vz = vz - c.tz; }
+            float ox, oy, oz;
+            rot3(c, vx, vy, vz, ox, oy, oz);
+            h[3 * i] = __float2half(ox); h[3 * i + 1] = __float2half(oy); h[3 * i + 2] = __float2half(oz);
+        }
+        p[0] = hv[0]; p[1] = hv[1]; p[2] = hv[2];
+    };
+    transform(tri, true);
+    if (vn) transform(vn, false);
+}
+
 // thread -> (token t in [0, seq_pad), table chunk j in [0, head_dim/16)).
 // Every thread rebuilds the token's 9 camera-space coordinates (27 FMAs); the j == 0
 // thread also stores the geometry outputs.
@@ -164,6 +194,13 @@ extern "C" int rfk_world_to_cam(const float* c2w, rfk_half* tri, rfk_half* vn, i
     if (batch == 0 || n_tris == 0) return RFK_OK;
     if (batch > 65535) return RFK_EUNSUPPORTED;
     const int n_verts = n_tris * 3;
+    const long long total = (long long)batch * n_verts;
+    if (total >= 8 * 256 * (long long)kNumSMs && total % 8 == 0 && aligned16(tri) && (!vn || aligned16(vn))) {
+        const long long n_groups = total / 8;
+        world_to_cam_vec8_kernel<<<ceil_div(n_groups, 256), 256, 0, as_stream(stream)>>>(c2w, (__half*)tri, (__half*)vn,
+                                                                                          n_verts, n_groups);
+        return launch_status();
+    }
     dim3 grid(ceil_div(n_verts, 256), batch);
     world_to_cam_kernel<__half><<<grid, 256, 0, as_stream(stream)>>>(c2w, (__half*)tri,
                                                                      (__half*)vn, n_verts);

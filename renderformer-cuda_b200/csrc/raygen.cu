@@ -21,7 +21,8 @@ namespace rfk {
 struct Ray3 { float x, y, z; };
 
 // x, y: camera-plane coordinates (px+0.5-cx)/fx and -(py+0.5-cx)/fx of the pixel
-__device__ __forceinline__ Ray3 rotate_normalize(const float* __restrict__ M, float x, float y) {
+template <typename Mat>
+__device__ __forceinline__ Ray3 rotate_normalize(const Mat& M, float x, float y) {
     float z = -1.0f;
     float dx = M[0] * x + M[1] * y + M[2] * z;
     float dy = M[4] * x + M[5] * y + M[6] * z;
@@ -44,10 +45,14 @@ __device__ __forceinline__ Ray3 pixel_ray(const float* __restrict__ M, float cx,
 // many views are batched; ROWS = 1 gives a single view 4x the threads and the shortest
 // critical path. PATCH == 0: rays_d [B,res,res,3]; PATCH == 1: tokens [B,(res/8)^2,192]
 // (requires ps == 8).
-template <int PATCH, int ROWS>
+// COALESCE (PATCH == 0, res a multiple of 256): the 32 lanes of a warp own 256 consecutive pixels of a
+// row, 1536 contiguous output bytes; each lane's 48 bytes go through shared memory so that every store
+// instruction of the warp writes 512 contiguous bytes instead of 16-byte pieces 48 bytes apart.
+template <int PATCH, int ROWS, int COALESCE = 0>
 __global__ void __launch_bounds__(256)
 ray_gen_vec_kernel(const float* __restrict__ c2w, const float* __restrict__ fov,
                    float* __restrict__ rays_o, __half* __restrict__ out, int batch, int res) {
+    __shared__ __align__(16) unsigned char s_stage[COALESCE ? 8 * 1536 : 16];
     const int groups_per_row = res / 8;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long per_image = (long long)groups_per_row * (res / ROWS);
@@ -56,14 +61,16 @@ ray_gen_vec_kernel(const float* __restrict__ c2w, const float* __restrict__ fov,
     const int rem = (int)(idx % per_image);
     const int py0 = (rem / groups_per_row) * ROWS;
     const int px0 = (rem % groups_per_row) * 8;
-    const float* M = c2w + b * 16;
+    float M[11];  // the rotation rows, kept in registers for the whole strip
+#pragma unroll
+    for (int i = 0; i < 11; ++i) M[i] = __ldg(c2w + b * 16 + i);
     if (rem == 0 && rays_o) {
         rays_o[b * 3 + 0] = M[3];
         rays_o[b * 3 + 1] = M[7];
-        rays_o[b * 3 + 2] = M[11];
+        rays_o[b * 3 + 2] = __ldg(c2w + b * 16 + 11);
     }
     const float cx = res * 0.5f;
-    const float fx = cx / tanf(0.5f * fov[b]);
+    const float fx = cx / tanf(0.5f * __ldg(fov + b));
     float xs[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) xs[i] = (px0 + i + 0.5f - cx) / fx;
@@ -93,6 +100,19 @@ ray_gen_vec_kernel(const float* __restrict__ c2w, const float* __restrict__ fov,
             *reinterpret_cast<uint4*>(o) = hv[0];
             *reinterpret_cast<uint4*>(o + 64) = hv[1];
             *reinterpret_cast<uint4*>(o + 128) = hv[2];
+        } else if (COALESCE) {
+            const int lane = threadIdx.x & 31;
+            unsigned char* stage = s_stage + (threadIdx.x >> 5) * 1536;
+            uint4* mine = reinterpret_cast<uint4*>(stage + lane * 48);
+            mine[0] = hv[0]; mine[1] = hv[1]; mine[2] = hv[2];
+            __syncwarp();
+            // first pixel of the warp's 256-pixel run: this lane's px0 minus its 8 * lane
+            uint4* o = reinterpret_cast<uint4*>(out + (((long long)b * res + py) * res + (px0 - 8 * lane)) * 3);
+            const uint4* sv = reinterpret_cast<const uint4*>(stage);
+            __stcs(o + lane, sv[lane]);
+            __stcs(o + 32 + lane, sv[32 + lane]);
+            __stcs(o + 64 + lane, sv[64 + lane]);
+            __syncwarp();
         } else {
             __half* o = out + (((long long)b * res + py) * res + px0) * 3;
             *reinterpret_cast<uint4*>(o) = hv[0];
@@ -150,6 +170,7 @@ static int launch_ray_gen(const float* c2w, const float* fov, float* rays_o, __h
         const unsigned grid = ceil_div(n, 256);
         if (ps && strips) ray_gen_vec_kernel<1, 4><<<grid, 256, 0, st>>>(c2w, fov, rays_o, out, batch, res);
         else if (ps) ray_gen_vec_kernel<1, 1><<<grid, 256, 0, st>>>(c2w, fov, rays_o, out, batch, res);
+        else if (strips && res % 256 == 0) ray_gen_vec_kernel<0, 4, 1><<<grid, 256, 0, st>>>(c2w, fov, rays_o, out, batch, res);
         else if (strips) ray_gen_vec_kernel<0, 4><<<grid, 256, 0, st>>>(c2w, fov, rays_o, out, batch, res);
         else ray_gen_vec_kernel<0, 1><<<grid, 256, 0, st>>>(c2w, fov, rays_o, out, batch, res);
     } else {

@@ -109,11 +109,15 @@ def suite() -> list[Entry]:
         return mk
     e.append(Entry("world_to_cam 5633 tris (tri+vn fp16)", 4, 2 * 2 * T * 9 * 2 + 64, w2c_set(1), "world_to_cam"))
     e.append(Entry("world_to_cam 5633 tris x64 batch", 4, 64 * (2 * 2 * T * 9 * 2 + 64), w2c_set(64), "world_to_cam"))
+    e.append(Entry("world_to_cam 5633 tris x512 batch", 4, 512 * (2 * 2 * T * 9 * 2 + 64), w2c_set(512), "world_to_cam"))
 
-    def pe_dirs():
-        d = torch.nn.functional.normalize(torch.randn(1, RES * RES, 3, device="cuda"), dim=-1).half()
-        return (d, torch.empty(1, RES * RES, 39, device="cuda", dtype=H16))
-    e.append(Entry("nerf_pe ray dirs [262144x3 -> 39]", 4, RES * RES * (3 + 39) * 2, pe_dirs, "nerf_pe_f16"))
+    def pe_dirs(b):
+        def mk():
+            d = torch.nn.functional.normalize(torch.randn(b, RES * RES, 3, device="cuda"), dim=-1).half()
+            return (d, torch.empty(b, RES * RES, 39, device="cuda", dtype=H16))
+        return mk
+    e.append(Entry("nerf_pe ray dirs [262144x3 -> 39]", 4, RES * RES * (3 + 39) * 2, pe_dirs(1), "nerf_pe_f16"))
+    e.append(Entry("nerf_pe ray dirs x8 batch", 4, 8 * RES * RES * (3 + 39) * 2, pe_dirs(8), "nerf_pe_f16"))
     e.append(Entry("fused_silu_mul [4096x4096] fp16", 4, 3 * 4096 * 4096 * 2,
                    lambda: (_r((4096, 4096), H16), _r((4096, 4096), H16), torch.empty(4096, 4096, device="cuda", dtype=H16)),
                    "silu_mul"))

@@ -199,3 +199,30 @@ def test_config4_front_end_full_size():
         orf = torch.empty_like(a)
         R.call("ref_fused_silu_mul", a, b, orf, a.numel())
         _close16(o, orf)
+
+
+def test_batched_world_to_cam_and_ray_gen_paths_equal_the_single_view_kernels():
+    """Large batches take other kernels (8 vertices per thread with 128-bit accesses; ray strips with stores staged
+    through shared memory). Both must give the bits of the one-view kernels, which are checked against the reference."""
+    import torch
+    import renderformer_cuda_b200 as pkg
+    import cases
+    ops = pkg.ops
+    B, n_tris, res = 40, 5633, 512        # 16899 vertices per view: threads straddle view boundaries
+    c2w_np, fov_np = cases.look_at_c2w(np.random.default_rng(11), B)
+    c2w, fov = torch.from_numpy(c2w_np).cuda(), torch.from_numpy(fov_np).cuda()
+    g = torch.Generator(device="cuda").manual_seed(3)
+    tri = (torch.rand(B, n_tris, 3, 3, device="cuda", generator=g) * 2 - 1).half()
+    vn = torch.nn.functional.normalize(torch.randn(B, n_tris, 3, 3, device="cuda", generator=g), dim=-1).half()
+    t_all, v_all = tri.clone(), vn.clone()
+    ops.world_to_cam(c2w, t_all, v_all, B, n_tris)
+    for b in range(B):
+        t1, v1 = tri[b:b + 1].clone(), vn[b:b + 1].clone()
+        ops.world_to_cam(c2w[b:b + 1].contiguous(), t1, v1, 1, n_tris)
+        assert torch.equal(t1[0], t_all[b]) and torch.equal(v1[0], v_all[b]), f"view {b}"
+    ro_all = torch.empty(B, 3, device="cuda"); rd_all = torch.empty(B, res, res, 3, device="cuda", dtype=torch.float16)
+    ops.ray_gen(c2w, fov, ro_all, rd_all, B, res)
+    for b in range(0, B, 5):
+        ro1 = torch.empty(1, 3, device="cuda"); rd1 = torch.empty(1, res, res, 3, device="cuda", dtype=torch.float16)
+        ops.ray_gen(c2w[b:b + 1].contiguous(), fov[b:b + 1].contiguous(), ro1, rd1, 1, res)
+        assert torch.equal(rd1[0], rd_all[b]) and torch.equal(ro1[0], ro_all[b]), f"view {b}"
