@@ -305,15 +305,26 @@ class ViewScheduler:
     """Data-parallel view scheduler: one process per GPU. Rank 0 encodes the scene; the scene
     state (cross-attention K/V cache + fp16 geometry) is broadcast once over NCCL into every
     GPU's own memory; each rank then renders its share of the camera views from its local
-    copy through its own captured graph. No collective runs on the per-view path."""
+    copy through its own captured graph. No collective runs on the per-view path.
 
-    def __init__(self, model: Model, n_tris: int, img_res: int = 512, process_group=None, pad_keys_attend=False):
+    `streams_per_gpu` > 1 keeps that many views in flight on the GPU: that many sessions (each with its
+    own stream, buffers and captured graphs) share one scene state and take this rank's views in turn,
+    so that one view's partial last wave of CTAs and its bandwidth-bound kernels overlap with another
+    view's compute-bound ones."""
+
+    def __init__(self, model: Model, n_tris: int, img_res: int = 512, process_group=None, pad_keys_attend=False,
+                 streams_per_gpu: int = 1):
         import torch.distributed as dist
         self.dist = dist if (dist.is_available() and dist.is_initialized()) else None
         self.group = process_group
         self.rank = self.dist.get_rank(process_group) if self.dist else 0
         self.world = self.dist.get_world_size(process_group) if self.dist else 1
+        if streams_per_gpu < 1:
+            raise ValueError("streams_per_gpu must be at least 1")
         self.session = RenderSession(model, n_tris, img_res, pad_keys_attend=pad_keys_attend)
+        self.sessions = [self.session] + [
+            RenderSession(model, n_tris, img_res, scene_state=self.session.scene_state, pad_keys_attend=pad_keys_attend)
+            for _ in range(streams_per_gpu - 1)]
         self.broadcast_ms = 0.0
 
     def load_scene(self, tri=None, vn=None, tex=None, src: int = 0):
@@ -331,7 +342,8 @@ class ViewScheduler:
             en.record()
             torch.cuda.synchronize()
             self.broadcast_ms = st.elapsed_time(en)
-        self.session.finalize()
+        for ses in self.sessions:
+            ses.finalize()
         return self.broadcast_ms
 
     def my_views(self, n_views: int) -> list[int]:
@@ -345,9 +357,16 @@ class ViewScheduler:
         c2ws = c2ws.contiguous()
         base, stride = c2ws.data_ptr(), 16 * 4
         fl = fovs.tolist()
+        n = len(self.sessions)
         for j, v in enumerate(mine):
-            self.session.render_frame_raw(base + v * stride, fl[v])
+            ses = self.sessions[j % n]
+            ses.render_frame_raw(base + v * stride, fl[v])
             if out is not None:
-                self.session.download_async(out[j])
-        self.session.drain()
+                ses.download_async(out[j])
+        for ses in self.sessions:
+            ses.drain()
         return mine
+
+    def close(self):
+        for ses in self.sessions:
+            ses.close()

@@ -417,6 +417,13 @@ def test_scheduler_single_rank_renders_all_views(small):
         assert torch.equal(sched.session.download(), out[v])
     assert session.shard_views(10, 1, 4) == [1, 5, 9]
     sched.session.close()
+    # three views in flight (three sessions on one scene state, taking the views in turn): the same frames
+    sched3 = session.ViewScheduler(small.model, n_tris, res, streams_per_gpu=3)
+    sched3.load_scene(tri, vn, tex)
+    out3 = torch.empty_like(out)
+    assert sched3.render(c2w, fov, out3) == list(range(V))
+    assert torch.equal(out3, out)
+    sched3.close()
 
 
 @pytest.mark.parametrize("B,Hh,Sq,Sk,n_keys,D", [
