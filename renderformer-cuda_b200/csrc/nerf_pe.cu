@@ -51,8 +51,7 @@ template <typename TI>
 __global__ void __launch_bounds__(kPeThreads)
 nerf_pe_tile_kernel(const TI* __restrict__ input, __half* __restrict__ output, long long rows,
                     int rows_per_block, int in_dim, int num_freqs, int include_input,
-                    const __grid_constant__ FreqTable ft, FastDiv div_per_row, FastDiv div_nf,
-                    FastDiv div_in, int vec_out) {
+                    const __grid_constant__ FreqTable ft, FastDiv div_in, int vec_out) {
     extern __shared__ __align__(16) __half s_out[];
     const int per_row = in_dim * num_freqs;
     const int off = include_input ? in_dim : 0;
@@ -285,8 +284,7 @@ static int launch_nerf_pe(const TI* input, __half* output, int batch, int seq_le
         else if (num_freqs == 10) RFK_PE_NF(10);
         else
             nerf_pe_tile_kernel<TI><<<grid, kPeThreads, smem, st>>>(
-                input, output, rows, rpb, in_dim, num_freqs, inc, ft, FastDiv((unsigned)(in_dim * num_freqs)),
-                FastDiv((unsigned)num_freqs), FastDiv((unsigned)in_dim), vec);
+                input, output, rows, rpb, in_dim, num_freqs, inc, ft, FastDiv((unsigned)in_dim), vec);
 #undef RFK_PE_NF
 #undef RFK_PE_ROWS
     } else {
