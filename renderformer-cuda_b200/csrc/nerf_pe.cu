@@ -152,13 +152,13 @@ nerf_pe_tile_nf_kernel(const TI* __restrict__ input, __half* __restrict__ output
     }
 }
 
+constexpr int kPeRowThreads = 128;
 // Input width and frequency count both known at compile time: one thread per row. The tile's inputs are
 // fetched with coalesced loads into shared memory, each thread then walks its own row with fully unrolled
 // loops (no index arithmetic per value), and the tile leaves with 128-bit stores as above.
-constexpr int kPeRowThreads = 128;
 template <typename TI, int IN_DIM, int NF, bool DOUBLING, bool INCLUDE>
 __global__ void __launch_bounds__(kPeRowThreads)
-nerf_pe_rows_kernel(const TI* __restrict__ input, __half* __restrict__ output, long long rows,
+nerf_pe_rows1_kernel(const TI* __restrict__ input, __half* __restrict__ output, long long rows,
                     const __grid_constant__ FreqTable ft, int vec_out) {
     constexpr int PER_ROW = IN_DIM * NF, OFF = INCLUDE ? IN_DIM : 0, OUT_DIM = 2 * PER_ROW + OFF;
     __shared__ __align__(16) __half s_out[kPeRowThreads * OUT_DIM];
@@ -201,6 +201,74 @@ nerf_pe_rows_kernel(const TI* __restrict__ input, __half* __restrict__ output, l
     __syncthreads();
     const int n_out = nrows * OUT_DIM;
     __half* dst = output + r0 * OUT_DIM;  // kPeRowThreads * OUT_DIM halves per tile: a multiple of 16 bytes
+    if (vec_out) {
+        const int nvec = n_out / 8;
+        for (int v = threadIdx.x; v < nvec; v += kPeRowThreads)
+            __stcs(reinterpret_cast<uint4*>(dst) + v, reinterpret_cast<const uint4*>(s_out)[v]);
+        for (int e = nvec * 8 + threadIdx.x; e < n_out; e += kPeRowThreads) dst[e] = s_out[e];
+    } else {
+        for (int e = threadIdx.x; e < n_out; e += kPeRowThreads) dst[e] = s_out[e];
+    }
+}
+
+// A thread owns two adjacent rows: their 2 * OUT_DIM halves start on a 4-byte boundary whatever the parity
+// of OUT_DIM (39 and 117 are odd), so the values leave the registers as packed pairs: half as many
+// shared-memory stores as with one row per thread.
+template <typename TI, int IN_DIM, int NF, bool DOUBLING, bool INCLUDE>
+__global__ void __launch_bounds__(kPeRowThreads)
+nerf_pe_rows_kernel(const TI* __restrict__ input, __half* __restrict__ output, long long rows,
+                    const __grid_constant__ FreqTable ft, int vec_out) {
+    constexpr int PER_ROW = IN_DIM * NF, OFF = INCLUDE ? IN_DIM : 0, OUT_DIM = 2 * PER_ROW + OFF;
+    constexpr int kRows = 2 * kPeRowThreads;
+    __shared__ __align__(16) __half s_out[kRows * OUT_DIM];
+    __shared__ TI s_in[kRows * IN_DIM];
+    const long long r0 = (long long)blockIdx.x * kRows;
+    const int nrows = (int)min((long long)kRows, rows - r0);
+    for (int i = threadIdx.x; i < nrows * IN_DIM; i += kPeRowThreads) s_in[i] = input[r0 * IN_DIM + i];
+    __syncthreads();
+    float f[NF];
+#pragma unroll
+    for (int k = 0; k < NF; ++k) f[k] = ft.f[k];
+    const int ra = 2 * threadIdx.x;  // rows ra and ra + 1 of the tile
+    if (ra < nrows) {
+        __half v[2 * OUT_DIM];
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            __half* o = v + rr * OUT_DIM;
+            const bool live = ra + rr < nrows;
+#pragma unroll
+            for (int d = 0; d < IN_DIM; ++d) {
+                const float x = live ? (float)s_in[(ra + rr) * IN_DIM + d] : 0.0f;
+                if (INCLUDE) o[d] = __float2half(x);
+                if (DOUBLING) {
+                    float sn, cs;
+                    sincos_fast(x * f[0], sn, cs);
+#pragma unroll
+                    for (int k = 0; k < NF; ++k) {
+                        o[OFF + d * NF + k] = __float2half(sn);
+                        o[OFF + PER_ROW + d * NF + k] = __float2half(cs);
+                        const float s2 = 2.0f * sn * cs;
+                        cs = fmaf(-2.0f * sn, sn, 1.0f);
+                        sn = s2;
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < NF; ++k) {
+                        float sn, cs;
+                        sincos_fast(x * f[k], sn, cs);
+                        o[OFF + d * NF + k] = __float2half(sn);
+                        o[OFF + PER_ROW + d * NF + k] = __float2half(cs);
+                    }
+                }
+            }
+        }
+        __half2* dst2 = reinterpret_cast<__half2*>(s_out + ra * OUT_DIM);  // ra even: 4-byte aligned
+#pragma unroll
+        for (int i = 0; i < OUT_DIM; ++i) dst2[i] = __halves2half2(v[2 * i], v[2 * i + 1]);
+    }
+    __syncthreads();
+    const int n_out = nrows * OUT_DIM;
+    __half* dst = output + r0 * OUT_DIM;  // kRows * OUT_DIM halves per tile: a multiple of 16 bytes
     if (vec_out) {
         const int nvec = n_out / 8;
         for (int v = threadIdx.x; v < nvec; v += kPeRowThreads)
@@ -271,14 +339,19 @@ static int launch_nerf_pe(const TI* input, __half* output, int batch, int seq_le
             nerf_pe_tile_nf_kernel<TI, NF, false><<<grid, kPeThreads, smem, st>>>(input, output, rows, rpb, in_dim, \
                                                                                   inc, ft, FastDiv((unsigned)in_dim), vec); \
     } while (0)
-        const unsigned row_grid = ceil_div(rows, kPeRowThreads);
+        const unsigned row_grid = ceil_div(rows, 2 * kPeRowThreads), row1_grid = ceil_div(rows, kPeRowThreads);
+#define RFK_PE_ROWS1(IN, NF)                                                                                  \
+    do {                                                                                                      \
+        if (doubling) nerf_pe_rows1_kernel<TI, IN, NF, true, true><<<row1_grid, kPeRowThreads, 0, st>>>(input, output, rows, ft, vec); \
+        else nerf_pe_rows1_kernel<TI, IN, NF, false, true><<<row1_grid, kPeRowThreads, 0, st>>>(input, output, rows, ft, vec);         \
+    } while (0)
 #define RFK_PE_ROWS(IN, NF)                                                                                   \
     do {                                                                                                      \
         if (doubling) nerf_pe_rows_kernel<TI, IN, NF, true, true><<<row_grid, kPeRowThreads, 0, st>>>(input, output, rows, ft, vec); \
         else nerf_pe_rows_kernel<TI, IN, NF, false, true><<<row_grid, kPeRowThreads, 0, st>>>(input, output, rows, ft, vec);         \
     } while (0)
         if (num_freqs == 6 && in_dim == 3 && inc) RFK_PE_ROWS(3, 6);
-        else if (num_freqs == 6 && in_dim == 9 && inc) RFK_PE_ROWS(9, 6);
+        else if (num_freqs == 6 && in_dim == 9 && inc) RFK_PE_ROWS1(9, 6);
         else if (num_freqs == 6) RFK_PE_NF(6);
         else if (num_freqs == 4) RFK_PE_NF(4);
         else if (num_freqs == 10) RFK_PE_NF(10);
@@ -287,6 +360,7 @@ static int launch_nerf_pe(const TI* input, __half* output, int batch, int seq_le
                 input, output, rows, rpb, in_dim, num_freqs, inc, ft, FastDiv((unsigned)in_dim), vec);
 #undef RFK_PE_NF
 #undef RFK_PE_ROWS
+#undef RFK_PE_ROWS1
     } else {
         const long long total = rows * out_dim;
         nerf_pe_flat_kernel<TI><<<ceil_div(total, 256), 256, 0, st>>>(
