@@ -37,7 +37,8 @@ enum {
     RFK_OK          = 0,
     RFK_EINVAL      = -1,  /* null pointer, negative size, unsupported shape */
     RFK_EUNSUPPORTED= -2,  /* shape outside what the kernels implement       */
-    RFK_ETOOBIG     = -3   /* size beyond a documented fixed maximum         */
+    RFK_ETOOBIG     = -3,  /* size beyond a documented fixed maximum         */
+    RFK_EKERNEL     = -4   /* a kernel gave up on a bounded device-side wait (rfk_flash_attention_error) */
 };
 
 /* Library identification: returns a static string "rfk <version> sm_100a". */

@@ -288,7 +288,9 @@ int rfk_session_feature_taps(rfk_session* s, const rfk_half** taps /* HOST array
 int rfk_session_download(rfk_session* s, rfk_half* h_out, size_t bytes);
 /* Queues the device->host copy of the last submitted frame's token map on the session's copy
  * stream (h_out should be pinned); it runs as soon as that frame is done, overlapping the
- * next frame. rfk_session_drain waits for every submitted frame and copy. */
+ * next frame. rfk_session_drain waits for every submitted frame and copy and returns RFK_EKERNEL if
+ * the fused attention kernel has reported a time-out since its error word was last cleared
+ * (rfk_flash_attention_error); rfk_session_finalize makes the same check after its warm-up view. */
 int rfk_session_download_async(rfk_session* s, rfk_half* h_out, size_t bytes);
 int rfk_session_drain(rfk_session* s);
 /* Timing marks: mark_begin records a CUDA event on the session's render stream; mark_end

@@ -13,6 +13,7 @@ extern "C" const char* rfk_status_string(int status) {
         case RFK_EINVAL: return "invalid argument (null pointer, negative size or inconsistent shape)";
         case RFK_EUNSUPPORTED: return "shape or alignment not supported by this entry point";
         case RFK_ETOOBIG: return "size exceeds a fixed maximum of this entry point";
+        case RFK_EKERNEL: return "a kernel gave up on a bounded device-side wait; its output is undefined";
         default: break;
     }
     if (status > 0) return cudaGetErrorString((cudaError_t)status);

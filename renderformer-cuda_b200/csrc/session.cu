@@ -417,6 +417,14 @@ extern "C" int rfk_session_encode_scene(rfk_session* d, const float* tri, const 
     return RFK_OK;
 }
 
+// The fused attention kernel reports a time-out of one of its bounded waits in a device word instead of hanging;
+// frames rendered since the word was last clear are not to be trusted.
+static int check_attention_error() {
+    int code = 0;
+    TRY(rfk_flash_attention_error(&code, 0));
+    return code ? RFK_EKERNEL : RFK_OK;
+}
+
 extern "C" int rfk_session_finalize(rfk_session* d) {
     if (!d) return RFK_EINVAL;
     if (d->finalized) return RFK_OK;
@@ -448,6 +456,8 @@ extern "C" int rfk_session_finalize(rfk_session* d) {
         d->kernels_per_view = (int)(rfk_launch_count() - n0);
         TRY_CUDA(cudaStreamSynchronize(d->stream));
     }
+    TRY_CUDA(cudaStreamSynchronize(d->stream));
+    TRY(check_attention_error());
     d->finalized = true;
     return RFK_OK;
 }
@@ -511,7 +521,7 @@ extern "C" int rfk_session_drain(rfk_session* d) {
     TRY_CUDA(cudaStreamSynchronize(d->stream));
     TRY_CUDA(cudaStreamSynchronize(d->copy_stream));
     for (int k = 0; k < kSlots; ++k) d->dl_pending[k] = false;
-    return RFK_OK;
+    return check_attention_error();
 }
 
 extern "C" int rfk_session_download(rfk_session* d, rfk_half* h_out, size_t bytes) {
