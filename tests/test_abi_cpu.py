@@ -33,6 +33,7 @@ def test_version_and_status_strings():
     lib = _abi.load("rfk.h")
     assert lib.rfk_status_string(0) == b"ok"
     assert b"invalid" in lib.rfk_status_string(-1)
+    assert b"bounded" in lib.rfk_status_string(-4)
 
 
 def test_null_and_bad_shapes_are_rejected_without_a_device():
@@ -49,6 +50,14 @@ def test_null_and_bad_shapes_are_rejected_without_a_device():
     assert lib.rfk_ray_gen(fake, fake, fake, fake, 1, 0, null) == -1
     assert lib.rfk_window_gather(fake, fake, 1, 10, 10, 8, 4, 0, null) == -1   # 10 % 4 != 0
     assert lib.rfk_rmsnorm_residual_f16(fake, fake, fake, fake, 2, 64, 1e-3, null) == -1  # y aliases x
+    # the fused attention entries: argument checks before any device work
+    assert lib.rfk_flash_attention(fake, fake, fake, fake, 1, 2, 16, 8, 9, 64, 0, 0.125, null) == -1   # n_keys > Sk
+    assert lib.rfk_flash_attention(fake, fake, fake, fake, 1, 2, 16, 8, 8, 48, 0, 0.125, null) == -2   # head size
+    assert lib.rfk_flash_attention(fake, fake, fake, fake, 0, 2, 16, 8, 8, 64, 0, 0.125, null) == 0    # empty batch
+    assert lib.rfk_flash_attention_set_path(7) == -1
+    assert lib.rfk_window_attention(fake, fake, fake, fake, null, 4, 2, 49, 64, 4, 0.125, null) == -2  # 7x7 windows
+    assert lib.rfk_rmsnorm_residual_f16_windows(fake, fake, fake, fake, 1, 10, 10, 64, 4, 0, 1, 1e-3, null) == -1
+    assert lib.rfk_rmsnorm_residual_f16_windows(fake, fake, fake, ctypes.c_void_p(512), 1, 8, 8, 60, 4, 0, 3, 1e-3, null) == -1
     assert lib.rfk_launch_count() == 0
 
 
