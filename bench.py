@@ -377,7 +377,7 @@ def run_kernels(args, backend, rank, world, peak, peak_src):
     from renderformer_cuda_b200 import kernel_bench as kb
     import renderformer_cuda_b200 as pkg
     entries = kb.suite()
-    step_entries = [e for e in entries if " batch" not in e.name]
+    step_entries = [e for e in entries if " batch" not in e.name and hasattr(backend, e.op)]
     sets = {e.name: [e.make() for _ in range(2 if e.bytes_per_launch > kb.L2_BYTES else 4)] for e in step_entries}
     fns = {e.name: getattr(backend, e.op) for e in step_entries}
 

@@ -285,13 +285,14 @@ static int launch_flash(const __half* Q, const __half* K, const __half* V, __hal
 // projection reads. Four warps, 16 query rows each; Q, K, V are 8 KB contiguous tiles.
 constexpr int kWinTokens = 64, kWinThreads = 128;
 
-__global__ void __launch_bounds__(kWinThreads)
+__global__ void __launch_bounds__(kWinThreads, 8)  // 8 CTAs per SM: the 1024 CTAs of a decoder layer are one wave
 window_attention_kernel(const __half* __restrict__ Q, const __half* __restrict__ K, const __half* __restrict__ V,
                         __half* __restrict__ O, const uint8_t* __restrict__ mask, int heads, int nW, float scale_log2e) {
     constexpr int HD = 64;
     __shared__ __align__(128) __half sQ[kWinTokens * HD];
     __shared__ __align__(128) __half sK[kWinTokens * HD];
     __shared__ __align__(128) __half sV[kWinTokens * HD];
+    __shared__ __align__(16) uint8_t sMask[kWinTokens * kWinTokens];  // this window's mask, fetched with the tiles
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, tig = lane & 3;
     const long long bh = blockIdx.x;
@@ -304,6 +305,10 @@ window_attention_kernel(const __half* __restrict__ Q, const __half* __restrict__
         cp_async16(tile_ptr<HD>(sQ, r, c), Qh + r * HD + c * 8, 16);
         cp_async16(tile_ptr<HD>(sK, r, c), Kh + r * HD + c * 8, 16);
         cp_async16(tile_ptr<HD>(sV, r, c), Vh + r * HD + c * 8, 16);
+    }
+    if (mask) {
+        const uint8_t* mw = mask + (long long)(bw % nW) * (kWinTokens * kWinTokens);
+        for (int i = tid; i < kWinTokens * kWinTokens / 16; i += kWinThreads) cp_async16(sMask + i * 16, mw + i * 16, 16);
     }
     cp_async_commit();
     cp_async_wait<0>();
@@ -331,8 +336,8 @@ window_attention_kernel(const __half* __restrict__ Q, const __half* __restrict__
     }
     // scores in the exponent's units; masked-out pairs get -FLT_MAX (a fully masked row ends up uniform)
     const int q_lo = warp * 16 + g;  // this thread's rows: q_lo (regs 0, 1) and q_lo + 8 (regs 2, 3)
-    const uint8_t* m0 = mask ? mask + ((long long)(bw % nW) * kWinTokens + q_lo) * kWinTokens : nullptr;
-    const uint8_t* m1 = mask ? m0 + 8 * kWinTokens : nullptr;
+    const uint8_t* m0 = sMask + q_lo * kWinTokens;
+    const uint8_t* m1 = m0 + 8 * kWinTokens;
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int n = 0; n < 8; ++n) {
@@ -446,7 +451,7 @@ extern "C" int rfk_window_attention(const rfk_half* Q, const rfk_half* K, const 
     if (window_tokens != kWinTokens || head_dim != 64) return RFK_EUNSUPPORTED;
     if (BnW == 0) return RFK_OK;
     if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O)) return RFK_EUNSUPPORTED;
-    if (mask && (reinterpret_cast<uintptr_t>(mask) & 1u)) return RFK_EUNSUPPORTED;
+    if (mask && !aligned16(mask)) return RFK_EUNSUPPORTED;
     const long long ctas = (long long)BnW * num_heads;
     if (ctas > 0x7fffffffLL) return RFK_EUNSUPPORTED;
     window_attention_kernel<<<(unsigned)ctas, kWinThreads, 0, as_stream(stream)>>>(

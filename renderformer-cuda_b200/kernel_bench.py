@@ -118,6 +118,17 @@ def suite() -> list[Entry]:
         return mk
     e.append(Entry("nerf_pe ray dirs [262144x3 -> 39]", 4, RES * RES * (3 + 39) * 2, pe_dirs(1), "nerf_pe_f16"))
     e.append(Entry("nerf_pe ray dirs x8 batch", 4, 8 * RES * RES * (3 + 39) * 2, pe_dirs(8), "nerf_pe_f16"))
+    # decoder-layer kernels that have no counterpart among the reference's src/kernels (library batches + glue there)
+    def win_set():
+        q = _r((64, HEADS, 64, HD), H16); k = _r((64, HEADS, 64, HD), H16); v = _r((64, HEADS, 64, HD), H16)
+        mask = (torch.rand(64, 64, 64, device="cuda") > 0.3).to(torch.uint8)
+        return (q, k, v, torch.empty(64 * 64, HEADS * HD, device="cuda", dtype=H16), mask)
+    e.append(Entry("window_attention [64 windows x 16 heads x 64x64x64, masked]", 5, 4 * 64 * HEADS * 64 * HD * 2 + 64 * 64 * 64,
+                   win_set, "window_attention"))
+
+    def normwin_set():
+        return (_r((4096, 1024), H16), _r((4096, 1024), H16), torch.ones(1024, device="cuda"), torch.empty(4096, 1024, device="cuda", dtype=H16))
+    e.append(Entry("rmsnorm_residual_f16 -> windows [4096x1024]", 5, 4 * 4096 * 1024 * 2 + 4096, normwin_set, "rmsnorm_windows"))
     e.append(Entry("fused_silu_mul [4096x4096] fp16", 4, 3 * 4096 * 4096 * 2,
                    lambda: (_r((4096, 4096), H16), _r((4096, 4096), H16), torch.empty(4096, 4096, device="cuda", dtype=H16)),
                    "silu_mul"))
@@ -163,6 +174,12 @@ class RfkBackend:
 
     def silu_mul(self, a, b, out):
         self.o.fused_silu_mul(a, b, out, a.numel())
+
+    def window_attention(self, q, k, v, o, mask):
+        self.o.window_attention(q, k, v, o, mask, 64, HEADS, 64)
+
+    def rmsnorm_windows(self, x, r, gamma, y):
+        self.o.rmsnorm_residual_f16_windows(x, r, gamma, y, 1, 64, 64, 1024, 8, 4, 1)
 
 
 def time_entry(entry: Entry, backend, iters: int = 20, warmup: int = 3, budget_bytes: int = 3 * L2_BYTES):
@@ -210,7 +227,7 @@ def time_entry(entry: Entry, backend, iters: int = 20, warmup: int = 3, budget_b
 def run_suite(backend, peak_gbs: float, iters: int = 20, warmup: int = 3, only: set | None = None) -> list[dict]:
     rows = []
     for entry in suite():
-        if only and entry.op not in only:
+        if (only and entry.op not in only) or not hasattr(backend, entry.op):
             continue
         ms, nsets, mode = time_entry(entry, backend, iters, warmup)
         gbs = entry.bytes_per_launch / (ms * 1e-3) / 1e9
