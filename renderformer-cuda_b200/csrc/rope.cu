@@ -224,19 +224,25 @@ struct QkvParts {
     int use_rope[3];
 };
 
-// One warp per token row and part. Lane owns rotation-pair chunks p = lane + 32k of the
-// dim/16 pairs in the row: head h = p / (D/16), chunk j = p % (D/16).
-template <int NPAIR>
-__global__ void __launch_bounds__(128)
+// WPR warps per token row and part, 4 warps per CTA. A thread owns rotation-pair chunks
+// p = t + 32 * WPR * k (t = its index within the row's threads) of the dim/16 pairs in the row:
+// head h = p / (D/16), chunk j = p % (D/16). With WPR > 1 the sum of squares crosses the warps
+// of a row through shared memory; rows past the end are clamped (and not stored) so that every
+// thread reaches the barrier.
+template <int NPAIR, int WPR>
+__global__ void __launch_bounds__(128, NPAIR == 1 ? 8 : 1)
 qkv_epilogue_kernel(const __half* __restrict__ x, long long row_stride,
                     const __grid_constant__ QkvParts parts,
                     const __half* __restrict__ cos_vals, const __half* __restrict__ sin_vals,
                     int batch, int seq_len, int num_heads, int head_dim, float eps,
                     long long out_seq_stride) {
-    const int lane = threadIdx.x & 31;
-    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    constexpr int RPC = 4 / WPR;  // rows per CTA
+    const int lane = (WPR == 1) ? (threadIdx.x & 31) : (threadIdx.x % (32 * WPR));  // index within the row's threads
     const long long rows = (long long)batch * seq_len;
-    if (row >= rows) return;
+    long long row = (long long)blockIdx.x * RPC + threadIdx.x / (32 * WPR);
+    const bool live = row < rows;
+    if (WPR == 1 && !live) return;
+    if (!live) row = rows - 1;
     const int part = blockIdx.y;
     const int dim = num_heads * head_dim;
     const int npairs = dim / 16, cpt = head_dim / 16, half_d = head_dim / 2;
@@ -245,15 +251,46 @@ qkv_epilogue_kernel(const __half* __restrict__ x, long long row_stride,
     const float* gamma = parts.gamma[part];
     __half* out = parts.out[part];
 
+    // every load of the row is issued before the first use: the row itself (streamed), the norm weights
+    // and the rotation tables (both shared by all rows, L2-resident)
+    const bool rope = parts.use_rope[part] != 0;
+    Half8 xl[NPAIR], xh[NPAIR], cl8[NPAIR], sl8[NPAIR], ch8[NPAIR], sh8[NPAIR];
+    float gl[NPAIR][8], gh[NPAIR][8];
+#pragma unroll
+    for (int k = 0; k < NPAIR; ++k) {
+        const int p = lane + 32 * WPR * k;
+        if (p < npairs) {
+            const int o = (p / cpt) * head_dim + (p % cpt) * 8;
+            xl[k] = ldcs_half8(xr + o);
+            xh[k] = ldcs_half8(xr + o + half_d);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < NPAIR; ++k) {
+        const int p = lane + 32 * WPR * k;
+        if (p < npairs) {
+            const int o = (p / cpt) * head_dim + (p % cpt) * 8;
+            if (gamma) {
+                ldg_float8(gamma + o, gl[k]);
+                ldg_float8(gamma + o + half_d, gh[k]);
+            }
+            if (rope) {
+                const size_t to = ((size_t)b * seq_len + s) * head_dim + (p % cpt) * 8;
+                cl8[k] = ldg_half8(cos_vals + to);
+                sl8[k] = ldg_half8(sin_vals + to);
+                ch8[k] = ldg_half8(cos_vals + to + half_d);
+                sh8[k] = ldg_half8(sin_vals + to + half_d);
+            }
+        }
+    }
     float lo[NPAIR][8], hi[NPAIR][8];
     float ss = 0.0f;
 #pragma unroll
     for (int k = 0; k < NPAIR; ++k) {
-        const int p = lane + 32 * k;
+        const int p = lane + 32 * WPR * k;
         if (p < npairs) {
-            const int o = (p / cpt) * head_dim + (p % cpt) * 8;
-            unpack8(ldcs_half8(xr + o), lo[k]);
-            unpack8(ldcs_half8(xr + o + half_d), hi[k]);
+            unpack8(xl[k], lo[k]);
+            unpack8(xh[k], hi[k]);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 ss = fmaf(lo[k][i], lo[k][i], ss);
@@ -261,44 +298,50 @@ qkv_epilogue_kernel(const __half* __restrict__ x, long long row_stride,
             }
         }
     }
-    if (gamma) {
+    if (gamma) {  // uniform over the CTA
         ss = warp_sum(ss);
+        if (WPR > 1) {
+            __shared__ float s_part[4];
+            const int w = threadIdx.x >> 5;
+            if ((threadIdx.x & 31) == 0) s_part[w] = ss;
+            __syncthreads();
+            const int w0 = (w / WPR) * WPR;
+            ss = 0.0f;
+#pragma unroll
+            for (int i = 0; i < WPR; ++i) ss += s_part[w0 + i];
+        }
         const float rinv = rsqrtf(ss / (float)dim + eps);
 #pragma unroll
         for (int k = 0; k < NPAIR; ++k) {
-            const int p = lane + 32 * k;
+            const int p = lane + 32 * WPR * k;
             if (p < npairs) {
-                const int o = (p / cpt) * head_dim + (p % cpt) * 8;
-                float gl[8], gh[8];
-                ldg_float8(gamma + o, gl);
-                ldg_float8(gamma + o + half_d, gh);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     // the unfused path stores the normalised value as fp16 before rotating it
-                    lo[k][i] = round_half((lo[k][i] * rinv) * gl[i]);
-                    hi[k][i] = round_half((hi[k][i] * rinv) * gh[i]);
+                    lo[k][i] = round_half((lo[k][i] * rinv) * gl[k][i]);
+                    hi[k][i] = round_half((hi[k][i] * rinv) * gh[k][i]);
                 }
             }
         }
     }
-    const bool rope = parts.use_rope[part] != 0;
 #pragma unroll
     for (int k = 0; k < NPAIR; ++k) {
-        const int p = lane + 32 * k;
+        const int p = lane + 32 * WPR * k;
         if (p < npairs) {
             const int h = p / cpt, j = p % cpt;
             if (rope) {
                 float cl[8], sl[8], ch[8], sh[8];
-                const size_t to = ((size_t)b * seq_len + s) * head_dim + j * 8;
-                unpack8(ldg_half8(cos_vals + to), cl);
-                unpack8(ldg_half8(sin_vals + to), sl);
-                unpack8(ldg_half8(cos_vals + to + half_d), ch);
-                unpack8(ldg_half8(sin_vals + to + half_d), sh);
+                unpack8(cl8[k], cl);
+                unpack8(sl8[k], sl);
+                unpack8(ch8[k], ch);
+                unpack8(sh8[k], sh);
                 rotate8(lo[k], hi[k], cl, sl, ch, sh);
             }
             const size_t oo = (((size_t)b * num_heads + h) * out_seq_stride + s) * head_dim + j * 8;
-            store8(out + oo, lo[k]);
-            store8(out + oo + half_d, hi[k]);
+            if (live) {
+                store8(out + oo, lo[k]);
+                store8(out + oo + half_d, hi[k]);
+            }
         }
     }
 }
@@ -403,18 +446,16 @@ extern "C" int rfk_qkv_norm_rope_transpose(const rfk_half* x, long long row_stri
     }
     const long long rows = (long long)batch * seq_len;
     if (rows == 0) return RFK_OK;
-    constexpr int WPB = 4;
-    dim3 grid(ceil_div(rows, WPB), n_parts);
     cudaStream_t st = as_stream(stream);
     const int npairs = (int)(dim / 16);
-#define RFK_QKV(N)                                                                               \
-    qkv_epilogue_kernel<N><<<grid, WPB * 32, 0, st>>>((const __half*)x, row_stride, parts,       \
-                                                      (const __half*)cos_vals,                   \
-                                                      (const __half*)sin_vals, batch, seq_len,   \
-                                                      num_heads, head_dim, eps, out_seq_stride)
-    if (npairs <= 32) RFK_QKV(1);
-    else if (npairs <= 64) RFK_QKV(2);
-    else RFK_QKV(4);
+    // two warps per row from 64 chunk pairs on (dim 1024: one pair per thread, 64 registers, 8 CTAs per SM)
+#define RFK_QKV(N, W)                                                                            \
+    qkv_epilogue_kernel<N, W><<<dim3(ceil_div(rows, 4 / W), n_parts), 128, 0, st>>>(             \
+        (const __half*)x, row_stride, parts, (const __half*)cos_vals, (const __half*)sin_vals,   \
+        batch, seq_len, num_heads, head_dim, eps, out_seq_stride)
+    if (npairs <= 32) RFK_QKV(1, 1);
+    else if (npairs <= 64) RFK_QKV(1, 2);
+    else RFK_QKV(2, 2);
 #undef RFK_QKV
     return launch_status();
 }

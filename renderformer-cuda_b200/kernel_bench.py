@@ -129,6 +129,17 @@ def suite() -> list[Entry]:
     def normwin_set():
         return (_r((4096, 1024), H16), _r((4096, 1024), H16), torch.ones(1024, device="cuda"), torch.empty(4096, 1024, device="cuda", dtype=H16))
     e.append(Entry("rmsnorm_residual_f16 -> windows [4096x1024]", 5, 4 * 4096 * 1024 * 2 + 4096, normwin_set, "rmsnorm_windows"))
+    def qproj_set(parts):
+        def mk():
+            x = _r((4096, parts * 1024), H16)
+            outs = [torch.empty(HEADS, 4096, HD, device="cuda", dtype=H16) for _ in range(parts)]
+            c = torch.rand(4096, HD, device="cuda").half(); s_ = torch.rand(4096, HD, device="cuda").half()
+            return (x, outs, torch.ones(1024, device="cuda"), c, s_)
+        return mk
+    e.append(Entry("qkv_norm_rope_transpose cross q [4096x1024 -> 16x4096x64, norm + rope]", 5,
+                   2 * 4096 * 1024 * 2 + 2 * 4096 * HD * 2 + 4096, qproj_set(1), "qkv_epilogue"))
+    e.append(Entry("qkv_norm_rope_transpose swin q,k,v [4096x3072 -> 3x16x4096x64, q,k norm]", 5,
+                   2 * 4096 * 3072 * 2 + 2 * 4096, qproj_set(3), "qkv_epilogue"))
     e.append(Entry("fused_silu_mul [4096x4096] fp16", 4, 3 * 4096 * 4096 * 2,
                    lambda: (_r((4096, 4096), H16), _r((4096, 4096), H16), torch.empty(4096, 4096, device="cuda", dtype=H16)),
                    "silu_mul"))
@@ -177,6 +188,13 @@ class RfkBackend:
 
     def window_attention(self, q, k, v, o, mask):
         self.o.window_attention(q, k, v, o, mask, 64, HEADS, 64)
+
+    def qkv_epilogue(self, x, outs, gamma, c, s):
+        n = len(outs)
+        if n == 1:
+            self.o.qkv_norm_rope_transpose(x, 1024, [gamma], outs, [1], c, s, 1, 4096, HEADS, HD)
+        else:
+            self.o.qkv_norm_rope_transpose(x, 3072, [gamma, gamma, None], outs, [0, 0, 0], None, None, 1, 4096, HEADS, HD)
 
     def rmsnorm_windows(self, x, r, gamma, y):
         self.o.rmsnorm_residual_f16_windows(x, r, gamma, y, 1, 64, 64, 1024, 8, 4, 1)

@@ -484,6 +484,10 @@ for B, S, Hh, D, nf in [(1, 45, 16, 64, 3), (2, 21, 8, 128, 6), (1, 10, 4, 32, 1
     case(name=f"qkv_norm_rope_transpose_b{B}s{S}h{Hh}d{D}", make=_qkv_make(B, S, Hh, D, nf),
          oracle=_qkv_oracle, rfk=_qkv_rfk, ref=_qkv_ref, kinds=dict(q="f16", k="f16", v="exact"),
          oracle_kinds=dict(v="exact"))
+# 2048-wide rows: two chunk pairs per thread, two warps per row (no reference output stored for this shape)
+case(name="qkv_norm_rope_transpose_b1s19h16d128", make=_qkv_make(1, 19, 16, 128, 6),
+     oracle=_qkv_oracle, rfk=_qkv_rfk, ref=None, kinds=dict(q="f16", k="f16", v="exact"),
+     oracle_kinds=dict(v="exact"))
 
 # --------------------------------------------------------------------- NeRF PE
 
