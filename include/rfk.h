@@ -294,6 +294,24 @@ int rfk_elu(const rfk_half* x, rfk_half* y, long long n, float alpha, rfk_stream
 /* y = 10^x - 1 fp32, in place allowed — replaces rf::pow10_minus1,
  * activations.h:20, activations.cu:52-63 */
 int rfk_pow10_minus1(const float* x, float* y, long long n, rfk_stream_t stream);
+
+/* ---- element-wise / layout operators of the DPT head (src/layers/dpt.h, dpt.cu); the convolutions of
+ * the head are library calls in the reference and are not part of this library ---- */
+/* [N,C,H_in,W_in] -> [N,C,H_out,W_out] fp16, bilinear, align_corners = true, the reference's
+ * expression term for term — replaces rf::bilinear_upsample, dpt.h:29-31, dpt.cu:240-286 */
+int rfk_bilinear_upsample(const rfk_half* in, rfk_half* out, int N, int C, int H_in, int W_in,
+                          int H_out, int W_out, rfk_stream_t stream);
+/* x = x * sigmoid(x) in place, fp16 — replaces rf::silu_inplace, dpt.h:34, dpt.cu:289-301 */
+int rfk_silu_inplace(rfk_half* x, long long n, rfk_stream_t stream);
+/* x[n,c,:] += bias[c] over [N,C,HW] fp16 (one rounding) — replaces add_bias_nchw_kernel,
+ * dpt.cu:88-96 (file-local in the reference, launched from conv2d / conv_transpose2d) */
+int rfk_add_bias_nchw(rfk_half* x, const rfk_half* bias, int N, int C, long long HW,
+                      rfk_stream_t stream);
+/* [B,S,D] -> [B,D,S] (= [B,D,pH,pW] with S = pH*pW) — replaces permute_bsd_to_nchw,
+ * dpt.cu:303-318 (file-local in the reference, launched from dpt_forward) */
+int rfk_permute_bsd_to_nchw(const rfk_half* in, rfk_half* out, int B, int S, int D,
+                            rfk_stream_t stream);
+
 /* y32 = 10^float(half(elu(x16))) - 1 in one launch — replaces the chain
  * elu -> k_fp16_to_fp32_s -> pow10_minus1, src/pipeline/render_session.cu:249-253 */
 int rfk_post_elu_pow10(const rfk_half* x, float* y, long long n, float alpha,

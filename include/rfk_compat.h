@@ -131,6 +131,15 @@ inline void pow10_minus1(const float* x, float* y, int n, cudaStream_t stream = 
     RFK_COMPAT_CALL(rfk_pow10_minus1(x, y, n, stream));
 }
 
+/* src/layers/dpt.h:29-34 (the element-wise operators of the DPT head; its convolutions stay library calls) */
+inline void bilinear_upsample(const half* in, half* out, int N, int C, int H_in, int W_in, int H_out, int W_out,
+                              cudaStream_t stream = nullptr) {
+    RFK_COMPAT_CALL(rfk_bilinear_upsample(rfk_detail::h(in), rfk_detail::h(out), N, C, H_in, W_in, H_out, W_out, stream));
+}
+inline void silu_inplace(half* x, int n, cudaStream_t stream = nullptr) {
+    RFK_COMPAT_CALL(rfk_silu_inplace(rfk_detail::h(x), n, stream));
+}
+
 /* src/kernels/ray_gen.h:11 */
 inline void ray_gen(const float* c2w, const float* fov, float* rays_o, half* rays_d, int batch, int img_res,
                     cudaStream_t stream = nullptr) {

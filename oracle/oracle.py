@@ -243,6 +243,30 @@ def post_elu_pow10(x, alpha=1e-3):
     lib().oracle_post_elu_pow10(_ptr(x), _ptr(o), L(x.size), Fl(alpha)); return o
 
 
+# ------------------------------------------------- DPT head glue
+
+
+def bilinear_upsample(x, H_out, W_out):
+    x = _c(x, f16); N, C, Hi, Wi = x.shape
+    o = np.empty((N, C, H_out, W_out), f16)
+    lib().oracle_bilinear_upsample(_ptr(x), _ptr(o), L(N * C), I(Hi), I(Wi), I(H_out), I(W_out)); return o
+
+
+def silu(x):
+    x = _c(x, f16); o = np.empty_like(x); lib().oracle_silu(_ptr(x), _ptr(o), L(x.size)); return o
+
+
+def add_bias_nchw(x, bias):
+    x = _c(x, f16).copy(); bias = _c(bias, f16); N, C = x.shape[:2]
+    lib().oracle_add_bias_nchw(_ptr(x), _ptr(bias), L(N), I(C), L(x.size // (N * C))); return x
+
+
+def permute_bsd_to_nchw(x):
+    x = _c(x, f16); B, S, D = x.shape
+    o = np.empty((B, D, S), f16)
+    lib().oracle_permute_bsd_to_nchw(_ptr(x), _ptr(o), L(B), L(S), L(D)); return o
+
+
 # ------------------------------------------------- per-view ray front end
 
 

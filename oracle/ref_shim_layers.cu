@@ -4,6 +4,7 @@
 // the reference's unmodified sources by oracle/Makefile into oracle/_ref/libref_layers.so.
 // Not part of the product.
 #include "layers/attention.h"
+#include "layers/dpt.h"
 #include "layers/linear.h"
 #include "layers/transformer.h"
 #include "kernels/rmsnorm.h"
@@ -46,6 +47,12 @@ void* ref_cublas_create(void) {
     return h;
 }
 void ref_cublas_destroy(void* h) { if (h) cublasDestroy((cublasHandle_t)h); }
+
+// glue operators of the DPT head that src/layers/dpt.h exports
+void ref_bilinear_upsample(const half* in, half* out, int N, int C, int H_in, int W_in, int H_out, int W_out, void* s) {
+    rf::bilinear_upsample(in, out, N, C, H_in, W_in, H_out, W_out, S(s));
+}
+void ref_silu_inplace(half* x, int n, void* s) { rf::silu_inplace(x, n, S(s)); }
 
 void ref_residual_add(half* y, const half* r, int n, void* s) { rf::residual_add(y, r, n, S(s)); }
 void ref_residual_add_f32(float* y, const float* r, int n, void* s) { rf::residual_add_f32(y, r, n, S(s)); }

@@ -386,6 +386,54 @@ void oracle_post_elu_pow10(const f16* x, float* y, long n, float alpha) {
     }
 }
 
+/* ------------------------------------------------- DPT head glue */
+
+/* src/layers/dpt.cu:240-277: NCHW fp16, align_corners = true */
+void oracle_bilinear_upsample(const f16* in, f16* out, long planes, int H_in, int W_in, int H_out, int W_out) {
+    const float h_scale = (H_out > 1) ? (float)(H_in - 1) / (H_out - 1) : 0.0f;
+    const float w_scale = (W_out > 1) ? (float)(W_in - 1) / (W_out - 1) : 0.0f;
+    PAR_FOR
+    for (long p = 0; p < planes; ++p) {
+        const f16* plane = in + p * H_in * W_in;
+        for (int ho = 0; ho < H_out; ++ho) {
+            float hf_in = ho * h_scale;
+            int h0 = (int)hf_in, h1 = h0 + 1 < H_in - 1 ? h0 + 1 : H_in - 1;
+            float hf = hf_in - h0;
+            for (int wo = 0; wo < W_out; ++wo) {
+                float wf_in = wo * w_scale;
+                int w0 = (int)wf_in, w1 = w0 + 1 < W_in - 1 ? w0 + 1 : W_in - 1;
+                float wf = wf_in - w0;
+                float v00 = (float)plane[h0 * W_in + w0], v01 = (float)plane[h0 * W_in + w1];
+                float v10 = (float)plane[h1 * W_in + w0], v11 = (float)plane[h1 * W_in + w1];
+                float val = v00 * (1 - hf) * (1 - wf) + v01 * (1 - hf) * wf + v10 * hf * (1 - wf) + v11 * hf * wf;
+                out[(p * H_out + ho) * W_out + wo] = (f16)val;
+            }
+        }
+    }
+}
+/* src/layers/dpt.cu:289-294 */
+void oracle_silu(const f16* x, f16* y, long n) {
+    for (long i = 0; i < n; ++i) {
+        float v = (float)x[i];
+        y[i] = (f16)(v / (1.0f + expf(-v)));
+    }
+}
+/* src/layers/dpt.cu:88-96 */
+void oracle_add_bias_nchw(f16* x, const f16* bias, long N, int C, long HW) {
+    for (long n = 0; n < N; ++n)
+        for (int c = 0; c < C; ++c)
+            for (long i = 0; i < HW; ++i) {
+                long o = (n * C + c) * HW + i;
+                x[o] = (f16)((float)x[o] + (float)bias[c]);
+            }
+}
+/* src/layers/dpt.cu:303-318: out[b,d,s] = in[b,s,d] */
+void oracle_permute_bsd_to_nchw(const f16* in, f16* out, long B, long S, long D) {
+    for (long b = 0; b < B; ++b)
+        for (long s = 0; s < S; ++s)
+            for (long d = 0; d < D; ++d) out[(b * D + d) * S + s] = in[(b * S + s) * D + d];
+}
+
 /* ------------------------------------------------- per-view ray front end */
 
 /* src/kernels/ray_gen.cu:25-44. patch_size == 0: rays_d [B,res,res,3]; otherwise tokens

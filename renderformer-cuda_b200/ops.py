@@ -294,6 +294,22 @@ def pow10_minus1(x, y, n):
     _call("rfk_pow10_minus1", _p(x, F, "x"), _p(y, F, "y"), n, _stream())
 
 
+def bilinear_upsample(inp, out, N, C, H_in, W_in, H_out, W_out):
+    _call("rfk_bilinear_upsample", _p(inp, H, "in"), _p(out, H, "out"), N, C, H_in, W_in, H_out, W_out, _stream())
+
+
+def silu_inplace(x, n):
+    _call("rfk_silu_inplace", _p(x, H, "x"), n, _stream())
+
+
+def add_bias_nchw(x, bias, N, C, HW):
+    _call("rfk_add_bias_nchw", _p(x, H, "x"), _p(bias, H, "bias"), N, C, HW, _stream())
+
+
+def permute_bsd_to_nchw(inp, out, B, S, D):
+    _call("rfk_permute_bsd_to_nchw", _p(inp, H, "in"), _p(out, H, "out"), B, S, D, _stream())
+
+
 def post_elu_pow10(x, y, n, alpha=1e-3):
     _call("rfk_post_elu_pow10", _p(x, H, "x"), _p(y, F, "y"), n, alpha, _stream())
 

@@ -755,6 +755,75 @@ case(name="post_elu_pow10", make=_post_make, oracle=_post_oracle, rfk=_post_rfk,
      kinds=dict(elu="exact", pow10="exact", fused="exact"),
      oracle_kinds=dict(elu="f16", pow10="f32", fused="f32"))
 
+# ------------------------------------------------------ DPT head glue (src/layers/dpt.cu)
+
+def _up_make(N, C, Hi, Wi, Ho, Wo):
+    def make(rng):
+        return dict(x=normal(rng, (N, C, Hi, Wi), np.float16, 1.0), Ho=Ho, Wo=Wo)
+    return make
+
+
+def _up_rfk(i):
+    import torch
+    x = _t(i["x"]); N, C, Hi, Wi = x.shape
+    o = torch.empty(N, C, i["Ho"], i["Wo"], device="cuda", dtype=torch.float16)
+    _ops().bilinear_upsample(x, o, N, C, Hi, Wi, i["Ho"], i["Wo"])
+    return dict(o=_n(o))
+
+
+def _up_ref(i):
+    import torch
+    x = _t(i["x"]); N, C, Hi, Wi = x.shape
+    o = torch.empty(N, C, i["Ho"], i["Wo"], device="cuda", dtype=torch.float16)
+    _ref().call("ref_bilinear_upsample", x, o, N, C, Hi, Wi, i["Ho"], i["Wo"])
+    return dict(o=_n(o))
+
+
+# the same expression compiled by the same compiler: exact GPU-vs-GPU; the CPU oracle does not contract to FMAs
+for shp in [(1, 3, 8, 8, 16, 16), (2, 5, 7, 9, 13, 20), (1, 4, 16, 16, 16, 16), (1, 2, 5, 6, 1, 1), (1, 6, 32, 32, 64, 64)]:
+    case(name="bilinear_upsample_" + "x".join(map(str, shp)), make=_up_make(*shp),
+         oracle=lambda i: dict(o=O.bilinear_upsample(i["x"], i["Ho"], i["Wo"])), rfk=_up_rfk, ref=_up_ref,
+         kinds=dict(o="exact"), oracle_kinds=dict(o="f16"))
+
+
+def _silu_rfk(i):
+    x = _t(i["x"]).clone(); _ops().silu_inplace(x, x.numel()); return dict(y=_n(x))
+
+
+def _silu_ref(i):
+    x = _t(i["x"]).clone(); _ref().call("ref_silu_inplace", x, x.numel()); return dict(y=_n(x))
+
+
+for n in (1, 1001, 32 * 24 * 24):
+    case(name=f"silu_inplace_n{n}", make=(lambda n: lambda rng: dict(x=normal(rng, (n,), np.float16, 2.0)))(n),
+         oracle=lambda i: dict(y=O.silu(i["x"])), rfk=_silu_rfk, ref=_silu_ref, kinds=dict(y="f16"))
+
+
+def _bias_rfk(i):
+    x = _t(i["x"]).clone(); N, C = x.shape[:2]
+    _ops().add_bias_nchw(x, _t(i["b"]), N, C, x.numel() // (N * C)); return dict(y=_n(x))
+
+
+for shp in [(2, 5, 7, 9), (1, 32, 16, 16), (3, 1, 1, 1)]:
+    case(name="add_bias_nchw_" + "x".join(map(str, shp)),
+         make=(lambda shp: lambda rng: dict(x=normal(rng, shp, np.float16, 1.0), b=normal(rng, (shp[1],), np.float16, 1.0)))(shp),
+         oracle=lambda i: dict(y=O.add_bias_nchw(i["x"], i["b"])), rfk=_bias_rfk, ref=None, kinds=dict(y="exact"),
+         oracle_kinds=dict(y="exact"))
+
+
+def _perm_rfk(i):
+    import torch
+    x = _t(i["x"]); B, S, D = x.shape
+    o = torch.empty(B, D, S, device="cuda", dtype=torch.float16)
+    _ops().permute_bsd_to_nchw(x, o, B, S, D); return dict(o=_n(o))
+
+
+for shp in [(1, 64, 64), (2, 49, 100), (1, 130, 33), (3, 1, 7)]:
+    case(name="permute_bsd_to_nchw_" + "x".join(map(str, shp)),
+         make=(lambda shp: lambda rng: dict(x=normal(rng, shp, np.float16, 1.0)))(shp),
+         oracle=lambda i: dict(o=O.permute_bsd_to_nchw(i["x"])), rfk=_perm_rfk, ref=None, kinds=dict(o="exact"),
+         oracle_kinds=dict(o="exact"))
+
 # ------------------------------------------------------ per-view ray front end
 
 def _ray_make(B, res):
