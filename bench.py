@@ -210,6 +210,12 @@ class RefBackend:
     def silu_mul(self, a, b, out):
         self.R.call("ref_fused_silu_mul", a, b, out, a.numel())
 
+    def bilinear_upsample(self, x, o, C, hi, ho):
+        self.R.call("ref_bilinear_upsample", x, o, 1, C, hi, hi, ho, ho, lib=self.R.layers())
+
+    def silu_inplace(self, x):
+        self.R.call("ref_silu_inplace", x, x.numel(), lib=self.R.layers())
+
 
 class RefViewPipeline:
     """Per-view decoder pipeline of the reference (oracle/ref_shim_layers.cu: ref_view_*)."""

@@ -22,45 +22,70 @@
 
 namespace rfk {
 
+// v00*(1-hf)*(1-wf) + v01*(1-hf)*wf + v10*hf*(1-wf) + v11*hf*wf with the roundings written out as nvcc
+// contracts the reference's expression: the second term is two rounded products, the first term's last
+// product is fused into it, then the third and fourth terms' last products are fused into the running
+// sum. Explicit here so that the pattern cannot change with the surrounding code; found by emulating
+// the candidate patterns on the CPU against the reference kernel's outputs, and checked bit for bit.
 __device__ __forceinline__ float bilerp_ref(float v00, float v01, float v10, float v11, float hf, float wf) {
-    return v00 * (1 - hf) * (1 - wf) + v01 * (1 - hf) * wf + v10 * hf * (1 - wf) + v11 * hf * wf;
+    const float omh = __fsub_rn(1.0f, hf), omw = __fsub_rn(1.0f, wf);
+    float s = __fmul_rn(__fmul_rn(v01, omh), wf);
+    s = __fmaf_rn(__fmul_rn(v00, omh), omw, s);
+    s = __fmaf_rn(__fmul_rn(v10, hf), omw, s);
+    s = __fmaf_rn(__fmul_rn(v11, hf), wf, s);
+    return s;
 }
 
-// one thread = 8 consecutive output pixels of one output row (fewer at the end of a ragged row)
+// One thread = 8 consecutive output columns x kUpRows consecutive output rows of one plane: the column
+// arithmetic (two int <-> float conversions per column, which run on the 16-per-clock conversion
+// unit) is done once and reused for every row, the row arithmetic once per 8 outputs.
+constexpr int kUpRows = 4;
 __global__ void __launch_bounds__(256)
 bilinear_upsample_kernel(const __half* __restrict__ in, __half* __restrict__ out, long long planes, int H_in, int W_in,
                          int H_out, int W_out, int vec) {
-    const int cpr = (W_out + 7) / 8;  // chunks per output row
+    const int cpr = (W_out + 7) / 8;                    // column chunks per output row
+    const int rpp = (H_out + kUpRows - 1) / kUpRows;    // row groups per plane
     const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= planes * H_out * cpr) return;
+    if (c >= planes * rpp * cpr) return;
     const int w0o = (int)(c % cpr) * 8;
-    const long long row = c / cpr;
-    const int h_out = (int)(row % H_out);
-    const long long plane = row / H_out;
+    const long long rg = c / cpr;
+    const int h_out0 = (int)(rg % rpp) * kUpRows;
+    const long long plane = rg / rpp;
     const float h_scale = (H_out > 1) ? (float)(H_in - 1) / (H_out - 1) : 0.0f;
     const float w_scale = (W_out > 1) ? (float)(W_in - 1) / (W_out - 1) : 0.0f;
-    const float h_in_f = h_out * h_scale;
-    const int h0 = (int)h_in_f;
-    const int h1 = min(h0 + 1, H_in - 1);
-    const float hf = h_in_f - h0;
-    const __half* r0 = in + (plane * H_in + h0) * W_in;
-    const __half* r1 = in + (plane * H_in + h1) * W_in;
-    __half* o = out + (plane * H_out + h_out) * (long long)W_out + w0o;
-    float v[8];
+    int w0[8];
+    float wf[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int w_out = min(w0o + i, W_out - 1);
         const float w_in_f = w_out * w_scale;
-        const int w0 = (int)w_in_f;
-        const int w1 = min(w0 + 1, W_in - 1);
-        const float wf = w_in_f - w0;
-        v[i] = bilerp_ref(__half2float(__ldg(r0 + w0)), __half2float(__ldg(r0 + w1)), __half2float(__ldg(r1 + w0)),
-                          __half2float(__ldg(r1 + w1)), hf, wf);
+        w0[i] = (int)w_in_f;
+        wf[i] = w_in_f - w0[i];
     }
-    if (vec) {
-        store8(o, v);
-    } else {
-        for (int i = 0; i < 8 && w0o + i < W_out; ++i) o[i] = __float2half(v[i]);
+    const __half* pin = in + plane * H_in * W_in;
+#pragma unroll
+    for (int r = 0; r < kUpRows; ++r) {
+        const int h_out = h_out0 + r;
+        if (h_out >= H_out) break;
+        const float h_in_f = h_out * h_scale;
+        const int h0 = (int)h_in_f;
+        const int h1 = min(h0 + 1, H_in - 1);
+        const float hf = h_in_f - h0;
+        const __half* r0 = pin + (long long)h0 * W_in;
+        const __half* r1 = pin + (long long)h1 * W_in;
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int w1 = min(w0[i] + 1, W_in - 1);
+            v[i] = bilerp_ref(__half2float(__ldg(r0 + w0[i])), __half2float(__ldg(r0 + w1)),
+                              __half2float(__ldg(r1 + w0[i])), __half2float(__ldg(r1 + w1)), hf, wf[i]);
+        }
+        __half* o = out + (plane * H_out + h_out) * (long long)W_out + w0o;
+        if (vec) {
+            store8(o, v);
+        } else {
+            for (int i = 0; i < 8 && w0o + i < W_out; ++i) o[i] = __float2half(v[i]);
+        }
     }
 }
 
@@ -148,7 +173,7 @@ extern "C" int rfk_bilinear_upsample(const rfk_half* in, rfk_half* out, int N, i
     if (!in || !out || N < 0 || C < 0 || H_in <= 0 || W_in <= 0 || H_out <= 0 || W_out <= 0) return RFK_EINVAL;
     const long long planes = (long long)N * C;
     if (planes == 0) return RFK_OK;
-    const long long chunks = planes * H_out * ((W_out + 7) / 8);
+    const long long chunks = planes * ((H_out + kUpRows - 1) / kUpRows) * ((W_out + 7) / 8);
     if (chunks > 0x7fffffffLL * 256) return RFK_EUNSUPPORTED;
     const int vec = (W_out % 8 == 0) && aligned16(out);
     bilinear_upsample_kernel<<<(unsigned)ceil_div(chunks, 256), 256, 0, as_stream(stream)>>>(

@@ -140,6 +140,16 @@ def suite() -> list[Entry]:
                    2 * 4096 * 1024 * 2 + 2 * 4096 * HD * 2 + 4096, qproj_set(1), "qkv_epilogue"))
     e.append(Entry("qkv_norm_rope_transpose swin q,k,v [4096x3072 -> 3x16x4096x64, q,k norm]", 5,
                    2 * 4096 * 3072 * 2 + 2 * 4096, qproj_set(3), "qkv_epilogue"))
+    # element-wise operators of the DPT head at the sizes of a 512x512 view (src/layers/dpt.cu)
+    def up_set(C, hi, ho):
+        return lambda: (_r((1, C, hi, hi), H16), torch.empty(1, C, ho, ho, device="cuda", dtype=H16), C, hi, ho)
+    e.append(Entry("bilinear_upsample [256 x 128^2 -> 256^2]", 5, 256 * (128 * 128 + 256 * 256) * 2, up_set(256, 128, 256), "bilinear_upsample"))
+    e.append(Entry("bilinear_upsample [256 x 256^2 -> 512^2]", 5, 256 * (256 * 256 + 512 * 512) * 2, up_set(256, 256, 512), "bilinear_upsample"))
+    e.append(Entry("silu_inplace [256 x 256^2]", 5, 2 * 256 * 256 * 256 * 2, lambda: (_r((256 * 256 * 256,), H16),), "silu_inplace"))
+    e.append(Entry("add_bias_nchw [256 x 256^2]", 5, 2 * 256 * 256 * 256 * 2 + 512,
+                   lambda: (_r((1, 256, 256, 256), H16), _r((256,), H16)), "add_bias_nchw"))
+    e.append(Entry("permute_bsd_to_nchw [4096 x 1024]", 5, 2 * 4096 * 1024 * 2,
+                   lambda: (_r((1, 4096, 1024), H16), torch.empty(1, 1024, 4096, device="cuda", dtype=H16)), "permute_bsd_to_nchw"))
     e.append(Entry("fused_silu_mul [4096x4096] fp16", 4, 3 * 4096 * 4096 * 2,
                    lambda: (_r((4096, 4096), H16), _r((4096, 4096), H16), torch.empty(4096, 4096, device="cuda", dtype=H16)),
                    "silu_mul"))
@@ -195,6 +205,18 @@ class RfkBackend:
             self.o.qkv_norm_rope_transpose(x, 1024, [gamma], outs, [1], c, s, 1, 4096, HEADS, HD)
         else:
             self.o.qkv_norm_rope_transpose(x, 3072, [gamma, gamma, None], outs, [0, 0, 0], None, None, 1, 4096, HEADS, HD)
+
+    def bilinear_upsample(self, x, o, C, hi, ho):
+        self.o.bilinear_upsample(x, o, 1, C, hi, hi, ho, ho)
+
+    def silu_inplace(self, x):
+        self.o.silu_inplace(x, x.numel())
+
+    def add_bias_nchw(self, x, b):
+        self.o.add_bias_nchw(x, b, 1, x.shape[1], x.shape[2] * x.shape[3])
+
+    def permute_bsd_to_nchw(self, x, o):
+        self.o.permute_bsd_to_nchw(x, o, 1, x.shape[1], x.shape[2])
 
     def rmsnorm_windows(self, x, r, gamma, y):
         self.o.rmsnorm_residual_f16_windows(x, r, gamma, y, 1, 64, 64, 1024, 8, 4, 1)
