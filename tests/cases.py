@@ -780,7 +780,8 @@ def _up_ref(i):
 
 
 # the same expression compiled by the same compiler: exact GPU-vs-GPU; the CPU oracle does not contract to FMAs
-for shp in [(1, 3, 8, 8, 16, 16), (2, 5, 7, 9, 13, 20), (1, 4, 16, 16, 16, 16), (1, 2, 5, 6, 1, 1), (1, 6, 32, 32, 64, 64)]:
+for shp in [(1, 3, 8, 8, 16, 16), (2, 5, 7, 9, 13, 20), (1, 4, 16, 16, 16, 16), (1, 2, 5, 6, 1, 1), (1, 6, 32, 32, 64, 64),
+            (1, 2, 40, 150, 70, 300), (1, 1, 300, 40, 300, 264), (1, 2, 20, 30, 9, 44)]:
     case(name="bilinear_upsample_" + "x".join(map(str, shp)), make=_up_make(*shp),
          oracle=lambda i: dict(o=O.bilinear_upsample(i["x"], i["Ho"], i["Wo"])), rfk=_up_rfk, ref=_up_ref,
          kinds=dict(o="exact"), oracle_kinds=dict(o="f16"))
