@@ -9,16 +9,21 @@
 //   src/layers/attention.cu:476-576      swin_self_attention
 //   src/layers/transformer.cu:151-224    decoder_layer_forward_cached, encoder_layer_forward_mixed
 //
-// What is re-cut here (launches per decoder layer: ~36 in the reference, 21 here):
+// What is re-cut here (launches per decoder layer: ~36 in the reference, 15 here plus the
+// rotation of the cached keys, which the session runs on a parallel graph branch):
 //   - residual add + RMSNorm (+ fp16 cast) is one kernel; the FFN residual of a layer is
 //     deferred into the first norm of the next layer;
 //   - QK-RMSNorm + [B,S,H,D]->[B,H,S,D] + RoPE (+ QKV de-interleave) is one kernel;
 //   - the cached K is rotated out of place (no device-to-device copy first);
-//   - softmax writes fp16 probabilities over its own fp32 score rows (no P buffer, no cast);
-//   - the PV GEMM of the cross-attention writes [B,Sq,H*D] directly (no transpose back);
-//   - w1 and w3 run as one GEMM when stored back to back; the gate overwrites its own input;
-//   - cyclic shift + window partition, and window reverse + un-shift + residual add, are one
-//     kernel each.
+//   - attention is one fused kernel whenever head_dim is 64 or 128 (rfk_flash_attention: no
+//     score matrix, output written [B,Sq,H*D] directly); other head sizes keep GEMM -> softmax
+//     (fp16 probabilities over its own fp32 score rows) -> GEMM;
+//   - swin attention with 64-token windows and head_dim 64 is one kernel per layer
+//     (rfk_window_attention); cyclic shift + window partition are folded into the norm before
+//     it, window reverse + un-shift + residual add into the norm after it
+//     (rfk_rmsnorm_residual_f16_windows); other window / head sizes keep the gather ->
+//     GEMM -> softmax -> GEMM -> scatter sequence;
+//   - w1 and w3 run as one GEMM when stored back to back; the gate overwrites its own input.
 #include "layers_internal.h"
 
 #include <algorithm>
