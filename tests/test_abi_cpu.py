@@ -58,6 +58,16 @@ def test_null_and_bad_shapes_are_rejected_without_a_device():
     assert lib.rfk_window_attention(fake, fake, fake, fake, null, 4, 2, 49, 64, 4, 0.125, null) == -2  # 7x7 windows
     assert lib.rfk_rmsnorm_residual_f16_windows(fake, fake, fake, fake, 1, 10, 10, 64, 4, 0, 1, 1e-3, null) == -1
     assert lib.rfk_rmsnorm_residual_f16_windows(fake, fake, fake, ctypes.c_void_p(512), 1, 8, 8, 60, 4, 0, 3, 1e-3, null) == -1
+    # DPT head glue: null pointers, non-positive extents; empty problems are successes
+    assert lib.rfk_bilinear_upsample(null, fake, 1, 1, 4, 4, 8, 8, null) == -1
+    assert lib.rfk_bilinear_upsample(fake, fake, 1, 1, 4, 0, 8, 8, null) == -1
+    assert lib.rfk_bilinear_upsample(fake, fake, 0, 3, 4, 4, 8, 8, null) == 0
+    assert lib.rfk_silu_inplace(null, 8, null) == -1
+    assert lib.rfk_silu_inplace(fake, 0, null) == 0
+    assert lib.rfk_add_bias_nchw(fake, null, 1, 2, 16, null) == -1
+    assert lib.rfk_add_bias_nchw(fake, fake, 1, 0, 16, null) == -1
+    assert lib.rfk_permute_bsd_to_nchw(fake, null, 1, 4, 4, null) == -1
+    assert lib.rfk_permute_bsd_to_nchw(fake, fake, 1, 0, 4, null) == 0
     assert lib.rfk_launch_count() == 0
 
 
