@@ -37,24 +37,26 @@ __device__ int g_attn_tc_error = 0;  // first time-out / failure code seen by an
 namespace tcattn {
 
 constexpr int BM = 128, BN = 64, HD = 64;
-constexpr int kThreads = 224;
+constexpr int kBlocks = 2;                     // 128-query blocks per CTA, sharing the K/V ring
+constexpr int kThreads = 416;                  // warps 0-7 softmax (block = warp / 4), 8 producer, 9-10 PV, 11-12 QK issuers
 constexpr int kStages = 6;
 constexpr int kQBytes = BM * HD * 2;           // 16 KB
 constexpr int kKBytes = BN * HD * 2;           // 8 KB; a stage is K then V
 constexpr int kStageBytes = 2 * kKBytes;
 constexpr int kSBufs = 3;                      // score buffers in tensor memory
-constexpr int kTmemCols = 256;                 // S0, S1, S2 at +0, +64, +128; O at +192
+constexpr int kTmemCols = 512;                 // per block: S0, S1, S2 at +0, +64, +128; O at +192
 
 struct __align__(8) Ctrl {
-    uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[kSBufs], p_full[kSBufs], pv_done[kSBufs];
+    uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[kBlocks][kSBufs], p_full[kBlocks][kSBufs],
+        pv_done[kBlocks][kSBufs];
     uint32_t tmem_base;
     int abort;
 };
 
 // The shared-memory window is declared 1024-byte aligned (swizzled tiles need it) and the kernel checks it.
-constexpr int kSmemBytes = kQBytes + kStages * kStageBytes + 256;
+constexpr int kSmemBytes = kBlocks * kQBytes + kStages * kStageBytes + 256;
 static_assert(sizeof(Ctrl) <= 256, "control block");
-static_assert(2 * (kSmemBytes + 1024) <= 228 * 1024, "two CTAs per SM");
+static_assert(kSmemBytes + 1024 <= 227 * 1024, "one CTA per SM");
 
 enum : int { kErrTimeout = 1, kErrSmemAlign = 2 };
 
@@ -135,7 +137,7 @@ __device__ __forceinline__ void exp_half(uint32_t (&v)[32], uint32_t* pk /* may 
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, __half* __restrict__ O, int H, int Sq, int n_keys,
                     int o_bshd, float scale_log2e) {
@@ -145,21 +147,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (threadIdx.x == 0) atomicCAS(&g_attn_tc_error, 0, kErrSmemAlign);
         return;
     }
-    const uint32_t sQ = base, sKV = base + kQBytes;
-    Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_raw + kQBytes + kStages * kStageBytes);
+    const uint32_t sQ = base, sKV = base + kBlocks * kQBytes;
+    Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_raw + kBlocks * kQBytes + kStages * kStageBytes);
     volatile int* abort_flag = &ctrl->abort;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int q0 = blockIdx.x * BM;
+    const int q0 = blockIdx.x * (kBlocks * BM);
     const int bh = blockIdx.y;
     const int n_tiles = (n_keys + BN - 1) / BN;
 
     if (tid == 0) {
         tc::mbar_init(&ctrl->q_full, 1);
-        for (int s = 0; s < kStages; ++s) { tc::mbar_init(&ctrl->kv_full[s], 1); tc::mbar_init(&ctrl->kv_empty[s], 1); }
-        for (int b = 0; b < kSBufs; ++b) {
-            tc::mbar_init(&ctrl->s_full[b], 1); tc::mbar_init(&ctrl->p_full[b], 4); tc::mbar_init(&ctrl->pv_done[b], 1);
-        }
+        for (int s = 0; s < kStages; ++s) { tc::mbar_init(&ctrl->kv_full[s], 1); tc::mbar_init(&ctrl->kv_empty[s], kBlocks); }
+        for (int k = 0; k < kBlocks; ++k)
+            for (int b = 0; b < kSBufs; ++b) {
+                tc::mbar_init(&ctrl->s_full[k][b], 1); tc::mbar_init(&ctrl->p_full[k][b], 4); tc::mbar_init(&ctrl->pv_done[k][b], 1);
+            }
         ctrl->abort = 0;
         tc::fence_barrier_init();
     }
@@ -170,15 +173,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     tc::tc_fence_before();
     __syncthreads();
     tc::tc_fence_after();
-    const uint32_t tmem = ctrl->tmem_base;
-    const uint32_t tmem_O = tmem + kSBufs * 64;
+    const uint32_t tmem_cta = ctrl->tmem_base;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------------------------------------ producer (one thread)
         if (lane == 0) {
             tc::prefetch_tensormap(&map_q); tc::prefetch_tensormap(&map_k); tc::prefetch_tensormap(&map_v);
-            tc::mbar_arrive_expect_tx(&ctrl->q_full, kQBytes);
-            tc::tma_load_3d(sQ, &map_q, 0, q0, bh, &ctrl->q_full);
+            tc::mbar_arrive_expect_tx(&ctrl->q_full, kBlocks * kQBytes);
+            for (int k = 0; k < kBlocks; ++k) tc::tma_load_3d(sQ + k * kQBytes, &map_q, 0, q0 + k * BM, bh, &ctrl->q_full);
             for (int j = 0; j < n_tiles; ++j) {
                 const int s = j % kStages;
                 // stage s was last read by the products of tile j - kStages (phase j / kStages - 1 of kv_empty[s])
@@ -189,7 +191,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
         }
         __syncwarp();
-    } else if (warp == 5) {
+    } else if (warp == 9 || warp == 10) {
+        const int blk = warp - 9;
+        const uint32_t tmem = tmem_cta + blk * 256, tmem_O = tmem + kSBufs * 64;
         // ------------------------------------------------------------ issuer of O += P V (one thread)
         // tile j: score buffer j % kSBufs (its use number j / kSBufs gives the barrier phase), ring stage j % kStages
         if (lane == 0) {
@@ -198,7 +202,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             bool ok = true;
             int buf = 0, buf_par = 0, st = 0;
             for (int j = 0; ok && j < n_tiles; ++j) {
-                ok = tc::mbar_wait(&ctrl->p_full[buf], buf_par, abort_flag);
+                ok = tc::mbar_wait(&ctrl->p_full[blk][buf], buf_par, abort_flag);
                 if (!ok) break;
                 tc::tc_fence_after();
                 const uint32_t p_tmem = tmem + buf * 64, vt_lo = v_lo + st * (kStageBytes >> 4);
@@ -206,42 +210,46 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 for (int ks = 0; ks < BN / 16; ++ks)  // P: 16 keys = 8 columns; V: 16 keys = 16 rows of 128 bytes
                     tc::umma_f16_ts_lo(tmem_O, p_tmem + ks * 8, vt_lo + ks * (2048 >> 4), idesc_pv, (j > 0) || (ks > 0));
                 tc::umma_commit(&ctrl->kv_empty[st]);  // K of this stage was consumed before its scores could be read
-                tc::umma_commit(&ctrl->pv_done[buf]);
+                tc::umma_commit(&ctrl->pv_done[blk][buf]);
                 if (++buf == kSBufs) { buf = 0; buf_par ^= 1; }
                 if (++st == kStages) st = 0;
             }
         }
         __syncwarp();
-    } else if (warp == 6) {
+    } else if (warp == 11 || warp == 12) {
+        const int blk = warp - 11;
+        const uint32_t tmem = tmem_cta + blk * 256;
         // ------------------------------------------------------------ issuer of S = Q K^T (one thread)
         if (lane == 0) {
             constexpr uint32_t idesc_qk = tc::umma_idesc_f16(BM, BN, 0);  // B = K tile, K-major
-            const uint32_t q_lo = tc::umma_desc_lo(sQ), k_lo = tc::umma_desc_lo(sKV);
+            const uint32_t q_lo = tc::umma_desc_lo(sQ + blk * kQBytes), k_lo = tc::umma_desc_lo(sKV);
             bool ok = tc::mbar_wait(&ctrl->q_full, 0, abort_flag);
             int buf = 0, buf_par = 0, st = 0, st_par = 0;
             for (int j = 0; ok && j < n_tiles; ++j) {
                 ok = tc::mbar_wait(&ctrl->kv_full[st], st_par, abort_flag);
                 // the buffer still holds P of tile j - kSBufs until that tile's P V is complete
-                if (ok && j >= kSBufs) ok = tc::mbar_wait(&ctrl->pv_done[buf], buf_par ^ 1, abort_flag);
+                if (ok && j >= kSBufs) ok = tc::mbar_wait(&ctrl->pv_done[blk][buf], buf_par ^ 1, abort_flag);
                 if (!ok) break;
                 tc::tc_fence_after();
                 const uint32_t kt_lo = k_lo + st * (kStageBytes >> 4);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks)  // 16 head-dim elements = 32 bytes along a row
                     tc::umma_f16_lo(tmem + buf * 64, q_lo + ks * 2, kt_lo + ks * 2, idesc_qk, ks > 0);
-                tc::umma_commit(&ctrl->s_full[buf]);
+                tc::umma_commit(&ctrl->s_full[blk][buf]);
                 if (++buf == kSBufs) { buf = 0; buf_par ^= 1; }
                 if (++st == kStages) { st = 0; st_par ^= 1; }
             }
         }
         __syncwarp();
     }
-    else {
-        // ------------------------------------------------------------ softmax, warps 0-3
+    else if (warp < 8) {
+        // ------------------------------------------------------------ softmax, warps 0-7 (query block = warp / 4)
         constexpr unsigned kFull = 0xffffffffu;
         constexpr float kRescaleThreshold = 8.0f;  // in exponent units: P stays below 2^8, well inside fp16
-        const int r = tid;                                          // query row of this thread = its tensor-memory lane
-        const uint32_t lane_off = (uint32_t)(warp * 32) << 16;      // a warp reaches lanes [32 * (warp % 4), +32)
+        const int blk = warp >> 2;
+        const int r = (warp & 3) * 32 + lane;                       // query row within the block = its tensor-memory lane
+        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;  // a warp reaches lanes [32 * (warp % 4), +32)
+        const uint32_t tmem = tmem_cta + blk * 256, tmem_O = tmem + kSBufs * 64;
         const uint32_t tO = tmem_O + lane_off;
         float m_run = -INFINITY, l_run = 0.0f;
         uint32_t va[32], vb[32];
@@ -249,7 +257,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         int buf = 0, buf_par = 0;  // score buffer of tile j and the phase parity of its barriers
         for (int j = 0; j < n_tiles; ++j) {
             const uint32_t tS = tmem + lane_off + buf * 64;
-            ok = tc::mbar_wait_warp(&ctrl->s_full[buf], buf_par, abort_flag);
+            ok = tc::mbar_wait_warp(&ctrl->s_full[blk][buf], buf_par, abort_flag);
             if (!ok) break;
             tc::tc_fence_after();
             tc::tmem_ld32(tS, va);
@@ -300,7 +308,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 // O belongs to the tensor core until the previous tile's P V is done. Having seen s_full of tile j,
                 // P V of tile j - 4 (the previous phase of this barrier) is known complete: the parity is unambiguous.
                 const int pbuf = buf == 0 ? kSBufs - 1 : buf - 1, pbuf_par = buf == 0 ? buf_par ^ 1 : buf_par;  // of tile j - 1
-                ok = tc::mbar_wait_warp(&ctrl->pv_done[pbuf], pbuf_par, abort_flag);
+                ok = tc::mbar_wait_warp(&ctrl->pv_done[blk][pbuf], pbuf_par, abort_flag);
                 if (!ok) break;
                 tc::tc_fence_after();
 #pragma unroll
@@ -318,18 +326,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tc::tc_wait_st();
             tc::tc_fence_before();    // the writes of P and O come before the arrival
             __syncwarp();
-            if (lane == 0) tc::mbar_arrive(&ctrl->p_full[buf]);
+            if (lane == 0) tc::mbar_arrive(&ctrl->p_full[blk][buf]);
             if (++buf == kSBufs) { buf = 0; buf_par ^= 1; }
         }
         // ---- epilogue: O / l -> fp16 -> global, one 128-byte row per thread
         if (ok) {  // buf / buf_par have moved on to tile n_tiles: step back to the last tile
             const int lbuf = buf == 0 ? kSBufs - 1 : buf - 1, lbuf_par = buf == 0 ? buf_par ^ 1 : buf_par;
-            ok = tc::mbar_wait_warp(&ctrl->pv_done[lbuf], lbuf_par, abort_flag);
+            ok = tc::mbar_wait_warp(&ctrl->pv_done[blk][lbuf], lbuf_par, abort_flag);
         }
         if (ok) {
             tc::tc_fence_after();
             const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            const int q = q0 + r;
+            const int q = q0 + blk * BM + r;
             const int b = bh / H, h = bh % H;
             __half* dst = o_bshd ? O + (((size_t)b * Sq + q) * H + h) * HD : O + ((size_t)bh * Sq + q) * HD;
 #pragma unroll
@@ -356,7 +364,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncthreads();
     if (warp == 0) {
         tc::tc_fence_after();
-        tc::tmem_dealloc(tmem, kTmemCols);
+        tc::tmem_dealloc(tmem_cta, kTmemCols);
     }
     if (tid == 0 && ctrl->abort) atomicCAS(&g_attn_tc_error, 0, kErrTimeout);
 }
@@ -421,7 +429,7 @@ int launch_attention_tc(const __half* Q, const __half* K, const __half* V, __hal
     if (!make_map(&mq, Q, (long long)B * H, Sq, tcattn::BM) || !make_map(&mk, K, (long long)B * H, Sk, tcattn::BN) ||
         !make_map(&mv, V, (long long)B * H, Sk, tcattn::BN))
         return RFK_EUNSUPPORTED;
-    dim3 grid(ceil_div(Sq, tcattn::BM), B * H);
+    dim3 grid(ceil_div(Sq, tcattn::kBlocks * tcattn::BM), B * H);
     tcattn::attention_tc_kernel<<<grid, tcattn::kThreads, tcattn::kSmemBytes, st>>>(mq, mk, mv, O, H, Sq, n_keys, o_bshd,
                                                                                     scale * 1.4426950408889634f);
     return launch_status();
