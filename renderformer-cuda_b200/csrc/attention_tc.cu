@@ -4,28 +4,31 @@
 // the first n_keys keys, fp16 operands, fp32 accumulation, probabilities rounded to fp16.
 // Reference boundary: rf::sdpa, src/layers/attention.cu:89-166 of BANANASJIM/renderformer-cuda.
 //
-// One CTA = 128 queries of one head, keys in tiles of 64, 7 warps with fixed roles:
-//   warp 4     producer: one thread issues TMA tile loads (Q once, then K and V tiles through a
-//              ring of kStages shared-memory stages); the copies land in the tensor core's
-//              128-byte-swizzled layout and complete on mbarriers, no thread touches the bytes.
-//   warp 6     one thread issues S = Q K^T (tcgen05.mma M128 N64 K16 x 4) into one of three score
-//              buffers in tensor memory, as soon as the P V product that read that buffer's
-//              previous contents is complete: the softmax warps find their next two tiles ready
-//              and never wait for a product.
-//   warps 0-3  softmax: thread r owns query row r = its tensor-memory lane, so row maximum and
-//              row sum are thread-local (no shuffles). The 64 scores come to registers with
-//              tcgen05.ld; P = exp2(...) is rounded to fp16 and stored back with tcgen05.st over the
-//              first 32 columns of the same score buffer, from where
-//   warp 5     one thread issues O += P V with P as the A operand from tensor memory and V
-//              (MN-major) from shared memory: P never passes through shared memory. The output
-//              accumulator O (128 x 64 fp32 in tensor memory) is rescaled in place only when a
-//              row's running maximum has grown by more than 2^8 (the factor cancels in O / l).
-// The two products have separate issuing threads because one thread's instruction stream
-// (8 products, 3 commits and 2-3 waits per tile, all dependent) takes about as long as the
-// softmax of a tile; the order between them is kept by mbarriers, not by issue order.
-// Tensor memory: 256 columns per CTA (S0, S1, S2, O: 64 each); shared memory 16 KB (Q) + kStages x 16 KB:
-// two CTAs per SM. Every mbarrier wait is bounded; on a time-out the CTA raises an error word,
-// frees its tensor memory and returns.
+// One CTA = 256 queries of one head as two blocks of 128 that share the K/V tiles in shared
+// memory (every key tile is fetched once per CTA, i.e. half as often as with one block per CTA),
+// keys in tiles of 64, 13 warps with fixed roles:
+//   warp 8       producer: one thread issues TMA tile loads (both Q blocks once, then K and V tiles
+//                through a ring of kStages shared-memory stages); the copies land in the tensor
+//                core's 128-byte-swizzled layout and complete on mbarriers, no thread touches the bytes.
+//   warps 11-12  one thread per block issues S = Q K^T (tcgen05.mma M128 N64 K16 x 4) into one of
+//                the block's three score buffers in tensor memory, as soon as the P V product that
+//                read that buffer's previous contents is complete: the softmax warps find their
+//                next two tiles ready and never wait for a product.
+//   warps 0-7    softmax (block = warp / 4): a thread owns one query row = its tensor-memory lane,
+//                so row maximum and row sum are thread-local (no shuffles). The 64 scores come to
+//                registers with tcgen05.ld; P = exp2(...) is rounded to fp16 and stored back with
+//                tcgen05.st over the first 32 columns of the same score buffer, from where
+//   warps 9-10   one thread per block issues O += P V with P as the A operand from tensor memory
+//                and V (MN-major) from shared memory: P never passes through shared memory. The
+//                output accumulator O (128 x 64 fp32 per block) is rescaled in place only when a
+//                row's running maximum has grown by more than 2^8 (the factor cancels in O / l).
+// A stage of the ring is free again when both blocks' P V products of its tile are complete
+// (kv_empty counts two arrivals). The products have separate issuing threads because one thread's
+// instruction stream (8 products, 3 commits and 2-3 waits per tile, all dependent) takes about as
+// long as the softmax of a tile; the order between them is kept by mbarriers, not by issue order.
+// Tensor memory: all 512 columns (per block S0, S1, S2, O: 64 each); shared memory 32 KB (Q) +
+// kStages x 16 KB; one CTA per SM. Every mbarrier wait is bounded; on a time-out the CTA raises an
+// error word, frees its tensor memory and returns.
 #include <cuda.h>  // CUtensorMap and its enums; the encoder itself is looked up at run time
 #include "attention_tc.cuh"
 #include "common.cuh"
