@@ -149,6 +149,19 @@ int rfk_rope_one_oop(const rfk_half* src, rfk_half* dst,
                      int src_seq_stride, int dst_seq_stride, int copy_tail,
                      rfk_stream_t stream);
 
+/* The same rotation with explicit batch strides (in elements) for src, dst and the
+ * tables, so that one launch serves tensors that are not densely packed: the cached keys
+ * of several decoder layers, [layer][K|V][heads][rows][head_dim], are rotated by one
+ * shared table (table_batch_stride = 0) with batch = layers and src_batch_stride = two
+ * cache slabs. Replaces one cudaMemcpyAsync + apply_rope_one pair per decoder layer —
+ * src/layers/attention.cu:355-361. */
+int rfk_rope_one_oop_strided(const rfk_half* src, rfk_half* dst,
+                             const rfk_half* cos_vals, const rfk_half* sin_vals,
+                             int batch, long long src_batch_stride, long long dst_batch_stride,
+                             long long table_batch_stride, int num_heads, int seq_len,
+                             int head_dim, int src_seq_stride, int dst_seq_stride,
+                             rfk_stream_t stream);
+
 /* Fused projection epilogue: for each of the n_parts (1..3) column blocks of a
  * [B*S, row_stride] fp16 GEMM output (block p starts at column p*dim), do
  *   optional RMSNorm over the full dim-wide vector (gamma[p] != NULL),

@@ -97,8 +97,10 @@ int rfk_ffn_swiglu(rfk_ctx* ctx, const rfk_ffn_weights* w, const rfk_half* x, rf
 
 /* Scaled dot-product attention on [B,H,S,D] fp16 tensors, scale 1/sqrt(D):
  * batched GEMM into fp32 scores, rfk softmax (probabilities written as fp16 over the first
- * half of each score row), batched GEMM. Sk must be a multiple of 8.
- *   workspace: B*H*Sq*Sk floats.
+ * half of each score row), batched GEMM. Any Sk is accepted; score rows have a pitch of
+ * roundup8(Sk) floats, and roundup8(Sk) must not exceed 8192 (the softmax keeps a row in
+ * registers; larger shapes return RFK_EUNSUPPORTED before anything is launched).
+ *   workspace: B*H*Sq*roundup8(Sk) floats.
  *   n_keys: keys that take part in the softmax (<= Sk); keys [n_keys, Sk) get probability 0.
  *           n_keys == Sk reproduces the reference, which attends its zero pad keys.
  *   o_bshd != 0: O is written as [B,Sq,H*D] (saves the transpose that follows).
@@ -113,7 +115,9 @@ int rfk_sdpa(rfk_ctx* ctx, const rfk_half* Q, const rfk_half* K, const rfk_half*
  * capture, stream host callbacks, plug-in hosts with a fixed memory budget): the fp32 score
  * matrix lives in a 32 MiB array inside the library instead of a caller-supplied workspace,
  * so B*H*Sq*roundup8(Sk) must not exceed 8 Mi (8388608) floats; larger shapes return
- * RFK_ETOOBIG. The call allocates and frees nothing. The first call on each device looks up
+ * RFK_ETOOBIG (and roundup8(Sk) > 8192 returns RFK_EUNSUPPORTED, as for rfk_sdpa). The device
+ * that is current at the call must be the one ctx was created on (RFK_EINVAL otherwise).
+ * The call allocates and frees nothing. The first call on each device looks up
  * the array's device address (cudaGetSymbolAddress, with that device current) and should
  * therefore be made before any stream capture begins; later calls only launch. All calls on
  * a device share the one array: it keeps the previous call's contents (no call depends on
@@ -133,7 +137,8 @@ int rfk_precompute_cross_kv(rfk_ctx* ctx, const rfk_cross_attn_weights* w,
                             int num_heads, rfk_stream_t stream);
 
 /* Cross-attention of q_in [B*Sq, q_dim] against cached K/V [B,H,Sk,D] (Sk a multiple of 8).
- * proj_buf: (2*B*Sq*dim + B*H*Sk*D) halves; score_buf: B*H*Sq*Sk floats, or NULL when the head
+ * proj_buf: (2*B*Sq*dim + max(B*Sq*dim, B*H*Sk*D)) halves (the third region holds the rotated
+ * keys and, for shapes the fused Q epilogue does not serve, a [B*Sq, dim] staging copy); score_buf: B*H*Sq*Sk floats, or NULL when the head
  * size is 64 or 128 (rfk_flash_attention then serves the attention and no score matrix exists;
  * with NULL any other head size returns RFK_EINVAL). The same holds for every score buffer below;
  * the swin score buffer may be NULL for 64-token windows of 64-wide heads.
@@ -281,7 +286,11 @@ int rfk_session_wait(rfk_session* s, float* ms);
  * [(img_res/patch)^2, dim] fp16 (the DPT image head is outside this library). */
 int rfk_session_result(rfk_session* s, const rfk_half** tokens, int* n_tokens, int* dim);
 /* Device pointers of the 4 decoder feature taps a DPT head consumes (layers at 1/4, 1/2, 3/4
- * and the end of the stack; render_session.cu:235-238). */
+ * and the end of the stack; render_session.cu:235-238), for the LAST submitted frame. Each of
+ * the two frame slots has its own set of taps: the pointers stay valid, and their contents
+ * untouched, until the second rfk_session_render_frame call after the one that produced them
+ * (the same lifetime as the slot's result buffer). The frame must have completed
+ * (rfk_session_wait) before a consumer on another stream reads them. */
 int rfk_session_feature_taps(rfk_session* s, const rfk_half** taps /* HOST array of 4 */);
 /* Copies the last frame's token map to HOST memory (waits for the frame).
  * replaces rf::RenderSession::download_frame_hwc — render_session.cu:550-559 */

@@ -2,7 +2,7 @@
 #include "common.cuh"
 
 namespace rfk {
-unsigned long long g_launches = 0;
+std::atomic<unsigned long long> g_launches{0};
 }
 
 extern "C" const char* rfk_version(void) { return "rfk 0.1 sm_100a"; }
@@ -20,4 +20,4 @@ extern "C" const char* rfk_status_string(int status) {
     return "unknown rfk status";
 }
 
-extern "C" unsigned long long rfk_launch_count(void) { return rfk::g_launches; }
+extern "C" unsigned long long rfk_launch_count(void) { return rfk::g_launches.load(std::memory_order_relaxed); }

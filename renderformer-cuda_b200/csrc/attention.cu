@@ -412,7 +412,7 @@ window_attention_kernel(const __half* __restrict__ Q, const __half* __restrict__
 }
 
 // attention_tc.cu
-extern int g_attn_path;
+extern std::atomic<int> g_attn_path;
 int launch_attention_tc(const __half* Q, const __half* K, const __half* V, __half* O, int B, int H, int Sq, int Sk,
                         int n_keys, int o_bshd, float scale, cudaStream_t st);
 
@@ -430,10 +430,11 @@ extern "C" int rfk_flash_attention(const rfk_half* Q, const rfk_half* K, const r
     if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O)) return RFK_EUNSUPPORTED;
     cudaStream_t st = as_stream(stream);
     const long long kvs = (long long)Sk * D;
-    if (D == 64 && g_attn_path != 1) {  // tcgen05 kernel; in automatic mode the mma.sync kernel takes over if it cannot run
+    const int path = g_attn_path.load(std::memory_order_relaxed);
+    if (D == 64 && path != 1) {  // tcgen05 kernel; in automatic mode the mma.sync kernel takes over if it cannot run
         const int rc = launch_attention_tc((const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, B, H, Sq, Sk,
                                            n_keys, o_bshd, scale, st);
-        if (rc != RFK_EUNSUPPORTED || g_attn_path == 2) return rc;
+        if (rc != RFK_EUNSUPPORTED || path == 2) return rc;
     }
     if (D == 64)
         return launch_flash<64>((const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, B, H, Sq, Sk, n_keys, kvs,

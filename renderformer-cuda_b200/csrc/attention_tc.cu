@@ -52,13 +52,14 @@ constexpr int kTmemCols = 512;                 // per block: S0, S1, S2 at +0, +
 struct __align__(8) Ctrl {
     uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[kBlocks][kSBufs], p_full[kBlocks][kSBufs],
         pv_done[kBlocks][kSBufs];
+    uint64_t drain[2 * kBlocks];  // abort path only, one per issuing thread: completes once that thread's products have finished
     uint32_t tmem_base;
     int abort;
 };
 
 // The shared-memory window is declared 1024-byte aligned (swizzled tiles need it) and the kernel checks it.
-constexpr int kSmemBytes = kBlocks * kQBytes + kStages * kStageBytes + 256;
-static_assert(sizeof(Ctrl) <= 256, "control block");
+constexpr int kSmemBytes = kBlocks * kQBytes + kStages * kStageBytes + 512;
+static_assert(sizeof(Ctrl) <= 512, "control block");
 static_assert(kSmemBytes + 1024 <= 227 * 1024, "one CTA per SM");
 
 enum : int { kErrTimeout = 1, kErrSmemAlign = 2 };
@@ -166,6 +167,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             for (int b = 0; b < kSBufs; ++b) {
                 tc::mbar_init(&ctrl->s_full[k][b], 1); tc::mbar_init(&ctrl->p_full[k][b], 4); tc::mbar_init(&ctrl->pv_done[k][b], 1);
             }
+        for (int k = 0; k < 2 * kBlocks; ++k) tc::mbar_init(&ctrl->drain[k], 1);
         ctrl->abort = 0;
         tc::fence_barrier_init();
     }
@@ -184,6 +186,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tc::prefetch_tensormap(&map_q); tc::prefetch_tensormap(&map_k); tc::prefetch_tensormap(&map_v);
             tc::mbar_arrive_expect_tx(&ctrl->q_full, kBlocks * kQBytes);
             for (int k = 0; k < kBlocks; ++k) tc::tma_load_3d(sQ + k * kQBytes, &map_q, 0, q0 + k * BM, bh, &ctrl->q_full);
+            int issued = 0;
             for (int j = 0; j < n_tiles; ++j) {
                 const int s = j % kStages;
                 // stage s was last read by the products of tile j - kStages (phase j / kStages - 1 of kv_empty[s])
@@ -191,6 +194,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 tc::mbar_arrive_expect_tx(&ctrl->kv_full[s], kStageBytes);
                 tc::tma_load_3d(sKV + s * kStageBytes, &map_k, 0, j * BN, bh, &ctrl->kv_full[s]);
                 tc::tma_load_3d(sKV + s * kStageBytes + kKBytes, &map_v, 0, j * BN, bh, &ctrl->kv_full[s]);
+                issued = j + 1;
+            }
+            if (*abort_flag) {
+                // The CTA is giving up. Every copy this thread started lands in this CTA's shared memory and counts
+                // on a kv_full / q_full barrier: wait (bounded) for the last copy of each stage before the CTA exits.
+                tc::mbar_wait_drain(&ctrl->q_full, 0);
+                for (int s = 0; s < kStages && s < issued; ++s) {
+                    const int last = ((issued - 1 - s) / kStages) * kStages + s;  // last tile loaded into stage s
+                    tc::mbar_wait_drain(&ctrl->kv_full[s], (last / kStages) & 1);
+                }
             }
         }
         __syncwarp();
@@ -217,6 +230,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (++buf == kSBufs) { buf = 0; buf_par ^= 1; }
                 if (++st == kStages) st = 0;
             }
+            if (*abort_flag) {  // giving up: let this thread's products finish before tensor memory is freed
+                tc::umma_commit(&ctrl->drain[blk]);
+                tc::mbar_wait_drain(&ctrl->drain[blk], 0);
+            }
         }
         __syncwarp();
     } else if (warp == 11 || warp == 12) {
@@ -241,6 +258,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 tc::umma_commit(&ctrl->s_full[blk][buf]);
                 if (++buf == kSBufs) { buf = 0; buf_par ^= 1; }
                 if (++st == kStages) { st = 0; st_par ^= 1; }
+            }
+            if (*abort_flag) {
+                tc::umma_commit(&ctrl->drain[kBlocks + blk]);
+                tc::mbar_wait_drain(&ctrl->drain[kBlocks + blk], 0);
             }
         }
         __syncwarp();
@@ -374,7 +395,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
 }  // namespace tcattn
 
-int g_attn_path = 0;  // 0 automatic, 1 mma.sync kernel, 2 tcgen05 kernel (head_dim 64 only)
+std::atomic<int> g_attn_path{0};  // 0 automatic, 1 mma.sync kernel, 2 tcgen05 kernel (head_dim 64 only)
 
 namespace {
 
@@ -414,19 +435,20 @@ bool make_map(CUtensorMap* m, const void* base, long long n_heads, long long row
 // Launches the tcgen05 kernel; the caller has validated pointers, alignment and sizes (D == 64).
 int launch_attention_tc(const __half* Q, const __half* K, const __half* V, __half* O, int B, int H, int Sq, int Sk,
                         int n_keys, int o_bshd, float scale, cudaStream_t st) {
-    static bool configured[64] = {};
+    // per-device "kernel attributes set" marks; setting them twice from racing threads is harmless
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= 64) return RFK_EUNSUPPORTED;
-    if (!configured[dev]) {
+    if (!configured[dev].load(std::memory_order_acquire)) {
         e = cudaFuncSetAttribute(tcattn::attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  tcattn::kSmemBytes);
         if (e != cudaSuccess) return (int)e;
         e = cudaFuncSetAttribute(tcattn::attention_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return (int)e;
-        configured[dev] = true;
+        configured[dev].store(true, std::memory_order_release);
     }
     CUtensorMap mq, mk, mv;
     if (!make_map(&mq, Q, (long long)B * H, Sq, tcattn::BM) || !make_map(&mk, K, (long long)B * H, Sk, tcattn::BN) ||
@@ -444,7 +466,7 @@ using namespace rfk;
 
 extern "C" int rfk_flash_attention_set_path(int path) {
     if (path < 0 || path > 2) return RFK_EINVAL;
-    g_attn_path = path;
+    g_attn_path.store(path, std::memory_order_relaxed);
     return RFK_OK;
 }
 

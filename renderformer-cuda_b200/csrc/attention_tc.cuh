@@ -51,6 +51,19 @@ __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, vola
     *abort = 1;
     return false;
 }
+// Used only on the way out of a CTA that has given up: waits (at most kDrainLimitNs) for asynchronous
+// work that this thread itself started - bulk copies into shared memory, tensor-core products - so that
+// nothing is still writing the CTA's shared or tensor memory when the CTA frees them. Ignores *abort.
+constexpr uint64_t kDrainLimitNs = 4ull * 1000 * 1000;
+__device__ __noinline__ bool mbar_wait_drain(uint64_t* bar, uint32_t parity) {
+    const uint64_t t0 = global_timer_ns();
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 15u) == 15u && global_timer_ns() - t0 > kDrainLimitNs) break;
+        __nanosleep(64);
+    }
+    return false;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
     if (mbar_try_wait(bar, parity)) return true;  // complete, or completed while this thread slept
     return mbar_wait_slow(bar, parity, abort);

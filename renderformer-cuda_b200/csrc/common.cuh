@@ -2,6 +2,7 @@
 #pragma once
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <atomic>
 #include <cfloat>
 #include <cstdint>
 #include "rfk.h"
@@ -16,11 +17,11 @@ constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs; grids are sized in multi
 
 // ---------------------------------------------------------------- host side
 
-extern unsigned long long g_launches;  // defined in abi.cu
+extern std::atomic<unsigned long long> g_launches;  // defined in abi.cu; launches may come from any host thread
 
 // Status of the most recent launch on this thread, mapped to the C-ABI convention.
 inline int launch_status() {
-    ++g_launches;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
     cudaError_t e = cudaPeekAtLastError();
     if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
     return RFK_OK;

@@ -27,6 +27,7 @@
 #include "layers_internal.h"
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 
 using namespace rfk_layers;
@@ -115,9 +116,10 @@ extern "C" int rfk_sdpa(rfk_ctx* ctx, const rfk_half* Q, const rfk_half* K, cons
     if (B < 0 || H <= 0 || Sq < 0 || Sk <= 0 || D <= 0 || n_keys <= 0 || n_keys > Sk) return RFK_EINVAL;
     if (mask) return RFK_EUNSUPPORTED;
     if (B == 0 || Sq == 0) return RFK_OK;
+    const int ld = (Sk + 7) & ~7;  // score row pitch in floats; P row pitch is 2*ld halves
+    if (ld > 8192) return RFK_EUNSUPPORTED;  // the in-place softmax holds a whole row in registers
     cudaStream_t st = (cudaStream_t)stream;
     TRY(blas_status(cublasSetStream(ctx->blas, st)));
-    const int ld = (Sk + 7) & ~7;  // score row pitch in floats; P row pitch is 2*ld halves
     const int BH = B * H;
     const float scale = 1.0f / sqrtf((float)D), zero = 0.0f, one = 1.0f;
     // scores[bh] (Sq x Sk, pitch ld) = scale * Q[bh] K[bh]^T
@@ -382,10 +384,10 @@ extern "C" int rfk_encoder_layer_forward_mixed(
 // ------------------------------------------------------------------------------------------
 // rfk_sdpa without a caller-supplied score buffer.
 //
-// Some callers of this library are not in a position to allocate device memory: code that
-// runs between cudaStreamBeginCapture and cudaStreamEndCapture (cudaMalloc is not permitted
-// there), host callbacks enqueued on a stream, and plug-in hosts that hand the library a fixed
-// set of tensors and forbid it to grow the process's memory. For them the fp32 score matrix of
+// Some callers of this library are not in a position to allocate device memory: host
+// callbacks enqueued on a stream (no CUDA allocation call is allowed there), code that runs
+// while another thread's stream capture forbids cudaMalloc, and plug-in hosts that hand the
+// library a fixed set of tensors and forbid it to grow the process's memory. For them the fp32 score matrix of
 // the attention lives in the library itself: a file-scope __device__ array of fixed size that
 // every GPU that loads this library holds until the process exits.
 constexpr size_t kStaticScoreFloats = 8u << 20;  // 8 Mi floats = 32 MiB
@@ -393,26 +395,35 @@ static __device__ __align__(256) float g_static_scores[kStaticScoreFloats];
 // In host code the array's name is only a handle for the symbol, not a device address: the
 // address is looked up once per device, with that device current, and cached here.
 constexpr int kMaxDevices = 64;
-static float* g_static_scores_addr[kMaxDevices] = {};
+static std::atomic<float*> g_static_scores_addr[kMaxDevices];
 
 extern "C" int rfk_sdpa_static(rfk_ctx* ctx, const rfk_half* Q, const rfk_half* K, const rfk_half* V,
                                rfk_half* O, int B, int H, int Sq, int Sk, int n_keys, int D, int o_bshd,
                                rfk_stream_t stream) {
-    if (B < 0 || H <= 0 || Sq < 0 || Sk <= 0) return RFK_EINVAL;
+    if (!ctx || !Q || !K || !V || !O) return RFK_EINVAL;
+    if (B < 0 || H <= 0 || Sq < 0 || Sk <= 0 || D <= 0 || n_keys <= 0 || n_keys > Sk) return RFK_EINVAL;
     const size_t ld = ((size_t)Sk + 7) & ~(size_t)7;
-    const size_t need = (size_t)B * H * Sq * ld;
-    if (need > kStaticScoreFloats) return RFK_ETOOBIG;  // B*H*Sq*roundup8(Sk) floats must fit in 32 MiB
+    if (ld > 8192) return RFK_EUNSUPPORTED;  // same limit as rfk_sdpa: the softmax keeps a row in registers
+    // B*H*Sq*roundup8(Sk) floats must fit in 32 MiB; each factor is bounded by division so that the
+    // product cannot wrap around for huge arguments
+    size_t room = kStaticScoreFloats / ld;
+    for (const int f : {B, H, Sq}) {
+        if (f == 0) return RFK_OK;  // nothing to compute
+        if ((size_t)f > room) return RFK_ETOOBIG;
+        room /= (size_t)f;
+    }
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
+    if (dev != ctx->device) return RFK_EINVAL;  // the array that is looked up below belongs to the current device
     if (dev < 0 || dev >= kMaxDevices) return RFK_EUNSUPPORTED;
-    if (!g_static_scores_addr[dev]) {
-        float* p = nullptr;
-        e = cudaGetSymbolAddress((void**)&p, g_static_scores);
+    float* scores = g_static_scores_addr[dev].load(std::memory_order_acquire);
+    if (!scores) {  // first call on this device (two threads racing here both store the same address)
+        e = cudaGetSymbolAddress((void**)&scores, g_static_scores);
         if (e != cudaSuccess) return (int)e;
-        g_static_scores_addr[dev] = p;
+        g_static_scores_addr[dev].store(scores, std::memory_order_release);
     }
     // Nothing in the array has to be cleared first: the score GEMM overwrites (beta = 0) every
     // element the softmax reads, and the softmax writes every element the second GEMM reads.
-    return rfk_sdpa(ctx, Q, K, V, O, g_static_scores_addr[dev], nullptr, B, H, Sq, Sk, n_keys, D, o_bshd, stream);
+    return rfk_sdpa(ctx, Q, K, V, O, scores, nullptr, B, H, Sq, Sk, n_keys, D, o_bshd, stream);
 }

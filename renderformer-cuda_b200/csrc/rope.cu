@@ -90,7 +90,8 @@ __global__ void __launch_bounds__(128)
 rope_apply_kernel(const T* src0, T* dst0, const T* src1, T* dst1,
                   const __half* __restrict__ cos_vals, const __half* __restrict__ sin_vals,
                   int batch, int num_heads, int seq_len, int rows_total, int head_dim,
-                  long long src_rows, long long dst_rows) {
+                  long long src_rows, long long dst_rows, long long src_bstride, long long dst_bstride,
+                  long long tab_bstride) {
     const int cpt = head_dim / 16;
     const int hgroups = num_heads / HP;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -107,7 +108,7 @@ rope_apply_kernel(const T* src0, T* dst0, const T* src1, T* dst1,
 
     float cl[8], sl[8], ch[8], sh[8];
     if (rotate) {
-        const size_t to = ((size_t)b * seq_len + s) * head_dim + j * 8;
+        const size_t to = (size_t)b * tab_bstride + (size_t)s * head_dim + j * 8;
         unpack8(ldg_half8(cos_vals + to), cl);
         unpack8(ldg_half8(sin_vals + to), sl);
         unpack8(ldg_half8(cos_vals + to + half_d), ch);
@@ -116,8 +117,8 @@ rope_apply_kernel(const T* src0, T* dst0, const T* src1, T* dst1,
 #pragma unroll
     for (int hh = 0; hh < HP; ++hh) {
         const int h = hg * HP + hh;
-        const size_t so = (((size_t)b * num_heads + h) * src_rows + s) * head_dim + j * 8;
-        const size_t dofs = (((size_t)b * num_heads + h) * dst_rows + s) * head_dim + j * 8;
+        const size_t so = (size_t)b * src_bstride + ((size_t)h * src_rows + s) * head_dim + j * 8;
+        const size_t dofs = (size_t)b * dst_bstride + ((size_t)h * dst_rows + s) * head_dim + j * 8;
 #pragma unroll
         for (int tsel = 0; tsel < NT; ++tsel) {
             const T* sp = tsel == 0 ? src0 : src1;
@@ -139,7 +140,8 @@ rope_apply_generic_kernel(const T* src0, T* dst0, const T* src1, T* dst1,
                           const __half* __restrict__ cos_vals,
                           const __half* __restrict__ sin_vals, int batch, int num_heads,
                           int seq_len, int rows_total, int head_dim, long long src_rows,
-                          long long dst_rows) {
+                          long long dst_rows, long long src_bstride, long long dst_bstride,
+                          long long tab_bstride) {
     const int half_d = head_dim / 2;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long total = (long long)batch * num_heads * rows_total * half_d;
@@ -150,8 +152,8 @@ rope_apply_generic_kernel(const T* src0, T* dst0, const T* src1, T* dst1,
     t /= rows_total;
     const int h = (int)(t % num_heads);
     const int b = (int)(t / num_heads);
-    const size_t so = (((size_t)b * num_heads + h) * src_rows + s) * head_dim + d;
-    const size_t dofs = (((size_t)b * num_heads + h) * dst_rows + s) * head_dim + d;
+    const size_t so = (size_t)b * src_bstride + ((size_t)h * src_rows + s) * head_dim + d;
+    const size_t dofs = (size_t)b * dst_bstride + ((size_t)h * dst_rows + s) * head_dim + d;
 #pragma unroll
     for (int tsel = 0; tsel < NT; ++tsel) {
         const T* sp = tsel == 0 ? src0 : src1;
@@ -159,7 +161,7 @@ rope_apply_generic_kernel(const T* src0, T* dst0, const T* src1, T* dst1,
         float x_lo = (float)sp[so], x_hi = (float)sp[so + half_d];
         float o_lo = x_lo, o_hi = x_hi;
         if (s < seq_len) {
-            const size_t to = ((size_t)b * seq_len + s) * head_dim + d;
+            const size_t to = (size_t)b * tab_bstride + (size_t)s * head_dim + d;
             const float c_lo = __half2float(cos_vals[to]), s_lo = __half2float(sin_vals[to]);
             const float c_hi = __half2float(cos_vals[to + half_d]);
             const float s_hi = __half2float(sin_vals[to + half_d]);
@@ -175,7 +177,12 @@ template <typename T, int NT>
 static int launch_rope(const T* src0, T* dst0, const T* src1, T* dst1, const __half* cos_vals,
                        const __half* sin_vals, int batch, int num_heads, int seq_len,
                        int rows_total, int head_dim, long long src_rows, long long dst_rows,
-                       cudaStream_t st) {
+                       cudaStream_t st, long long src_bstride = -1, long long dst_bstride = -1,
+                       long long tab_bstride = -1) {
+    // batch strides in elements; by default the tensors and the tables are densely packed
+    if (src_bstride < 0) src_bstride = (long long)num_heads * src_rows * head_dim;
+    if (dst_bstride < 0) dst_bstride = (long long)num_heads * dst_rows * head_dim;
+    if (tab_bstride < 0) tab_bstride = (long long)seq_len * head_dim;
     if (!src0 || !dst0 || (NT == 2 && (!src1 || !dst1)) || !cos_vals || !sin_vals)
         return RFK_EINVAL;
     if (batch < 0 || num_heads <= 0 || seq_len < 0 || head_dim <= 0 || (head_dim & 1))
@@ -184,7 +191,8 @@ static int launch_rope(const T* src0, T* dst0, const T* src1, T* dst1, const __h
     if (batch == 0 || rows_total == 0) return RFK_OK;
     const bool vec = head_dim % 16 == 0 && aligned16(src0) && aligned16(dst0) &&
                      (NT == 1 || (aligned16(src1) && aligned16(dst1))) && aligned16(cos_vals) &&
-                     aligned16(sin_vals);
+                     aligned16(sin_vals) && src_bstride % 8 == 0 && dst_bstride % 8 == 0 &&
+                     tab_bstride % 8 == 0;
     if (vec) {
         const int cpt = head_dim / 16;
         // One head per thread unless the problem is large: at the benchmark size (47 MB) the
@@ -202,7 +210,8 @@ static int launch_rope(const T* src0, T* dst0, const T* src1, T* dst1, const __h
     rope_apply_kernel<T, NT, HPV><<<grid, 128, 0, st>>>(src0, dst0, src1, dst1, cos_vals,     \
                                                         sin_vals, batch, num_heads, seq_len,  \
                                                         rows_total, head_dim, src_rows,       \
-                                                        dst_rows)
+                                                        dst_rows, src_bstride, dst_bstride,   \
+                                                        tab_bstride)
         if (hp == 4) RFK_ROPE(4);
         else if (hp == 2) RFK_ROPE(2);
         else RFK_ROPE(1);
@@ -211,7 +220,7 @@ static int launch_rope(const T* src0, T* dst0, const T* src1, T* dst1, const __h
         const long long total = (long long)batch * num_heads * rows_total * (head_dim / 2);
         rope_apply_generic_kernel<T, NT><<<ceil_div(total, 256), 256, 0, st>>>(
             src0, dst0, src1, dst1, cos_vals, sin_vals, batch, num_heads, seq_len, rows_total,
-            head_dim, src_rows, dst_rows);
+            head_dim, src_rows, dst_rows, src_bstride, dst_bstride, tab_bstride);
     }
     return launch_status();
 }
@@ -418,6 +427,20 @@ extern "C" int rfk_rope_one_oop(const rfk_half* src, rfk_half* dst, const rfk_ha
                                   (const __half*)c, (const __half*)s, batch, num_heads, seq_len,
                                   rows_total, head_dim, src_seq_stride, dst_seq_stride,
                                   as_stream(stream));
+}
+
+extern "C" int rfk_rope_one_oop_strided(const rfk_half* src, rfk_half* dst, const rfk_half* c,
+                                        const rfk_half* s, int batch, long long src_batch_stride,
+                                        long long dst_batch_stride, long long table_batch_stride,
+                                        int num_heads, int seq_len, int head_dim, int src_seq_stride,
+                                        int dst_seq_stride, rfk_stream_t stream) {
+    if (src_seq_stride < seq_len || dst_seq_stride < seq_len) return RFK_EINVAL;
+    if (src_batch_stride < 0 || dst_batch_stride < 0 || table_batch_stride < 0) return RFK_EINVAL;
+    return launch_rope<__half, 1>((const __half*)src, (__half*)dst, nullptr, nullptr,
+                                  (const __half*)c, (const __half*)s, batch, num_heads, seq_len,
+                                  seq_len, head_dim, src_seq_stride, dst_seq_stride,
+                                  as_stream(stream), src_batch_stride, dst_batch_stride,
+                                  table_batch_stride);
 }
 
 extern "C" int rfk_qkv_norm_rope_transpose(const rfk_half* x, long long row_stride, int n_parts,

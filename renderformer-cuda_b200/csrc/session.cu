@@ -78,24 +78,26 @@ __global__ void add3_bc_kernel(float* out, const float* a, const float* b, const
 
 inline unsigned blocks_for(long long n) { return (unsigned)((n + 255) / 256); }
 
-// swin shift mask [nWin, ws2, ws2]: 1 where both tokens come from the same pre-shift region
-// (render_session.cu:99-116)
-std::vector<uint8_t> make_shift_mask(int pH, int pW, int ws, int shift) {
-    const int nH = pH / ws, nW = pW / ws, ws2 = ws * ws;
-    std::vector<int> reg((size_t)pH * pW);
-    for (int i = 0; i < pH; ++i)
-        for (int j = 0; j < pW; ++j) reg[(size_t)i * pW + j] = ((i + shift) % pH / ws) * nW + ((j + shift) % pW / ws);
-    std::vector<uint8_t> mask((size_t)nH * nW * ws2 * ws2, 1);
-    for (int wi = 0; wi < nH; ++wi)
-        for (int wj = 0; wj < nW; ++wj) {
-            const int wid = wi * nW + wj;
-            for (int a = 0; a < ws2; ++a) {
-                const int ra = reg[(size_t)(wi * ws + a / ws) * pW + wj * ws + a % ws];
-                for (int b = 0; b < ws2; ++b) {
-                    const int rb = reg[(size_t)(wi * ws + b / ws) * pW + wj * ws + b % ws];
-                    mask[((size_t)wid * ws2 + a) * ws2 + b] = (ra == rb);
-                }
+// Attention mask of the shifted windows, [windows, ws*ws, ws*ws] bytes. After the cyclic shift
+// the token at row y of the shifted map is the token of row (y + shift) mod extent of the
+// unshifted one (columns alike). Two tokens of a window may see each other only if both came
+// out of the same ws x ws cell of the unshifted map; since a cell is a product of a row band
+// and a column band, the test separates per axis. (The reference states the same rule through
+// one region number per token, src/pipeline/render_session.cu:99-116.)
+std::vector<uint8_t> build_window_mask(int rows, int cols, int ws, int shift) {
+    const int win_y = rows / ws, win_x = cols / ws, T = ws * ws;
+    const auto band = [ws, shift](int p, int extent) { return ((p + shift) % extent) / ws; };
+    std::vector<uint8_t> mask((size_t)win_y * win_x * T * T);
+    std::vector<int> by(T), bx(T);
+    uint8_t* out = mask.data();
+    for (int wy = 0; wy < win_y; ++wy)
+        for (int wx = 0; wx < win_x; ++wx) {
+            for (int t = 0; t < T; ++t) {
+                by[t] = band(wy * ws + t / ws, rows);
+                bx[t] = band(wx * ws + t % ws, cols);
             }
+            for (int q = 0; q < T; ++q)
+                for (int k = 0; k < T; ++k) *out++ = (uint8_t)((by[q] == by[k]) & (bx[q] == bx[k]));
         }
     return mask;
 }
@@ -121,7 +123,7 @@ struct rfk_session {
     rfk_half* k_rot = nullptr;  // [dec_layers][heads][Se_pad][hd]: this view's rotated keys of every layer
     cudaEvent_t ev_fork = nullptr, ev_rot[RFK_MAX_LAYERS]{};
     uint8_t* shift_mask = nullptr;
-    rfk_half* dft[4] = {nullptr, nullptr, nullptr, nullptr};
+    rfk_half* dft[kSlots][4] = {};  // the four decoder feature taps of each frame slot
     rfk_half* result[kSlots] = {nullptr, nullptr};
 
     // frame slots
@@ -151,11 +153,11 @@ struct rfk_session {
         return RFK_OK;
     }
 
-    int render_view(const float* pinned_cam, rfk_half* result_out);
+    int render_view(const float* pinned_cam, rfk_half* result_out, rfk_half* const* taps_out);
 };
 
 // The per-view work; everything here is captured into the graph.
-int rfk_session::render_view(const float* pinned_cam, rfk_half* result_out) {
+int rfk_session::render_view(const float* pinned_cam, rfk_half* result_out, rfk_half* const* taps_out) {
     rfk_stream_t s = (rfk_stream_t)stream;
     const int dim = m.dim, nr = m.num_register_tokens, ps = m.patch_size;
     TRY_CUDA(cudaMemcpyAsync(cam_gpu, pinned_cam, 17 * sizeof(float), cudaMemcpyHostToDevice, stream));
@@ -163,15 +165,21 @@ int rfk_session::render_view(const float* pinned_cam, rfk_half* result_out) {
     TRY(rfk_view_geometry(cam_gpu, tri16(), vn16(), center(), m.vt_rope_freqs, vtri, vvn, vpos, k_cos, k_sin, N, nr,
                           Se_pad, m.rope_num_freqs, hd, s));
     // The rotation of the cached keys by this view's tables is the same for every query and independent of the
-    // layers' data flow, so all layers' keys are rotated on a second stream (a parallel branch of the graph) while
-    // the front end and the first layers run; layer i waits for its own buffer only. These launches are bound by
-    // memory bandwidth, the kernels they overlap with are not.
+    // layers' data flow, so it runs on a second stream (a parallel branch of the graph) while the front end and the
+    // first layer's projections run. Two launches: layer 0 alone (the first attention waits only for 23 MB of work),
+    // then all remaining layers at once (one shared table, batch = layers, source stride = a K and a V slab).
     TRY_CUDA(cudaEventRecord(ev_fork, stream));
     TRY_CUDA(cudaStreamWaitEvent(side_stream, ev_fork, 0));
-    for (int i = 0; i < m.dec_layers; ++i) {
-        TRY(rfk_rope_one_oop(kvK(i), kRot(i), k_cos, k_sin, 1, m.num_heads, Se_pad, hd, Se_pad, Se_pad, 0,
-                             (rfk_stream_t)side_stream));
-        TRY_CUDA(cudaEventRecord(ev_rot[i], side_stream));
+    {
+        const long long slab = (long long)(L.kv_layer_bytes / sizeof(__half));
+        TRY(rfk_rope_one_oop_strided(kvK(0), kRot(0), k_cos, k_sin, 1, 2 * slab, slab, 0, m.num_heads, Se_pad, hd, Se_pad,
+                                     Se_pad, (rfk_stream_t)side_stream));
+        TRY_CUDA(cudaEventRecord(ev_rot[0], side_stream));
+        if (m.dec_layers > 1) {
+            TRY(rfk_rope_one_oop_strided(kvK(1), kRot(1), k_cos, k_sin, m.dec_layers - 1, 2 * slab, slab, 0, m.num_heads,
+                                         Se_pad, hd, Se_pad, Se_pad, (rfk_stream_t)side_stream));
+            TRY_CUDA(cudaEventRecord(ev_rot[1], side_stream));
+        }
     }
     // camera-space rays (identity pose, as the reference does) written straight as patch tokens
     TRY(rfk_ray_gen_patchify(id_c2w, cam_gpu + 16, nullptr, ray_pat, 1, res, ps, s));
@@ -189,14 +197,14 @@ int rfk_session::render_view(const float* pinned_cam, rfk_half* result_out) {
         const rfk_half* next_pending = nullptr;
         // a tapped (or the last) layer finishes x itself; the others leave their FFN residual
         // to the first kernel of the next layer
-        TRY_CUDA(cudaStreamWaitEvent(stream, ev_rot[i], 0));
+        if (i < 2) TRY_CUDA(cudaStreamWaitEvent(stream, ev_rot[i], 0));
         TRY(rfk_decoder_layer_forward_cached(ctx, &m.dec[i], rtok, pending, (tap || last) ? nullptr : &next_pending,
                                              temp, proj, qkv, ffn, win, score, self_score, kRot(i), kvV(i), 1, nP,
                                              Se_pad, n_keys, dim, m.num_heads, m.ffn_hidden, pH, pW, m.window_size,
                                              shift, shift > 0 ? shift_mask : nullptr, nullptr, nullptr, nullptr, nullptr, s));
         pending = next_pending;
         if (tap)
-            TRY_CUDA(cudaMemcpyAsync(dft[(i + 1) / L4 - 1], rtok, (size_t)nP * dim * sizeof(rfk_half),
+            TRY_CUDA(cudaMemcpyAsync(taps_out[(i + 1) / L4 - 1], rtok, (size_t)nP * dim * sizeof(rfk_half),
                                      cudaMemcpyDeviceToDevice, stream));
     }
     TRY_CUDA(cudaMemcpyAsync(result_out, rtok, (size_t)nP * dim * sizeof(rfk_half), cudaMemcpyDeviceToDevice, stream));
@@ -274,7 +282,8 @@ extern "C" int rfk_session_create(const rfk_model* model, int n_tris, int img_re
     if (!fused_attention) ALLOC(score, (size_t)nh * nP * Se_pad);
     if (!(ws * ws == 64 && d->hd == 64)) ALLOC(self_score, (size_t)nWin * nh * ws * ws * ws * ws);
     ALLOC(shift_mask, (size_t)nWin * ws * ws * ws * ws);
-    for (int j = 0; j < 4; ++j) ALLOC(dft[j], (size_t)nP * dim);
+    for (int k = 0; k < kSlots; ++k)
+        for (int j = 0; j < 4; ++j) ALLOC(dft[k][j], (size_t)nP * dim);
     for (int k = 0; k < kSlots; ++k) ALLOC(result[k], (size_t)nP * dim);
 #undef ALLOC
     const float id[16] = {1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1};
@@ -341,15 +350,16 @@ extern "C" int rfk_session_encode_scene(rfk_session* d, const float* tri, const 
     // fp16 copies of the geometry kept for every view (render_session.cu:301-304)
     TRY(rfk_cast_fp32_to_fp16(tri, d->tri16(), (long long)N * 9, s));
     TRY(rfk_cast_fp32_to_fp16(vn, d->vn16(), (long long)N * 9, s));
-    // world-space centroid, on the host in double as the reference does (render_session.cu:62-70)
+    // Scene centre = mean of all 3N fp16 vertices, summed on the host in double precision (the
+    // reference's centroid is the same quantity, src/pipeline/render_session.cu:62-70).
     std::vector<__half> h_tri((size_t)N * 9);
     TRY_CUDA(cudaMemcpyAsync(h_tri.data(), d->tri16(), h_tri.size() * sizeof(__half), cudaMemcpyDeviceToHost, st));
     TRY_CUDA(cudaStreamSynchronize(st));
-    double mean[9] = {};
-    for (int i = 0; i < N; ++i)
-        for (int k = 0; k < 9; ++k) mean[k] += __half2float(h_tri[(size_t)i * 9 + k]);
+    double axis_sum[3] = {0.0, 0.0, 0.0};
+    for (size_t v = 0; v < (size_t)N * 3; ++v)
+        for (int a = 0; a < 3; ++a) axis_sum[a] += (double)__half2float(h_tri[v * 3 + a]);
     float c[3];
-    for (int j = 0; j < 3; ++j) c[j] = (float)(((mean[j] + mean[3 + j] + mean[6 + j]) / N) / 3.0);
+    for (int a = 0; a < 3; ++a) c[a] = (float)(axis_sum[a] / (3.0 * N));
     TRY_CUDA(cudaMemcpyAsync(d->center(), c, sizeof(c), cudaMemcpyHostToDevice, st));
 
     // normals: NeRF PE -> linear -> fp32 RMSNorm (render_session.cu:310-318)
@@ -429,18 +439,18 @@ extern "C" int rfk_session_finalize(rfk_session* d) {
     if (!d) return RFK_EINVAL;
     if (d->finalized) return RFK_OK;
     const rfk_model& m = d->m;
-    std::vector<uint8_t> mask = make_shift_mask(d->pH, d->pW, m.window_size, m.shift_size);
+    std::vector<uint8_t> mask = build_window_mask(d->pH, d->pW, m.window_size, m.shift_size);
     TRY_CUDA(cudaMemcpy(d->shift_mask, mask.data(), mask.size(), cudaMemcpyHostToDevice));
     // warm-up view (also lets cuBLAS pick and load its kernels before capture)
     float cam[17] = {1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 3, 0, 0, 0, 1, 0.7f};
     for (int k = 0; k < kSlots; ++k) memcpy(d->pin_cam[k], cam, sizeof(cam));
-    TRY(d->render_view(d->pin_cam[0], d->result[0]));
+    TRY(d->render_view(d->pin_cam[0], d->result[0], d->dft[0]));
     TRY_CUDA(cudaStreamSynchronize(d->stream));
     if (!(d->flags & RFK_SESSION_NO_GRAPH)) {
         for (int k = 0; k < kSlots; ++k) {
             const unsigned long long n0 = rfk_launch_count();
             TRY_CUDA(cudaStreamBeginCapture(d->stream, cudaStreamCaptureModeThreadLocal));
-            int rc = d->render_view(d->pin_cam[k], d->result[k]);
+            int rc = d->render_view(d->pin_cam[k], d->result[k], d->dft[k]);
             cudaError_t e = cudaStreamEndCapture(d->stream, &d->graph[k]);
             if (rc != RFK_OK) return rc;
             TRY_CUDA(e);
@@ -452,7 +462,7 @@ extern "C" int rfk_session_finalize(rfk_session* d) {
         }
     } else {
         const unsigned long long n0 = rfk_launch_count();
-        TRY(d->render_view(d->pin_cam[0], d->result[0]));
+        TRY(d->render_view(d->pin_cam[0], d->result[0], d->dft[0]));
         d->kernels_per_view = (int)(rfk_launch_count() - n0);
         TRY_CUDA(cudaStreamSynchronize(d->stream));
     }
@@ -476,7 +486,7 @@ extern "C" int rfk_session_render_frame(rfk_session* d, const float* h_c2w, floa
     d->pin_cam[k][16] = fov_rad;
     TRY_CUDA(cudaEventRecord(d->ev_start[k], d->stream));
     if (d->exec[k]) TRY_CUDA(cudaGraphLaunch(d->exec[k], d->stream));
-    else TRY(d->render_view(d->pin_cam[k], d->result[k]));
+    else TRY(d->render_view(d->pin_cam[k], d->result[k], d->dft[k]));
     TRY_CUDA(cudaEventRecord(d->ev_done[k], d->stream));
     d->frames++;
     return RFK_OK;
@@ -499,8 +509,9 @@ extern "C" int rfk_session_result(rfk_session* d, const rfk_half** tokens, int* 
 }
 
 extern "C" int rfk_session_feature_taps(rfk_session* d, const rfk_half** taps) {
-    if (!d || !taps) return RFK_EINVAL;
-    for (int j = 0; j < 4; ++j) taps[j] = d->dft[j];
+    if (!d || !taps || d->frames == 0) return RFK_EINVAL;
+    const int k = (int)((d->frames - 1) % kSlots);
+    for (int j = 0; j < 4; ++j) taps[j] = d->dft[k][j];
     return RFK_OK;
 }
 

@@ -301,6 +301,10 @@ def shard_views(n_views: int, rank: int, world: int) -> list[int]:
     return list(range(rank, n_views, world))
 
 
+class SchedulerError(RuntimeError):
+    pass
+
+
 class ViewScheduler:
     """Data-parallel view scheduler: one process per GPU. Rank 0 encodes the scene; the scene
     state (cross-attention K/V cache + fp16 geometry) is broadcast once over NCCL into every
@@ -310,10 +314,18 @@ class ViewScheduler:
     `streams_per_gpu` > 1 keeps that many views in flight on the GPU: that many sessions (each with its
     own stream, buffers and captured graphs) share one scene state and take this rank's views in turn,
     so that one view's partial last wave of CTAs and its bandwidth-bound kernels overlap with another
-    view's compute-bound ones."""
+    view's compute-bound ones.
+
+    Failure handling is host-side only and happens between views: a session call that raises marks this
+    rank as failed for the rest of the `render` call; after the local pass the ranks exchange (one object
+    all-gather on the host) which views are still undone, and the surviving ranks render them. Nothing is
+    in flight on a rank when it joins that exchange (its sessions are drained first).
+
+    `session_factory(scene_state_or_None)` builds one session; the default builds a RenderSession. Tests
+    inject a host-only stand-in to drive this class without a GPU."""
 
     def __init__(self, model: Model, n_tris: int, img_res: int = 512, process_group=None, pad_keys_attend=False,
-                 streams_per_gpu: int = 1):
+                 streams_per_gpu: int = 1, session_factory=None):
         import torch.distributed as dist
         self.dist = dist if (dist.is_available() and dist.is_initialized()) else None
         self.group = process_group
@@ -321,51 +333,125 @@ class ViewScheduler:
         self.world = self.dist.get_world_size(process_group) if self.dist else 1
         if streams_per_gpu < 1:
             raise ValueError("streams_per_gpu must be at least 1")
-        self.session = RenderSession(model, n_tris, img_res, pad_keys_attend=pad_keys_attend)
-        self.sessions = [self.session] + [
-            RenderSession(model, n_tris, img_res, scene_state=self.session.scene_state, pad_keys_attend=pad_keys_attend)
-            for _ in range(streams_per_gpu - 1)]
+        if session_factory is None:
+            def session_factory(scene_state):
+                return RenderSession(model, n_tris, img_res, scene_state=scene_state, pad_keys_attend=pad_keys_attend)
+        self.session = session_factory(None)
+        self.sessions = [self.session] + [session_factory(self.session.scene_state) for _ in range(streams_per_gpu - 1)]
         self.broadcast_ms = 0.0
+        self.failed = False          # this rank hit an error in its last render() call
+        self.last_error = None
+
+    # -- scene ---------------------------------------------------------------------------
+    def encode_scene(self, tri, vn, tex):
+        """Runs the scene encoder on this rank (the source of the broadcast)."""
+        self.session.encode_scene(tri, vn, tex)
+
+    def broadcast_scene(self, src: int = 0, warm: bool = True) -> float:
+        """Broadcasts the scene state from rank `src` into every rank's own buffer; returns the device time of
+        that one broadcast in ms (0 for a single rank). With `warm`, two broadcasts of a scratch buffer of the
+        same size go first: the communicator allocates its channels and staging buffers on its first large
+        message, which otherwise costs an order of magnitude more than the transfer itself."""
+        if not (self.dist and self.world > 1):
+            return 0.0
+        state = self.session.scene_state
+        if warm:
+            scratch = torch.empty_like(state)
+            for _ in range(2):
+                self.dist.broadcast(scratch, src=src, group=self.group)
+            del scratch
+        if state.is_cuda:
+            st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            st.record()
+            self.dist.broadcast(state, src=src, group=self.group)
+            en.record()
+            torch.cuda.synchronize()
+            self.broadcast_ms = st.elapsed_time(en)
+        else:
+            import time
+            t0 = time.perf_counter()
+            self.dist.broadcast(state, src=src, group=self.group)
+            self.broadcast_ms = (time.perf_counter() - t0) * 1e3
+        return self.broadcast_ms
+
+    def finalize(self):
+        for ses in self.sessions:
+            ses.finalize()
 
     def load_scene(self, tri=None, vn=None, tex=None, src: int = 0):
         """Rank `src` passes the scene tensors and runs the encoder; every rank receives the
         scene state. Returns the broadcast time in ms (device events, this rank)."""
         if self.rank == src:
-            self.session.encode_scene(tri, vn, tex)
-        if self.dist and self.world > 1:
-            # a 4-byte collective first: communicator set-up is not part of the broadcast's cost
-            self.dist.broadcast(torch.zeros(1, device=self.session.scene_state.device), src=src, group=self.group)
-            st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            st.record()
-            self.dist.broadcast(self.session.scene_state, src=src, group=self.group)
-            en.record()
-            torch.cuda.synchronize()
-            self.broadcast_ms = st.elapsed_time(en)
-        for ses in self.sessions:
-            ses.finalize()
+            self.encode_scene(tri, vn, tex)
+        self.broadcast_scene(src)
+        self.finalize()
         return self.broadcast_ms
 
+    # -- views ---------------------------------------------------------------------------
     def my_views(self, n_views: int) -> list[int]:
         return shard_views(n_views, self.rank, self.world)
 
+    def _render_list(self, views, base, stride, fl, out, out_pos) -> list[int]:
+        """Renders `views` in order; returns those NOT rendered because a session call raised."""
+        n = len(self.sessions)
+        for j, v in enumerate(views):
+            if self.failed:
+                return list(views[j:])
+            ses = self.sessions[j % n]
+            try:
+                ses.render_frame_raw(base + v * stride, fl[v])
+                if out is not None:
+                    ses.download_async(out[out_pos + j])
+            except Exception as e:  # a failing rank keeps running on the host: it reports, the others take over
+                self.failed, self.last_error = True, e
+                return list(views[j:])
+        return []
+
+    def _drain(self):
+        for ses in self.sessions:
+            try:
+                ses.drain()
+            except Exception as e:
+                self.failed, self.last_error = True, e
+
     def render(self, c2ws: torch.Tensor, fovs: torch.Tensor, out: torch.Tensor | None = None) -> list[int]:
         """c2ws [V,4,4] fp32 and fovs [V] fp32 (radians) on the HOST. Renders this rank's views;
-        if `out` (pinned host [n_local, n_tokens, dim] fp16) is given, each frame is downloaded
-        into it while the next one renders. Returns the view ids rendered here."""
+        if `out` (pinned host [n_local (+ spare rows for re-issued views), n_tokens, dim] fp16) is given, each
+        frame is downloaded into it while the next one renders. Returns the view ids rendered here, in the
+        order of the rows of `out`. If a rank fails, its undone views are re-issued to the surviving ranks
+        (round-robin) and appended to their lists; SchedulerError if views remain that nobody could render."""
         mine = self.my_views(c2ws.shape[0])
         c2ws = c2ws.contiguous()
         base, stride = c2ws.data_ptr(), 16 * 4
         fl = fovs.tolist()
-        n = len(self.sessions)
-        for j, v in enumerate(mine):
-            ses = self.sessions[j % n]
-            ses.render_frame_raw(base + v * stride, fl[v])
-            if out is not None:
-                ses.download_async(out[j])
-        for ses in self.sessions:
-            ses.drain()
-        return mine
+        self.failed, self.last_error = False, None
+        undone = self._render_list(mine, base, stride, fl, out, 0)
+        self._drain()
+        if self.failed and not undone:
+            undone = list(mine)          # the error surfaced while draining: none of this pass can be trusted
+        done = [v for v in mine if v not in set(undone)]
+        if not (self.dist and self.world > 1):
+            if undone:
+                raise SchedulerError(f"views {undone} could not be rendered: {self.last_error}") from self.last_error
+            return done
+        # host-side exchange between passes: who survived, which views are left
+        reports = [None] * self.world
+        self.dist.all_gather_object(reports, (not self.failed, undone), group=self.group)
+        survivors = [r for r, (ok, _) in enumerate(reports) if ok]
+        pool = sorted(v for _, u in reports for v in u)
+        if pool and not survivors:
+            raise SchedulerError(f"views {pool} could not be rendered: every rank failed") from self.last_error
+        if pool and not self.failed:
+            extra = [v for i, v in enumerate(pool) if survivors[i % len(survivors)] == self.rank]
+            if out is not None and len(done) + len(extra) > out.shape[0]:
+                raise SchedulerError("`out` has no spare rows for the views re-issued from a failed rank")
+            left = self._render_list(extra, base, stride, fl, out, len(done))
+            self._drain()
+            if left or self.failed:
+                raise SchedulerError(f"re-issued views {left or extra} failed on rank {self.rank}") from self.last_error
+            done += extra
+        return done
 
     def close(self):
         for ses in self.sessions:

@@ -1,5 +1,8 @@
-"""CPU tests of the view scheduler's host logic: sharding arithmetic, and the broadcast +
-shard protocol over a world_size-2 gloo group (no GPU, no kernels)."""
+"""CPU tests of the view scheduler's host logic: sharding arithmetic, the broadcast + shard
+protocol over a world_size-2 gloo group, and the ViewScheduler class itself driven through an
+injected host-only session (scene broadcast, view sharding, and a rank whose render call fails:
+its undone views are re-issued to the surviving rank). No GPU, no kernels; the failure is an
+exception raised on the host, between views."""
 import os
 import socket
 
@@ -49,3 +52,91 @@ def test_broadcast_and_shard_protocol_gloo_world2():
     assert ret[0][1] == [0, 2, 4, 6, 8, 10] and ret[1][1] == [1, 3, 5, 7, 9]
     want = [[float(v) + i for i in range(4)] for v in range(11)]
     assert ret[0][2] == want and ret[1][2] == want
+
+
+class FakeSession:
+    """Host-only stand-in for RenderSession: the 'frame' of a view is its fov plus one byte of the scene state."""
+
+    def __init__(self, scene_state, fail_after=None):
+        self.scene_state = scene_state if scene_state is not None else torch.zeros(64, dtype=torch.uint8)
+        self.fail_after, self.count, self.last_fov, self.finalized = fail_after, 0, None, False
+
+    def encode_scene(self, tri, vn, tex):
+        self.scene_state.copy_(torch.arange(64, dtype=torch.uint8) + 3)
+
+    def finalize(self):
+        self.finalized = True
+
+    def render_frame_raw(self, c2w_ptr, fov):
+        assert self.finalized
+        if self.fail_after is not None and self.count >= self.fail_after:
+            raise session.RfkLayersError("injected failure of this rank's device")
+        self.count += 1
+        self.last_fov = fov
+
+    def download_async(self, host):
+        host.fill_(self.last_fov + float(self.scene_state[1]))
+
+    def drain(self):
+        pass
+
+    def close(self):
+        pass
+
+
+def _sched_worker(rank, world, port, ret, fail_rank, streams):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    V = 11
+    factory = lambda st: FakeSession(st, fail_after=2 if rank == fail_rank else None)
+    sched = session.ViewScheduler(None, 0, session_factory=factory, streams_per_gpu=streams)
+    sched.load_scene("tri", "vn", "tex")              # rank 0 encodes, the state travels, every session finalizes
+    state_ok = bool((sched.session.scene_state == torch.arange(64, dtype=torch.uint8) + 3).all())
+    shared = all(s.scene_state is sched.session.scene_state for s in sched.sessions)
+    out = torch.zeros(V, 4)
+    try:
+        done = sched.render(torch.zeros(V, 4, 4), torch.arange(V, dtype=torch.float32), out)
+        err = None
+    except session.SchedulerError as e:
+        done, err = [], str(e)
+    rows_ok = all(float(out[i, 0]) == float(v) + 4.0 for i, v in enumerate(done))
+    ret[rank] = (state_ok and shared, done, rows_ok, sched.failed, err)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _run_sched(fail_rank, streams=1):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ret = mp.Manager().dict()
+    mp.spawn(_sched_worker, args=(2, port, ret, fail_rank, streams), nprocs=2, join=True)
+    return ret
+
+
+def test_view_scheduler_class_world2_no_failure():
+    ret = _run_sched(fail_rank=-1, streams=2)
+    assert ret[0][0] and ret[1][0]
+    assert ret[0][1] == [0, 2, 4, 6, 8, 10] and ret[1][1] == [1, 3, 5, 7, 9]
+    assert ret[0][2] and ret[1][2] and not ret[0][3] and not ret[1][3]
+
+
+def test_view_scheduler_reissues_views_of_a_failed_rank():
+    ret = _run_sched(fail_rank=1)
+    assert ret[0][0] and ret[1][0]
+    # rank 1 rendered its first two views, then its session raised: views 5, 7, 9 go to the survivor
+    assert ret[1][1] == [1, 3] and ret[1][3] is True and ret[1][4] is None
+    assert ret[0][1] == [0, 2, 4, 6, 8, 10, 5, 7, 9] and ret[0][3] is False
+    assert ret[0][2] and ret[1][2]                    # every downloaded row belongs to the view listed for it
+    assert sorted(ret[0][1] + ret[1][1]) == list(range(11))
+
+
+def test_view_scheduler_single_rank_failure_raises():
+    sched = session.ViewScheduler(None, 0, session_factory=lambda st: FakeSession(st, fail_after=1))
+    sched.load_scene("tri", "vn", "tex")
+    try:
+        sched.render(torch.zeros(3, 4, 4), torch.arange(3, dtype=torch.float32))
+        raised = False
+    except session.SchedulerError as e:
+        raised = "[1, 2]" in str(e)
+    assert raised
