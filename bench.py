@@ -684,6 +684,9 @@ def main():
         if rank == 0 and not args.no_kernel_table:
             from renderformer_cuda_b200 import kernel_bench as kb
             line["kernels"] = kb.run_suite(backend, peak, iters=10, warmup=3)
+            if args.impl == "rfk":
+                # every projection of a decoder layer: the tcgen05 kernel with its fused epilogue beside the library route
+                line["config"]["gemm_vs_library"] = kb.gemm_table(iters=10)
     if rank == 0:
         if args.impl == "reference":
             line["impl"] = "reference"

@@ -91,7 +91,8 @@ int rfk_rmsnorm_residual_f16(rfk_half* x, const rfk_half* r, const float* gamma,
  * 9-19, 179-182) -> cyclic_shift -> window_partition (src/layers/attention.cu:495-506).
  * windowed_operand = 2: r is read in window order, i.e. window reverse + shift back + residual add +
  * norm — replaces window_reverse -> cyclic_shift (src/layers/attention.cu:568-575) -> residual_add ->
- * rmsnorm. r must not be NULL; y must alias neither x nor r. dim % 8 == 0 and dim <= 2048
+ * rmsnorm. r may be NULL only with windowed_operand = 1 (plain norm written in window order, x left
+ * untouched); y must alias neither x nor r. dim % 8 == 0 and dim <= 2048
  * (RFK_EUNSUPPORTED otherwise). */
 int rfk_rmsnorm_residual_f16_windows(rfk_half* x, const rfk_half* r, const float* gamma,
                                      rfk_half* y, int B, int H, int W, int dim, int window_size,
@@ -271,6 +272,37 @@ int rfk_flash_attention_set_path(int path);
  * are undefined), 2 shared memory window not 1024-byte aligned. Synchronises the device.
  * No reference counterpart. */
 int rfk_flash_attention_error(int* code, int clear);
+
+/* ---------------------------------------------------------------- dense projections
+ * C[M,N] = epilogue(A[M,K] W[N,K]^T): row-major fp16 operands with row pitches lda, ldw, ldc
+ * (elements), fp32 accumulation on the tcgen05 tensor cores (accumulators in tensor memory,
+ * operand tiles by TMA), one rounding to fp16 in the epilogue:
+ *   RFK_GEMM_EPI_NONE      C = A W^T, + bias[N] if bias != NULL (the product is rounded to fp16
+ *                          before the bias is added, as the unfused GEMM + bias kernel does)
+ *   RFK_GEMM_EPI_RESIDUAL  C = A W^T (+ bias) + R, R [M,N] fp16 with pitch ldr; R may be C (in place)
+ *   RFK_GEMM_EPI_SWIGLU    C = silu(A W^T) * (A W_up^T), W and W_up both [N,K] with pitch ldw: the
+ *                          gate and up projections of a SwiGLU feed-forward and its activation in
+ *                          one kernel; no [M, 2N] intermediate exists. bias must be NULL.
+ * Needs 16-byte aligned pointers, pitches, N and K multiples of 8 (RFK_EUNSUPPORTED otherwise, and
+ * when the path is set to 1 below; callers then use their library GEMM). A kernel that gives up on
+ * a bounded wait reports through rfk_gemm_error.
+ * replaces rf::linear (cublasGemmEx + add_bias) — src/layers/linear.h:9, src/layers/linear.cu:7-25 —
+ * and, with the SwiGLU epilogue, the first two GEMMs + fused_silu_mul of rf::ffn_swiglu —
+ * src/layers/transformer.cu:63-76; with the residual epilogue the GEMM + rf::residual_add pairs of
+ * src/layers/transformer.cu:176-192. */
+enum { RFK_GEMM_EPI_NONE = 0, RFK_GEMM_EPI_RESIDUAL = 1, RFK_GEMM_EPI_SWIGLU = 2 };
+int rfk_gemm_f16(const rfk_half* A, long long lda, const rfk_half* W, long long ldw,
+                 const rfk_half* W_up, const rfk_half* bias, const rfk_half* R, long long ldr,
+                 rfk_half* C, long long ldc, int M, int N, int K, int epilogue,
+                 rfk_stream_t stream);
+/* 0 automatic (the tcgen05 kernel whenever the shape allows), 1 never (rfk_gemm_f16 returns
+ * RFK_EUNSUPPORTED, so the layer functions fall back to their cuBLAS calls: used to time both side
+ * by side), 2 as 0. Process-wide. No reference counterpart. */
+int rfk_gemm_set_path(int path);
+/* Reads (and with clear != 0 resets) the current device's error word of the GEMM kernel: 0 none,
+ * 1 a bounded wait ran out, 2 shared memory window not 1024-byte aligned. Synchronises the device.
+ * No reference counterpart. */
+int rfk_gemm_error(int* code, int clear);
 
 /* Swin window attention core in one kernel: per (window, head) O = softmax(scale * Q K^T [masked]) V.
  * Q, K, V [BnW, heads, 64, 64] fp16; O [BnW * 64, heads * 64] fp16 (token-major, what the output

@@ -181,9 +181,11 @@ int rfk_self_attention(rfk_ctx* ctx, const rfk_mha_weights* w, const rfk_half* x
  *   self_score_buf B*nW*heads*ws^4 floats.
  * pending_residual: if non-NULL, a sub-layer output of the PREVIOUS layer that has not been
  * added to x yet; it is added by this layer's first fused residual+RMSNorm kernel.
- * On return *pending_out (if pending_out != NULL) names this layer's FFN output, not yet
- * added to x (the caller passes it to the next layer, or adds it with rfk_residual_add);
- * with pending_out == NULL the layer adds it itself and x is complete.
+ * On return *pending_out (if pending_out != NULL) names a sub-layer output of this layer that
+ * is not yet added to x (the caller passes it to the next layer, or adds it with
+ * rfk_residual_add), or is NULL when x is complete: the decoder layer adds its FFN output in the
+ * epilogue of the last projection and always returns NULL; the encoder layer defers it.
+ * With pending_out == NULL x is complete on return.
  * replaces rf::decoder_layer_forward_cached — src/layers/transformer.h:88-103,
  * transformer.cu:151-194 */
 int rfk_decoder_layer_forward_cached(rfk_ctx* ctx, const rfk_decoder_layer_weights* w,

@@ -33,7 +33,7 @@ LAYER_SOURCES = ["layers.cu", "session.cu"]
 
 KERNEL_SOURCES = [
     "abi.cu", "rmsnorm.cu", "softmax.cu", "rope.cu", "layout.cu",
-    "activations.cu", "nerf_pe.cu", "raygen.cu", "geometry.cu", "attention.cu", "attention_tc.cu", "dpt_glue.cu",
+    "activations.cu", "nerf_pe.cu", "raygen.cu", "geometry.cu", "attention.cu", "attention_tc.cu", "gemm_tc.cu", "dpt_glue.cu",
 ]
 
 

@@ -38,7 +38,7 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // or as soon as another thread of the CTA has raised *abort.
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000 * 1000;
 constexpr uint32_t kSpinLimit = 1u << 22;
-__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort) {
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort) {
     const uint64_t t0 = global_timer_ns();
     for (uint32_t it = 0; it < kSpinLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -55,7 +55,7 @@ __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, vola
 // work that this thread itself started - bulk copies into shared memory, tensor-core products - so that
 // nothing is still writing the CTA's shared or tensor memory when the CTA frees them. Ignores *abort.
 constexpr uint64_t kDrainLimitNs = 4ull * 1000 * 1000;
-__device__ __noinline__ bool mbar_wait_drain(uint64_t* bar, uint32_t parity) {
+static __device__ __noinline__ bool mbar_wait_drain(uint64_t* bar, uint32_t parity) {
     const uint64_t t0 = global_timer_ns();
     for (uint32_t it = 0; it < kSpinLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;

@@ -1,0 +1,406 @@
+// Dense projection C = epilogue(A W^T) on the 5th-generation tensor cores (tcgen05 + tensor memory
+// + TMA), fp16 operands, fp32 accumulation, with the element-wise step that follows the projection
+// in the layer fused into the epilogue:
+//   RFK_GEMM_EPI_NONE      C = A W^T (+ bias)                                   rf::linear
+//   RFK_GEMM_EPI_RESIDUAL  C = A W^T (+ bias) + R                               rf::linear + rf::residual_add
+//   RFK_GEMM_EPI_SWIGLU    C = silu(A Wg^T) * (A Wu^T)                          the two projections and the
+//                                                                               gate of rf::ffn_swiglu
+// Reference boundary: rf::linear, src/layers/linear.cu:7-25 (one cublasGemmEx + a bias kernel), and
+// rf::ffn_swiglu, src/layers/transformer.cu:63-79 (two GEMMs into [M, hidden] buffers, fused_silu_mul,
+// a third GEMM) of BANANASJIM/renderformer-cuda.
+//
+// One persistent CTA per SM walks output tiles of 128 rows x 256 accumulator columns (row-tile index
+// fastest, so that the CTAs running together share weight tiles in L2). K is consumed in blocks of
+// 64 halves (one 128-byte swizzle row) through a ring of kStages shared-memory stages:
+//   warp 0   producer: one thread issues three TMA tile loads per stage (A 128 x 64; two weight boxes
+//            of 128 x 64 - rows n0..n0+127 and n0+128..n0+255 of W, or, with the SwiGLU epilogue,
+//            the gate rows and the up rows of the same 128 hidden units) that complete on the
+//            stage's mbarrier; rows and columns past the end of a tensor arrive as zeros.
+//   warp 1   one thread issues tcgen05.mma M128 N256 K16 x 4 per stage into one of two accumulators
+//            in tensor memory (2 x 256 columns), then commits the stage's "empty" barrier; after
+//            the last K block it commits the accumulator's "full" barrier.
+//   warps 2-5 epilogue: a thread owns one output row (= its tensor-memory lane), reads the row in
+//            chunks of 32 columns with tcgen05.ld, applies bias / residual / gate in fp32, rounds
+//            once to fp16 and writes 64 contiguous bytes per chunk. While they drain accumulator a,
+//            the tensor core already fills accumulator a ^ 1 with the CTA's next tile.
+// Every mbarrier wait is bounded; on a time-out the CTA raises an error word, waits (bounded) for its
+// own copies and products in flight, frees its tensor memory and returns.
+#include <cuda.h>  // CUtensorMap and its enums; the encoder itself is looked up at run time
+#include "attention_tc.cuh"
+#include "common.cuh"
+
+namespace rfk {
+
+__device__ int g_gemm_tc_error = 0;  // first time-out / failure code seen by any CTA since load
+
+namespace tcgemm {
+
+constexpr int BM = 128, BNACC = 256, BK = 64;
+constexpr int kStages = 4;
+constexpr int kThreads = 192;                  // warp 0 producer, warp 1 MMA issuer, warps 2-5 epilogue
+constexpr int kABytes = BM * BK * 2;           // 16 KB
+constexpr int kWBoxBytes = 128 * BK * 2;       // 16 KB, two per stage
+constexpr int kStageBytes = kABytes + 2 * kWBoxBytes;
+constexpr int kTmemCols = 512;                 // two accumulators of 256 fp32 columns
+
+struct __align__(8) Ctrl {
+    uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2], drain;
+    uint32_t tmem_base;
+    int abort;
+};
+constexpr int kSmemBytes = kStages * kStageBytes + 256;
+static_assert(sizeof(Ctrl) <= 256, "control block");
+static_assert(kSmemBytes + 1024 <= 227 * 1024, "one CTA per SM");
+
+enum : int { kErrTimeout = 1, kErrSmemAlign = 2 };
+
+struct Params {
+    __half* C; long long ldc;
+    const __half* R; long long ldr;     // residual (EPI_RESIDUAL), may alias C
+    const __half* bias;                 // [N] or null
+    int M, N, K;                        // N = output columns
+    int tiles_m, tiles_n;
+};
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float2 unpack_half2(uint32_t w) {
+    return __half22float2(*reinterpret_cast<__half2*>(&w));
+}
+
+// Tiled copy global -> shared of one box of a rank-2 tensor map (x innermost, in elements; x * 2 bytes
+// is always a multiple of 128 here); the bytes are counted on `bar`.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tmap, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst_smem), "l"(tmap), "r"(x), "r"(y), "r"(tc::smem_addr(bar)) : "memory");
+}
+
+// out columns per tile: 256 (plain / residual) or 128 (SwiGLU: 128 gate + 128 up accumulator columns)
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w0,
+               const __grid_constant__ CUtensorMap map_w1, const Params p) {
+    constexpr int BN_OUT = (EPI == RFK_GEMM_EPI_SWIGLU) ? 128 : 256;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    const uint32_t base = tc::smem_addr(smem_raw);
+    if (base & 1023u) {  // uniform over the CTA, nothing allocated yet
+        if (threadIdx.x == 0) atomicCAS(&g_gemm_tc_error, 0, kErrSmemAlign);
+        return;
+    }
+    Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_raw + kStages * kStageBytes);
+    volatile int* abort_flag = &ctrl->abort;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int num_kb = (p.K + BK - 1) / BK;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) { tc::mbar_init(&ctrl->full[s], 1); tc::mbar_init(&ctrl->empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { tc::mbar_init(&ctrl->acc_full[a], 1); tc::mbar_init(&ctrl->acc_empty[a], 4); }
+        tc::mbar_init(&ctrl->drain, 1);
+        ctrl->abort = 0;
+        tc::fence_barrier_init();
+    }
+    if (warp == 0) {  // one warp allocates the CTA's tensor memory and later frees it
+        tc::tmem_alloc(&ctrl->tmem_base, kTmemCols);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    tc::tc_fence_after();
+    const uint32_t tmem_cta = ctrl->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer (one thread)
+        if (lane == 0) {
+            tc::prefetch_tensormap(&map_a); tc::prefetch_tensormap(&map_w0); tc::prefetch_tensormap(&map_w1);
+            int it = 0;       // K blocks issued so far by this CTA, over all of its tiles
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+                const int m0 = (t % p.tiles_m) * BM, n0 = (t / p.tiles_m) * BN_OUT;
+                // second weight box: the next 128 rows of W, or the up-projection rows of the same hidden units
+                const int n1 = (EPI == RFK_GEMM_EPI_SWIGLU) ? n0 : n0 + 128;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % kStages;
+                    // stage s was last read by the products of K block it - kStages
+                    if (it >= kStages && !tc::mbar_wait(&ctrl->empty[s], ((it / kStages) + 1) & 1, abort_flag)) { ok = false; break; }
+                    const uint32_t sA = base + s * kStageBytes;
+                    tc::mbar_arrive_expect_tx(&ctrl->full[s], kStageBytes);
+                    tma_load_2d(sA, &map_a, kb * BK, m0, &ctrl->full[s]);
+                    tma_load_2d(sA + kABytes, &map_w0, kb * BK, n0, &ctrl->full[s]);
+                    tma_load_2d(sA + kABytes + kWBoxBytes, &map_w1, kb * BK, n1, &ctrl->full[s]);
+                }
+            }
+            if (*abort_flag) {
+                // The CTA is giving up: every copy this thread started lands in this CTA's shared memory and counts on a
+                // full[] barrier; wait (bounded) for the last copy of each stage before the CTA exits.
+                for (int s = 0; s < kStages && s < it; ++s) {
+                    const int last = ((it - 1 - s) / kStages) * kStages + s;
+                    tc::mbar_wait_drain(&ctrl->full[s], (last / kStages) & 1);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ issuer of the products (one thread)
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc::umma_idesc_f16(BM, BNACC, 0);  // A and B both K-major
+            int it = 0, tl = 0;  // K blocks and tiles consumed so far
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++tl) {
+                const int acc = tl & 1;
+                // the epilogue must have drained this accumulator's previous tile (tile tl - 2)
+                if (tl >= 2) ok = tc::mbar_wait(&ctrl->acc_empty[acc], ((tl >> 1) + 1) & 1, abort_flag);
+                if (!ok) break;
+                tc::tc_fence_after();
+                const uint32_t d_tmem = tmem_cta + acc * BNACC;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % kStages;
+                    ok = tc::mbar_wait(&ctrl->full[s], (it / kStages) & 1, abort_flag);
+                    if (!ok) break;
+                    tc::tc_fence_after();
+                    const uint32_t a_lo = tc::umma_desc_lo(base + s * kStageBytes);
+                    const uint32_t b_lo = tc::umma_desc_lo(base + s * kStageBytes + kABytes);
+#pragma unroll
+                    for (int ks = 0; ks < BK / 16; ++ks)  // 16 halves = 32 bytes along a swizzled row
+                        tc::umma_f16_lo(d_tmem, a_lo + ks * 2, b_lo + ks * 2, idesc, (kb > 0) || (ks > 0));
+                    tc::umma_commit(&ctrl->empty[s]);     // the stage is free once these products have read it
+                }
+                if (ok) tc::umma_commit(&ctrl->acc_full[acc]);
+            }
+            if (*abort_flag) {  // giving up: let this thread's products finish before tensor memory is freed
+                tc::umma_commit(&ctrl->drain);
+                tc::mbar_wait_drain(&ctrl->drain, 0);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ epilogue, warps 2-5
+        const int lane_grp = warp & 3;                        // a warp reaches tensor-memory lanes [32 * (warp % 4), +32)
+        const int r = lane_grp * 32 + lane;                   // row within the tile
+        const uint32_t lane_off = (uint32_t)(lane_grp * 32) << 16;
+        bool ok = true;
+        int tl = 0;
+        uint32_t v[32];
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tl) {
+            const int acc = tl & 1;
+            const int m0 = (t % p.tiles_m) * BM, n0 = (t / p.tiles_m) * BN_OUT;
+            ok = tc::mbar_wait_warp(&ctrl->acc_full[acc], (tl >> 1) & 1, abort_flag);
+            if (!ok) break;
+            tc::tc_fence_after();
+            const uint32_t t_acc = tmem_cta + lane_off + acc * BNACC;
+            const int row = m0 + r;
+            const bool row_ok = row < p.M;
+            __half* crow = p.C + (size_t)(row_ok ? row : 0) * p.ldc + n0;
+            if (EPI == RFK_GEMM_EPI_SWIGLU) {
+                uint32_t u[32];
+#pragma unroll 1
+                for (int c = 0; c < BN_OUT / 32; ++c) {
+                    tc::tmem_ld32(t_acc + c * 32, v);          // gate columns
+                    tc::tmem_ld32(t_acc + 128 + c * 32, u);    // up columns of the same hidden units
+                    tc::tc_wait_ld(v);
+                    tc::tc_wait_ld(u);
+                    uint32_t o[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float g0 = __uint_as_float(v[i]), g1 = __uint_as_float(v[i + 1]);
+                        // silu(g) * u = g * u / (1 + 2^(-g log2 e))
+                        const float s0 = g0 * fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * g0));
+                        const float s1 = g1 * fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * g1));
+                        o[i >> 1] = pack_half2(s0 * __uint_as_float(u[i]), s1 * __uint_as_float(u[i + 1]));
+                    }
+                    if (row_ok) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int col = n0 + c * 32 + q * 8;
+                            if (col < p.N)
+                                *reinterpret_cast<uint4*>(crow + c * 32 + q * 8) = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+                        }
+                    }
+                }
+            } else {
+                const __half* rrow = (EPI == RFK_GEMM_EPI_RESIDUAL) ? p.R + (size_t)(row_ok ? row : 0) * p.ldr + n0 : nullptr;
+#pragma unroll 1
+                for (int c = 0; c < BN_OUT / 32; ++c) {
+                    if (n0 + c * 32 >= p.N) break;             // uniform over the CTA: the tile's tail lies beyond N
+                    tc::tmem_ld32(t_acc + c * 32, v);
+                    uint4 res[4];
+                    if (EPI == RFK_GEMM_EPI_RESIDUAL) {        // issued before the wait so that both latencies overlap
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int col = n0 + c * 32 + q * 8;
+                            res[q] = (row_ok && col < p.N) ? *reinterpret_cast<const uint4*>(rrow + c * 32 + q * 8) : make_uint4(0, 0, 0, 0);
+                        }
+                    }
+                    tc::tc_wait_ld(v);
+                    if (p.bias) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const int col = n0 + c * 32 + i;
+                            if (col < p.N) {
+                                const float2 b = unpack_half2(__ldg(reinterpret_cast<const uint32_t*>(p.bias + col)));
+                                // the unfused path rounds the product to fp16 before the bias is added (linear.cu:15-25)
+                                v[i] = __float_as_uint(round_half(__uint_as_float(v[i])) + b.x);
+                                v[i + 1] = __float_as_uint(round_half(__uint_as_float(v[i + 1])) + b.y);
+                            }
+                        }
+                    }
+                    uint32_t o[16];
+                    if (EPI == RFK_GEMM_EPI_RESIDUAL) {
+                        const uint32_t* rw = reinterpret_cast<const uint32_t*>(res);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float2 rr = unpack_half2(rw[i]);
+                            o[i] = pack_half2(__uint_as_float(v[2 * i]) + rr.x, __uint_as_float(v[2 * i + 1]) + rr.y);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) o[i] = pack_half2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                    }
+                    if (row_ok) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int col = n0 + c * 32 + q * 8;
+                            if (col < p.N)
+                                *reinterpret_cast<uint4*>(crow + c * 32 + q * 8) = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+                        }
+                    }
+                }
+            }
+            // every tcgen05.ld of this warp has completed (wait::ld above): hand the accumulator back
+            tc::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&ctrl->acc_empty[acc]);
+        }
+    }
+
+    // ---- teardown: every path (normal or aborted) arrives here with no divergence inside a warp
+    tc::tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc::tc_fence_after();
+        tc::tmem_dealloc(tmem_cta, kTmemCols);
+    }
+    if (tid == 0 && ctrl->abort) atomicCAS(&g_gemm_tc_error, 0, kErrTimeout);
+}
+
+}  // namespace tcgemm
+
+std::atomic<int> g_gemm_path{0};  // 0 automatic (tcgen05 kernel when the shape allows), 1 never, 2 tcgen05 or RFK_EUNSUPPORTED
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled, taken from the driver the runtime already has loaded (no link against libcuda)
+EncodeTiledFn tensor_map_encoder() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// fp16 matrix [rows][cols] with a row pitch of ld elements; boxes of 128 rows x 64 columns in the
+// 128-byte-swizzled layout; elements outside the matrix read as zeros
+bool make_map_2d(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld) {
+    EncodeTiledFn enc = tensor_map_encoder();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int EPI>
+int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw0, const CUtensorMap& mw1, const tcgemm::Params& p, int dev,
+                cudaStream_t st) {
+    static std::atomic<bool> configured[64];
+    static std::atomic<int> sm_count[64];
+    if (!configured[dev].load(std::memory_order_acquire)) {
+        cudaError_t e = cudaFuncSetAttribute(tcgemm::gemm_tc_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             tcgemm::kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        int n = 0;
+        e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return (int)e;
+        sm_count[dev].store(n, std::memory_order_relaxed);
+        configured[dev].store(true, std::memory_order_release);
+    }
+    const int tiles = p.tiles_m * p.tiles_n;
+    const int grid = std::min(tiles, std::max(1, sm_count[dev].load(std::memory_order_relaxed)));
+    tcgemm::gemm_tc_kernel<EPI><<<grid, tcgemm::kThreads, tcgemm::kSmemBytes, st>>>(ma, mw0, mw1, p);
+    return launch_status();
+}
+
+}  // namespace
+}  // namespace rfk
+
+using namespace rfk;
+
+extern "C" int rfk_gemm_f16(const rfk_half* A, long long lda, const rfk_half* W, long long ldw, const rfk_half* W_up,
+                            const rfk_half* bias, const rfk_half* R, long long ldr, rfk_half* C, long long ldc, int M,
+                            int N, int K, int epilogue, rfk_stream_t stream) {
+    if (!A || !W || !C || M < 0 || N <= 0 || K <= 0) return RFK_EINVAL;
+    if (epilogue < RFK_GEMM_EPI_NONE || epilogue > RFK_GEMM_EPI_SWIGLU) return RFK_EINVAL;
+    if (epilogue == RFK_GEMM_EPI_SWIGLU && (!W_up || bias)) return RFK_EINVAL;
+    if (epilogue == RFK_GEMM_EPI_RESIDUAL && !R) return RFK_EINVAL;
+    if (lda < K || ldw < K || ldc < N || (epilogue == RFK_GEMM_EPI_RESIDUAL && ldr < N)) return RFK_EINVAL;
+    if (M == 0) return RFK_OK;
+    if (g_gemm_path.load(std::memory_order_relaxed) == 1) return RFK_EUNSUPPORTED;
+    // TMA needs 16-byte aligned bases and pitches; the epilogue moves 8 halves per access
+    if ((lda | ldw | ldc | (epilogue == RFK_GEMM_EPI_RESIDUAL ? ldr : 0)) % 8 != 0 || N % 8 != 0 || K % 8 != 0)
+        return RFK_EUNSUPPORTED;
+    if (!aligned16(A) || !aligned16(W) || !aligned16(C) || (W_up && !aligned16(W_up)) || (R && !aligned16(R)) ||
+        (bias && (reinterpret_cast<uintptr_t>(bias) & 3u)))
+        return RFK_EUNSUPPORTED;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return RFK_EUNSUPPORTED;
+    CUtensorMap ma, mw0, mw1;
+    const bool swiglu = epilogue == RFK_GEMM_EPI_SWIGLU;
+    if (!make_map_2d(&ma, A, M, K, lda) || !make_map_2d(&mw0, W, N, K, ldw) ||
+        !make_map_2d(&mw1, swiglu ? W_up : W, N, K, ldw))
+        return RFK_EUNSUPPORTED;
+    tcgemm::Params p{};
+    p.C = (__half*)C; p.ldc = ldc; p.R = (const __half*)R; p.ldr = ldr; p.bias = (const __half*)bias;
+    p.M = M; p.N = N; p.K = K;
+    p.tiles_m = (M + tcgemm::BM - 1) / tcgemm::BM;
+    p.tiles_n = (N + (swiglu ? 128 : 256) - 1) / (swiglu ? 128 : 256);
+    cudaStream_t st = as_stream(stream);
+    switch (epilogue) {
+        case RFK_GEMM_EPI_NONE: return launch_gemm<RFK_GEMM_EPI_NONE>(ma, mw0, mw1, p, dev, st);
+        case RFK_GEMM_EPI_RESIDUAL: return launch_gemm<RFK_GEMM_EPI_RESIDUAL>(ma, mw0, mw1, p, dev, st);
+        default: return launch_gemm<RFK_GEMM_EPI_SWIGLU>(ma, mw0, mw1, p, dev, st);
+    }
+}
+
+extern "C" int rfk_gemm_set_path(int path) {
+    if (path < 0 || path > 2) return RFK_EINVAL;
+    g_gemm_path.store(path, std::memory_order_relaxed);
+    return RFK_OK;
+}
+
+extern "C" int rfk_gemm_error(int* code, int clear) {
+    if (!code) return RFK_EINVAL;
+    cudaError_t e = cudaMemcpyFromSymbol(code, g_gemm_tc_error, sizeof(int));
+    if (e != cudaSuccess) return (int)e;
+    if (clear) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(g_gemm_tc_error, &zero, sizeof(int));
+        if (e != cudaSuccess) return (int)e;
+    }
+    return RFK_OK;
+}

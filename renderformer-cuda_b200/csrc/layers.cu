@@ -43,10 +43,16 @@ static int blas_status(cublasStatus_t s) {
     return 1000 + (int)s;  // distinct from cudaError_t values used by the kernels
 }
 
-// C[M,N] (ldc) = alpha * A[M,K] (lda) * B[N,K]^T (ldb), row-major fp16, fp32 accumulation
+// C[M,N] (ldc) = alpha * A[M,K] (lda) * B[N,K]^T (ldb), row-major fp16, fp32 accumulation: the tcgen05 kernel of
+// librfk.so (rfk_gemm_f16) when it serves the shape, the library GEMM otherwise
 static int gemm_nt(rfk_ctx* ctx, cudaStream_t st, int M, int N, int K, float alpha, const __half* A,
                    int lda, const __half* B, int ldb, __half* C, int ldc) {
     if (M == 0 || N == 0) return RFK_OK;
+    if (alpha == 1.0f) {
+        const int rc = rfk_gemm_f16((const rfk_half*)A, lda, (const rfk_half*)B, ldb, nullptr, nullptr, nullptr, 0,
+                                    (rfk_half*)C, ldc, M, N, K, RFK_GEMM_EPI_NONE, (rfk_stream_t)st);
+        if (rc != RFK_EUNSUPPORTED) return rc;
+    }
     TRY(blas_status(cublasSetStream(ctx->blas, st)));
     const float beta = 0.0f;
     return blas_status(cublasGemmEx(ctx->blas, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha, B,
@@ -83,9 +89,64 @@ extern "C" int rfk_linear(rfk_ctx* ctx, const rfk_half* X, const rfk_half* W, co
                           rfk_half* Y, int M, int N, int K, rfk_stream_t stream) {
     if (!ctx || !X || !W || !Y || M < 0 || N <= 0 || K <= 0) return RFK_EINVAL;
     cudaStream_t st = (cudaStream_t)stream;
+    if (bias && M > 0) {  // bias added in the GEMM's epilogue when the tcgen05 kernel serves the shape
+        const int rc = rfk_gemm_f16(X, K, W, K, nullptr, bias, nullptr, 0, Y, N, M, N, K, RFK_GEMM_EPI_NONE, stream);
+        if (rc != RFK_EUNSUPPORTED) return rc;
+    }
     TRY(gemm_nt(ctx, st, M, N, K, 1.0f, (const __half*)X, K, (const __half*)W, K, (__half*)Y, N));
     if (bias) TRY(rfk_broadcast_add(Y, bias, (long long)M * N, N, stream));
     return RFK_OK;
+}
+
+// C = A B^T + R (R [M,N] fp16 with pitch ldr, may be C itself): the residual add rides in the epilogue of the
+// tcgen05 GEMM; on the library route R is first copied into C (unless it is C) and the GEMM accumulates onto it
+// (beta = 1), which rounds once as well.
+static int gemm_nt_residual(rfk_ctx* ctx, cudaStream_t st, int M, int N, int K, const __half* A, int lda, const __half* B,
+                            int ldb, __half* C, int ldc, const __half* R, int ldr) {
+    if (M == 0 || N == 0) return RFK_OK;
+    const int rc = rfk_gemm_f16((const rfk_half*)A, lda, (const rfk_half*)B, ldb, nullptr, nullptr, (const rfk_half*)R, ldr,
+                                (rfk_half*)C, ldc, M, N, K, RFK_GEMM_EPI_RESIDUAL, (rfk_stream_t)st);
+    if (rc != RFK_EUNSUPPORTED) return rc;
+    if (R != C) {
+        cudaError_t e = cudaMemcpy2DAsync(C, (size_t)ldc * 2, R, (size_t)ldr * 2, (size_t)N * 2, (size_t)M,
+                                          cudaMemcpyDeviceToDevice, st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    TRY(blas_status(cublasSetStream(ctx->blas, st)));
+    const float one = 1.0f;
+    return blas_status(cublasGemmEx(ctx->blas, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &one, B, CUDA_R_16F, ldb, A, CUDA_R_16F,
+                                    lda, &one, C, CUDA_R_16F, ldc, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT));
+}
+
+// out = (residual +) W2 (silu(W1 x) * (W3 x)). With the tcgen05 GEMM the gate and up projections and the
+// activation are one kernel that writes [M, hidden] directly (no gate|up intermediate); otherwise one or two
+// library GEMMs into a [M, 2*hidden] gate|up buffer and the gate kernel. The residual add (if asked; `residual`
+// may be `out`) is part of the W2 product either way.
+static int ffn_core(rfk_ctx* ctx, const rfk_ffn_weights* w, const rfk_half* x, rfk_half* out, const rfk_half* residual,
+                    rfk_half* buf, int M, int dim, int hidden, rfk_stream_t stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (M == 0) return RFK_OK;
+    const __half* act = (const __half*)buf;
+    int act_ld = hidden;
+    const int rc = rfk_gemm_f16(x, dim, w->w1, dim, w->w3, nullptr, nullptr, 0, buf, hidden, M, hidden, dim,
+                                RFK_GEMM_EPI_SWIGLU, stream);
+    if (rc == RFK_EUNSUPPORTED) {
+        __half* gu = (__half*)buf;  // [M, 2*hidden]: gate | up per row
+        if (w->w3 == w->w1 + (size_t)hidden * dim) {
+            TRY(gemm_nt(ctx, st, M, 2 * hidden, dim, 1.0f, (const __half*)x, dim, (const __half*)w->w1, dim, gu, 2 * hidden));
+        } else {
+            TRY(gemm_nt(ctx, st, M, hidden, dim, 1.0f, (const __half*)x, dim, (const __half*)w->w1, dim, gu, 2 * hidden));
+            TRY(gemm_nt(ctx, st, M, hidden, dim, 1.0f, (const __half*)x, dim, (const __half*)w->w3, dim, gu + hidden, 2 * hidden));
+        }
+        TRY(rfk_swiglu_inplace(buf, M, hidden, stream));  // activation over the gate half, pitch 2*hidden
+        act_ld = 2 * hidden;
+    } else if (rc != RFK_OK) {
+        return rc;
+    }
+    if (residual)
+        return gemm_nt_residual(ctx, st, M, dim, hidden, act, act_ld, (const __half*)w->w2, hidden, (__half*)out, dim,
+                                (const __half*)residual, dim);
+    return gemm_nt(ctx, st, M, dim, hidden, 1.0f, act, act_ld, (const __half*)w->w2, hidden, (__half*)out, dim);
 }
 
 extern "C" int rfk_ffn_swiglu(rfk_ctx* ctx, const rfk_ffn_weights* w, const rfk_half* x,
@@ -93,20 +154,7 @@ extern "C" int rfk_ffn_swiglu(rfk_ctx* ctx, const rfk_ffn_weights* w, const rfk_
                               rfk_stream_t stream) {
     if (!ctx || !w || !w->w1 || !w->w2 || !w->w3 || !x || !out || !buf) return RFK_EINVAL;
     if (M < 0 || dim <= 0 || hidden <= 0) return RFK_EINVAL;
-    cudaStream_t st = (cudaStream_t)stream;
-    __half* gu = (__half*)buf;  // [M, 2*hidden]: gate | up per row
-    if (w->w3 == w->w1 + (size_t)hidden * dim) {
-        TRY(gemm_nt(ctx, st, M, 2 * hidden, dim, 1.0f, (const __half*)x, dim, (const __half*)w->w1,
-                    dim, gu, 2 * hidden));
-    } else {
-        TRY(gemm_nt(ctx, st, M, hidden, dim, 1.0f, (const __half*)x, dim, (const __half*)w->w1, dim,
-                    gu, 2 * hidden));
-        TRY(gemm_nt(ctx, st, M, hidden, dim, 1.0f, (const __half*)x, dim, (const __half*)w->w3, dim,
-                    gu + hidden, 2 * hidden));
-    }
-    TRY(rfk_swiglu_inplace(buf, M, hidden, stream));  // activation over the gate half, pitch 2*hidden
-    return gemm_nt(ctx, st, M, dim, hidden, 1.0f, gu, 2 * hidden, (const __half*)w->w2, hidden,
-                   (__half*)out, dim);
+    return ffn_core(ctx, w, x, out, nullptr, buf, M, dim, hidden, stream);
 }
 
 extern "C" int rfk_sdpa(rfk_ctx* ctx, const rfk_half* Q, const rfk_half* K, const rfk_half* V,
@@ -213,8 +261,11 @@ extern "C" int rfk_precompute_cross_kv(rfk_ctx* ctx, const rfk_cross_attn_weight
                             nullptr, stream);
 }
 
-extern "C" int rfk_cross_attention_cached(rfk_ctx* ctx, const rfk_cross_attn_weights* w,
-                                          const rfk_half* q_in, rfk_half* out, rfk_half* proj_buf,
+// `residual` (may be `out`, may be NULL): out = residual + attention output, the add being the epilogue of the
+// output projection.
+static int cross_attention_impl(rfk_ctx* ctx, const rfk_cross_attn_weights* w,
+                                          const rfk_half* q_in, rfk_half* out, const rfk_half* residual,
+                                          rfk_half* proj_buf,
                                           float* score_buf, const rfk_half* K_cached,
                                           const rfk_half* V_cached, int B, int Sq, int Sk, int n_keys,
                                           int q_dim, int dim, int num_heads,
@@ -239,7 +290,23 @@ extern "C" int rfk_cross_attention_cached(rfk_ctx* ctx, const rfk_cross_attn_wei
     }
     TRY(attention_core(ctx, Q_bhsd, K_use, V_cached, Q /* [B,Sq,dim] */, score_buf, B, num_heads, Sq, Sk, n_keys,
                        hd, 1, stream));
+    if (residual && !w->out_proj_b)
+        return gemm_nt_residual(ctx, (cudaStream_t)stream, Mq, q_dim, dim, (const __half*)Q, dim, (const __half*)w->out_proj_w,
+                                dim, (__half*)out, q_dim, (const __half*)residual, q_dim);
+    if (residual) return RFK_EUNSUPPORTED;  // callers with a bias keep the separate residual add
     return rfk_linear(ctx, Q, w->out_proj_w, w->out_proj_b, out, Mq, q_dim, dim, stream);
+}
+
+extern "C" int rfk_cross_attention_cached(rfk_ctx* ctx, const rfk_cross_attn_weights* w,
+                                          const rfk_half* q_in, rfk_half* out, rfk_half* proj_buf,
+                                          float* score_buf, const rfk_half* K_cached,
+                                          const rfk_half* V_cached, int B, int Sq, int Sk, int n_keys,
+                                          int q_dim, int dim, int num_heads,
+                                          const rfk_half* q_rope_cos, const rfk_half* q_rope_sin,
+                                          const rfk_half* k_rope_cos, const rfk_half* k_rope_sin,
+                                          rfk_stream_t stream) {
+    return cross_attention_impl(ctx, w, q_in, out, nullptr, proj_buf, score_buf, K_cached, V_cached, B, Sq, Sk, n_keys,
+                                q_dim, dim, num_heads, q_rope_cos, q_rope_sin, k_rope_cos, k_rope_sin, stream);
 }
 
 // Window attention over tokens that are already in window order: window_buf [BnW * ws2, dim] in,
@@ -329,39 +396,52 @@ extern "C" int rfk_decoder_layer_forward_cached(
     if (!ctx || !w || !x || !temp || !proj_buf || !qkv_buf || !ffn_buf || !window_buf) return RFK_EINVAL;
     if (Sq != patch_h * patch_w) return RFK_EINVAL;
     const int Mq = B * Sq;
-    // 1) (deferred FFN residual of the previous layer +) pre-norm -> cached cross-attention
+    // 1) (deferred residual of the previous layer, if any +) pre-norm -> cached cross-attention
     TRY(rfk_rmsnorm_residual_f16(x, pending_residual, w->query_norm_gamma, temp, Mq, dim, kEpsFp16, stream));
-    rfk_half* cross_out = qkv_buf;
-    TRY(rfk_cross_attention_cached(ctx, &w->cross_attn, temp, cross_out, proj_buf, cross_score_buf, K_cached,
-                                   V_cached, B, Sq, Sk, n_keys, dim, dim, num_heads, q_rope_cos, q_rope_sin,
-                                   k_rope_cos, k_rope_sin, stream));
     // 2) residual + pre-norm -> swin attention -> residual + pre-norm of the FFN. When the fused norm can take an
     //    operand in window order, the cyclic shift / window partition and their inverse cost no launch: the first norm
-    //    writes the windows, the second reads the attention output out of them.
+    //    writes the windows, the second reads the attention output out of them; and the residual add of the
+    //    cross-attention is the epilogue of its output projection (x += ...), so the first norm reads x only.
+    auto a16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     const bool win_ok = window_size > 0 && patch_h % window_size == 0 && patch_w % window_size == 0 &&
-                        num_heads > 0 && dim % num_heads == 0 && dim % 8 == 0 && dim <= 2048;
-    int rc = win_ok ? rfk_rmsnorm_residual_f16_windows(x, cross_out, w->self_attn_norm_gamma, window_buf, B, patch_h,
-                                                       patch_w, dim, window_size, shift_size, 1, kEpsFp16, stream)
-                    : RFK_EUNSUPPORTED;
-    if (rc == RFK_OK) {
+                        num_heads > 0 && dim % num_heads == 0 && dim % 8 == 0 && dim <= 2048 && a16(x) && a16(window_buf) &&
+                        a16(temp) && a16(qkv_buf) && a16(w->self_attn_norm_gamma) && a16(w->ffn_norm_gamma);
+    if (win_ok) {
+        if (!w->cross_attn.out_proj_b) {
+            TRY(cross_attention_impl(ctx, &w->cross_attn, temp, x, x, proj_buf, cross_score_buf, K_cached, V_cached, B, Sq, Sk,
+                                     n_keys, dim, dim, num_heads, q_rope_cos, q_rope_sin, k_rope_cos, k_rope_sin, stream));
+            TRY(rfk_rmsnorm_residual_f16_windows(x, nullptr, w->self_attn_norm_gamma, window_buf, B, patch_h, patch_w, dim,
+                                                 window_size, shift_size, 1, kEpsFp16, stream));
+        } else {
+            rfk_half* cross_out = qkv_buf;
+            TRY(rfk_cross_attention_cached(ctx, &w->cross_attn, temp, cross_out, proj_buf, cross_score_buf, K_cached, V_cached,
+                                           B, Sq, Sk, n_keys, dim, dim, num_heads, q_rope_cos, q_rope_sin, k_rope_cos,
+                                           k_rope_sin, stream));
+            TRY(rfk_rmsnorm_residual_f16_windows(x, cross_out, w->self_attn_norm_gamma, window_buf, B, patch_h, patch_w, dim,
+                                                 window_size, shift_size, 1, kEpsFp16, stream));
+        }
         const int ws2 = window_size * window_size, nW = (patch_h / window_size) * (patch_w / window_size);
         TRY(swin_core(ctx, &w->self_attn, window_buf, qkv_buf, self_score_buf, proj_buf, B * nW, nW, ws2, dim, num_heads,
                       (shift_mask && shift_size > 0) ? shift_mask : nullptr, stream));
         TRY(rfk_rmsnorm_residual_f16_windows(x, qkv_buf, w->ffn_norm_gamma, temp, B, patch_h, patch_w, dim, window_size,
                                              shift_size, 2, kEpsFp16, stream));
-    } else if (rc == RFK_EUNSUPPORTED) {
+    } else {
+        rfk_half* cross_out = qkv_buf;
+        TRY(rfk_cross_attention_cached(ctx, &w->cross_attn, temp, cross_out, proj_buf, cross_score_buf, K_cached, V_cached, B,
+                                       Sq, Sk, n_keys, dim, dim, num_heads, q_rope_cos, q_rope_sin, k_rope_cos, k_rope_sin,
+                                       stream));
         TRY(rfk_rmsnorm_residual_f16(x, cross_out, w->self_attn_norm_gamma, temp, Mq, dim, kEpsFp16, stream));
         TRY(rfk_swin_self_attention(ctx, &w->self_attn, temp, nullptr, x, window_buf, qkv_buf, self_score_buf,
                                     proj_buf, B, patch_h, patch_w, dim, num_heads, window_size, shift_size,
                                     shift_mask, stream));
         TRY(rfk_rmsnorm(x, w->ffn_norm_gamma, temp, Mq, dim, kEpsFp16, stream));
-    } else {
-        return rc;
     }
-    // 3) FFN; its residual is left to the next layer's first kernel when asked
-    TRY(rfk_ffn_swiglu(ctx, &w->ffn, temp, ffn_buf, qkv_buf, Mq, dim, ffn_hidden, stream));
-    if (pending_out) { *pending_out = ffn_buf; return RFK_OK; }
-    return rfk_residual_add(x, ffn_buf, (long long)Mq * dim, stream);
+    // 3) FFN with its residual add in the epilogue of the W2 product: x is complete when the layer returns and
+    //    nothing is left pending for the next layer
+    if (!w->ffn.w1 || !w->ffn.w2 || !w->ffn.w3 || ffn_hidden <= 0) return RFK_EINVAL;
+    TRY(ffn_core(ctx, &w->ffn, temp, x, x, qkv_buf, Mq, dim, ffn_hidden, stream));
+    if (pending_out) *pending_out = nullptr;
+    return RFK_OK;
 }
 
 extern "C" int rfk_encoder_layer_forward_mixed(

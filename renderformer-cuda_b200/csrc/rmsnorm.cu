@@ -221,11 +221,12 @@ extern "C" int rfk_rmsnorm_residual_f16_windows(rfk_half* x, const rfk_half* r, 
                                                 rfk_half* y, int B, int H, int W, int dim,
                                                 int window_size, int shift_size, int windowed_operand,
                                                 float eps, rfk_stream_t stream) {
-    if (!x || !r || !gamma || !y || B < 0 || H <= 0 || W <= 0 || dim <= 0) return RFK_EINVAL;
+    if (!x || !gamma || !y || B < 0 || H <= 0 || W <= 0 || dim <= 0) return RFK_EINVAL;
     if (window_size <= 0 || H % window_size || W % window_size || shift_size < 0) return RFK_EINVAL;
     if (windowed_operand != 1 && windowed_operand != 2) return RFK_EINVAL;
-    if ((const void*)x == (const void*)y || (const void*)r == (const void*)y) return RFK_EINVAL;
-    if (dim % 8 != 0 || dim > 2048 || !aligned16(x) || !aligned16(y) || !aligned16(gamma) || !aligned16(r))
+    if (!r && windowed_operand != 1) return RFK_EINVAL;  // without a residual only the output can be in window order
+    if ((const void*)x == (const void*)y || (r && (const void*)r == (const void*)y)) return RFK_EINVAL;
+    if (dim % 8 != 0 || dim > 2048 || !aligned16(x) || !aligned16(y) || !aligned16(gamma) || (r && !aligned16(r)))
         return RFK_EUNSUPPORTED;
     const long long rows_ll = (long long)B * H * W;
     if (rows_ll > 0x7fffffffLL) return RFK_EUNSUPPORTED;
@@ -234,15 +235,20 @@ extern "C" int rfk_rmsnorm_residual_f16_windows(rfk_half* x, const rfk_half* r, 
     const WinRows wr{H, W, window_size, shift_size};
     cudaStream_t st = as_stream(stream);
     __half* xh = (__half*)x;
-#define RFK_RMS_WIN(N, WW, M)                                                                               \
-    rmsnorm_row_kernel<__half, __half, __half, N, WW, true, true, M>                                        \
-        <<<ceil_div(rows, (kRmsThreads / 32) / WW), kRmsThreads, 0, st>>>(xh, xh, (const __half*)r, gamma,   \
-                                                                           (__half*)y, rows, dim, eps, wr)
-#define RFK_RMS_WIN_DIM(M)                          \
-    if (dim <= 256) RFK_RMS_WIN(1, 1, M);           \
-    else if (dim <= 512) RFK_RMS_WIN(1, 2, M);      \
-    else if (dim <= 1024) RFK_RMS_WIN(1, 4, M);     \
-    else RFK_RMS_WIN(2, 4, M)
+#define RFK_RMS_WIN(N, WW, M)                                                                                   \
+    if (r)                                                                                                      \
+        rmsnorm_row_kernel<__half, __half, __half, N, WW, true, true, M>                                        \
+            <<<ceil_div(rows, (kRmsThreads / 32) / WW), kRmsThreads, 0, st>>>(xh, xh, (const __half*)r, gamma,   \
+                                                                               (__half*)y, rows, dim, eps, wr); \
+    else                                                                                                        \
+        rmsnorm_row_kernel<__half, __half, __half, N, WW, false, false, 1>                                      \
+            <<<ceil_div(rows, (kRmsThreads / 32) / WW), kRmsThreads, 0, st>>>(xh, xh, nullptr, gamma,            \
+                                                                               (__half*)y, rows, dim, eps, wr)
+#define RFK_RMS_WIN_DIM(M)                            \
+    if (dim <= 256) { RFK_RMS_WIN(1, 1, M); }         \
+    else if (dim <= 512) { RFK_RMS_WIN(1, 2, M); }    \
+    else if (dim <= 1024) { RFK_RMS_WIN(1, 4, M); }   \
+    else { RFK_RMS_WIN(2, 4, M); }
     if (windowed_operand == 1) { RFK_RMS_WIN_DIM(1); } else { RFK_RMS_WIN_DIM(2); }
 #undef RFK_RMS_WIN_DIM
 #undef RFK_RMS_WIN

@@ -432,6 +432,8 @@ extern "C" int rfk_session_encode_scene(rfk_session* d, const float* tri, const 
 static int check_attention_error() {
     int code = 0;
     TRY(rfk_flash_attention_error(&code, 0));
+    if (code) return RFK_EKERNEL;
+    TRY(rfk_gemm_error(&code, 0));  // the tcgen05 GEMM kernel reports the same way
     return code ? RFK_EKERNEL : RFK_OK;
 }
 

@@ -279,6 +279,85 @@ def run_suite(backend, peak_gbs: float, iters: int = 20, warmup: int = 3, only: 
     return rows
 
 
+def _time_graph(fn, nsets, iters):
+    for i in range(3):
+        fn(i % nsets)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(iters):
+            fn(i % nsets)
+    graph.replay()
+    torch.cuda.synchronize()
+    st = torch.cuda.Event(enable_timing=True); en = torch.cuda.Event(enable_timing=True)
+    st.record(); graph.replay(); en.record()
+    torch.cuda.synchronize()
+    return st.elapsed_time(en) / iters
+
+
+def gemm_table(iters: int = 20, nsets: int = 6) -> list[dict]:
+    """The projections of one decoder layer at the benchmark shape (4096 tokens, dim 1024, FFN 4096), each timed
+    through rfk_gemm_f16 (tcgen05 kernel, fused epilogue) and through the library route the layer functions fall
+    back to (cublasGemmEx, plus the separate gate / residual kernel the fused epilogue replaces), on rotating
+    weight and activation sets (graph replay, CUDA events)."""
+    import ctypes
+    from . import _abi, ops, session
+    L = _abi.load("rfk_layers.h")
+    VP = ctypes.c_void_p
+    ctx = session.Ctx()
+    H16 = torch.float16
+    M, dim, ffn = NP, D, 4096
+    rows = []
+
+    def P(t):
+        return VP(t.data_ptr())
+
+    def st():
+        return VP(torch.cuda.current_stream().cuda_stream)
+
+    def case(name, N, K, epi, flop):
+        a = [_r((M, K), H16) for _ in range(nsets)]
+        w = [_r((N, K), H16, K ** -0.5) for _ in range(nsets)]
+        wu = [_r((N, K), H16, K ** -0.5) for _ in range(nsets)] if epi == "swiglu" else None
+        c = [torch.empty(M, N, device="cuda", dtype=H16) for _ in range(nsets)]
+        r = [_r((M, N), H16) for _ in range(nsets)] if epi == "residual" else None
+        gu = torch.empty(M, 2 * N, device="cuda", dtype=H16) if epi == "swiglu" else None
+        wcat = [torch.cat([w[i], wu[i]]) for i in range(nsets)] if epi == "swiglu" else None
+
+        def fused(i):
+            ops.gemm_f16(a[i], w[i], c[i], M, N, K, w_up=wu[i] if wu else None, residual=r[i] if r else None)
+
+        def library(i):
+            if epi == "swiglu":   # one [M, 2N] product + the in-place gate kernel
+                assert L.rfk_linear(ctx.h, P(a[i]), P(wcat[i]), None, P(gu), M, 2 * N, K, st()) == 0
+                ops.swiglu_inplace(gu, M, N)
+            else:
+                assert L.rfk_linear(ctx.h, P(a[i]), P(w[i]), None, P(c[i]), M, N, K, st()) == 0
+                if epi == "residual":
+                    ops.residual_add(c[i], r[i], M * N)
+
+        ops.gemm_set_path(2)
+        t_f = _time_graph(fused, nsets, iters)
+        ops.gemm_set_path(1)
+        t_l = _time_graph(library, nsets, iters)
+        ops.gemm_set_path(0)
+        rows.append({"gemm": name, "M": M, "N": N, "K": K, "epilogue": epi, "us_tcgen05": round(t_f * 1e3, 2),
+                     "tflops_tcgen05": round(flop / (t_f * 1e-3) / 1e12, 1), "us_library": round(t_l * 1e3, 2),
+                     "tflops_library": round(flop / (t_l * 1e-3) / 1e12, 1), "speedup": round(t_l / t_f, 3)})
+        torch.cuda.empty_cache()
+
+    case("q / out projection", dim, dim, "none", 2.0 * M * dim * dim)
+    case("out projection + residual", dim, dim, "residual", 2.0 * M * dim * dim)
+    case("swin in projection", 3 * dim, dim, "none", 2.0 * M * 3 * dim * dim)
+    case("FFN w1|w3 + SwiGLU", ffn, dim, "swiglu", 2.0 * M * 2 * ffn * dim)
+    case("FFN w2 + residual", dim, ffn, "residual", 2.0 * M * dim * ffn)
+    err = ops.gemm_error(clear=False)
+    ctx.close()
+    if err:
+        raise RuntimeError(f"tcgen05 GEMM kernel reported error word {err}")
+    return rows
+
+
 def _main():
     """python -m renderformer_cuda_b200.kernel_bench [--op NAME ...] [--iters N] [--eager]
 
@@ -293,7 +372,12 @@ def _main():
     ap.add_argument("--eager", action="store_true")
     ap.add_argument("--peak", type=float, default=6455.6, help="HBM GB/s used for the fraction column")
     ap.add_argument("--softmax-rows", type=int, default=SOFTMAX_ROWS)
+    ap.add_argument("--gemm", action="store_true", help="print the tcgen05-vs-library GEMM table instead")
     a = ap.parse_args()
+    if a.gemm:
+        for row in gemm_table(a.iters):
+            print(json.dumps(row))
+        return
     globals()["SOFTMAX_ROWS"] = a.softmax_rows
     backend = RfkBackend()
     if a.eager:

@@ -268,6 +268,34 @@ def flash_attention_error(clear=True):
     return code.value
 
 
+# ------------------------------------------------------- dense projections
+
+GEMM_EPI_NONE, GEMM_EPI_RESIDUAL, GEMM_EPI_SWIGLU = 0, 1, 2
+
+
+def gemm_f16(a, w, c, M, N, K, w_up=None, bias=None, residual=None, lda=None, ldw=None, ldc=None, ldr=None):
+    """c[M,N] = epilogue(a[M,K] w[N,K]^T) on the tcgen05 tensor cores (rfk_gemm_f16): plain (+ bias), with
+    `residual` added, or - with `w_up` - silu(a w^T) * (a w_up^T). Mirrors rf::linear (src/layers/linear.h:9)
+    and the fused steps of rf::ffn_swiglu (src/layers/transformer.cu:63-76)."""
+    epi = GEMM_EPI_SWIGLU if w_up is not None else GEMM_EPI_RESIDUAL if residual is not None else GEMM_EPI_NONE
+    _call("rfk_gemm_f16", _p(a, H, "a"), lda or K, _p(w, H, "w"), ldw or K, _p(w_up, H, "w_up"), _p(bias, H, "bias"),
+          _p(residual, H, "residual"), (ldr or N) if residual is not None else 0, _p(c, H, "c"), ldc or N, M, N, K, epi,
+          _stream())
+
+
+def gemm_set_path(path):
+    """0 automatic (tcgen05 kernel), 1 library GEMM only (rfk_gemm_f16 refuses), 2 as 0."""
+    _call("rfk_gemm_set_path", int(path))
+
+
+def gemm_error(clear=True):
+    """Error word of the tcgen05 GEMM kernel on the current device (0 = none)."""
+    import ctypes
+    code = ctypes.c_int(-1)
+    _call("rfk_gemm_error", ctypes.byref(code), int(clear))
+    return code.value
+
+
 # -------------------------------------------------------------- activations
 
 def fused_silu_mul(a, b, out, n):

@@ -135,7 +135,8 @@ def test_linear_and_ffn_match_reference(small, ctx, ref_blas):
     assert L.rfk_linear(ctx.h, _p(x), _p(t["dec0.swin_in_w"]), _p(bias), _p(y), M, 3 * dim, dim, _s()) == 0
     R.call("ref_linear", R.Raw(ref_blas), x, t["dec0.swin_in_w"], bias, yr, M, 3 * dim, dim, lib=R.layers())
     torch.cuda.synchronize()
-    assert torch.equal(y, yr)                                  # same cuBLAS call, same bias add
+    # different GEMM kernels, same products: equal up to one fp16 rounding step of the result
+    _close(y, yr, "linear + bias", atol=2e-3, rtol=2.0 ** -9, mean_tol=2e-4)
     w = small.model.decoder_record(0).ffn
     out = torch.empty(M, dim, device="cuda", dtype=H16); outr = torch.empty_like(out)
     buf = torch.empty(M * 2 * ffn, device="cuda", dtype=H16); bufr = torch.empty_like(buf)
