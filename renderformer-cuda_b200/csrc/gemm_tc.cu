@@ -26,6 +26,7 @@
 // Every mbarrier wait is bounded; on a time-out the CTA raises an error word, waits (bounded) for its
 // own copies and products in flight, frees its tensor memory and returns.
 #include <cuda.h>  // CUtensorMap and its enums; the encoder itself is looked up at run time
+#include <cstdlib>
 #include "attention_tc.cuh"
 #include "common.cuh"
 
@@ -288,7 +289,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
 }  // namespace tcgemm
 
-std::atomic<int> g_gemm_path{0};  // 0 automatic (tcgen05 kernel when the shape allows), 1 never, 2 tcgen05 or RFK_EUNSUPPORTED
+// 0 automatic (tcgen05 kernel when the shape allows), 1 never (callers use their library GEMM), 2 as 0. The
+// environment variable RFK_GEMM_PATH sets the initial value, for side-by-side runs of an unchanged program.
+static int initial_gemm_path() {
+    const char* e = getenv("RFK_GEMM_PATH");
+    return (e && e[0] >= '0' && e[0] <= '2' && e[1] == 0) ? e[0] - '0' : 0;
+}
+std::atomic<int> g_gemm_path{initial_gemm_path()};
 
 namespace {
 
