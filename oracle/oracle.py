@@ -193,6 +193,21 @@ def softmax_inplace(data, mask=None, swin=None):
     return data
 
 
+# ------------------------------------------------------------------- linear
+
+
+def linear(x, w, bias=None):
+    """x [M,K] fp16 (any row pitch), w [N,K] fp16 -> half(x w^T) (+ bias), fp32 accumulation (rf::linear)."""
+    x = np.asarray(x)
+    assert x.dtype == f16 and x.ndim == 2 and x.strides[1] == 2 and x.strides[0] % 2 == 0
+    w = _c(w, f16)
+    M, K = x.shape; N = w.shape[0]
+    out = np.empty((M, N), f16)
+    lib().oracle_linear_f16(_ptr(x), L(x.strides[0] // 2), _ptr(w), _ptr(None if bias is None else _c(bias, f16)), _ptr(out),
+                            L(M), I(N), I(K))
+    return out
+
+
 # ---------------------------------------------------------------- attention
 
 
@@ -208,6 +223,16 @@ def sdpa(Q, K, V, n_keys=None, mask=None, o_bshd=False, scale=None):
     out = np.empty((B, Sq, Hh * D) if o_bshd else (B, Hh, Sq, D), f16)
     lib().oracle_sdpa(_ptr(Q), _ptr(K), _ptr(V), _ptr(out), I(B), I(Hh), I(Sq), I(Sk), I(n_keys), I(D),
                       Fl(scale if scale is not None else D ** -0.5), _ptr(mask), I(nW), I(int(o_bshd)))
+    return out
+
+
+def sdpa_f32acc(Q, K, V, n_keys=None, scale=None):
+    """The unmasked attention with fp32 accumulation (the timed host-core port); O [B,Sq,H*D] fp16."""
+    Q, K, V = _c(Q, f16), _c(K, f16), _c(V, f16)
+    B, Hh, Sq, D = Q.shape; Sk = K.shape[2]
+    out = np.empty((B, Sq, Hh * D), f16)
+    lib().oracle_sdpa_f32acc(_ptr(Q), _ptr(K), _ptr(V), _ptr(out), I(B), I(Hh), I(Sq), I(Sk), I(Sk if n_keys is None else n_keys),
+                             I(D), Fl(scale if scale is not None else D ** -0.5))
     return out
 
 

@@ -18,11 +18,12 @@
  * pinned against outputs of the reference's own CUDA kernels run on a B200 on seeded
  * inputs; those outputs are committed under tests/golden/ with the script that made them.
  *
- * Build: gcc -O2 -fopenmp -shared -fPIC rfk_oracle.c -o liboracle.so -lm   (see Makefile)
+ * Build: gcc -O3 -fopenmp -shared -fPIC rfk_oracle.c -o liboracle.so -lm   (see Makefile)
  */
 #include <float.h>
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 #ifdef _OPENMP
 #include <omp.h>
@@ -338,6 +339,100 @@ void oracle_sdpa(const f16* Q, const f16* K, const f16* V, f16* O, int B, int H,
             for (int j = 0; j < n_keys; ++j) acc += (double)(float)(f16)(s[j] * inv) * (double)(float)Vh[(long)j * D + d];
             orow[d] = (f16)(float)acc;
         }
+    }
+}
+
+/* ------------------------------------------------------------------- linear */
+
+/* The two functions that carry the timed host baseline's contractions are compiled twice, for the
+ * x86-64-v3 level (AVX2, FMA, hardware fp16 conversion) and for the base instruction set; the loader
+ * picks one per machine, so the library runs on any x86-64 host. */
+#if defined(__x86_64__) && defined(__GNUC__) && !defined(__clang__)
+#define HOT_CLONES __attribute__((target_clones("arch=x86-64-v3", "default")))
+#else
+#define HOT_CLONES
+#endif
+
+/* Eight independent partial sums, so that the compiler can keep them in vector lanes without
+ * reordering a single floating-point chain. */
+static inline __attribute__((always_inline)) float dot_f32(const float* a, const float* b, int n) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    int k = 0;
+    for (; k + 8 <= n; k += 8)
+        for (int j = 0; j < 8; ++j) acc[j] += a[k + j] * b[k + j];
+    float s = ((acc[0] + acc[4]) + (acc[1] + acc[5])) + ((acc[2] + acc[6]) + (acc[3] + acc[7]));
+    for (; k < n; ++k) s += a[k] * b[k];
+    return s;
+}
+
+/* src/layers/linear.cu:7-25 — Y[M,N] = half(sum_k X[m,k] W[n,k]) over fp16 operands with fp32
+ * accumulation (cublasGemmEx, CUBLAS_COMPUTE_32F), then, if bias != NULL,
+ * Y = half(float(Y) + float(bias[n])) (add_bias, linear.cu:27-40). X has row pitch ldx >= K.
+ * Blocks of 8 rows of X and one row of W at a time are widened to fp32 once and reused. */
+HOT_CLONES void oracle_linear_f16(const f16* X, long ldx, const f16* W, const f16* bias, f16* Y, long M, int N, int K) {
+    enum { RB = 8 };
+    const long blocks = (M + RB - 1) / RB;
+    PAR_FOR
+    for (long blk = 0; blk < blocks; ++blk) {
+        const long m0 = blk * RB;
+        const int rb = (int)((M - m0) < RB ? (M - m0) : RB);
+        float xf[RB][K];
+        float wf[K];
+        for (int r = 0; r < rb; ++r)
+            for (int k = 0; k < K; ++k) xf[r][k] = (float)X[(m0 + r) * ldx + k];
+        for (int n = 0; n < N; ++n) {
+            for (int k = 0; k < K; ++k) wf[k] = (float)W[(long)n * K + k];
+            for (int r = 0; r < rb; ++r) {
+                f16 y = (f16)dot_f32(xf[r], wf, K);
+                if (bias) y = (f16)((float)y + (float)bias[n]);
+                Y[(m0 + r) * N + n] = y;
+            }
+        }
+    }
+}
+
+/* The same attention (no mask) with fp32 accumulation and operands widened once per head, written for
+ * the timed host-core baseline: oracle_sdpa above accumulates in double with strided access and is the
+ * checker; this one is the port that is timed, and a CPU test holds the two together.
+ * Q [B,H,Sq,D], K,V [B,H,Sk,D], O [B,Sq,H*D]; the first n_keys keys take part. */
+HOT_CLONES void oracle_sdpa_f32acc(const f16* Q, const f16* K, const f16* V, f16* O, int B, int H, int Sq, int Sk,
+                        int n_keys, int D, float scale) {
+    enum { QB = 64 };
+    const int qblocks = (Sq + QB - 1) / QB;
+    const long jobs = (long)B * H * qblocks;
+    PAR_FOR
+    for (long job = 0; job < jobs; ++job) {
+        const int qb = (int)(job % qblocks);
+        const long bh = job / qblocks;
+        const int h = (int)(bh % H), b = (int)(bh / H);
+        const f16* Kh = K + bh * (long)Sk * D;
+        const f16* Vh = V + bh * (long)Sk * D;
+        float qf[D], s[n_keys], acc[D];
+        float* kf = (float*)malloc((size_t)2 * n_keys * D * sizeof(float));  /* this head's keys and values, widened once */
+        float* vf = kf + (size_t)n_keys * D;
+        for (long i = 0; i < (long)n_keys * D; ++i) { kf[i] = (float)Kh[i]; vf[i] = (float)Vh[i]; }
+        for (int q = qb * QB; q < Sq && q < (qb + 1) * QB; ++q) {
+            const f16* qr = Q + (bh * Sq + q) * (long)D;
+            for (int d = 0; d < D; ++d) qf[d] = (float)qr[d];
+            float m = -FLT_MAX;
+            for (int j = 0; j < n_keys; ++j) {
+                const float x = dot_f32(qf, kf + (size_t)j * D, D) * scale;
+                s[j] = x;
+                if (x > m) m = x;
+            }
+            float l = 0.0f;
+            for (int j = 0; j < n_keys; ++j) { s[j] = expf(s[j] - m); l += s[j]; }
+            const float inv = 1.0f / l;
+            for (int d = 0; d < D; ++d) acc[d] = 0.0f;
+            for (int j = 0; j < n_keys; ++j) {
+                const float p = (float)(f16)(s[j] * inv);  /* probabilities are stored as fp16 (softmax_cast_fp16) */
+                const float* vr = vf + (size_t)j * D;
+                for (int d = 0; d < D; ++d) acc[d] += p * vr[d];
+            }
+            f16* orow = O + (((long)b * Sq + q) * H + h) * D;
+            for (int d = 0; d < D; ++d) orow[d] = (f16)acc[d];
+        }
+        free(kf);
     }
 }
 

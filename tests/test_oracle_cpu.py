@@ -126,3 +126,29 @@ def test_threads_do_not_change_results():
     O.set_threads(O.max_threads()); b = O.rmsnorm_f32(x, g, 1e-6)
     O.set_threads(1)
     np.testing.assert_array_equal(a, b)
+
+
+def test_timed_port_functions_agree_with_the_checker():
+    """oracle_linear_f16 and oracle_sdpa_f32acc carry the host-core baseline that bench.py times; they must
+    compute what the checked oracle functions compute: linear = fp32-accumulated product rounded to fp16
+    (+ bias added after the rounding), attention = oracle_sdpa within one fp16 step."""
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((37, 264)).astype(np.float16)[:, :200]            # row pitch larger than the row
+    w = (rng.standard_normal((56, 200)) * 0.1).astype(np.float16)
+    b = rng.standard_normal(56).astype(np.float16)
+    prod = x.astype(np.float64) @ w.astype(np.float64).T
+    got = O.linear(x, w).astype(np.float64)
+    assert np.abs(got - prod).max() <= 2.0 ** -10 * np.abs(prod).max() + 1e-6
+    want_b = (prod.astype(np.float16).astype(np.float32) + b.astype(np.float32)).astype(np.float16)
+    got_b = O.linear(x, w, b)
+    assert np.abs(got_b.astype(np.float32) - want_b.astype(np.float32)).max() <= 2.0 ** -9 * np.abs(prod).max()
+    Q = rng.standard_normal((2, 3, 70, 64)).astype(np.float16)
+    K = rng.standard_normal((2, 3, 93, 64)).astype(np.float16)
+    V = rng.standard_normal((2, 3, 93, 64)).astype(np.float16)
+    a = O.sdpa(Q, K, V, n_keys=90, o_bshd=True).astype(np.float32)
+    f = O.sdpa_f32acc(Q, K, V, n_keys=90).astype(np.float32)
+    assert np.abs(a - f).max() <= 1e-3
+    O.set_threads(O.max_threads())
+    f2 = O.sdpa_f32acc(Q, K, V, n_keys=90).astype(np.float32)
+    O.set_threads(1)
+    assert np.array_equal(f, f2)                                               # threads split rows, not sums
