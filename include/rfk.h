@@ -295,10 +295,16 @@ int rfk_gemm_f16(const rfk_half* A, long long lda, const rfk_half* W, long long 
                  const rfk_half* W_up, const rfk_half* bias, const rfk_half* R, long long ldr,
                  rfk_half* C, long long ldc, int M, int N, int K, int epilogue,
                  rfk_stream_t stream);
-/* 0 automatic (the tcgen05 kernel whenever the shape allows), 1 never (rfk_gemm_f16 returns
+/* 0 automatic (the tcgen05 kernel whenever the shape allows: on CTA pairs, tcgen05.mma.cta_group::2,
+ * or on single CTAs if the device cannot co-schedule pairs), 1 never (rfk_gemm_f16 returns
  * RFK_EUNSUPPORTED, so the layer functions fall back to their cuBLAS calls: used to time both side
- * by side), 2 as 0. Process-wide. No reference counterpart. */
+ * by side), 2 as 0, 3 the single-CTA kernel. Process-wide; the environment variable RFK_GEMM_PATH
+ * sets the initial value. No reference counterpart. */
 int rfk_gemm_set_path(int path);
+/* CTA pairs (clusters of two) that the current device runs at once for the pair kernel, as the
+ * occupancy query answered at the first launch: 0 before any launch, -1 if pairs cannot be scheduled
+ * (the single-CTA kernel then serves every call). Diagnostic. No reference counterpart. */
+int rfk_gemm_pair_clusters(void);
 /* Reads (and with clear != 0 resets) the current device's error word of the GEMM kernel: 0 none,
  * 1 a bounded wait ran out, 2 shared memory window not 1024-byte aligned. Synchronises the device.
  * No reference counterpart. */

@@ -79,6 +79,100 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tmap,
         ::"r"(dst_smem), "l"(tmap), "r"(x), "r"(y), "r"(tc::smem_addr(bar)) : "memory");
 }
 
+// Epilogue of one thread for one tile: the thread's accumulator row (tensor-memory address t_acc, BN_OUT output
+// columns, for SwiGLU the up columns 128 further on) -> bias / residual / gate in fp32 -> fp16 -> global row `row`.
+template <int EPI>
+__device__ __forceinline__ void epilogue_tile(const Params& p, uint32_t t_acc, int row, int n0) {
+    constexpr int BN_OUT = (EPI == RFK_GEMM_EPI_SWIGLU) ? 128 : 256;
+    uint32_t v[32];
+    const bool row_ok = row < p.M;
+    __half* crow = p.C + (size_t)(row_ok ? row : 0) * p.ldc + n0;
+    if (EPI == RFK_GEMM_EPI_SWIGLU) {
+        uint32_t u[32];
+#pragma unroll 1
+        for (int c = 0; c < BN_OUT / 32; ++c) {
+            tc::tmem_ld32(t_acc + c * 32, v);          // gate columns
+            tc::tmem_ld32(t_acc + 128 + c * 32, u);    // up columns of the same hidden units
+            tc::tc_wait_ld(v);
+            tc::tc_wait_ld(u);
+            uint32_t o[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                const float g0 = __uint_as_float(v[i]), g1 = __uint_as_float(v[i + 1]);
+                // silu(g) * u = g * u / (1 + 2^(-g log2 e))
+                const float s0 = g0 * fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * g0));
+                const float s1 = g1 * fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * g1));
+                o[i >> 1] = pack_half2(s0 * __uint_as_float(u[i]), s1 * __uint_as_float(u[i + 1]));
+            }
+            if (row_ok) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int col = n0 + c * 32 + q * 8;
+                    if (col < p.N)
+                        *reinterpret_cast<uint4*>(crow + c * 32 + q * 8) = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+                }
+            }
+        }
+    } else {
+        const __half* rrow = (EPI == RFK_GEMM_EPI_RESIDUAL) ? p.R + (size_t)(row_ok ? row : 0) * p.ldr + n0 : nullptr;
+        // The residual row is read two chunks ahead of its use (each thread reads 64 bytes of its own row per chunk:
+        // the latency of these scattered loads, not their volume, is what an un-pipelined epilogue pays 8 times).
+        constexpr int kAhead = 2;
+        uint4 res[kAhead + 1][4];
+        auto load_res = [&](int c) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int col = n0 + c * 32 + q * 8;
+                res[c % (kAhead + 1)][q] = (row_ok && c < BN_OUT / 32 && col < p.N)
+                                               ? *reinterpret_cast<const uint4*>(rrow + c * 32 + q * 8) : make_uint4(0, 0, 0, 0);
+            }
+        };
+        if (EPI == RFK_GEMM_EPI_RESIDUAL) {
+#pragma unroll
+            for (int c = 0; c < kAhead; ++c) load_res(c);
+        }
+#pragma unroll
+        for (int c = 0; c < BN_OUT / 32; ++c) {
+            if (n0 + c * 32 >= p.N) break;             // uniform over the CTA: the tile's tail lies beyond N
+            tc::tmem_ld32(t_acc + c * 32, v);
+            if (EPI == RFK_GEMM_EPI_RESIDUAL) load_res(c + kAhead);
+            tc::tc_wait_ld(v);
+            if (p.bias) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const int col = n0 + c * 32 + i;
+                    if (col < p.N) {
+                        const float2 b = unpack_half2(__ldg(reinterpret_cast<const uint32_t*>(p.bias + col)));
+                        // the unfused path rounds the product to fp16 before the bias is added (linear.cu:15-25)
+                        v[i] = __float_as_uint(round_half(__uint_as_float(v[i])) + b.x);
+                        v[i + 1] = __float_as_uint(round_half(__uint_as_float(v[i + 1])) + b.y);
+                    }
+                }
+            }
+            uint32_t o[16];
+            if (EPI == RFK_GEMM_EPI_RESIDUAL) {
+                const uint32_t* rw = reinterpret_cast<const uint32_t*>(res[c % (kAhead + 1)]);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float2 rr = unpack_half2(rw[i]);
+                    o[i] = pack_half2(__uint_as_float(v[2 * i]) + rr.x, __uint_as_float(v[2 * i + 1]) + rr.y);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) o[i] = pack_half2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+            }
+            if (row_ok) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int col = n0 + c * 32 + q * 8;
+                    if (col < p.N)
+                        *reinterpret_cast<uint4*>(crow + c * 32 + q * 8) = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+                }
+            }
+        }
+    }
+}
+
 // out columns per tile: 256 (plain / residual) or 128 (SwiGLU: 128 gate + 128 up accumulator columns)
 template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -184,92 +278,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t lane_off = (uint32_t)(lane_grp * 32) << 16;
         bool ok = true;
         int tl = 0;
-        uint32_t v[32];
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tl) {
             const int acc = tl & 1;
             const int m0 = (t % p.tiles_m) * BM, n0 = (t / p.tiles_m) * BN_OUT;
             ok = tc::mbar_wait_warp(&ctrl->acc_full[acc], (tl >> 1) & 1, abort_flag);
             if (!ok) break;
             tc::tc_fence_after();
-            const uint32_t t_acc = tmem_cta + lane_off + acc * BNACC;
-            const int row = m0 + r;
-            const bool row_ok = row < p.M;
-            __half* crow = p.C + (size_t)(row_ok ? row : 0) * p.ldc + n0;
-            if (EPI == RFK_GEMM_EPI_SWIGLU) {
-                uint32_t u[32];
-#pragma unroll 1
-                for (int c = 0; c < BN_OUT / 32; ++c) {
-                    tc::tmem_ld32(t_acc + c * 32, v);          // gate columns
-                    tc::tmem_ld32(t_acc + 128 + c * 32, u);    // up columns of the same hidden units
-                    tc::tc_wait_ld(v);
-                    tc::tc_wait_ld(u);
-                    uint32_t o[16];
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const float g0 = __uint_as_float(v[i]), g1 = __uint_as_float(v[i + 1]);
-                        // silu(g) * u = g * u / (1 + 2^(-g log2 e))
-                        const float s0 = g0 * fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * g0));
-                        const float s1 = g1 * fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * g1));
-                        o[i >> 1] = pack_half2(s0 * __uint_as_float(u[i]), s1 * __uint_as_float(u[i + 1]));
-                    }
-                    if (row_ok) {
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const int col = n0 + c * 32 + q * 8;
-                            if (col < p.N)
-                                *reinterpret_cast<uint4*>(crow + c * 32 + q * 8) = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
-                        }
-                    }
-                }
-            } else {
-                const __half* rrow = (EPI == RFK_GEMM_EPI_RESIDUAL) ? p.R + (size_t)(row_ok ? row : 0) * p.ldr + n0 : nullptr;
-#pragma unroll 1
-                for (int c = 0; c < BN_OUT / 32; ++c) {
-                    if (n0 + c * 32 >= p.N) break;             // uniform over the CTA: the tile's tail lies beyond N
-                    tc::tmem_ld32(t_acc + c * 32, v);
-                    uint4 res[4];
-                    if (EPI == RFK_GEMM_EPI_RESIDUAL) {        // issued before the wait so that both latencies overlap
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const int col = n0 + c * 32 + q * 8;
-                            res[q] = (row_ok && col < p.N) ? *reinterpret_cast<const uint4*>(rrow + c * 32 + q * 8) : make_uint4(0, 0, 0, 0);
-                        }
-                    }
-                    tc::tc_wait_ld(v);
-                    if (p.bias) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            const int col = n0 + c * 32 + i;
-                            if (col < p.N) {
-                                const float2 b = unpack_half2(__ldg(reinterpret_cast<const uint32_t*>(p.bias + col)));
-                                // the unfused path rounds the product to fp16 before the bias is added (linear.cu:15-25)
-                                v[i] = __float_as_uint(round_half(__uint_as_float(v[i])) + b.x);
-                                v[i + 1] = __float_as_uint(round_half(__uint_as_float(v[i + 1])) + b.y);
-                            }
-                        }
-                    }
-                    uint32_t o[16];
-                    if (EPI == RFK_GEMM_EPI_RESIDUAL) {
-                        const uint32_t* rw = reinterpret_cast<const uint32_t*>(res);
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const float2 rr = unpack_half2(rw[i]);
-                            o[i] = pack_half2(__uint_as_float(v[2 * i]) + rr.x, __uint_as_float(v[2 * i + 1]) + rr.y);
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) o[i] = pack_half2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
-                    }
-                    if (row_ok) {
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const int col = n0 + c * 32 + q * 8;
-                            if (col < p.N)
-                                *reinterpret_cast<uint4*>(crow + c * 32 + q * 8) = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
-                        }
-                    }
-                }
-            }
+            epilogue_tile<EPI>(p, tmem_cta + lane_off + acc * BNACC, m0 + r, n0);
             // every tcgen05.ld of this warp has completed (wait::ld above): hand the accumulator back
             tc::tc_fence_before();
             __syncwarp();
@@ -287,13 +302,217 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (tid == 0 && ctrl->abort) atomicCAS(&g_gemm_tc_error, 0, kErrTimeout);
 }
 
+// ------------------------------------------------------------------------------------------------
+// The same product on CTA pairs: a cluster of two CTAs (two SMs of one TPC) owns a tile of 256 rows x 256
+// accumulator columns and one thread of the pair's first CTA issues tcgen05.mma.cta_group::2 (M = 256):
+// each CTA stages only ITS 128 rows of A and ITS half of the weight tile (128 of the 256 accumulator
+// columns' rows; with the SwiGLU epilogue CTA 0 holds the gate rows and CTA 1 the up rows), so a K block
+// costs each SM 32 KB of L2 -> shared-memory traffic instead of 48 KB for the same number of products.
+// That traffic, not the tensor pipe, bounds the single-CTA kernel above (the same ~510 ns per K block on
+// every shape = 14 TB/s over 148 SMs). Both accumulator halves live in the two CTAs' tensor memories at the
+// same address; each CTA's epilogue warps drain their own 128 rows.
+//   barriers: full[s] in CTA 0 collects both CTAs' copies (one arrive.expect_tx of 64 KB by CTA 0); empty[s] and
+//   acc_full[a] exist in both CTAs and are signalled together by one multicast tcgen05.commit;
+//   acc_empty[a] in CTA 0 counts the 8 epilogue warps of the pair.
+// The copies are ordinary per-CTA TMA loads (no cluster multicast), with the .cta_group::2 form that lets
+// CTA 1's copies count on CTA 0's barrier.
+namespace pair {
+
+constexpr int kStages = 7;
+constexpr int kStageBytes = kABytes + kWBoxBytes;   // 32 KB per CTA
+constexpr int kSmemBytes = kStages * kStageBytes + 256;
+static_assert(kSmemBytes + 1024 <= 227 * 1024, "one CTA per SM");
+
+struct __align__(8) Ctrl {
+    uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2], drain;
+    uint32_t tmem_base;
+    int abort;
+};
+static_assert(sizeof(Ctrl) <= 256, "control block");
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the location `smem_addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void remote_arrive(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void remote_arrive_expect_tx(uint32_t cluster_bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar), "r"(bytes) : "memory");
+}
+// per-CTA tiled copy whose bytes are counted on a barrier that may live in the pair's other CTA
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const void* tmap, int x, int y, uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst_smem), "l"(tmap), "r"(x), "r"(y), "r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void umma_pair_f16_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %5};\n\t"
+        "mov.b64 db, {%2, %5};\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(tc::kDescHiSw128) : "memory");
+}
+// one arrival on the barrier at this shared-memory offset in BOTH CTAs of the pair when every product issued so far is complete
+__device__ __forceinline__ void umma_pair_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(tc::smem_addr(bar)), "h"((uint16_t)3) : "memory");
+}
+// bounded pause on the abort path: lets copies that were started a moment ago land
+__device__ __forceinline__ void drain_pause() {
+    const uint64_t t0 = tc::global_timer_ns();
+    for (int i = 0; i < 4096 && tc::global_timer_ns() - t0 < 50000; ++i) __nanosleep(256);
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w0,
+                    const __grid_constant__ CUtensorMap map_w1, const Params p) {
+    constexpr int BN_OUT = (EPI == RFK_GEMM_EPI_SWIGLU) ? 128 : 256;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    const uint32_t base = tc::smem_addr(smem_raw);
+    const uint32_t rank = cluster_rank();            // 0: issues the products for the pair; 1: its peer
+    Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_raw + kStages * kStageBytes);
+    volatile int* abort_flag = &ctrl->abort;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int num_kb = (p.K + BK - 1) / BK;
+    const int num_tiles = p.tiles_m * p.tiles_n;      // pair tiles: tiles_m counts 256-row blocks
+    const int first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
+    const bool aligned = (base & 1023u) == 0;         // the same in both CTAs (same kernel, same shared-memory layout)
+    auto wait = [&](uint64_t* bar, uint32_t parity) { return tc::mbar_wait(bar, parity, abort_flag); };
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) { tc::mbar_init(&ctrl->full[s], 1); tc::mbar_init(&ctrl->empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { tc::mbar_init(&ctrl->acc_full[a], 1); tc::mbar_init(&ctrl->acc_empty[a], 8); }
+        tc::mbar_init(&ctrl->drain, 1);
+        ctrl->abort = 0;
+        tc::fence_barrier_init();
+    }
+    if (warp == 0 && aligned) {  // each CTA allocates its own tensor memory (all 512 columns: both get the same address)
+        tc::tmem_alloc(&ctrl->tmem_base, kTmemCols);
+        tc::tmem_relinquish();
+    }
+    tc::tc_fence_before();
+    __syncthreads();
+    cluster_sync();              // both CTAs' barriers are initialised before either signals the other
+    tc::tc_fence_after();
+    if (!aligned) {
+        if (tid == 0) atomicCAS(&g_gemm_tc_error, 0, kErrSmemAlign);
+        return;
+    }
+    const uint32_t tmem_cta = ctrl->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer (one thread per CTA)
+        if (lane == 0) {
+            const void* map_w = rank == 0 ? (const void*)&map_w0 : (const void*)&map_w1;
+            tc::prefetch_tensormap(&map_a); tc::prefetch_tensormap(map_w);
+            int it = 0;
+            bool ok = true;
+            for (int t = first_tile; ok && t < num_tiles; t += tile_step) {
+                const int m0 = (t % p.tiles_m) * (2 * BM) + (int)rank * BM, n0 = (t / p.tiles_m) * BN_OUT;
+                // this CTA's half of the weight tile: rows n0.. (CTA 0) / n0+128.. (CTA 1) of W, or the gate / up rows
+                const int nw = (EPI == RFK_GEMM_EPI_SWIGLU || rank == 0) ? n0 : n0 + 128;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % kStages;
+                    if (it >= kStages && !wait(&ctrl->empty[s], ((it / kStages) + 1) & 1)) { ok = false; break; }
+                    const uint32_t sA = base + s * kStageBytes;
+                    const uint32_t full0 = map_to_cta(tc::smem_addr(&ctrl->full[s]), 0);
+                    // CTA 0 announces the bytes of both CTAs' copies on its own barrier (one local arrival); CTA 1 only
+                    // copies. CTA 1's bytes may land before CTA 0's announcement: the phase still cannot complete before
+                    // that arrival, and the transaction count balances once it is made.
+                    if (rank == 0) tc::mbar_arrive_expect_tx(&ctrl->full[s], 2 * kStageBytes);
+                    tma_load_2d_pair(sA, &map_a, kb * BK, m0, full0);
+                    tma_load_2d_pair(sA + kABytes, map_w, kb * BK, nw, full0);
+                }
+            }
+            if (*abort_flag) drain_pause();   // this CTA's copies count on CTA 0's barriers: give them time to land
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ issuer of the pair's products (one thread of CTA 0)
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = tc::umma_idesc_f16(2 * BM, BNACC, 0);
+            int it = 0, tl = 0;
+            bool ok = true;
+            for (int t = first_tile; ok && t < num_tiles; t += tile_step, ++tl) {
+                const int acc = tl & 1;
+                if (tl >= 2) ok = wait(&ctrl->acc_empty[acc], ((tl >> 1) + 1) & 1);
+                if (!ok) break;
+                tc::tc_fence_after();
+                const uint32_t d_tmem = tmem_cta + acc * BNACC;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % kStages;
+                    ok = wait(&ctrl->full[s], (it / kStages) & 1);
+                    if (!ok) break;
+                    tc::tc_fence_after();
+                    const uint32_t a_lo = tc::umma_desc_lo(base + s * kStageBytes);
+                    const uint32_t b_lo = tc::umma_desc_lo(base + s * kStageBytes + kABytes);
+#pragma unroll
+                    for (int ks = 0; ks < BK / 16; ++ks)
+                        umma_pair_f16_lo(d_tmem, a_lo + ks * 2, b_lo + ks * 2, idesc, (kb > 0) || (ks > 0));
+                    umma_pair_commit(&ctrl->empty[s]);
+                }
+                if (ok) umma_pair_commit(&ctrl->acc_full[acc]);
+            }
+            if (*abort_flag) {
+                umma_pair_commit(&ctrl->drain);
+                tc::mbar_wait_drain(&ctrl->drain, 0);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ epilogue, warps 2-5 of both CTAs
+        const int lane_grp = warp & 3;
+        const int r = lane_grp * 32 + lane;
+        const uint32_t lane_off = (uint32_t)(lane_grp * 32) << 16;
+        bool ok = true;
+        int tl = 0;
+        for (int t = first_tile; t < num_tiles; t += tile_step, ++tl) {
+            const int acc = tl & 1;
+            const int m0 = (t % p.tiles_m) * (2 * BM) + (int)rank * BM, n0 = (t / p.tiles_m) * BN_OUT;
+            ok = tc::mbar_wait_warp(&ctrl->acc_full[acc], (tl >> 1) & 1, abort_flag);
+            if (!ok) break;
+            tc::tc_fence_after();
+            epilogue_tile<EPI>(p, tmem_cta + lane_off + acc * BNACC, m0 + r, n0);
+            tc::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) remote_arrive(map_to_cta(tc::smem_addr(&ctrl->acc_empty[acc]), 0));
+        }
+    }
+
+    // ---- teardown: neither CTA leaves while the other may still signal its barriers or read its shared memory
+    tc::tc_fence_before();
+    __syncthreads();
+    cluster_sync();
+    if (warp == 0) {
+        tc::tc_fence_after();
+        tc::tmem_dealloc(tmem_cta, kTmemCols);
+    }
+    if (tid == 0 && ctrl->abort) atomicCAS(&g_gemm_tc_error, 0, kErrTimeout);
+}
+
+}  // namespace pair
 }  // namespace tcgemm
 
-// 0 automatic (tcgen05 kernel when the shape allows), 1 never (callers use their library GEMM), 2 as 0. The
+// 0 automatic (tcgen05 kernel on CTA pairs when the shape allows), 1 never (callers use their library GEMM), 2 as 0,
+// 3 the single-CTA tcgen05 kernel. The
 // environment variable RFK_GEMM_PATH sets the initial value, for side-by-side runs of an unchanged program.
 static int initial_gemm_path() {
     const char* e = getenv("RFK_GEMM_PATH");
-    return (e && e[0] >= '0' && e[0] <= '2' && e[1] == 0) ? e[0] - '0' : 0;
+    return (e && e[0] >= '0' && e[0] <= '3' && e[1] == 0) ? e[0] - '0' : 0;
 }
 std::atomic<int> g_gemm_path{initial_gemm_path()};
 
@@ -331,8 +550,8 @@ bool make_map_2d(CUtensorMap* m, const void* base, long long rows, long long col
 }
 
 template <int EPI>
-int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw0, const CUtensorMap& mw1, const tcgemm::Params& p, int dev,
-                cudaStream_t st) {
+int launch_gemm_single(const CUtensorMap& ma, const CUtensorMap& mw0, const CUtensorMap& mw1, tcgemm::Params p, int dev,
+                       cudaStream_t st) {
     static std::atomic<bool> configured[64];
     static std::atomic<int> sm_count[64];
     if (!configured[dev].load(std::memory_order_acquire)) {
@@ -349,6 +568,56 @@ int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw0, const CUtensorMap
     const int grid = std::min(tiles, std::max(1, sm_count[dev].load(std::memory_order_relaxed)));
     tcgemm::gemm_tc_kernel<EPI><<<grid, tcgemm::kThreads, tcgemm::kSmemBytes, st>>>(ma, mw0, mw1, p);
     return launch_status();
+}
+
+std::atomic<int> g_pair_clusters[64];  // CTA pairs the device can run at once, per device (0 not asked yet, -1 none)
+
+// CTA-pair kernel: clusters of two; returns RFK_EUNSUPPORTED (nothing launched) when the device cannot co-schedule pairs
+template <int EPI>
+int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mw0, const CUtensorMap& mw1, tcgemm::Params p, int dev,
+                     cudaStream_t st) {
+    std::atomic<int>* max_clusters = g_pair_clusters;   // 0 not asked yet, -1 unavailable
+    static std::atomic<bool> configured[64];            // per instantiation of the kernel
+    cudaLaunchConfig_t cfg{};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(tcgemm::kThreads); cfg.dynamicSmemBytes = tcgemm::pair::kSmemBytes; cfg.stream = st;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    int nc = max_clusters[dev].load(std::memory_order_acquire);
+    if (nc == 0 || !configured[dev].load(std::memory_order_acquire)) {
+        cudaError_t e = cudaFuncSetAttribute(tcgemm::pair::gemm_tc_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             tcgemm::pair::kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        int sms = 0;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return (int)e;
+        cfg.gridDim = dim3(2 * std::max(1, sms / 2));
+        int n = 0;
+        e = cudaOccupancyMaxActiveClusters(&n, tcgemm::pair::gemm_tc_pair_kernel<EPI>, &cfg);
+        if (e != cudaSuccess) { cudaGetLastError(); n = 0; }
+        nc = n > 0 ? std::min(n, sms / 2) : -1;
+        max_clusters[dev].store(nc, std::memory_order_release);
+        configured[dev].store(true, std::memory_order_release);
+    }
+    if (nc < 0) return RFK_EUNSUPPORTED;
+    p.tiles_m = (p.M + 2 * tcgemm::BM - 1) / (2 * tcgemm::BM);
+    const int tiles = p.tiles_m * p.tiles_n;
+    cfg.gridDim = dim3(2 * std::min(tiles, nc));
+    cudaError_t e = cudaLaunchKernelEx(&cfg, tcgemm::pair::gemm_tc_pair_kernel<EPI>, ma, mw0, mw1, p);
+    if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+    return launch_status();
+}
+
+// path 0 / 2: CTA pairs, the single-CTA kernel if pairs are unavailable; path 3: the single-CTA kernel
+template <int EPI>
+int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw0, const CUtensorMap& mw1, const tcgemm::Params& p, int dev,
+                cudaStream_t st) {
+    if (g_gemm_path.load(std::memory_order_relaxed) != 3) {
+        const int rc = launch_gemm_pair<EPI>(ma, mw0, mw1, p, dev, st);
+        if (rc != RFK_EUNSUPPORTED) return rc;
+    }
+    return launch_gemm_single<EPI>(ma, mw0, mw1, p, dev, st);
 }
 
 }  // namespace
@@ -394,8 +663,14 @@ extern "C" int rfk_gemm_f16(const rfk_half* A, long long lda, const rfk_half* W,
     }
 }
 
+extern "C" int rfk_gemm_pair_clusters(void) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    return g_pair_clusters[dev].load(std::memory_order_relaxed);
+}
+
 extern "C" int rfk_gemm_set_path(int path) {
-    if (path < 0 || path > 2) return RFK_EINVAL;
+    if (path < 0 || path > 3) return RFK_EINVAL;
     g_gemm_path.store(path, std::memory_order_relaxed);
     return RFK_OK;
 }

@@ -338,11 +338,13 @@ def gemm_table(iters: int = 20, nsets: int = 6) -> list[dict]:
 
         ops.gemm_set_path(2)
         t_f = _time_graph(fused, nsets, iters)
+        ops.gemm_set_path(3)
+        t_s = _time_graph(fused, nsets, iters)
         ops.gemm_set_path(1)
         t_l = _time_graph(library, nsets, iters)
         ops.gemm_set_path(0)
         rows.append({"gemm": name, "M": M, "N": N, "K": K, "epilogue": epi, "us_tcgen05": round(t_f * 1e3, 2),
-                     "tflops_tcgen05": round(flop / (t_f * 1e-3) / 1e12, 1), "us_library": round(t_l * 1e3, 2),
+                     "tflops_tcgen05": round(flop / (t_f * 1e-3) / 1e12, 1), "us_tcgen05_single_cta": round(t_s * 1e3, 2), "us_library": round(t_l * 1e3, 2),
                      "tflops_library": round(flop / (t_l * 1e-3) / 1e12, 1), "speedup": round(t_l / t_f, 3)})
         torch.cuda.empty_cache()
 

@@ -284,7 +284,7 @@ def gemm_f16(a, w, c, M, N, K, w_up=None, bias=None, residual=None, lda=None, ld
 
 
 def gemm_set_path(path):
-    """0 automatic (tcgen05 kernel), 1 library GEMM only (rfk_gemm_f16 refuses), 2 as 0."""
+    """0 automatic (tcgen05 kernel on CTA pairs), 1 library GEMM only (rfk_gemm_f16 refuses), 2 as 0, 3 single-CTA kernel."""
     _call("rfk_gemm_set_path", int(path))
 
 

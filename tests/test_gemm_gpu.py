@@ -17,11 +17,13 @@ def _ops():
     return pkg.ops
 
 
-@pytest.fixture(autouse=True)
-def _error_word_clear():
+@pytest.fixture(autouse=True, params=[2, 3], ids=["cta_pair", "single_cta"])
+def _error_word_clear(request):
+    """Every test runs once through the CTA-pair kernel (tcgen05.mma.cta_group::2, the default) and once through
+    the single-CTA kernel."""
     o = _ops()
     o.gemm_error(clear=True)
-    o.gemm_set_path(2)
+    o.gemm_set_path(request.param)
     yield
     o.gemm_set_path(0)
     torch.cuda.synchronize()
@@ -154,7 +156,7 @@ def test_linear_and_ffn_through_both_gemm_paths_match_reference():
     w = session.FfnW(w13.data_ptr(), w2.data_ptr(), w13.data_ptr() + ffn * dim * 2)
     errs = {}
     for path in (2, 1):
-        _ops().gemm_set_path(path)
+        _ops().gemm_set_path(path)   # (this test drives the path itself: tcgen05 on CTA pairs, then the library)
         y = torch.empty_like(yr)
         assert L.rfk_linear(ctx.h, P(x), P(w13), P(bias), P(y), M, 2 * ffn, dim, st()) == 0
         out = torch.empty_like(outr); buf = torch.empty_like(bufr)
