@@ -55,6 +55,15 @@ static_assert(kSmemBytes + 1024 <= 227 * 1024, "one CTA per SM");
 
 enum : int { kErrTimeout = 1, kErrSmemAlign = 2 };
 
+// Build with -DRFK_GEMM_TIMELINE to make CTA 0 of the pair kernel record %globaltimer stamps (ns) of its phases
+// in a device array that rfk_gemm_timeline() reads back; compiled out otherwise.
+#ifdef RFK_GEMM_TIMELINE
+__device__ unsigned long long g_timeline[16];
+#define RFK_STAMP(i) do { if (blockIdx.x == 0) g_timeline[i] = tc::global_timer_ns(); } while (0)
+#else
+#define RFK_STAMP(i) do { } while (0)
+#endif
+
 struct Params {
     __half* C; long long ldc;
     const __half* R; long long ldr;     // residual (EPI_RESIDUAL), may alias C
@@ -318,17 +327,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // CTA 1's copies count on CTA 0's barrier.
 namespace pair {
 
-constexpr int kStages = 7;
 constexpr int kStageBytes = kABytes + kWBoxBytes;   // 32 KB per CTA
-constexpr int kSmemBytes = kStages * kStageBytes + 256;
-static_assert(kSmemBytes + 1024 <= 227 * 1024, "one CTA per SM");
+// The epilogue goes through shared memory both ways: an epilogue warp owns staging buffers of 32 rows x 64 halves
+// (4 KB, the 128-byte-swizzled layout of a TMA box) for its 32 rows of the tile; it writes the finished fp16 values
+// of 64 output columns there and one lane issues a TMA tile store, so the global writes are whole 128-byte lines
+// issued by the copy engine instead of 16-byte pieces of 32 different rows per store instruction (measured:
+// 2.8 us per tile for the register-to-global epilogue, most of it the scattered stores). With the residual
+// epilogue the same buffers first receive the residual tile by TMA loads issued before the accumulator is ready
+// (one buffer per 64-column unit, so the loads of a whole tile are in flight during its main loop); the sum
+// overwrites the residual in place and is stored from there. Plain / SwiGLU: two buffers per warp in turn.
+constexpr int kUnitCols = 64;
+constexpr int kUnitBytes = 32 * kUnitCols * 2;       // 4 KB
+template <int EPI> struct Cfg {
+    static constexpr int kUnits = (EPI == RFK_GEMM_EPI_SWIGLU) ? 2 : 4;                    // 64-column units per tile
+    static constexpr int kBufsPerWarp = (EPI == RFK_GEMM_EPI_RESIDUAL) ? 4 : 2;
+    static constexpr int kStagingBytes = 4 * kBufsPerWarp * kUnitBytes;                      // 4 epilogue warps
+    static constexpr int kStages = (EPI == RFK_GEMM_EPI_RESIDUAL) ? 5 : 6;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 512;
+    static_assert(kSmemBytes + 1024 <= 227 * 1024, "one CTA per SM");
+};
+constexpr int kMaxStages = 6;
 
 struct __align__(8) Ctrl {
-    uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2], drain;
+    uint64_t full[kMaxStages], empty[kMaxStages], acc_full[2], acc_empty[2], drain;
+    uint64_t res_full[4][4];   // residual epilogue: [epilogue warp][unit], completes when that unit's residual box has landed
     uint32_t tmem_base;
     int abort;
 };
-static_assert(sizeof(Ctrl) <= 256, "control block");
+static_assert(sizeof(Ctrl) <= 512, "control block");
+
+// ---- shared <-> global tile copies used by the epilogue
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src_smem, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(tmap), "r"(src_smem), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until at most N of this thread's committed store groups still READ their shared-memory source
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -376,17 +411,124 @@ __device__ __forceinline__ void drain_pause() {
     for (int i = 0; i < 4096 && tc::global_timer_ns() - t0 < 50000; ++i) __nanosleep(256);
 }
 
+// Byte offset of 16-byte chunk j (0..7) of row r (0..31) inside a staging buffer (SWIZZLE_128B box layout).
+__device__ __forceinline__ uint32_t staged(int r, int j) { return (uint32_t)(r * 128 + ((j ^ (r & 7)) << 4)); }
+
+// Residual epilogue, before the tile's accumulator is waited for: bring the warp's residual rows of the whole tile
+// into its four staging buffers. Lane 0 only. The buffers were last read by the TMA stores of the previous tile.
+template <int EPI>
+__device__ __forceinline__ void epilogue_prefetch_residual(const CUtensorMap* map_r, uint32_t stage_base, uint64_t* res_full,
+                                                           int row0, int n0) {
+    if (EPI != RFK_GEMM_EPI_RESIDUAL) return;
+    bulk_wait_read<0>();
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {   // units beyond N are loaded too (all zeros): every barrier sees one phase per tile
+        tc::mbar_arrive_expect_tx(&res_full[u], kUnitBytes);
+        tma_load_2d(stage_base + u * kUnitBytes, map_r, n0 + u * kUnitCols, row0, &res_full[u]);
+    }
+}
+
+// One epilogue warp, one tile: accumulator rows [lane] -> (bias / residual / gate) -> fp16 -> staging buffer -> TMA store.
+// t_acc: tensor-memory address of the thread's accumulator row; row0: global row of the warp's lane 0.
+template <int EPI>
+__device__ __forceinline__ bool epilogue_tile_staged(const Params& p, const CUtensorMap* map_c, uint32_t t_acc,
+                                                     unsigned char* stage_ptr, uint64_t* res_full, uint32_t res_parity,
+                                                     int row0, int n0, int lane, volatile int* abort_flag) {
+    constexpr int kUnits = Cfg<EPI>::kUnits;
+    const uint32_t stage_base = tc::smem_addr(stage_ptr);
+    uint32_t v[32];
+#pragma unroll 1
+    for (int u = 0; u < kUnits; ++u) {
+        const int b = (EPI == RFK_GEMM_EPI_RESIDUAL) ? u : (u & 1);
+        unsigned char* buf = stage_ptr + b * kUnitBytes;
+        if (EPI == RFK_GEMM_EPI_RESIDUAL) {                 // this unit's residual box has landed (also for units beyond N)
+            if (!tc::mbar_wait_warp(&res_full[u], res_parity, abort_flag)) return false;
+        }
+
+        if (n0 + u * kUnitCols >= p.N) continue;            // uniform: the tile's tail lies beyond N
+        if (EPI != RFK_GEMM_EPI_RESIDUAL) {                 // the store issued two units ago must have read this buffer
+            if (lane == 0) bulk_wait_read<1>();
+            __syncwarp();
+        }
+#pragma unroll
+        for (int hc = 0; hc < 2; ++hc) {                    // two half units of 32 output columns
+            const int c32 = u * 2 + hc;                     // 32-column chunk index within the tile's output
+            uint32_t o[16];
+            if (EPI == RFK_GEMM_EPI_SWIGLU) {
+                uint32_t up[32];
+                tc::tmem_ld32(t_acc + c32 * 32, v);          // gate columns
+                tc::tmem_ld32(t_acc + 128 + c32 * 32, up);   // up columns of the same hidden units
+                tc::tc_wait_ld(v);
+                tc::tc_wait_ld(up);
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float g0 = __uint_as_float(v[i]), g1 = __uint_as_float(v[i + 1]);
+                    // silu(g) * u = g * u / (1 + 2^(-g log2 e))
+                    const float s0 = g0 * fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * g0));
+                    const float s1 = g1 * fast_rcp(1.0f + fast_exp2(-1.4426950408889634f * g1));
+                    o[i >> 1] = pack_half2(s0 * __uint_as_float(up[i]), s1 * __uint_as_float(up[i + 1]));
+                }
+            } else {
+                tc::tmem_ld32(t_acc + c32 * 32, v);
+                uint4 res[4];
+                if (EPI == RFK_GEMM_EPI_RESIDUAL) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) res[q] = *reinterpret_cast<const uint4*>(buf + staged(lane, hc * 4 + q));
+                }
+                tc::tc_wait_ld(v);
+                if (p.bias) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const int col = n0 + c32 * 32 + i;
+                        if (col < p.N) {
+                            const float2 bb = unpack_half2(__ldg(reinterpret_cast<const uint32_t*>(p.bias + col)));
+                            // the unfused path rounds the product to fp16 before the bias is added (linear.cu:15-25)
+                            v[i] = __float_as_uint(round_half(__uint_as_float(v[i])) + bb.x);
+                            v[i + 1] = __float_as_uint(round_half(__uint_as_float(v[i + 1])) + bb.y);
+                        }
+                    }
+                }
+                if (EPI == RFK_GEMM_EPI_RESIDUAL) {
+                    const uint32_t* rw = reinterpret_cast<const uint32_t*>(res);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float2 rr = unpack_half2(rw[i]);
+                        o[i] = pack_half2(__uint_as_float(v[2 * i]) + rr.x, __uint_as_float(v[2 * i + 1]) + rr.y);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) o[i] = pack_half2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                *reinterpret_cast<uint4*>(buf + staged(lane, hc * 4 + q)) = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+        }
+        tc::fence_proxy_async();                            // the copy engine reads what the threads just wrote
+        __syncwarp();
+        if (lane == 0) {
+            tma_store_2d(map_c, stage_base + b * kUnitBytes, n0 + u * kUnitCols, row0);   // rows >= M, columns >= N are clipped
+            bulk_commit();
+        }
+    }
+    return true;
+}
+
 template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w0,
-                    const __grid_constant__ CUtensorMap map_w1, const Params p) {
+                    const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUtensorMap map_c,
+                    const __grid_constant__ CUtensorMap map_r, const Params p) {
     constexpr int BN_OUT = (EPI == RFK_GEMM_EPI_SWIGLU) ? 128 : 256;
+    constexpr int kStages = Cfg<EPI>::kStages;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const uint32_t base = tc::smem_addr(smem_raw);
     const uint32_t rank = cluster_rank();            // 0: issues the products for the pair; 1: its peer
-    Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_raw + kStages * kStageBytes);
+    unsigned char* staging = smem_raw + kStages * kStageBytes;   // 1024-byte aligned: the stages are 32 KB each
+    Ctrl* ctrl = reinterpret_cast<Ctrl*>(staging + Cfg<EPI>::kStagingBytes);
     volatile int* abort_flag = &ctrl->abort;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) RFK_STAMP(0);   // kernel entry
     const int num_kb = (p.K + BK - 1) / BK;
     const int num_tiles = p.tiles_m * p.tiles_n;      // pair tiles: tiles_m counts 256-row blocks
     const int first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
@@ -397,6 +539,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int s = 0; s < kStages; ++s) { tc::mbar_init(&ctrl->full[s], 1); tc::mbar_init(&ctrl->empty[s], 1); }
         for (int a = 0; a < 2; ++a) { tc::mbar_init(&ctrl->acc_full[a], 1); tc::mbar_init(&ctrl->acc_empty[a], 8); }
         tc::mbar_init(&ctrl->drain, 1);
+        for (int w = 0; w < 4; ++w)
+            for (int u = 0; u < 4; ++u) tc::mbar_init(&ctrl->res_full[w][u], 1);
         ctrl->abort = 0;
         tc::fence_barrier_init();
     }
@@ -413,12 +557,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         return;
     }
     const uint32_t tmem_cta = ctrl->tmem_base;
+    if (tid == 0) RFK_STAMP(1);   // prologue done (barriers, tensor memory, cluster barrier)
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer (one thread per CTA)
         if (lane == 0) {
             const void* map_w = rank == 0 ? (const void*)&map_w0 : (const void*)&map_w1;
-            tc::prefetch_tensormap(&map_a); tc::prefetch_tensormap(map_w);
+            tc::prefetch_tensormap(&map_a); tc::prefetch_tensormap(map_w); tc::prefetch_tensormap(&map_c);
+            if (EPI == RFK_GEMM_EPI_RESIDUAL) tc::prefetch_tensormap(&map_r);
             int it = 0;
             bool ok = true;
             for (int t = first_tile; ok && t < num_tiles; t += tile_step) {
@@ -457,6 +603,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const int s = it % kStages;
                     ok = wait(&ctrl->full[s], (it / kStages) & 1);
                     if (!ok) break;
+                    if (it == 0) RFK_STAMP(2);   // first K block has landed
                     tc::tc_fence_after();
                     const uint32_t a_lo = tc::umma_desc_lo(base + s * kStageBytes);
                     const uint32_t b_lo = tc::umma_desc_lo(base + s * kStageBytes + kABytes);
@@ -466,6 +613,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     umma_pair_commit(&ctrl->empty[s]);
                 }
                 if (ok) umma_pair_commit(&ctrl->acc_full[acc]);
+                if (tl == 0) RFK_STAMP(3);       // all products of the first tile issued
             }
             if (*abort_flag) {
                 umma_pair_commit(&ctrl->drain);
@@ -475,22 +623,42 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         __syncwarp();
     } else {
         // ------------------------------------------------------------ epilogue, warps 2-5 of both CTAs
-        const int lane_grp = warp & 3;
-        const int r = lane_grp * 32 + lane;
+        const int lane_grp = warp & 3;                        // a warp reaches tensor-memory lanes [32 * (warp % 4), +32)
         const uint32_t lane_off = (uint32_t)(lane_grp * 32) << 16;
+        unsigned char* my_stage = staging + lane_grp * Cfg<EPI>::kBufsPerWarp * kUnitBytes;
+        uint64_t* my_res = ctrl->res_full[lane_grp];
         bool ok = true;
         int tl = 0;
         for (int t = first_tile; t < num_tiles; t += tile_step, ++tl) {
             const int acc = tl & 1;
             const int m0 = (t % p.tiles_m) * (2 * BM) + (int)rank * BM, n0 = (t / p.tiles_m) * BN_OUT;
+            const int row0 = m0 + lane_grp * 32;
+            if (lane == 0) {
+                // The residual boxes of the CTA's first tile are asked for only once the first K block has been consumed
+                // (first multicast commit): issued at kernel start they delay the first operand tiles by ~0.5 us.
+                if (EPI == RFK_GEMM_EPI_RESIDUAL && tl == 0) tc::mbar_wait(&ctrl->empty[0], 0, abort_flag);
+                epilogue_prefetch_residual<EPI>(&map_r, tc::smem_addr(my_stage), my_res, row0, n0);
+            }
             ok = tc::mbar_wait_warp(&ctrl->acc_full[acc], (tl >> 1) & 1, abort_flag);
             if (!ok) break;
             tc::tc_fence_after();
-            epilogue_tile<EPI>(p, tmem_cta + lane_off + acc * BNACC, m0 + r, n0);
+            if (tl == 0 && warp == 2 && lane == 0) RFK_STAMP(4);   // first tile's accumulator complete
+            ok = epilogue_tile_staged<EPI>(p, &map_c, tmem_cta + lane_off + acc * BNACC, my_stage, my_res, tl & 1, row0, n0,
+                                           lane, abort_flag);
+            if (!ok) break;
+            if (tl == 0 && warp == 2 && lane == 0) RFK_STAMP(5);   // its epilogue done (stores issued)
+            // every tcgen05.ld of this warp has completed: hand the accumulator back
             tc::tc_fence_before();
             __syncwarp();
             if (lane == 0) remote_arrive(map_to_cta(tc::smem_addr(&ctrl->acc_empty[acc]), 0));
         }
+        // this lane's stores must have left shared memory (and, on an aborted run, its residual loads landed) before
+        // the CTA gives the memory up
+        if (lane == 0) {
+            if (*abort_flag) drain_pause();
+            bulk_wait_read<0>();   // the stores themselves complete with the grid; shared memory only has to outlive their reads
+        }
+        __syncwarp();
     }
 
     // ---- teardown: neither CTA leaves while the other may still signal its barriers or read its shared memory
@@ -502,6 +670,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tc::tmem_dealloc(tmem_cta, kTmemCols);
     }
     if (tid == 0 && ctrl->abort) atomicCAS(&g_gemm_tc_error, 0, kErrTimeout);
+    if (tid == 0) RFK_STAMP(6);   // CTA exit
 }
 
 }  // namespace pair
@@ -537,12 +706,12 @@ EncodeTiledFn tensor_map_encoder() {
 
 // fp16 matrix [rows][cols] with a row pitch of ld elements; boxes of 128 rows x 64 columns in the
 // 128-byte-swizzled layout; elements outside the matrix read as zeros
-bool make_map_2d(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld) {
+bool make_map_2d(CUtensorMap* m, const void* base, long long rows, long long cols, long long ld, int box_rows = 128) {
     EncodeTiledFn enc = tensor_map_encoder();
     if (!enc) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -576,18 +745,25 @@ std::atomic<int> g_pair_clusters[64];  // CTA pairs the device can run at once, 
 template <int EPI>
 int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mw0, const CUtensorMap& mw1, tcgemm::Params p, int dev,
                      cudaStream_t st) {
+    // tile maps of the output (stores) and of the residual (loads): boxes of 32 rows x 64 columns, one per epilogue warp
+    CUtensorMap mc, mr;
+    if (!make_map_2d(&mc, p.C, p.M, p.N, p.ldc, 32) ||
+        !make_map_2d(&mr, EPI == RFK_GEMM_EPI_RESIDUAL ? (const void*)p.R : (const void*)p.C, p.M, p.N,
+                     EPI == RFK_GEMM_EPI_RESIDUAL ? p.ldr : p.ldc, 32))
+        return RFK_EUNSUPPORTED;
+    constexpr int kSmem = tcgemm::pair::Cfg<EPI>::kSmemBytes;
     std::atomic<int>* max_clusters = g_pair_clusters;   // 0 not asked yet, -1 unavailable
     static std::atomic<bool> configured[64];            // per instantiation of the kernel
     cudaLaunchConfig_t cfg{};
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.blockDim = dim3(tcgemm::kThreads); cfg.dynamicSmemBytes = tcgemm::pair::kSmemBytes; cfg.stream = st;
+    cfg.blockDim = dim3(tcgemm::kThreads); cfg.dynamicSmemBytes = kSmem; cfg.stream = st;
     cfg.attrs = attr; cfg.numAttrs = 1;
     int nc = max_clusters[dev].load(std::memory_order_acquire);
     if (nc == 0 || !configured[dev].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(tcgemm::pair::gemm_tc_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             tcgemm::pair::kSmemBytes);
+                                             kSmem);
         if (e != cudaSuccess) return (int)e;
         int sms = 0;
         e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -604,7 +780,7 @@ int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mw0, const CUtens
     p.tiles_m = (p.M + 2 * tcgemm::BM - 1) / (2 * tcgemm::BM);
     const int tiles = p.tiles_m * p.tiles_n;
     cfg.gridDim = dim3(2 * std::min(tiles, nc));
-    cudaError_t e = cudaLaunchKernelEx(&cfg, tcgemm::pair::gemm_tc_pair_kernel<EPI>, ma, mw0, mw1, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, tcgemm::pair::gemm_tc_pair_kernel<EPI>, ma, mw0, mw1, mc, mr, p);
     if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
     return launch_status();
 }
@@ -668,6 +844,12 @@ extern "C" int rfk_gemm_pair_clusters(void) {
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
     return g_pair_clusters[dev].load(std::memory_order_relaxed);
 }
+
+#ifdef RFK_GEMM_TIMELINE
+extern "C" int rfk_gemm_timeline(unsigned long long* host_out8) {
+    return (int)cudaMemcpyFromSymbol(host_out8, tcgemm::g_timeline, 16 * sizeof(unsigned long long));
+}
+#endif
 
 extern "C" int rfk_gemm_set_path(int path) {
     if (path < 0 || path > 3) return RFK_EINVAL;
