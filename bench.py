@@ -668,8 +668,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernel-table", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the one-frame comparison with the reference pipeline")
+    ap.add_argument("--reps", type=int, default=N_REPS, help="repetitions of the K-step loop per figure (median reported)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    globals()["N_REPS"] = max(1, args.reps)
 
     import torch
     if not torch.cuda.is_available():

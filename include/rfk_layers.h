@@ -216,6 +216,58 @@ int rfk_encoder_layer_forward_mixed(rfk_ctx* ctx, const rfk_encoder_layer_weight
                                     const rfk_half* rope_cos, const rfk_half* rope_sin,
                                     rfk_stream_t stream);
 
+/* ------------------------------------------------------------ DPT image head */
+
+/* replaces rf::RCUWeights / rf::FFBWeights / rf::DPTWeights — src/layers/dpt.h:36-62 (device pointers;
+ * convolution weights [Cout, Cin, kH, kW] fp16, biases [Cout] fp16), with the head's shape
+ * parameters (rf::Config::dpt_features / dpt_out_dim / dpt_out_channels, src/model/config.h:38-42)
+ * carried in the record instead of compiled in. */
+typedef struct {
+    const rfk_half* conv1_w; const rfk_half* conv1_b;   /* [F, F, 3, 3], [F] */
+    const rfk_half* conv2_w; const rfk_half* conv2_b;
+} rfk_rcu_weights;
+typedef struct {
+    rfk_rcu_weights rcu1;        /* used only when has_resconv1 != 0 */
+    rfk_rcu_weights rcu2;
+    const rfk_half* out_conv_w;  /* [F, F, 1, 1] */
+    const rfk_half* out_conv_b;
+    int has_resconv1;
+} rfk_ffb_weights;
+typedef struct {
+    const rfk_half* project_w[4];   /* [out_channels[i], dim, 1, 1] */
+    const rfk_half* project_b[4];
+    const rfk_half* resize_w[4];    /* 0: transposed 4x4 stride 4, 1: transposed 2x2 stride 2, 2: none (NULL), 3: 3x3 stride 2 */
+    const rfk_half* resize_b[4];
+    const rfk_half* layer_rn_w[4];  /* [features_dim, out_channels[i], 3, 3], no bias */
+    rfk_ffb_weights refinenet[4];
+    const rfk_half* output_conv1_w;  const rfk_half* output_conv1_b;   /* [F/2, F, 3, 3] */
+    const rfk_half* output_conv2a_w; const rfk_half* output_conv2a_b;  /* [32, F/2, 3, 3] */
+    const rfk_half* output_conv2b_w; const rfk_half* output_conv2b_b;  /* [out_dim, 32, 1, 1] */
+    int features_dim, out_dim;
+    int out_channels[4];
+} rfk_dpt_weights;
+
+typedef struct rfk_dpt rfk_dpt;  /* a planned head: buffers, cuDNN descriptors and algorithms, the list of steps */
+
+/* Plans the head for B images of patch_h x patch_w tokens of width dim (image patch_h*patch_size x
+ * patch_w*patch_size): sizes and allocates every intermediate, creates a cuDNN handle, chooses the
+ * convolution algorithms and allocates one workspace. Everything that allocates happens here.
+ * replaces the cudaMallocAsync / cudaFreeAsync calls and the lazy plan cache of rf::dpt_forward /
+ * rf::conv2d — src/layers/dpt.cu:23-47,130-160,329-337 */
+int rfk_dpt_create(rfk_ctx* ctx, const rfk_dpt_weights* w, int B, int dim, int patch_h, int patch_w,
+                   int patch_size, rfk_dpt** out);
+int rfk_dpt_destroy(rfk_dpt* dpt);
+/* features: HOST array of 4 device pointers, the decoder feature taps [B, patch_h*patch_w, dim]
+ * fp16. Writes the image [B, out_dim, H, W] fp16 (before the ELU / 10^x - 1 post-process) into the
+ * plan's own buffer (rfk_dpt_output) and, if image_out != NULL, copies it there. Launch-only:
+ * capturable. cuDNN convolutions for k > 1 and the transposed ones, cuBLAS for 1x1 (as the
+ * reference), rfk kernels for permute / bias / SiLU / residual / bilinear upsampling.
+ * replaces rf::dpt_forward — src/layers/dpt.h:64-72, src/layers/dpt.cu:322-461 */
+int rfk_dpt_forward(rfk_dpt* dpt, const rfk_half* const* features, rfk_half* image_out,
+                    rfk_stream_t stream);
+const rfk_half* rfk_dpt_output(rfk_dpt* dpt);
+int rfk_dpt_num_convolutions(rfk_dpt* dpt);
+
 /* ------------------------------------------------------------ render session */
 
 #define RFK_MAX_LAYERS 32
@@ -240,6 +292,10 @@ typedef struct {
     const float* vt_rope_freqs;
     rfk_encoder_layer_weights enc[RFK_MAX_LAYERS];
     rfk_decoder_layer_weights dec[RFK_MAX_LAYERS];
+    const rfk_dpt_weights* dpt;  /* HOST pointer, read at rfk_session_create; NULL: the view ends at the token map.
+                                    Otherwise the captured view continues through the DPT head and the image
+                                    post-process (rf::RenderFormerModel::dpt, src/model/renderformer.h:43-44;
+                                    render_session.cu:239-253) */
 } rfk_model;
 
 enum {
@@ -294,6 +350,12 @@ int rfk_session_result(rfk_session* s, const rfk_half** tokens, int* n_tokens, i
  * (the same lifetime as the slot's result buffer). The frame must have completed
  * (rfk_session_wait) before a consumer on another stream reads them. */
 int rfk_session_feature_taps(rfk_session* s, const rfk_half** taps /* HOST array of 4 */);
+/* With a DPT head in the model: device pointer and shape of the last frame's image
+ * [channels, img_res, img_res] fp32 after ELU(1e-3) and 10^x - 1 (what rf::RenderSession::
+ * download_frame_hwc reads, planar instead of interleaved) — render_session.cu:249-253, 550-559.
+ * RFK_EINVAL without a head. rfk_session_download_image copies it to HOST memory (waits for the frame). */
+int rfk_session_image(rfk_session* s, const float** image, int* channels, int* img_res);
+int rfk_session_download_image(rfk_session* s, float* h_out, size_t bytes);
 /* Copies the last frame's token map to HOST memory (waits for the frame).
  * replaces rf::RenderSession::download_frame_hwc — render_session.cu:550-559 */
 int rfk_session_download(rfk_session* s, rfk_half* h_out, size_t bytes);

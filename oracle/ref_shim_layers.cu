@@ -154,6 +154,38 @@ void ref_encoder_layer_forward_mixed(void* h, const float* query_norm, const hal
 
 }  // extern "C"
 
+// rf::dpt_forward (src/layers/dpt.cu:322-461) behind a flat weight record. RefDptW has the field order of
+// rfk_dpt_weights in include/rfk_layers.h, so a test passes one ctypes structure to both libraries.
+struct RefRcuW { const half *conv1_w, *conv1_b, *conv2_w, *conv2_b; };
+struct RefFfbW { RefRcuW rcu1, rcu2; const half *out_conv_w, *out_conv_b; int has_resconv1; };
+struct RefDptW {
+    const half* project_w[4]; const half* project_b[4]; const half* resize_w[4]; const half* resize_b[4];
+    const half* layer_rn_w[4]; RefFfbW refinenet[4];
+    const half *output_conv1_w, *output_conv1_b, *output_conv2a_w, *output_conv2a_b, *output_conv2b_w, *output_conv2b_b;
+    int features_dim, out_dim; int out_channels[4];
+};
+
+extern "C" void ref_dpt_forward(void* h, const RefDptW* w, const half* f0, const half* f1, const half* f2, const half* f3,
+                                half* out, half* col_buf, int B, int dim, int pH, int pW, int ps, void* s) {
+    rf::DPTWeights d{};
+    for (int i = 0; i < 4; ++i) {
+        d.project_w[i] = w->project_w[i]; d.project_b[i] = w->project_b[i];
+        d.resize_w[i] = w->resize_w[i]; d.resize_b[i] = w->resize_b[i];
+        d.layer_rn_w[i] = w->layer_rn_w[i];
+        const RefFfbW& f = w->refinenet[i];
+        d.refinenet[i].rcu1 = rf::RCUWeights{f.rcu1.conv1_w, f.rcu1.conv1_b, f.rcu1.conv2_w, f.rcu1.conv2_b};
+        d.refinenet[i].rcu2 = rf::RCUWeights{f.rcu2.conv1_w, f.rcu2.conv1_b, f.rcu2.conv2_w, f.rcu2.conv2_b};
+        d.refinenet[i].out_conv_w = f.out_conv_w; d.refinenet[i].out_conv_b = f.out_conv_b;
+        d.refinenet[i].has_resconv1 = f.has_resconv1 != 0;
+    }
+    d.output_conv1_w = w->output_conv1_w; d.output_conv1_b = w->output_conv1_b;
+    d.output_conv2a_w = w->output_conv2a_w; d.output_conv2a_b = w->output_conv2a_b;
+    d.output_conv2b_w = w->output_conv2b_w; d.output_conv2b_b = w->output_conv2b_b;
+    const half* feats[4] = {f0, f1, f2, f3};
+    rf::dpt_forward((cublasHandle_t)h, d, feats, out, col_buf, B, dim, pH, pW, ps, w->features_dim, w->out_dim,
+                    w->out_channels, S(s));
+}
+
 // ---------------------------------------------------------------------------------------
 // Per-view decoder pipeline of the reference, composed from the reference's own functions in
 // the order of src/pipeline/render_session.cu:189-238 (RenderSession::Impl::render_view) and

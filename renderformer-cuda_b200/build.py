@@ -29,7 +29,7 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
 ]
 
-LAYER_SOURCES = ["layers.cu", "session.cu"]
+LAYER_SOURCES = ["layers.cu", "session.cu", "dpt.cu"]
 
 KERNEL_SOURCES = [
     "abi.cu", "rmsnorm.cu", "softmax.cu", "rope.cu", "layout.cu",
@@ -74,7 +74,7 @@ def build_library(name: str, sources: list[str], extra: list[str], force: bool,
         s = CSRC / src
         o = objdir / (s.stem + ".o")
         if force or not _newer(o, [s] + headers):
-            cmd = [nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", f"-I{CSRC}", "-c", str(s), "-o", str(o)]
+            cmd = [nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", f"-I{CSRC}", f"-I{cudnn_include()}", "-c", str(s), "-o", str(o)]
             if ptxas_info:
                 cmd[1:1] = ["-Xptxas", "-v"]
             _run(cmd, verbose or ptxas_info)
@@ -85,12 +85,19 @@ def build_library(name: str, sources: list[str], extra: list[str], force: bool,
     return out
 
 
+def cudnn_include() -> str:
+    """cudnn.h ships with the Python environment's cuDNN package; the library itself is the system's libcudnn.so.9."""
+    import sysconfig
+    return os.path.join(sysconfig.get_paths()["purelib"], "nvidia", "cudnn", "include")
+
+
 def build_all(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> dict[str, Path]:
     libs = {"rfk": build_library("rfk", KERNEL_SOURCES, [], force, verbose, ptxas_info)}
-    # layer boundaries + session: cuBLAS for the GEMMs, librfk.so (same directory) for everything else
+    # layer boundaries + session + DPT head: cuBLAS for the fallback GEMMs, cuDNN for the head's convolutions,
+    # librfk.so (same directory) for everything else
     libs["rfk_layers"] = build_library(
         "rfk_layers", LAYER_SOURCES,
-        ["-lcublas", f"-L{PKG}", "-lrfk", "-Xlinker", "-rpath=$ORIGIN"], force, verbose, ptxas_info)
+        ["-lcublas", "-lcudnn", f"-L{PKG}", "-lrfk", "-Xlinker", "-rpath=$ORIGIN"], force, verbose, ptxas_info)
     return libs
 
 

@@ -1,8 +1,11 @@
 // Library-level entry points of the C ABI: identification, status text, launch counter.
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace rfk {
 std::atomic<unsigned long long> g_launches{0};
+bool g_pdl_enabled = [] { const char* e = getenv("RFK_PDL"); return !(e && e[0] == '0'); }();
 }
 
 extern "C" const char* rfk_version(void) { return "rfk 0.1 sm_100a"; }

@@ -295,6 +295,8 @@ window_attention_kernel(const __half* __restrict__ Q, const __half* __restrict__
     __shared__ __align__(16) uint8_t sMask[kWinTokens * kWinTokens];  // this window's mask, fetched with the tiles
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, tig = lane & 3;
+    pdl_wait();
+    pdl_trigger();
     const long long bh = blockIdx.x;
     const int bw = (int)(bh / heads), h = (int)(bh % heads);
     const __half* Qh = Q + bh * (kWinTokens * HD);
@@ -455,8 +457,8 @@ extern "C" int rfk_window_attention(const rfk_half* Q, const rfk_half* K, const 
     if (mask && !aligned16(mask)) return RFK_EUNSUPPORTED;
     const long long ctas = (long long)BnW * num_heads;
     if (ctas > 0x7fffffffLL) return RFK_EUNSUPPORTED;
-    window_attention_kernel<<<(unsigned)ctas, kWinThreads, 0, as_stream(stream)>>>(
-        (const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, mask, num_heads, nW,
-        scale * 1.4426950408889634f);
+    launch_pdl(window_attention_kernel, dim3((unsigned)ctas), dim3(kWinThreads), 0, as_stream(stream),
+               (const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, mask, num_heads, nW,
+               scale * 1.4426950408889634f);
     return launch_status();
 }

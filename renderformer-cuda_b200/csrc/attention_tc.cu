@@ -179,6 +179,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem_cta = ctrl->tmem_base;
+    // everything above touched only this CTA's shared and tensor memory; the operands below are another kernel's output
+    pdl_wait();
+    pdl_trigger();
 
     if (warp == 8) {
         // ------------------------------------------------------------ producer (one thread)
@@ -455,8 +458,8 @@ int launch_attention_tc(const __half* Q, const __half* K, const __half* V, __hal
         !make_map(&mv, V, (long long)B * H, Sk, tcattn::BN))
         return RFK_EUNSUPPORTED;
     dim3 grid(ceil_div(Sq, tcattn::kBlocks * tcattn::BM), B * H);
-    tcattn::attention_tc_kernel<<<grid, tcattn::kThreads, tcattn::kSmemBytes, st>>>(mq, mk, mv, O, H, Sq, n_keys, o_bshd,
-                                                                                    scale * 1.4426950408889634f);
+    launch_pdl(tcattn::attention_tc_kernel, grid, dim3(tcattn::kThreads), tcattn::kSmemBytes, st, mq, mk, mv, O, H, Sq, n_keys,
+               o_bshd, scale * 1.4426950408889634f);
     return launch_status();
 }
 

@@ -5,6 +5,7 @@
 #include <atomic>
 #include <cfloat>
 #include <cstdint>
+#include <utility>
 #include "rfk.h"
 
 #if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ < 1000)
@@ -29,12 +30,34 @@ inline int launch_status() {
 
 inline cudaStream_t as_stream(rfk_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// Programmatic dependent launch. A kernel launched through launch_pdl may be scheduled as soon as every CTA of the
+// kernel before it in the stream has called pdl_trigger() (or exited), so its launch latency and its on-chip
+// set-up overlap that kernel's tail; it must call pdl_wait() before it touches global memory, which blocks until the
+// preceding kernel has completed and its writes are visible. Every kernel launched this way calls pdl_wait() in all
+// of its CTAs, so completion of a kernel implies completion of everything before it. Inside a stream capture the
+// launches become programmatic edges of the graph. RFK_PDL=0 in the environment turns the attribute off (the
+// device-side calls are then no-ops).
+extern bool g_pdl_enabled;  // defined in abi.cu
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = g_pdl_enabled ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline bool aligned8(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7u) == 0; }
 
 inline unsigned ceil_div(long long a, long long b) { return (unsigned)((a + b - 1) / b); }
 
 // ------------------------------------------------------------- device side
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // 8 fp16 values moved as one 128-bit transaction.
 struct __align__(16) Half8 {

@@ -1,0 +1,308 @@
+// DPT image head: the four decoder feature taps -> [out_dim, H, W] image, composed from library
+// convolutions (cuDNN for k > 1 and the transposed ones, cuBLAS for 1x1) and the rfk element-wise
+// kernels (token-map permute, NCHW bias add, SiLU, residual add, bilinear upsample).
+//
+// Reference: rf::dpt_forward, src/layers/dpt.cu:322-461 (BANANASJIM/renderformer-cuda), with
+// rf::conv2d (:100-178) and rf::conv_transpose2d (:182-236); same operator sequence and the same
+// library calls. What is different:
+//   - nothing is allocated on the launch path. The reference calls cudaMallocAsync / cudaFreeAsync
+//     for every intermediate inside dpt_forward (and so inside its captured graph); here
+//     rfk_dpt_create sizes every intermediate once, picks the cuDNN algorithms, allocates one
+//     workspace, and records the whole head as a list of steps over fixed buffers.
+//     rfk_dpt_forward only walks that list, so it can be captured.
+//   - bias adds, SiLU, residual adds, the upsampling and the permute are the rfk kernels
+//     (vectorised; the bilinear kernel is bit-identical to the reference's).
+#include "layers_internal.h"
+
+#include <cudnn.h>
+
+#include <algorithm>
+#include <functional>
+#include <vector>
+
+namespace {
+
+#define DNN_TRY(expr)                                      \
+    do {                                                   \
+        cudnnStatus_t s_ = (expr);                         \
+        if (s_ != CUDNN_STATUS_SUCCESS) return 2000 + (int)s_; \
+    } while (0)
+#define TRY(expr)                       \
+    do {                                \
+        int rc_ = (expr);               \
+        if (rc_ != RFK_OK) return rc_;  \
+    } while (0)
+
+using Step = std::function<int(const rfk_half* const* feats, cudaStream_t st)>;
+
+}  // namespace
+
+struct rfk_dpt {
+    rfk_ctx* ctx = nullptr;  // borrowed: cuBLAS handle for the 1x1 convolutions
+    cudnnHandle_t dnn = nullptr;
+    rfk_dpt_weights w{};
+    int B = 0, dim = 0, pH = 0, pW = 0, ps = 0;
+    std::vector<void*> owned;
+    std::vector<cudnnTensorDescriptor_t> tdescs;
+    std::vector<cudnnFilterDescriptor_t> fdescs;
+    std::vector<cudnnConvolutionDescriptor_t> cdescs;
+    void* workspace = nullptr;
+    size_t ws_bytes = 0;
+    std::vector<Step> program;
+    rfk_half* out = nullptr;  // [B, out_dim, pH*ps, pW*ps]
+    int n_convs = 0;
+
+    rfk_half* alloc(size_t halves) {
+        void* p = nullptr;
+        if (cudaMalloc(&p, std::max<size_t>(halves * sizeof(rfk_half), 256)) != cudaSuccess) return nullptr;
+        owned.push_back(p);
+        return (rfk_half*)p;
+    }
+    cudnnTensorDescriptor_t tensor(int n, int c, int h, int w_) {
+        cudnnTensorDescriptor_t d = nullptr;
+        if (cudnnCreateTensorDescriptor(&d) != CUDNN_STATUS_SUCCESS) return nullptr;
+        tdescs.push_back(d);
+        if (cudnnSetTensor4dDescriptor(d, CUDNN_TENSOR_NCHW, CUDNN_DATA_HALF, n, c, h, w_) != CUDNN_STATUS_SUCCESS) return nullptr;
+        return d;
+    }
+    cudnnFilterDescriptor_t filter(int k, int c, int r, int s) {
+        cudnnFilterDescriptor_t d = nullptr;
+        if (cudnnCreateFilterDescriptor(&d) != CUDNN_STATUS_SUCCESS) return nullptr;
+        fdescs.push_back(d);
+        if (cudnnSetFilter4dDescriptor(d, CUDNN_DATA_HALF, CUDNN_TENSOR_NCHW, k, c, r, s) != CUDNN_STATUS_SUCCESS) return nullptr;
+        return d;
+    }
+    cudnnConvolutionDescriptor_t conv(int pad, int stride) {
+        cudnnConvolutionDescriptor_t d = nullptr;
+        if (cudnnCreateConvolutionDescriptor(&d) != CUDNN_STATUS_SUCCESS) return nullptr;
+        cdescs.push_back(d);
+        if (cudnnSetConvolution2dDescriptor(d, pad, pad, stride, stride, 1, 1, CUDNN_CROSS_CORRELATION, CUDNN_DATA_FLOAT) !=
+                CUDNN_STATUS_SUCCESS ||
+            cudnnSetConvolutionMathType(d, CUDNN_TENSOR_OP_MATH) != CUDNN_STATUS_SUCCESS)
+            return nullptr;
+        return d;
+    }
+
+    // out [B, Cout, Ho, Wo] = conv(in [B, Cin, H, W], weight [Cout, Cin, k, k]) (+ bias). `in` may be null: then the step
+    // reads feature tap `feat_index` through `nchw_in` (already permuted by the previous step).
+    int add_conv(const rfk_half* in, const rfk_half* weight, const rfk_half* bias, rfk_half* o, int Cin, int H, int W, int Cout,
+                 int k, int stride, int pad) {
+        const int Ho = (H + 2 * pad - k) / stride + 1, Wo = (W + 2 * pad - k) / stride + 1;
+        const int Bn = B;
+        ++n_convs;
+        if (k == 1 && stride == 1 && pad == 0) {
+            // 1x1: per image out[Cout, HW] = weight[Cout, Cin] in[Cin, HW] (src/layers/dpt.cu:112-126)
+            rfk_ctx* c = ctx;
+            program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {
+                if (cublasSetStream(c->blas, st) != CUBLAS_STATUS_SUCCESS) return 1000;
+                const float one = 1.0f, zero = 0.0f;
+                for (int n = 0; n < Bn; ++n) {
+                    cublasStatus_t s = cublasGemmEx(c->blas, CUBLAS_OP_N, CUBLAS_OP_N, H * W, Cout, Cin, &one,
+                                                    in + (size_t)n * Cin * H * W, CUDA_R_16F, H * W, weight, CUDA_R_16F, Cin, &zero,
+                                                    o + (size_t)n * Cout * H * W, CUDA_R_16F, H * W, CUBLAS_COMPUTE_32F,
+                                                    CUBLAS_GEMM_DEFAULT);
+                    if (s != CUBLAS_STATUS_SUCCESS) return 1000 + (int)s;
+                }
+                return bias ? rfk_add_bias_nchw(o, bias, Bn, Cout, (long long)H * W, (rfk_stream_t)st) : RFK_OK;
+            });
+            return RFK_OK;
+        }
+        cudnnTensorDescriptor_t xd = tensor(B, Cin, H, W), yd = tensor(B, Cout, Ho, Wo);
+        cudnnFilterDescriptor_t fd = filter(Cout, Cin, k, k);
+        cudnnConvolutionDescriptor_t cd = conv(pad, stride);
+        if (!xd || !yd || !fd || !cd) return RFK_EINVAL;
+        int returned = 0;
+        cudnnConvolutionFwdAlgoPerf_t perf[4];
+        DNN_TRY(cudnnGetConvolutionForwardAlgorithm_v7(dnn, xd, fd, cd, yd, 4, &returned, perf));
+        if (returned < 1) return RFK_EUNSUPPORTED;
+        const cudnnConvolutionFwdAlgo_t algo = perf[0].algo;
+        size_t ws = 0;
+        DNN_TRY(cudnnGetConvolutionForwardWorkspaceSize(dnn, xd, fd, cd, yd, algo, &ws));
+        ws_bytes = std::max(ws_bytes, ws);
+        rfk_dpt* self = this;
+        program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {
+            const float one = 1.0f, zero = 0.0f;
+            DNN_TRY(cudnnSetStream(self->dnn, st));
+            DNN_TRY(cudnnConvolutionForward(self->dnn, &one, xd, in, fd, weight, cd, algo, self->workspace, ws, &zero, yd, o));
+            return bias ? rfk_add_bias_nchw(o, bias, Bn, Cout, (long long)Ho * Wo, (rfk_stream_t)st) : RFK_OK;
+        });
+        return RFK_OK;
+    }
+
+    // transposed convolution = data gradient of a convolution with the same filter (src/layers/dpt.cu:182-236)
+    int add_conv_transpose(const rfk_half* in, const rfk_half* weight, const rfk_half* bias, rfk_half* o, int Cin, int H, int W,
+                           int Cout, int k, int stride, int pad) {
+        const int Ho = (H - 1) * stride - 2 * pad + k, Wo = (W - 1) * stride - 2 * pad + k;
+        const int Bn = B;
+        ++n_convs;
+        cudnnTensorDescriptor_t dyd = tensor(B, Cin, H, W), dxd = tensor(B, Cout, Ho, Wo);
+        cudnnFilterDescriptor_t fd = filter(Cin, Cout, k, k);
+        cudnnConvolutionDescriptor_t cd = conv(pad, stride);
+        if (!dyd || !dxd || !fd || !cd) return RFK_EINVAL;
+        int returned = 0;
+        cudnnConvolutionBwdDataAlgoPerf_t perf[4];
+        DNN_TRY(cudnnGetConvolutionBackwardDataAlgorithm_v7(dnn, fd, dyd, cd, dxd, 4, &returned, perf));
+        if (returned < 1) return RFK_EUNSUPPORTED;
+        const cudnnConvolutionBwdDataAlgo_t algo = perf[0].algo;
+        size_t ws = 0;
+        DNN_TRY(cudnnGetConvolutionBackwardDataWorkspaceSize(dnn, fd, dyd, cd, dxd, algo, &ws));
+        ws_bytes = std::max(ws_bytes, ws);
+        rfk_dpt* self = this;
+        program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {
+            const float one = 1.0f, zero = 0.0f;
+            DNN_TRY(cudnnSetStream(self->dnn, st));
+            DNN_TRY(cudnnConvolutionBackwardData(self->dnn, &one, fd, weight, dyd, in, cd, algo, self->workspace, ws, &zero, dxd, o));
+            return bias ? rfk_add_bias_nchw(o, bias, Bn, Cout, (long long)Ho * Wo, (rfk_stream_t)st) : RFK_OK;
+        });
+        return RFK_OK;
+    }
+
+    // residual convolution unit, in place on x (src/layers/dpt.cu:397-409): x <- conv2(silu(conv1(silu(x)))) + x
+    int add_rcu(const rfk_rcu_weights& r, rfk_half* x, int F, int H, int W) {
+        const long long n = (long long)B * F * H * W;
+        rfk_half* x_orig = alloc((size_t)n);
+        rfk_half* t1 = alloc((size_t)n);
+        if (!x_orig || !t1) return (int)cudaErrorMemoryAllocation;
+        program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {
+            cudaError_t e = cudaMemcpyAsync(x_orig, x, (size_t)n * sizeof(rfk_half), cudaMemcpyDeviceToDevice, st);
+            if (e != cudaSuccess) return (int)e;
+            return rfk_silu_inplace(x, n, (rfk_stream_t)st);
+        });
+        TRY(add_conv(x, r.conv1_w, r.conv1_b, t1, F, H, W, F, 3, 1, 1));
+        program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int { return rfk_silu_inplace(t1, n, (rfk_stream_t)st); });
+        TRY(add_conv(t1, r.conv2_w, r.conv2_b, x, F, H, W, F, 3, 1, 1));
+        program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int { return rfk_residual_add(x, x_orig, n, (rfk_stream_t)st); });
+        return RFK_OK;
+    }
+
+    // feature fusion block (src/layers/dpt.cu:411-426); returns the [B, F, th, tw] result buffer in *result
+    int add_refinenet(int i, rfk_half* path_in, rfk_half* lr, int ph, int pw, int th, int tw, rfk_half** result) {
+        const int F = w.features_dim;
+        const rfk_ffb_weights& f = w.refinenet[i];
+        if (f.has_resconv1) {
+            if (!lr) return RFK_EINVAL;
+            TRY(add_rcu(f.rcu1, lr, F, ph, pw));
+            const long long n = (long long)B * F * ph * pw;
+            program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int { return rfk_residual_add(path_in, lr, n, (rfk_stream_t)st); });
+        }
+        TRY(add_rcu(f.rcu2, path_in, F, ph, pw));
+        rfk_half* up = alloc((size_t)B * F * th * tw);
+        rfk_half* res = alloc((size_t)B * F * th * tw);
+        if (!up || !res) return (int)cudaErrorMemoryAllocation;
+        const int Bn = B;
+        program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {
+            return rfk_bilinear_upsample(path_in, up, Bn, F, ph, pw, th, tw, (rfk_stream_t)st);
+        });
+        TRY(add_conv(up, f.out_conv_w, f.out_conv_b, res, F, th, tw, F, 1, 1, 0));
+        *result = res;
+        return RFK_OK;
+    }
+
+    int build() {
+        const int S = pH * pW, F = w.features_dim;
+        rfk_half* resized[4];
+        int rh[4], rw[4];
+        for (int i = 0; i < 4; ++i) {
+            const int C = w.out_channels[i];
+            rfk_half* nchw = alloc((size_t)B * dim * S);
+            rfk_half* projected = alloc((size_t)B * C * S);
+            if (!nchw || !projected) return (int)cudaErrorMemoryAllocation;
+            const int Bn = B, Sn = S, dn = dim;
+            program.push_back([=](const rfk_half* const* feats, cudaStream_t st) -> int {
+                return rfk_permute_bsd_to_nchw(feats[i], nchw, Bn, Sn, dn, (rfk_stream_t)st);
+            });
+            TRY(add_conv(nchw, w.project_w[i], w.project_b[i], projected, dim, pH, pW, C, 1, 1, 0));
+            if (i == 0 || i == 1) {  // x4 / x2 transposed convolution, kernel = stride
+                const int f = i == 0 ? 4 : 2;
+                rh[i] = pH * f; rw[i] = pW * f;
+                resized[i] = alloc((size_t)B * C * rh[i] * rw[i]);
+                if (!resized[i]) return (int)cudaErrorMemoryAllocation;
+                TRY(add_conv_transpose(projected, w.resize_w[i], w.resize_b[i], resized[i], C, pH, pW, C, f, f, 0));
+            } else if (i == 2) {
+                rh[i] = pH; rw[i] = pW;
+                resized[i] = projected;
+            } else {  // stride-2 3x3
+                rh[i] = (pH + 1) / 2; rw[i] = (pW + 1) / 2;
+                resized[i] = alloc((size_t)B * C * rh[i] * rw[i]);
+                if (!resized[i]) return (int)cudaErrorMemoryAllocation;
+                TRY(add_conv(projected, w.resize_w[i], w.resize_b[i], resized[i], C, pH, pW, C, 3, 2, 1));
+            }
+        }
+        rfk_half* layer_rn[4];
+        for (int i = 0; i < 4; ++i) {
+            layer_rn[i] = alloc((size_t)B * F * rh[i] * rw[i]);
+            if (!layer_rn[i]) return (int)cudaErrorMemoryAllocation;
+            TRY(add_conv(resized[i], w.layer_rn_w[i], nullptr, layer_rn[i], w.out_channels[i], rh[i], rw[i], F, 3, 1, 1));
+        }
+        rfk_half *path4, *path3, *path2, *path1;
+        TRY(add_refinenet(3, layer_rn[3], nullptr, rh[3], rw[3], rh[2], rw[2], &path4));
+        TRY(add_refinenet(2, path4, layer_rn[2], rh[2], rw[2], rh[1], rw[1], &path3));
+        TRY(add_refinenet(1, path3, layer_rn[1], rh[1], rw[1], rh[0], rw[0], &path2));
+        const int oh = rh[0] * 2, ow = rw[0] * 2;
+        TRY(add_refinenet(0, path2, layer_rn[0], rh[0], rw[0], oh, ow, &path1));
+        // output head (src/layers/dpt.cu:440-460)
+        const int fh = F / 2, full_h = pH * ps, full_w = pW * ps;
+        rfk_half* oc1 = alloc((size_t)B * fh * oh * ow);
+        rfk_half* oc1_up = alloc((size_t)B * fh * full_h * full_w);
+        rfk_half* oc2a = alloc((size_t)B * 32 * full_h * full_w);
+        out = alloc((size_t)B * w.out_dim * full_h * full_w);
+        if (!oc1 || !oc1_up || !oc2a || !out) return (int)cudaErrorMemoryAllocation;
+        TRY(add_conv(path1, w.output_conv1_w, w.output_conv1_b, oc1, F, oh, ow, fh, 3, 1, 1));
+        const int Bn = B;
+        program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {
+            return rfk_bilinear_upsample(oc1, oc1_up, Bn, fh, oh, ow, full_h, full_w, (rfk_stream_t)st);
+        });
+        TRY(add_conv(oc1_up, w.output_conv2a_w, w.output_conv2a_b, oc2a, fh, full_h, full_w, 32, 3, 1, 1));
+        const long long n2a = (long long)B * 32 * full_h * full_w;
+        program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int { return rfk_silu_inplace(oc2a, n2a, (rfk_stream_t)st); });
+        TRY(add_conv(oc2a, w.output_conv2b_w, w.output_conv2b_b, out, 32, full_h, full_w, w.out_dim, 1, 1, 0));
+        if (ws_bytes) {
+            if (cudaMalloc(&workspace, ws_bytes) != cudaSuccess) return (int)cudaErrorMemoryAllocation;
+            owned.push_back(workspace);
+        }
+        return RFK_OK;
+    }
+};
+
+extern "C" int rfk_dpt_destroy(rfk_dpt* d) {
+    if (!d) return RFK_OK;
+    for (auto t : d->tdescs) cudnnDestroyTensorDescriptor(t);
+    for (auto f : d->fdescs) cudnnDestroyFilterDescriptor(f);
+    for (auto c : d->cdescs) cudnnDestroyConvolutionDescriptor(c);
+    for (void* p : d->owned) cudaFree(p);
+    if (d->dnn) cudnnDestroy(d->dnn);
+    delete d;
+    return RFK_OK;
+}
+
+extern "C" int rfk_dpt_create(rfk_ctx* ctx, const rfk_dpt_weights* w, int B, int dim, int patch_h, int patch_w, int patch_size,
+                              rfk_dpt** out) {
+    if (!ctx || !w || !out || B <= 0 || dim <= 0 || patch_h <= 0 || patch_w <= 0 || patch_size <= 0) return RFK_EINVAL;
+    if (w->features_dim <= 0 || w->features_dim % 2 || w->out_dim <= 0) return RFK_EINVAL;
+    for (int i = 0; i < 4; ++i)
+        if (w->out_channels[i] <= 0 || !w->project_w[i] || !w->layer_rn_w[i] || (i != 2 && !w->resize_w[i])) return RFK_EINVAL;
+    rfk_dpt* d = new rfk_dpt();
+    d->ctx = ctx; d->w = *w; d->B = B; d->dim = dim; d->pH = patch_h; d->pW = patch_w; d->ps = patch_size;
+    if (cudnnCreate(&d->dnn) != CUDNN_STATUS_SUCCESS) { delete d; return 2000; }
+    const int rc = d->build();
+    if (rc != RFK_OK) { rfk_dpt_destroy(d); return rc; }
+    *out = d;
+    return RFK_OK;
+}
+
+extern "C" int rfk_dpt_forward(rfk_dpt* d, const rfk_half* const* features, rfk_half* image_out, rfk_stream_t stream) {
+    if (!d || !features) return RFK_EINVAL;
+    for (int i = 0; i < 4; ++i)
+        if (!features[i]) return RFK_EINVAL;
+    cudaStream_t st = (cudaStream_t)stream;
+    for (const Step& s : d->program) TRY(s(features, st));
+    if (image_out && image_out != d->out) {
+        const size_t bytes = (size_t)d->B * d->w.out_dim * d->pH * d->ps * d->pW * d->ps * sizeof(rfk_half);
+        cudaError_t e = cudaMemcpyAsync(image_out, d->out, bytes, cudaMemcpyDeviceToDevice, st);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return RFK_OK;
+}
+
+extern "C" const rfk_half* rfk_dpt_output(rfk_dpt* d) { return d ? d->out : nullptr; }
+extern "C" int rfk_dpt_num_convolutions(rfk_dpt* d) { return d ? d->n_convs : 0; }

@@ -215,6 +215,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem_cta = ctrl->tmem_base;
+    pdl_wait();      // set-up above is on-chip only; the operands are another kernel's output
+    pdl_trigger();
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer (one thread)
@@ -557,6 +559,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         return;
     }
     const uint32_t tmem_cta = ctrl->tmem_base;
+    pdl_wait();      // set-up above is on-chip only; the operands are another kernel's output
+    pdl_trigger();
     if (tid == 0) RFK_STAMP(1);   // prologue done (barriers, tensor memory, cluster barrier)
 
     if (warp == 0) {
@@ -735,7 +739,7 @@ int launch_gemm_single(const CUtensorMap& ma, const CUtensorMap& mw0, const CUte
     }
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = std::min(tiles, std::max(1, sm_count[dev].load(std::memory_order_relaxed)));
-    tcgemm::gemm_tc_kernel<EPI><<<grid, tcgemm::kThreads, tcgemm::kSmemBytes, st>>>(ma, mw0, mw1, p);
+    launch_pdl(tcgemm::gemm_tc_kernel<EPI>, dim3(grid), dim3(tcgemm::kThreads), tcgemm::kSmemBytes, st, ma, mw0, mw1, p);
     return launch_status();
 }
 
@@ -755,9 +759,11 @@ int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mw0, const CUtens
     std::atomic<int>* max_clusters = g_pair_clusters;   // 0 not asked yet, -1 unavailable
     static std::atomic<bool> configured[64];            // per instantiation of the kernel
     cudaLaunchConfig_t cfg{};
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see launch_pdl in common.cuh
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.blockDim = dim3(tcgemm::kThreads); cfg.dynamicSmemBytes = kSmem; cfg.stream = st;
     cfg.attrs = attr; cfg.numAttrs = 1;
     int nc = max_clusters[dev].load(std::memory_order_acquire);
@@ -780,6 +786,7 @@ int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mw0, const CUtens
     p.tiles_m = (p.M + 2 * tcgemm::BM - 1) / (2 * tcgemm::BM);
     const int tiles = p.tiles_m * p.tiles_n;
     cfg.gridDim = dim3(2 * std::min(tiles, nc));
+    cfg.numAttrs = g_pdl_enabled ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, tcgemm::pair::gemm_tc_pair_kernel<EPI>, ma, mw0, mw1, mc, mr, p);
     if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
     return launch_status();

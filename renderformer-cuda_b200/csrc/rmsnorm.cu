@@ -55,6 +55,8 @@ rmsnorm_row_kernel(const TH* x, TH* xw, const TR* __restrict__ r,
     constexpr int kWarps = kRmsThreads / 32;
     constexpr int kRowsPerCta = kWarps / W;
     __shared__ float s_part[kWarps];
+    pdl_wait();
+    pdl_trigger();
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int wir = warp % W;  // warp index within its row
@@ -162,10 +164,10 @@ static int launch_variant(const TH* x, TH* xw, const TR* r, const float* gamma, 
                      aligned16(gamma) && (!HAS_RES || aligned16(r)) &&
                      (!WRITE_H || aligned16(xw));
     if (vec) {
-#define RFK_RMS_LAUNCH(N, WW)                                                                  \
-    rmsnorm_row_kernel<TH, TR, TY, N, WW, HAS_RES, WRITE_H>                                    \
-        <<<ceil_div(rows, (kRmsThreads / 32) / WW), kRmsThreads, 0, st>>>(x, xw, r, gamma, y,  \
-                                                                           rows, dim, eps)
+#define RFK_RMS_LAUNCH(N, WW)                                                                         \
+    launch_pdl(rmsnorm_row_kernel<TH, TR, TY, N, WW, HAS_RES, WRITE_H, 0>,                             \
+               dim3(ceil_div(rows, (kRmsThreads / 32) / WW)), dim3(kRmsThreads), 0, st, x, xw, r, gamma, y, \
+               rows, dim, eps, WinRows{})
         if (dim <= 256) RFK_RMS_LAUNCH(1, 1);
         else if (dim <= 512) RFK_RMS_LAUNCH(1, 2);
         else if (dim <= 1024) RFK_RMS_LAUNCH(1, 4);
@@ -237,13 +239,13 @@ extern "C" int rfk_rmsnorm_residual_f16_windows(rfk_half* x, const rfk_half* r, 
     __half* xh = (__half*)x;
 #define RFK_RMS_WIN(N, WW, M)                                                                                   \
     if (r)                                                                                                      \
-        rmsnorm_row_kernel<__half, __half, __half, N, WW, true, true, M>                                        \
-            <<<ceil_div(rows, (kRmsThreads / 32) / WW), kRmsThreads, 0, st>>>(xh, xh, (const __half*)r, gamma,   \
-                                                                               (__half*)y, rows, dim, eps, wr); \
+        launch_pdl(rmsnorm_row_kernel<__half, __half, __half, N, WW, true, true, M>,                             \
+                   dim3(ceil_div(rows, (kRmsThreads / 32) / WW)), dim3(kRmsThreads), 0, st, (const __half*)xh, xh, \
+                   (const __half*)r, gamma, (__half*)y, rows, dim, eps, wr);                                     \
     else                                                                                                        \
-        rmsnorm_row_kernel<__half, __half, __half, N, WW, false, false, 1>                                      \
-            <<<ceil_div(rows, (kRmsThreads / 32) / WW), kRmsThreads, 0, st>>>(xh, xh, nullptr, gamma,            \
-                                                                               (__half*)y, rows, dim, eps, wr)
+        launch_pdl(rmsnorm_row_kernel<__half, __half, __half, N, WW, false, false, 1>,                           \
+                   dim3(ceil_div(rows, (kRmsThreads / 32) / WW)), dim3(kRmsThreads), 0, st, (const __half*)xh, xh, \
+                   (const __half*)nullptr, gamma, (__half*)y, rows, dim, eps, wr)
 #define RFK_RMS_WIN_DIM(M)                            \
     if (dim <= 256) { RFK_RMS_WIN(1, 1, M); }         \
     else if (dim <= 512) { RFK_RMS_WIN(1, 2, M); }    \

@@ -92,6 +92,8 @@ rope_apply_kernel(const T* src0, T* dst0, const T* src1, T* dst1,
                   int batch, int num_heads, int seq_len, int rows_total, int head_dim,
                   long long src_rows, long long dst_rows, long long src_bstride, long long dst_bstride,
                   long long tab_bstride) {
+    pdl_wait();
+    pdl_trigger();
     const int cpt = head_dim / 16;
     const int hgroups = num_heads / HP;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -207,11 +209,9 @@ static int launch_rope(const T* src0, T* dst0, const T* src1, T* dst1, const __h
         const long long total = (long long)batch * (num_heads / hp) * rows_total * cpt;
         const unsigned grid = ceil_div(total, 128);
 #define RFK_ROPE(HPV)                                                                         \
-    rope_apply_kernel<T, NT, HPV><<<grid, 128, 0, st>>>(src0, dst0, src1, dst1, cos_vals,     \
-                                                        sin_vals, batch, num_heads, seq_len,  \
-                                                        rows_total, head_dim, src_rows,       \
-                                                        dst_rows, src_bstride, dst_bstride,   \
-                                                        tab_bstride)
+    launch_pdl(rope_apply_kernel<T, NT, HPV>, dim3(grid), dim3(128), 0, st, src0, dst0, src1, dst1, \
+               cos_vals, sin_vals, batch, num_heads, seq_len, rows_total, head_dim, src_rows,        \
+               dst_rows, src_bstride, dst_bstride, tab_bstride)
         if (hp == 4) RFK_ROPE(4);
         else if (hp == 2) RFK_ROPE(2);
         else RFK_ROPE(1);
@@ -246,6 +246,8 @@ qkv_epilogue_kernel(const __half* __restrict__ x, long long row_stride,
                     int batch, int seq_len, int num_heads, int head_dim, float eps,
                     long long out_seq_stride) {
     constexpr int RPC = 4 / WPR;  // rows per CTA
+    pdl_wait();
+    pdl_trigger();
     const int lane = (WPR == 1) ? (threadIdx.x & 31) : (threadIdx.x % (32 * WPR));  // index within the row's threads
     const long long rows = (long long)batch * seq_len;
     long long row = (long long)blockIdx.x * RPC + threadIdx.x / (32 * WPR);
@@ -473,9 +475,9 @@ extern "C" int rfk_qkv_norm_rope_transpose(const rfk_half* x, long long row_stri
     const int npairs = (int)(dim / 16);
     // two warps per row from 64 chunk pairs on (dim 1024: one pair per thread, 64 registers, 8 CTAs per SM)
 #define RFK_QKV(N, W)                                                                            \
-    qkv_epilogue_kernel<N, W><<<dim3(ceil_div(rows, 4 / W), n_parts), 128, 0, st>>>(             \
-        (const __half*)x, row_stride, parts, (const __half*)cos_vals, (const __half*)sin_vals,   \
-        batch, seq_len, num_heads, head_dim, eps, out_seq_stride)
+    launch_pdl(qkv_epilogue_kernel<N, W>, dim3(ceil_div(rows, 4 / W), n_parts), dim3(128), 0, st, \
+               (const __half*)x, row_stride, parts, (const __half*)cos_vals, (const __half*)sin_vals, \
+               batch, seq_len, num_heads, head_dim, eps, (long long)out_seq_stride)
     if (npairs <= 32) RFK_QKV(1, 1);
     else if (npairs <= 64) RFK_QKV(1, 2);
     else RFK_QKV(2, 2);

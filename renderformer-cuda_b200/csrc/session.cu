@@ -124,6 +124,9 @@ struct rfk_session {
     cudaEvent_t ev_fork = nullptr, ev_rot[RFK_MAX_LAYERS]{};
     uint8_t* shift_mask = nullptr;
     rfk_half* dft[kSlots][4] = {};  // the four decoder feature taps of each frame slot
+    rfk_dpt_weights dptw{};          // copy of the model's DPT record (if any)
+    rfk_dpt* dpt = nullptr;          // planned image head; null: the view ends at the token map
+    float* image[kSlots] = {nullptr, nullptr};  // [out_dim, res, res] fp32 after the post-process
     rfk_half* result[kSlots] = {nullptr, nullptr};
 
     // frame slots
@@ -153,11 +156,11 @@ struct rfk_session {
         return RFK_OK;
     }
 
-    int render_view(const float* pinned_cam, rfk_half* result_out, rfk_half* const* taps_out);
+    int render_view(const float* pinned_cam, rfk_half* result_out, rfk_half* const* taps_out, float* image_out);
 };
 
 // The per-view work; everything here is captured into the graph.
-int rfk_session::render_view(const float* pinned_cam, rfk_half* result_out, rfk_half* const* taps_out) {
+int rfk_session::render_view(const float* pinned_cam, rfk_half* result_out, rfk_half* const* taps_out, float* image_out) {
     rfk_stream_t s = (rfk_stream_t)stream;
     const int dim = m.dim, nr = m.num_register_tokens, ps = m.patch_size;
     TRY_CUDA(cudaMemcpyAsync(cam_gpu, pinned_cam, 17 * sizeof(float), cudaMemcpyHostToDevice, stream));
@@ -208,6 +211,11 @@ int rfk_session::render_view(const float* pinned_cam, rfk_half* result_out, rfk_
                                      cudaMemcpyDeviceToDevice, stream));
     }
     TRY_CUDA(cudaMemcpyAsync(result_out, rtok, (size_t)nP * dim * sizeof(rfk_half), cudaMemcpyDeviceToDevice, stream));
+    if (dpt) {
+        // image head over this frame's taps, then ELU(1e-3) -> fp32 -> 10^x - 1 in one kernel (render_session.cu:239-253)
+        TRY(rfk_dpt_forward(dpt, taps_out, nullptr, s));
+        TRY(rfk_post_elu_pow10(rfk_dpt_output(dpt), image_out, (long long)dptw.out_dim * res * res, 1e-3f, s));
+    }
     return RFK_OK;
 }
 
@@ -235,6 +243,7 @@ extern "C" int rfk_session_create(const rfk_model* model, int n_tris, int img_re
     if (img_res % model->patch_size || (img_res / model->patch_size) % model->window_size) return RFK_EINVAL;
     rfk_session* d = new rfk_session();
     d->m = *model;
+    if (model->dpt) { d->dptw = *model->dpt; d->m.dpt = &d->dptw; }
     d->N = n_tris; d->res = img_res; d->flags = flags;
     d->Se = model->num_register_tokens + n_tris;
     d->Se_pad = (d->Se + 7) & ~7;
@@ -285,6 +294,10 @@ extern "C" int rfk_session_create(const rfk_model* model, int n_tris, int img_re
     for (int k = 0; k < kSlots; ++k)
         for (int j = 0; j < 4; ++j) ALLOC(dft[k][j], (size_t)nP * dim);
     for (int k = 0; k < kSlots; ++k) ALLOC(result[k], (size_t)nP * dim);
+    if (model->dpt) {
+        for (int k = 0; k < kSlots; ++k) ALLOC(image[k], (size_t)d->dptw.out_dim * img_res * img_res);
+        if ((rc = rfk_dpt_create(d->ctx, &d->dptw, 1, dim, d->pH, d->pW, model->patch_size, &d->dpt))) return fail(rc);
+    }
 #undef ALLOC
     const float id[16] = {1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1};
     if (cudaMemcpy(d->id_c2w, id, sizeof(id), cudaMemcpyHostToDevice) != cudaSuccess) return fail((int)cudaGetLastError());
@@ -311,6 +324,7 @@ extern "C" int rfk_session_destroy(rfk_session* d) {
     if (d->ev_mark0) cudaEventDestroy(d->ev_mark0);
     if (d->ev_mark1) cudaEventDestroy(d->ev_mark1);
     for (void* p : d->owned) cudaFree(p);
+    rfk_dpt_destroy(d->dpt);
     if (d->stream) cudaStreamDestroy(d->stream);
     if (d->copy_stream) cudaStreamDestroy(d->copy_stream);
     if (d->side_stream) cudaStreamDestroy(d->side_stream);
@@ -446,13 +460,13 @@ extern "C" int rfk_session_finalize(rfk_session* d) {
     // warm-up view (also lets cuBLAS pick and load its kernels before capture)
     float cam[17] = {1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 3, 0, 0, 0, 1, 0.7f};
     for (int k = 0; k < kSlots; ++k) memcpy(d->pin_cam[k], cam, sizeof(cam));
-    TRY(d->render_view(d->pin_cam[0], d->result[0], d->dft[0]));
+    TRY(d->render_view(d->pin_cam[0], d->result[0], d->dft[0], d->image[0]));
     TRY_CUDA(cudaStreamSynchronize(d->stream));
     if (!(d->flags & RFK_SESSION_NO_GRAPH)) {
         for (int k = 0; k < kSlots; ++k) {
             const unsigned long long n0 = rfk_launch_count();
             TRY_CUDA(cudaStreamBeginCapture(d->stream, cudaStreamCaptureModeThreadLocal));
-            int rc = d->render_view(d->pin_cam[k], d->result[k], d->dft[k]);
+            int rc = d->render_view(d->pin_cam[k], d->result[k], d->dft[k], d->image[k]);
             cudaError_t e = cudaStreamEndCapture(d->stream, &d->graph[k]);
             if (rc != RFK_OK) return rc;
             TRY_CUDA(e);
@@ -464,7 +478,7 @@ extern "C" int rfk_session_finalize(rfk_session* d) {
         }
     } else {
         const unsigned long long n0 = rfk_launch_count();
-        TRY(d->render_view(d->pin_cam[0], d->result[0], d->dft[0]));
+        TRY(d->render_view(d->pin_cam[0], d->result[0], d->dft[0], d->image[0]));
         d->kernels_per_view = (int)(rfk_launch_count() - n0);
         TRY_CUDA(cudaStreamSynchronize(d->stream));
     }
@@ -488,7 +502,7 @@ extern "C" int rfk_session_render_frame(rfk_session* d, const float* h_c2w, floa
     d->pin_cam[k][16] = fov_rad;
     TRY_CUDA(cudaEventRecord(d->ev_start[k], d->stream));
     if (d->exec[k]) TRY_CUDA(cudaGraphLaunch(d->exec[k], d->stream));
-    else TRY(d->render_view(d->pin_cam[k], d->result[k], d->dft[k]));
+    else TRY(d->render_view(d->pin_cam[k], d->result[k], d->dft[k], d->image[k]));
     TRY_CUDA(cudaEventRecord(d->ev_done[k], d->stream));
     d->frames++;
     return RFK_OK;
@@ -514,6 +528,25 @@ extern "C" int rfk_session_feature_taps(rfk_session* d, const rfk_half** taps) {
     if (!d || !taps || d->frames == 0) return RFK_EINVAL;
     const int k = (int)((d->frames - 1) % kSlots);
     for (int j = 0; j < 4; ++j) taps[j] = d->dft[k][j];
+    return RFK_OK;
+}
+
+extern "C" int rfk_session_image(rfk_session* d, const float** image, int* channels, int* img_res) {
+    if (!d || !d->dpt || d->frames == 0) return RFK_EINVAL;
+    if (image) *image = d->image[(d->frames - 1) % kSlots];
+    if (channels) *channels = d->dptw.out_dim;
+    if (img_res) *img_res = d->res;
+    return RFK_OK;
+}
+
+extern "C" int rfk_session_download_image(rfk_session* d, float* h_out, size_t bytes) {
+    if (!d || !d->dpt || !h_out || d->frames == 0) return RFK_EINVAL;
+    const size_t need = (size_t)d->dptw.out_dim * d->res * d->res * sizeof(float);
+    if (bytes < need) return RFK_EINVAL;
+    const int k = (int)((d->frames - 1) % kSlots);
+    TRY_CUDA(cudaStreamWaitEvent(d->copy_stream, d->ev_done[k], 0));
+    TRY_CUDA(cudaMemcpyAsync(h_out, d->image[k], need, cudaMemcpyDeviceToHost, d->copy_stream));
+    TRY_CUDA(cudaStreamSynchronize(d->copy_stream));
     return RFK_OK;
 }
 

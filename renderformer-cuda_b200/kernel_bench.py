@@ -375,10 +375,38 @@ def _main():
     ap.add_argument("--peak", type=float, default=6455.6, help="HBM GB/s used for the fraction column")
     ap.add_argument("--softmax-rows", type=int, default=SOFTMAX_ROWS)
     ap.add_argument("--gemm", action="store_true", help="print the tcgen05-vs-library GEMM table instead")
+    ap.add_argument("--profile", choices=["attention", "gemm"],
+                    help="a few plain launches of the fused cross-attention (16 x 4096 queries x 5665 keys) or of the "
+                         "decoder layer's projections through rfk_gemm_f16, for a profiler capture")
     a = ap.parse_args()
     if a.gemm:
         for row in gemm_table(a.iters):
             print(json.dumps(row))
+        return
+    if a.profile:
+        from . import ops
+        H16 = torch.float16
+        if a.profile == "attention":
+            Se = 5665; Sp = (Se + 7) & ~7
+            q, k, v = _r((1, HEADS, NP, HD), H16), _r((1, HEADS, Sp, HD), H16), _r((1, HEADS, Sp, HD), H16)
+            o = torch.empty(1, NP, HEADS * HD, device="cuda", dtype=H16)
+            for _ in range(a.iters):
+                ops.flash_attention(q, k, v, o, 1, HEADS, NP, Sp, Se, HD, o_bshd=True)
+            torch.cuda.synchronize()
+            print(json.dumps({"kernel": "flash_attention 16x4096x5665 d64", "launched": a.iters, "error_word": ops.flash_attention_error()}))
+        else:
+            M, dim, ffn = NP, D, 4096
+            x, xh = _r((M, dim), H16), _r((M, ffn), H16)
+            w_q, w_in, w1, w3, w2 = (_r(s_, H16, 0.03) for s_ in ((dim, dim), (3 * dim, dim), (ffn, dim), (ffn, dim), (dim, ffn)))
+            y, y3, act, res = (torch.empty(M, n, device="cuda", dtype=H16) for n in (dim, 3 * dim, ffn, dim))
+            res.normal_()
+            for _ in range(a.iters):
+                ops.gemm_f16(x, w_q, y, M, dim, dim)                       # q / out projection
+                ops.gemm_f16(x, w_in, y3, M, 3 * dim, dim)                 # swin in projection
+                ops.gemm_f16(x, w1, act, M, ffn, dim, w_up=w3)             # FFN w1 | w3 + SwiGLU
+                ops.gemm_f16(xh, w2, res, M, dim, ffn, residual=res)       # FFN w2 + residual, in place
+            torch.cuda.synchronize()
+            print(json.dumps({"kernel": "rfk_gemm_f16 x4 shapes", "launched": 4 * a.iters, "error_word": ops.gemm_error()}))
         return
     globals()["SOFTMAX_ROWS"] = a.softmax_rows
     backend = RfkBackend()

@@ -47,6 +47,23 @@ class DecLayerW(ctypes.Structure):
                 ("self_attn_norm_gamma", VP), ("self_attn", MhaW), ("ffn_norm_gamma", VP), ("ffn", FfnW)]
 
 
+class RcuW(ctypes.Structure):
+    _fields_ = [(n, VP) for n in ("conv1_w", "conv1_b", "conv2_w", "conv2_b")]
+
+
+class FfbW(ctypes.Structure):
+    _fields_ = [("rcu1", RcuW), ("rcu2", RcuW), ("out_conv_w", VP), ("out_conv_b", VP), ("has_resconv1", ctypes.c_int)]
+
+
+class DptW(ctypes.Structure):
+    """rfk_dpt_weights (include/rfk_layers.h); oracle/ref_shim_layers.cu mirrors the same layout."""
+    _fields_ = [("project_w", VP * 4), ("project_b", VP * 4), ("resize_w", VP * 4), ("resize_b", VP * 4),
+                ("layer_rn_w", VP * 4), ("refinenet", FfbW * 4),
+                ("output_conv1_w", VP), ("output_conv1_b", VP), ("output_conv2a_w", VP), ("output_conv2a_b", VP),
+                ("output_conv2b_w", VP), ("output_conv2b_b", VP),
+                ("features_dim", ctypes.c_int), ("out_dim", ctypes.c_int), ("out_channels", ctypes.c_int * 4)]
+
+
 class ModelW(ctypes.Structure):
     _fields_ = ([(n, ctypes.c_int) for n in ("dim", "num_heads", "ffn_hidden", "num_register_tokens", "enc_layers",
                                              "dec_layers", "rope_num_freqs", "patch_size", "window_size", "shift_size",
@@ -54,7 +71,7 @@ class ModelW(ctypes.Structure):
                 + [(n, VP) for n in ("tri_token", "reg_tokens", "tex_enc_w", "tex_enc_b", "tex_enc_norm", "vn_proj_w",
                                      "vn_proj_b", "vn_enc_norm", "enc_rope_freqs", "ray_map_patch_token", "ray_enc_w",
                                      "ray_enc_b", "ray_enc_norm", "vt_rope_freqs")]
-                + [("enc", EncLayerW * MAX_LAYERS), ("dec", DecLayerW * MAX_LAYERS)])
+                + [("enc", EncLayerW * MAX_LAYERS), ("dec", DecLayerW * MAX_LAYERS), ("dpt", ctypes.POINTER(DptW))])
 
 
 RFK_SESSION_PAD_KEYS_ATTEND = 1
@@ -84,7 +101,12 @@ class Model:
     RenderFormerModel (src/model/renderformer.h:12-44) with runtime dimensions."""
 
     def __init__(self, dim=1024, num_heads=16, ffn_hidden=4096, num_register_tokens=32, enc_layers=12, dec_layers=12,
-                 patch_size=8, window_size=8, shift_size=4, texture_channels=13, vn_pe_num_freqs=6, device="cuda"):
+                 patch_size=8, window_size=8, shift_size=4, texture_channels=13, vn_pe_num_freqs=6, device="cuda",
+                 with_dpt=False, dpt_features=256, dpt_out_channels=(256, 512, 1024, 1024), dpt_out_dim=3):
+        # DPT image head (src/model/config.h:38-42); without it a view ends at the decoder's token map
+        self.with_dpt, self.dpt_features, self.dpt_out_dim = with_dpt, dpt_features, dpt_out_dim
+        self.dpt_out_channels = tuple(dpt_out_channels)
+        self.dpt_c = None
         self.dim, self.num_heads, self.ffn_hidden = dim, num_heads, ffn_hidden
         self.head_dim = dim // num_heads
         # frequencies per coordinate: as many as fit, 9*nf <= head_dim/2, at most 6 (src/model/config.h:28)
@@ -135,8 +157,53 @@ class Model:
                 t[p + n] = W(dim, dim)
             t[p + "swin_in_w"] = W(3 * dim, dim)
             t[p + "w13"], t[p + "w2"] = W(2 * ffn, dim), W(dim, ffn)
+        if m.with_dpt:
+            # convolution weights scaled so that activations keep their magnitude through the head: N(0, 1/sqrt(fan_in))
+            def C(cout, cin, k):
+                return (torch.randn(cout, cin, k, k, device=m.device, generator=g) * (cin * k * k) ** -0.5).half().contiguous()
+
+            def Bv(n):
+                return (0.02 * torch.randn(n, device=m.device, generator=g)).half().contiguous()
+
+            F, oc = m.dpt_features, m.dpt_out_channels
+            for i in range(4):
+                t[f"dpt.project{i}_w"], t[f"dpt.project{i}_b"] = C(oc[i], dim, 1), Bv(oc[i])
+                t[f"dpt.layer_rn{i}_w"] = C(F, oc[i], 3)
+                for u in ("rcu1", "rcu2"):
+                    if u == "rcu1" and i == 3:
+                        continue        # the deepest fusion block has no skip input (has_resconv1 = false)
+                    for c_ in ("conv1", "conv2"):
+                        t[f"dpt.ref{i}.{u}.{c_}_w"], t[f"dpt.ref{i}.{u}.{c_}_b"] = C(F, F, 3), Bv(F)
+                t[f"dpt.ref{i}.out_w"], t[f"dpt.ref{i}.out_b"] = C(F, F, 1), Bv(F)
+            # transposed convolutions store [Cin, Cout, k, k]
+            t["dpt.resize0_w"], t["dpt.resize0_b"] = (torch.randn(oc[0], oc[0], 4, 4, device=m.device, generator=g) * oc[0] ** -0.5).half(), Bv(oc[0])
+            t["dpt.resize1_w"], t["dpt.resize1_b"] = (torch.randn(oc[1], oc[1], 2, 2, device=m.device, generator=g) * oc[1] ** -0.5).half(), Bv(oc[1])
+            t["dpt.resize3_w"], t["dpt.resize3_b"] = C(oc[3], oc[3], 3), Bv(oc[3])
+            t["dpt.out1_w"], t["dpt.out1_b"] = C(F // 2, F, 3), Bv(F // 2)
+            t["dpt.out2a_w"], t["dpt.out2a_b"] = C(32, F // 2, 3), Bv(32)
+            t["dpt.out2b_w"], t["dpt.out2b_b"] = C(m.dpt_out_dim, 32, 1), Bv(m.dpt_out_dim)
         m._fill_record()
         return m
+
+    def dpt_record(self) -> DptW:
+        t, d = self.t, DptW()
+        P = lambda k: t[k].data_ptr() if k in t else None
+        for i in range(4):
+            d.project_w[i], d.project_b[i] = P(f"dpt.project{i}_w"), P(f"dpt.project{i}_b")
+            d.resize_w[i], d.resize_b[i] = P(f"dpt.resize{i}_w"), P(f"dpt.resize{i}_b")
+            d.layer_rn_w[i] = P(f"dpt.layer_rn{i}_w")
+            f = d.refinenet[i]
+            f.has_resconv1 = int(f"dpt.ref{i}.rcu1.conv1_w" in t)
+            for u, rec in (("rcu1", f.rcu1), ("rcu2", f.rcu2)):
+                rec.conv1_w, rec.conv1_b = P(f"dpt.ref{i}.{u}.conv1_w"), P(f"dpt.ref{i}.{u}.conv1_b")
+                rec.conv2_w, rec.conv2_b = P(f"dpt.ref{i}.{u}.conv2_w"), P(f"dpt.ref{i}.{u}.conv2_b")
+            f.out_conv_w, f.out_conv_b = P(f"dpt.ref{i}.out_w"), P(f"dpt.ref{i}.out_b")
+            d.out_channels[i] = self.dpt_out_channels[i]
+        d.output_conv1_w, d.output_conv1_b = P("dpt.out1_w"), P("dpt.out1_b")
+        d.output_conv2a_w, d.output_conv2a_b = P("dpt.out2a_w"), P("dpt.out2a_b")
+        d.output_conv2b_w, d.output_conv2b_b = P("dpt.out2b_w"), P("dpt.out2b_b")
+        d.features_dim, d.out_dim = self.dpt_features, self.dpt_out_dim
+        return d
 
     def _fill_record(self):
         c, t = self.c, self.t
@@ -155,6 +222,9 @@ class Model:
             e.ffn = FfnW(t[p + "w13"].data_ptr(), t[p + "w2"].data_ptr(), t[p + "w13"].data_ptr() + half_w13)
         for i in range(self.dec_layers):
             c.dec[i] = self.decoder_record(i)
+        if self.with_dpt:
+            self.dpt_c = self.dpt_record()
+            c.dpt = ctypes.pointer(self.dpt_c)
 
     @staticmethod
     def mha_record(in_w, out_w, qn, kn) -> MhaW:
@@ -260,6 +330,14 @@ class RenderSession:
         if host is None:
             host = torch.empty(self.n_tokens, self.model.dim, dtype=torch.float16).pin_memory()
         _check("rfk_session_download", _lib().rfk_session_download(self.h, host.data_ptr(), host.numel() * 2))
+        return host
+
+    def download_image(self, host: torch.Tensor | None = None) -> torch.Tensor:
+        """The last frame's image [out_dim, img_res, img_res] fp32 (models with a DPT head), waits for the frame."""
+        m = self.model
+        if host is None:
+            host = torch.empty(m.dpt_out_dim, self.img_res, self.img_res, dtype=torch.float32).pin_memory()
+        _check("rfk_session_download_image", _lib().rfk_session_download_image(self.h, host.data_ptr(), host.numel() * 4))
         return host
 
     def download_async(self, host: torch.Tensor):

@@ -79,3 +79,43 @@ def layer_weights(model, i):
 def err_stats(a, truth):
     e = (a.double() - truth.double()).abs()
     return float(e.mean()), float(e.max())
+
+
+def dpt_forward(feats, t, pH, pW, ps, out_channels, dtype=torch.float32):
+    """fp32 evaluation of the DPT image head (rf::dpt_forward, src/layers/dpt.cu:322-461): feats = four token maps
+    [S, dim]; t = the model's weight dict ("dpt.*" entries of session.Model); returns [out_dim, pH*ps, pW*ps]."""
+    import torch.nn.functional as F
+    f = lambda k: t[k].to(dtype)
+    has = lambda k: k in t
+    up = lambda x, h, w: F.interpolate(x, size=(h, w), mode="bilinear", align_corners=True)
+    resized = []
+    for i in range(4):
+        x = feats[i].to(dtype).t().reshape(1, -1, pH, pW)                    # [1, dim, pH, pW]
+        x = F.conv2d(x, f(f"dpt.project{i}_w"), f(f"dpt.project{i}_b"))
+        if i == 0:
+            x = F.conv_transpose2d(x, f("dpt.resize0_w"), f("dpt.resize0_b"), stride=4)
+        elif i == 1:
+            x = F.conv_transpose2d(x, f("dpt.resize1_w"), f("dpt.resize1_b"), stride=2)
+        elif i == 3:
+            x = F.conv2d(x, f("dpt.resize3_w"), f("dpt.resize3_b"), stride=2, padding=1)
+        resized.append(x)
+    rn = [F.conv2d(resized[i], f(f"dpt.layer_rn{i}_w"), None, padding=1) for i in range(4)]
+
+    def rcu(x, p):
+        y = F.conv2d(F.silu(x), f(p + "conv1_w"), f(p + "conv1_b"), padding=1)
+        return F.conv2d(F.silu(y), f(p + "conv2_w"), f(p + "conv2_b"), padding=1) + x
+
+    def refine(i, path, lr, th, tw):
+        if has(f"dpt.ref{i}.rcu1.conv1_w"):
+            path = path + rcu(lr, f"dpt.ref{i}.rcu1.")
+        path = rcu(path, f"dpt.ref{i}.rcu2.")
+        return F.conv2d(up(path, th, tw), f(f"dpt.ref{i}.out_w"), f(f"dpt.ref{i}.out_b"))
+
+    p4 = refine(3, rn[3], None, rn[2].shape[2], rn[2].shape[3])
+    p3 = refine(2, p4, rn[2], rn[1].shape[2], rn[1].shape[3])
+    p2 = refine(1, p3, rn[1], rn[0].shape[2], rn[0].shape[3])
+    p1 = refine(0, p2, rn[0], rn[0].shape[2] * 2, rn[0].shape[3] * 2)
+    x = F.conv2d(p1, f("dpt.out1_w"), f("dpt.out1_b"), padding=1)
+    x = up(x, pH * ps, pW * ps)
+    x = F.silu(F.conv2d(x, f("dpt.out2a_w"), f("dpt.out2a_b"), padding=1))
+    return F.conv2d(x, f("dpt.out2b_w"), f("dpt.out2b_b"))[0]
