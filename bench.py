@@ -578,6 +578,9 @@ def run_views(args, rank, world, peak, peak_src):
     v64_ms = max_over_ranks((time.perf_counter() - tb) * 1e3, world)
     barrier_sync(world)
 
+    image = None
+    if not args.no_image:
+        image = image_figure(args, rank, world, ref_arm, state, base, fl, n_streams, pipe)
     parity = None
     checksum = float(host[(len(mine) - 1) % max(2 * n_streams, 2)].float().abs().mean())
     if not ref_arm and rank == 0 and not args.no_parity:
@@ -603,7 +606,8 @@ def run_views(args, rank, world, peak, peak_src):
                    "pad_keys_attend": True,
                    "l2": "per-view working set (0.43 GB of decoder weights + 0.28 GB K/V cache + activations) exceeds the 126 MB L2",
                    "impl": args.impl, "params": model.num_params(), "n_tris": N_TRIS, "img_res": IMG_RES,
-                   "parallelism": f"view-sharded dp{world}", "parity_vs_reference": parity},
+                   "parallelism": f"view-sharded dp{world}", "parity_vs_reference": parity,
+                   "with_dpt_image_head": image},
         "e2e": {"value": estat["median"], "unit": "views/s",
                 "h2d_bytes_per_step": 68, "d2h_bytes_per_step": result_bytes,
                 "clock": "host wall clock, first submit to last byte in pinned memory (both arms)",
@@ -631,6 +635,69 @@ def run_views(args, rank, world, peak, peak_src):
                                               model.head_dim)
         sched.close()
     return line
+
+
+def image_figure(args, rank, world, ref_arm, state, cam_base, fovs, n_streams, ref_pipe):
+    """The same views carried on to an image: decoder stack + DPT head (random-init weights of the v1.1 head: 256
+    features, taps of 256/512/1024/1024 channels) + ELU / 10^x - 1, the [3, 512, 512] fp32 image copied to pinned host
+    memory every view; host wall clock, 3 repetitions of K steps, median. Reported beside the decoder-only headline,
+    which both arms keep for continuity. rfk: sessions whose captured graph contains the head (no allocation);
+    reference: its view graph followed by rf::dpt_forward (allocating per call) and its post-process kernels."""
+    import torch
+    from renderformer_cuda_b200 import session as S
+    K = args.steps
+    model = S.Model.random(seed=4, with_dpt=True)          # same seed: the decoder weights are those of the headline model
+    himg = torch.empty(max(2 * n_streams, 2), 3, IMG_RES, IMG_RES, dtype=torch.float32).pin_memory()
+    if ref_arm:
+        from oracle import ref_pipeline as RP
+        head = RP.ImageHead(model, ref_pipe, IMG_RES)
+
+        def loop(k):
+            torch.cuda.synchronize()
+            t = time.perf_counter()
+            for j in range(k):
+                v = (rank + j * world) % N_CAMERAS
+                ref_pipe.render(cam_base + v * 64, fovs[v])
+                head.run()
+                head.download(himg[j % 2])
+            torch.cuda.synchronize()
+            return (time.perf_counter() - t) * 1e3
+        closer = head.close
+    else:
+        sessions = [S.RenderSession(model, N_TRIS, IMG_RES, scene_state=state, pad_keys_attend=True) for _ in range(n_streams)]
+        for s_ in sessions:
+            s_.finalize()
+
+        def loop(k):
+            torch.cuda.synchronize()
+            t = time.perf_counter()
+            for j in range(k):
+                v = (rank + j * world) % N_CAMERAS
+                s_ = sessions[j % n_streams]
+                if j >= n_streams:   # this session's previous frame first (waits for it; the other sessions keep the GPU busy)
+                    s_.download_image(himg[j % (2 * n_streams)])
+                s_.render_frame_raw(cam_base + v * 64, fovs[v])
+            for i_, s_ in enumerate(sessions[:min(k, n_streams)]):
+                s_.download_image(himg[i_])
+            torch.cuda.synchronize()
+            return (time.perf_counter() - t) * 1e3
+
+        def closer():
+            for s_ in sessions:
+                s_.close()
+    loop(args.warmup)
+    wall = []
+    for _ in range(3):
+        barrier_sync(world)
+        w = loop(K)
+        barrier_sync(world)
+        wall.append(max_over_ranks(w, world))
+    finite = bool(torch.isfinite(himg[0]).all())
+    closer()
+    st = _stats(wall, world * K)
+    return {"views_per_s": st["median"], "min": st["min"], "max": st["max"], "d2h_bytes_per_view": 3 * IMG_RES * IMG_RES * 4,
+            "image_finite": finite, "views_in_flight_per_gpu": n_streams,
+            "note": "decoder stack + DPT head + post-process per view, image to pinned host memory; wall clock"}
 
 
 def parity_vs_reference(model, sched, state, cam_base, fovs, host):
@@ -668,6 +735,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernel-table", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the one-frame comparison with the reference pipeline")
+    ap.add_argument("--no-image", action="store_true", help="skip the figure with the DPT image head")
     ap.add_argument("--reps", type=int, default=N_REPS, help="repetitions of the K-step loop per figure (median reported)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -195,7 +195,53 @@ class ViewPipeline:
         rc = self.L.ref_view_download(VP(self.h), VP(host.data_ptr()), ctypes.c_size_t(host.numel() * 2))
         assert rc == 0
 
+    def taps(self):
+        out = (VP * 4)()
+        self.L.ref_view_taps(VP(self.h), out)
+        return [int(v) for v in out]
+
+    def stream(self) -> int:
+        self.L.ref_view_stream.restype = VP
+        return int(self.L.ref_view_stream(VP(self.h)))
+
     def close(self):
         if self.h:
             self.L.ref_view_destroy(VP(self.h))
             self.h = None
+
+
+class ImageHead:
+    """The reference's DPT head and image post-process after a view (src/pipeline/render_session.cu:239-253):
+    rf::dpt_forward over the pipeline's feature taps, elu, cast to fp32, pow10_minus1, launched on the pipeline's
+    stream. rf::dpt_forward allocates and frees its intermediates per call (stream-ordered)."""
+
+    def __init__(self, model, pipe: ViewPipeline, img_res: int):
+        self.pipe, self.m, self.res = pipe, model, img_res
+        self.blas = ref.cublas_create()
+        n = model.dpt_out_dim * img_res * img_res
+        self.out16 = torch.empty(n, device="cuda", dtype=torch.float16)
+        self.out32 = torch.empty(n, device="cuda", dtype=torch.float32)
+        self.col = torch.empty(1 << 29, device="cuda", dtype=torch.float16)      # cuDNN workspace (the reference reserves 4.8 GB)
+        self.taps = pipe.taps()
+        self.ts = torch.cuda.ExternalStream(pipe.stream())
+
+    def run(self):
+        m, p = self.m, self.pipe
+        R = ref
+        st = p.stream()
+        pH = self.res // m.patch_size
+        R.call("ref_dpt_forward", R.Raw(self.blas), ctypes.byref(m.dpt_c), R.Raw(self.taps[0]), R.Raw(self.taps[1]),
+               R.Raw(self.taps[2]), R.Raw(self.taps[3]), self.out16, self.col, 1, m.dim, pH, pH, m.patch_size, lib=ref.layers(),
+               stream=st)
+        R.call("ref_elu", self.out16, self.out16, self.out16.numel(), 1e-3, stream=st)
+        with torch.cuda.stream(self.ts):
+            self.out32.copy_(self.out16)                                           # k_fp16_to_fp32_s (:251-252)
+        R.call("ref_pow10_minus1", self.out32, self.out32, self.out32.numel(), stream=st)
+
+    def download(self, host: torch.Tensor):
+        with torch.cuda.stream(self.ts):
+            host.copy_(self.out32.view_as(host), non_blocking=True)
+        self.ts.synchronize()
+
+    def close(self):
+        ref.cublas_destroy(self.blas)

@@ -359,6 +359,12 @@ float ref_view_wait(void* p) {
 }
 // device pointer of the final token map [nP, dim]
 const void* ref_view_result(void* p) { return ((RefViewPipeline*)p)->rtok; }
+// device pointers of the four decoder feature taps [nP, dim] (src/pipeline/render_session.cu:235-238)
+void ref_view_taps(void* p, const void** out4) {
+    auto* d = (RefViewPipeline*)p;
+    for (int j = 0; j < 4; ++j) out4[j] = d->dft[j];
+}
+cudaStream_t ref_view_stream(void* p) { return ((RefViewPipeline*)p)->stream; }
 int ref_view_download(void* p, void* h_out, size_t bytes) {
     auto* d = (RefViewPipeline*)p;
     return (int)cudaMemcpyAsync(h_out, d->rtok, bytes, cudaMemcpyDeviceToHost, d->stream) |
