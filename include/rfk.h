@@ -154,13 +154,17 @@ int rfk_rope_one_oop(const rfk_half* src, rfk_half* dst,
  * tables, so that one launch serves tensors that are not densely packed: the cached keys
  * of several decoder layers, [layer][K|V][heads][rows][head_dim], are rotated by one
  * shared table (table_batch_stride = 0) with batch = layers and src_batch_stride = two
- * cache slabs. Replaces one cudaMemcpyAsync + apply_rope_one pair per decoder layer —
+ * cache slabs. col_scale (may be NULL): [batch][num_heads * head_dim] floats with batch stride
+ * col_scale_batch_stride; the rotated value is multiplied by col_scale[b][h * head_dim + d] before its
+ * one rounding to fp16 (the query's RMSNorm weight folded into the keys, see rfk_flash_attention_rowscale;
+ * head_dim % 16 == 0 required then). Replaces one cudaMemcpyAsync + apply_rope_one pair per decoder layer —
  * src/layers/attention.cu:355-361. */
 int rfk_rope_one_oop_strided(const rfk_half* src, rfk_half* dst,
                              const rfk_half* cos_vals, const rfk_half* sin_vals,
                              int batch, long long src_batch_stride, long long dst_batch_stride,
                              long long table_batch_stride, int num_heads, int seq_len,
                              int head_dim, int src_seq_stride, int dst_seq_stride,
+                             const float* col_scale, long long col_scale_batch_stride,
                              rfk_stream_t stream);
 
 /* Fused projection epilogue: for each of the n_parts (1..3) column blocks of a
@@ -260,6 +264,17 @@ int rfk_flash_attention(const rfk_half* Q, const rfk_half* K, const rfk_half* V,
                         int B, int H, int Sq, int Sk, int n_keys, int D, int o_bshd, float scale,
                         rfk_stream_t stream);
 
+/* rfk_flash_attention for queries that come un-normalised out of rfk_gemm_f16_heads: q_row_ss [B*Sq][ss_tiles]
+ * holds the partial sums of squares of each token's whole projection row (all heads); the kernel multiplies a
+ * row's scores by rsqrt(sum / norm_dim + eps), which is what normalising the query first would do up to rounding.
+ * The norm's per-element weight has no per-row form: the caller folds it into the keys (col_scale of
+ * rfk_rope_one_oop_strided). tcgen05 kernel only (D = 64): RFK_EUNSUPPORTED otherwise, and callers normalise with
+ * rfk_qkv_norm_rope_transpose instead.
+ * replaces rmsnorm(Q) -> transpose -> sdpa — src/layers/attention.cu:341-349,364-366 */
+int rfk_flash_attention_rowscale(const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,
+                                 const float* q_row_ss, int ss_tiles, int norm_dim, float eps, int B, int H,
+                                 int Sq, int Sk, int n_keys, int D, int o_bshd, float scale, rfk_stream_t stream);
+
 /* Which kernel serves rfk_flash_attention at D = 64: 0 automatic (the tcgen05 / tensor-memory
  * kernel; the mma.sync kernel only if the driver cannot encode tensor maps), 1 the mma.sync kernel,
  * 2 the tcgen05 kernel or RFK_EUNSUPPORTED. Process-wide; D = 128 always takes the mma.sync kernel.
@@ -272,6 +287,17 @@ int rfk_flash_attention_set_path(int path);
  * are undefined), 2 shared memory window not 1024-byte aligned. Synchronises the device.
  * No reference counterpart. */
 int rfk_flash_attention_error(int* code, int clear);
+
+/* rfk_window_attention for Q and K that come un-normalised out of rfk_gemm_f16_heads (rows in window order):
+ * q_row_ss / k_row_ss [BnW * 64][ss_tiles] partial sums of squares, gamma_q / gamma_k [num_heads * 64] the RMSNorm
+ * weights; the kernel forms half((x * rsqrt(sum / norm_dim + eps)) * gamma) - the separate norm kernel's formula and
+ * rounding - while it stages the tiles, then proceeds as rfk_window_attention.
+ * replaces rmsnorm(Q), rmsnorm(K), the transposes and the window attention core — src/layers/attention.cu:524-566 */
+int rfk_window_attention_normed(const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,
+                                const uint8_t* mask, const float* q_row_ss, const float* k_row_ss, int ss_tiles,
+                                const float* gamma_q, const float* gamma_k, int norm_dim, float eps, int BnW,
+                                int num_heads, int window_tokens, int head_dim, int nW, float scale,
+                                rfk_stream_t stream);
 
 /* ---------------------------------------------------------------- dense projections
  * C[M,N] = epilogue(A[M,K] W[N,K]^T): row-major fp16 operands with row pitches lda, ldw, ldc
@@ -295,6 +321,22 @@ int rfk_gemm_f16(const rfk_half* A, long long lda, const rfk_half* W, long long 
                  const rfk_half* W_up, const rfk_half* bias, const rfk_half* R, long long ldr,
                  rfk_half* C, long long ldc, int M, int N, int K, int epilogue,
                  rfk_stream_t stream);
+/* Projection whose output feeds an attention: C = A W^T stored head-split and the statistic of the QK-RMSNorm that
+ * follows computed on the way, so that no separate norm / head-split kernel runs. N = parts * num_heads * 64 columns
+ * (parts = 1: a query projection; 3: packed q | k | v); rows are M = groups * seq_len tokens. Output: part p at
+ * out + p * part_stride (elements), each part [groups][num_heads][seq_len][64] fp16. row_ss (may be NULL if
+ * ss_parts_mask == 0): [parts][M][num_heads * 64 / 256] floats; entry (p, row, t) = sum of squares of the fp16-rounded
+ * outputs of that row in columns [256 t, 256 t + 256) of part p, written (not accumulated, no zeroing needed, bit-
+ * reproducible) for the parts whose bit is set in ss_parts_mask; the consumer adds the entries of a row and applies
+ * rsqrt(sum / dim + eps) and the norm weight while it loads (rfk_flash_attention_rowscale, rfk_window_attention_normed).
+ * CTA-pair tcgen05 kernel only: RFK_EUNSUPPORTED (nothing launched) unless num_heads % 4 == 0, seq_len % 32 == 0,
+ * M % seq_len == 0 and the alignment rules of rfk_gemm_f16 hold; callers then run the projection and
+ * rfk_qkv_norm_rope_transpose separately.
+ * replaces linear -> (deinterleave_qkv) -> rmsnorm -> transpose_bshd_to_bhsd — src/layers/attention.cu:180-206,336-349,
+ * 511-535 — up to the point where the normalised values are formed. */
+int rfk_gemm_f16_heads(const rfk_half* A, long long lda, const rfk_half* W, long long ldw, rfk_half* out,
+                       long long part_stride, float* row_ss, int ss_parts_mask, int M, int N, int K,
+                       int seq_len, int num_heads, rfk_stream_t stream);
 /* 0 automatic (the tcgen05 kernel whenever the shape allows: on CTA pairs, tcgen05.mma.cta_group::2,
  * or on single CTAs if the device cannot co-schedule pairs), 1 never (rfk_gemm_f16 returns
  * RFK_EUNSUPPORTED, so the layer functions fall back to their cuBLAS calls: used to time both side

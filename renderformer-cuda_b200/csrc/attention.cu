@@ -285,9 +285,20 @@ static int launch_flash(const __half* Q, const __half* K, const __half* V, __hal
 // projection reads. Four warps, 16 query rows each; Q, K, V are 8 KB contiguous tiles.
 constexpr int kWinTokens = 64, kWinThreads = 128;
 
+// NORMED: Q and K arrive un-normalised (straight from the projection) together with the partial sums of squares of
+// their rows (rfk_gemm_f16_heads); the QK-RMSNorm - half((x * rsqrt(mean x^2 + eps)) * gamma), the formula and the
+// rounding of the separate kernel - is applied while the tiles are staged into shared memory.
+struct WinNorm {
+    const float* q_ss; const float* k_ss;      // [rows][tiles] partial sums of squares (rows in window order)
+    const float* gamma_q; const float* gamma_k;  // [heads * 64]
+    int tiles; float inv_dim, eps;
+};
+
+template <bool NORMED>
 __global__ void __launch_bounds__(kWinThreads, 8)  // 8 CTAs per SM: the 1024 CTAs of a decoder layer are one wave
 window_attention_kernel(const __half* __restrict__ Q, const __half* __restrict__ K, const __half* __restrict__ V,
-                        __half* __restrict__ O, const uint8_t* __restrict__ mask, int heads, int nW, float scale_log2e) {
+                        __half* __restrict__ O, const uint8_t* __restrict__ mask, int heads, int nW, float scale_log2e,
+                        const WinNorm nrm) {
     constexpr int HD = 64;
     __shared__ __align__(128) __half sQ[kWinTokens * HD];
     __shared__ __align__(128) __half sK[kWinTokens * HD];
@@ -304,9 +315,30 @@ window_attention_kernel(const __half* __restrict__ Q, const __half* __restrict__
     const __half* Vh = V + bh * (kWinTokens * HD);
     for (int i = tid; i < kWinTokens * 8; i += kWinThreads) {
         const int r = i >> 3, c = i & 7;
-        cp_async16(tile_ptr<HD>(sQ, r, c), Qh + r * HD + c * 8, 16);
-        cp_async16(tile_ptr<HD>(sK, r, c), Kh + r * HD + c * 8, 16);
+        if (!NORMED) {
+            cp_async16(tile_ptr<HD>(sQ, r, c), Qh + r * HD + c * 8, 16);
+            cp_async16(tile_ptr<HD>(sK, r, c), Kh + r * HD + c * 8, 16);
+        }
         cp_async16(tile_ptr<HD>(sV, r, c), Vh + r * HD + c * 8, 16);
+    }
+    if (NORMED) {
+        for (int i = tid; i < kWinTokens * 8; i += kWinThreads) {
+            const int r = i >> 3, c = i & 7;
+            const long long row = (long long)bw * kWinTokens + r;   // token row in window order
+#pragma unroll
+            for (int which = 0; which < 2; ++which) {
+                const float* ssp = (which ? nrm.k_ss : nrm.q_ss) + row * nrm.tiles;
+                float ss = 0.0f;
+                for (int t = 0; t < nrm.tiles; ++t) ss += __ldg(ssp + t);
+                const float rinv = rsqrtf(ss * nrm.inv_dim + nrm.eps);
+                float x[8], gm[8];
+                unpack8(ldg_half8((which ? Kh : Qh) + r * HD + c * 8), x);
+                ldg_float8((which ? nrm.gamma_k : nrm.gamma_q) + h * HD + c * 8, gm);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] = (x[e] * rinv) * gm[e];
+                *reinterpret_cast<Half8*>(tile_ptr<HD>(which ? sK : sQ, r, c)) = pack8(x);
+            }
+        }
     }
     if (mask) {
         const uint8_t* mw = mask + (long long)(bw % nW) * (kWinTokens * kWinTokens);
@@ -416,7 +448,8 @@ window_attention_kernel(const __half* __restrict__ Q, const __half* __restrict__
 // attention_tc.cu
 extern std::atomic<int> g_attn_path;
 int launch_attention_tc(const __half* Q, const __half* K, const __half* V, __half* O, int B, int H, int Sq, int Sk,
-                        int n_keys, int o_bshd, float scale, cudaStream_t st);
+                        int n_keys, int o_bshd, float scale, cudaStream_t st, const float* row_ss, int ss_tiles,
+                        int norm_dim, float norm_eps);
 
 }  // namespace rfk
 
@@ -435,7 +468,7 @@ extern "C" int rfk_flash_attention(const rfk_half* Q, const rfk_half* K, const r
     const int path = g_attn_path.load(std::memory_order_relaxed);
     if (D == 64 && path != 1) {  // tcgen05 kernel; in automatic mode the mma.sync kernel takes over if it cannot run
         const int rc = launch_attention_tc((const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, B, H, Sq, Sk,
-                                           n_keys, o_bshd, scale, st);
+                                           n_keys, o_bshd, scale, st, nullptr, 0, 0, 0.0f);
         if (rc != RFK_EUNSUPPORTED || path == 2) return rc;
     }
     if (D == 64)
@@ -445,6 +478,19 @@ extern "C" int rfk_flash_attention(const rfk_half* Q, const rfk_half* K, const r
         return launch_flash<128>((const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, B, H, Sq, Sk, n_keys, kvs,
                                  o_bshd, scale, st);
     return RFK_EUNSUPPORTED;
+}
+
+extern "C" int rfk_flash_attention_rowscale(const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,
+                                            const float* q_row_ss, int ss_tiles, int norm_dim, float eps, int B, int H,
+                                            int Sq, int Sk, int n_keys, int D, int o_bshd, float scale, rfk_stream_t stream) {
+    if (!Q || !K || !V || !O || !q_row_ss || ss_tiles <= 0 || norm_dim <= 0 || B < 0 || H <= 0 || Sq < 0 || Sk <= 0 ||
+        n_keys <= 0 || n_keys > Sk || !(scale > 0.0f))
+        return RFK_EINVAL;
+    if (B == 0 || Sq == 0) return RFK_OK;
+    if (D != 64 || (long long)B * H > 65535 || g_attn_path.load(std::memory_order_relaxed) == 1) return RFK_EUNSUPPORTED;
+    if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O)) return RFK_EUNSUPPORTED;
+    return launch_attention_tc((const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, B, H, Sq, Sk, n_keys, o_bshd,
+                               scale, as_stream(stream), q_row_ss, ss_tiles, norm_dim, eps);
 }
 
 extern "C" int rfk_window_attention(const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,
@@ -457,8 +503,30 @@ extern "C" int rfk_window_attention(const rfk_half* Q, const rfk_half* K, const 
     if (mask && !aligned16(mask)) return RFK_EUNSUPPORTED;
     const long long ctas = (long long)BnW * num_heads;
     if (ctas > 0x7fffffffLL) return RFK_EUNSUPPORTED;
-    launch_pdl(window_attention_kernel, dim3((unsigned)ctas), dim3(kWinThreads), 0, as_stream(stream),
+    launch_pdl(window_attention_kernel<false>, dim3((unsigned)ctas), dim3(kWinThreads), 0, as_stream(stream),
                (const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, mask, num_heads, nW,
-               scale * 1.4426950408889634f);
+               scale * 1.4426950408889634f, WinNorm{});
+    return launch_status();
+}
+
+extern "C" int rfk_window_attention_normed(const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,
+                                           const uint8_t* mask, const float* q_row_ss, const float* k_row_ss, int ss_tiles,
+                                           const float* gamma_q, const float* gamma_k, int norm_dim, float eps, int BnW,
+                                           int num_heads, int window_tokens, int head_dim, int nW, float scale,
+                                           rfk_stream_t stream) {
+    if (!Q || !K || !V || !O || !q_row_ss || !k_row_ss || !gamma_q || !gamma_k || BnW < 0 || num_heads <= 0 || nW <= 0 ||
+        ss_tiles <= 0 || norm_dim <= 0)
+        return RFK_EINVAL;
+    if (window_tokens != kWinTokens || head_dim != 64) return RFK_EUNSUPPORTED;
+    if (BnW == 0) return RFK_OK;
+    if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O) || !aligned16(gamma_q) || !aligned16(gamma_k))
+        return RFK_EUNSUPPORTED;
+    if (mask && !aligned16(mask)) return RFK_EUNSUPPORTED;
+    const long long ctas = (long long)BnW * num_heads;
+    if (ctas > 0x7fffffffLL) return RFK_EUNSUPPORTED;
+    const WinNorm nrm{q_row_ss, k_row_ss, gamma_q, gamma_k, ss_tiles, 1.0f / (float)norm_dim, eps};
+    launch_pdl(window_attention_kernel<true>, dim3((unsigned)ctas), dim3(kWinThreads), 0, as_stream(stream),
+               (const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, mask, num_heads, nW,
+               scale * 1.4426950408889634f, nrm);
     return launch_status();
 }

@@ -144,7 +144,8 @@ __device__ __forceinline__ void exp_half(uint32_t (&v)[32], uint32_t* pk /* may 
 __global__ void __launch_bounds__(kThreads, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, __half* __restrict__ O, int H, int Sq, int n_keys,
-                    int o_bshd, float scale_log2e) {
+                    int o_bshd, float scale_log2e_all, const float* __restrict__ row_ss, int ss_tiles, float inv_norm_dim,
+                    float norm_eps) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const uint32_t base = tc::smem_addr(smem_raw);
     if (base & 1023u) {  // uniform over the CTA, nothing allocated yet
@@ -278,6 +279,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;  // a warp reaches lanes [32 * (warp % 4), +32)
         const uint32_t tmem = tmem_cta + blk * 256, tmem_O = tmem + kSBufs * 64;
         const uint32_t tO = tmem_O + lane_off;
+        // Queries that arrive un-normalised (rfk_gemm_f16_heads) bring the partial sums of squares of their rows: the
+        // RMSNorm's 1 / rms is a per-row factor of the scores, i.e. of this thread's exponent scale (the norm's weight
+        // is folded into the keys by the caller). The row statistic spans all heads of the token.
+        float scale_log2e = scale_log2e_all;
+        if (row_ss) {
+            const int q = min(q0 + blk * BM + r, Sq - 1);
+            const float* sp = row_ss + ((size_t)(bh / H) * Sq + q) * ss_tiles;
+            float ss = 0.0f;
+            for (int t = 0; t < ss_tiles; ++t) ss += __ldg(sp + t);
+            scale_log2e *= rsqrtf(ss * inv_norm_dim + norm_eps);
+        }
         float m_run = -INFINITY, l_run = 0.0f;
         uint32_t va[32], vb[32];
         bool ok = true;
@@ -437,7 +449,8 @@ bool make_map(CUtensorMap* m, const void* base, long long n_heads, long long row
 
 // Launches the tcgen05 kernel; the caller has validated pointers, alignment and sizes (D == 64).
 int launch_attention_tc(const __half* Q, const __half* K, const __half* V, __half* O, int B, int H, int Sq, int Sk,
-                        int n_keys, int o_bshd, float scale, cudaStream_t st) {
+                        int n_keys, int o_bshd, float scale, cudaStream_t st, const float* row_ss, int ss_tiles,
+                        int norm_dim, float norm_eps) {
     // per-device "kernel attributes set" marks; setting them twice from racing threads is harmless
     static std::atomic<bool> configured[64];
     int dev = 0;
@@ -459,7 +472,7 @@ int launch_attention_tc(const __half* Q, const __half* K, const __half* V, __hal
         return RFK_EUNSUPPORTED;
     dim3 grid(ceil_div(Sq, tcattn::kBlocks * tcattn::BM), B * H);
     launch_pdl(tcattn::attention_tc_kernel, grid, dim3(tcattn::kThreads), tcattn::kSmemBytes, st, mq, mk, mv, O, H, Sq, n_keys,
-               o_bshd, scale * 1.4426950408889634f);
+               o_bshd, scale * 1.4426950408889634f, row_ss, ss_tiles, norm_dim > 0 ? 1.0f / (float)norm_dim : 0.0f, norm_eps);
     return launch_status();
 }
 

@@ -64,12 +64,20 @@ __device__ unsigned long long g_timeline[16];
 #define RFK_STAMP(i) do { } while (0)
 #endif
 
+// Fourth epilogue of the pair kernel (own entry point, rfk_gemm_f16_heads): the output is stored head-split,
+// [part][group][head][seq][64], through a rank-5 tile store, and every row's sum of squares over each 256-column
+// tile (of the fp16-rounded values) is written to row_ss[part][row][tile] for the parts selected by ss_mask: the
+// statistic of the QK-RMSNorm that follows the projection, so that the consumer can normalise while it loads.
+constexpr int kEpiHeads = 3;
+
 struct Params {
     __half* C; long long ldc;
     const __half* R; long long ldr;     // residual (EPI_RESIDUAL), may alias C
     const __half* bias;                 // [N] or null
     int M, N, K;                        // N = output columns
     int tiles_m, tiles_n;
+    float* row_ss;                      // kEpiHeads: [parts][M][tiles per part] partial sums of squares, or null
+    int seq, heads, ss_mask;            // kEpiHeads: rows per group, heads per part (64 wide), parts that get row_ss
 };
 
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
@@ -363,6 +371,10 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src_smem
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
                  ::"l"(tmap), "r"(src_smem), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void tma_store_5d(const void* tmap, uint32_t src_smem, int c0, int c1, int c2, int c3, int c4) {
+    asm volatile("cp.async.bulk.tensor.5d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];"
+                 ::"l"(tmap), "r"(src_smem), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // waits until at most N of this thread's committed store groups still READ their shared-memory source
 template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
@@ -439,6 +451,7 @@ __device__ __forceinline__ bool epilogue_tile_staged(const Params& p, const CUte
     constexpr int kUnits = Cfg<EPI>::kUnits;
     const uint32_t stage_base = tc::smem_addr(stage_ptr);
     uint32_t v[32];
+    float ss = 0.0f;   // kEpiHeads: this row's sum of squares over the tile
 #pragma unroll 1
     for (int u = 0; u < kUnits; ++u) {
         const int b = (EPI == RFK_GEMM_EPI_RESIDUAL) ? u : (u & 1);
@@ -500,6 +513,14 @@ __device__ __forceinline__ bool epilogue_tile_staged(const Params& p, const CUte
                 } else {
 #pragma unroll
                     for (int i = 0; i < 16; ++i) o[i] = pack_half2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                    if (EPI == kEpiHeads) {   // the norm that follows sees the stored fp16 values
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float2 r2 = unpack_half2(o[i]);
+                            ss = fmaf(r2.x, r2.x, ss);
+                            ss = fmaf(r2.y, r2.y, ss);
+                        }
+                    }
                 }
             }
 #pragma unroll
@@ -509,9 +530,19 @@ __device__ __forceinline__ bool epilogue_tile_staged(const Params& p, const CUte
         tc::fence_proxy_async();                            // the copy engine reads what the threads just wrote
         __syncwarp();
         if (lane == 0) {
-            tma_store_2d(map_c, stage_base + b * kUnitBytes, n0 + u * kUnitCols, row0);   // rows >= M, columns >= N are clipped
+            if (EPI == kEpiHeads) {
+                const int g = (n0 + u * kUnitCols) / kUnitCols;   // 64-wide head index over all parts
+                tma_store_5d(map_c, stage_base + b * kUnitBytes, 0, row0 % p.seq, g % p.heads, row0 / p.seq, g / p.heads);
+            } else {
+                tma_store_2d(map_c, stage_base + b * kUnitBytes, n0 + u * kUnitCols, row0);   // rows >= M, columns >= N are clipped
+            }
             bulk_commit();
         }
+    }
+    if (EPI == kEpiHeads && p.row_ss) {
+        const int dim = p.heads * kUnitCols, part = n0 / dim, row = row0 + lane;
+        if (((p.ss_mask >> part) & 1) && row < p.M)
+            p.row_ss[((size_t)part * p.M + row) * (dim / 256) + (n0 % dim) / 256] = ss;
     }
     return true;
 }
@@ -748,10 +779,11 @@ std::atomic<int> g_pair_clusters[64];  // CTA pairs the device can run at once, 
 // CTA-pair kernel: clusters of two; returns RFK_EUNSUPPORTED (nothing launched) when the device cannot co-schedule pairs
 template <int EPI>
 int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mw0, const CUtensorMap& mw1, tcgemm::Params p, int dev,
-                     cudaStream_t st) {
+                     cudaStream_t st, const CUtensorMap* heads_map = nullptr) {
     // tile maps of the output (stores) and of the residual (loads): boxes of 32 rows x 64 columns, one per epilogue warp
     CUtensorMap mc, mr;
-    if (!make_map_2d(&mc, p.C, p.M, p.N, p.ldc, 32) ||
+    if (heads_map) mc = *heads_map;
+    if ((!heads_map && !make_map_2d(&mc, p.C, p.M, p.N, p.ldc, 32)) ||
         !make_map_2d(&mr, EPI == RFK_GEMM_EPI_RESIDUAL ? (const void*)p.R : (const void*)p.C, p.M, p.N,
                      EPI == RFK_GEMM_EPI_RESIDUAL ? p.ldr : p.ldc, 32))
         return RFK_EUNSUPPORTED;
@@ -790,6 +822,19 @@ int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mw0, const CUtens
     cudaError_t e = cudaLaunchKernelEx(&cfg, tcgemm::pair::gemm_tc_pair_kernel<EPI>, ma, mw0, mw1, mc, mr, p);
     if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
     return launch_status();
+}
+
+// rank-5 map of a head-split output: [part][group][head][seq][64] halves, boxes of 32 rows x 64 columns
+bool make_map_heads(CUtensorMap* m, const void* base, int seq, int heads, long long groups, int parts, long long part_stride) {
+    EncodeTiledFn enc = tensor_map_encoder();
+    if (!enc) return false;
+    const cuuint64_t dims[5] = {64, (cuuint64_t)seq, (cuuint64_t)heads, (cuuint64_t)groups, (cuuint64_t)parts};
+    const cuuint64_t strides[4] = {128, (cuuint64_t)seq * 128, (cuuint64_t)heads * seq * 128, (cuuint64_t)part_stride * 2};
+    const cuuint32_t box[5] = {64, 32, 1, 1, 1};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // path 0 / 2: CTA pairs, the single-CTA kernel if pairs are unavailable; path 3: the single-CTA kernel
@@ -844,6 +889,38 @@ extern "C" int rfk_gemm_f16(const rfk_half* A, long long lda, const rfk_half* W,
         case RFK_GEMM_EPI_RESIDUAL: return launch_gemm<RFK_GEMM_EPI_RESIDUAL>(ma, mw0, mw1, p, dev, st);
         default: return launch_gemm<RFK_GEMM_EPI_SWIGLU>(ma, mw0, mw1, p, dev, st);
     }
+}
+
+extern "C" int rfk_gemm_f16_heads(const rfk_half* A, long long lda, const rfk_half* W, long long ldw, rfk_half* out,
+                                  long long part_stride, float* row_ss, int ss_parts_mask, int M, int N, int K, int seq_len,
+                                  int num_heads, rfk_stream_t stream) {
+    if (!A || !W || !out || M < 0 || N <= 0 || K <= 0 || seq_len <= 0 || num_heads <= 0 || lda < K || ldw < K) return RFK_EINVAL;
+    const int dim = num_heads * 64;
+    if (N % dim != 0 || (ss_parts_mask && !row_ss)) return RFK_EINVAL;
+    const int parts = N / dim;
+    if (parts > 1 && part_stride < (long long)M * dim) return RFK_EINVAL;
+    if (M == 0) return RFK_OK;
+    const int path = g_gemm_path.load(std::memory_order_relaxed);
+    if (path == 1 || path == 3) return RFK_EUNSUPPORTED;   // pair kernel only
+    // a 256-column tile must lie inside one part, a 32-row store box inside one group
+    if (dim % 256 != 0 || seq_len % 32 != 0 || M % seq_len != 0) return RFK_EUNSUPPORTED;
+    if ((lda | ldw | part_stride) % 8 != 0 || K % 8 != 0 || !aligned16(A) || !aligned16(W) || !aligned16(out) ||
+        (row_ss && !aligned16(row_ss)))
+        return RFK_EUNSUPPORTED;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return RFK_EUNSUPPORTED;
+    CUtensorMap ma, mw, mh;
+    if (!make_map_2d(&ma, A, M, K, lda) || !make_map_2d(&mw, W, N, K, ldw) ||
+        !make_map_heads(&mh, out, seq_len, num_heads, M / seq_len, parts, parts > 1 ? part_stride : (long long)M * dim))
+        return RFK_EUNSUPPORTED;
+    tcgemm::Params p{};
+    p.C = (__half*)out; p.ldc = N; p.M = M; p.N = N; p.K = K;
+    p.tiles_m = (M + tcgemm::BM - 1) / tcgemm::BM;
+    p.tiles_n = N / 256;
+    p.row_ss = row_ss; p.seq = seq_len; p.heads = num_heads; p.ss_mask = ss_parts_mask;
+    return launch_gemm_pair<tcgemm::kEpiHeads>(ma, mw, mw, p, dev, as_stream(stream), &mh);
 }
 
 extern "C" int rfk_gemm_pair_clusters(void) {

@@ -263,9 +263,12 @@ extern "C" int rfk_precompute_cross_kv(rfk_ctx* ctx, const rfk_cross_attn_weight
 
 // `residual` (may be `out`, may be NULL): out = residual + attention output, the add being the epilogue of the
 // output projection.
+// norm_ss (may be NULL): scratch of B*Sq*(dim/256) floats for the row statistics of the deferred Q-RMSNorm;
+// k_prescaled: K_cached is already rotated AND multiplied by the query's norm weight (the session does both for all
+// layers at once).
 static int cross_attention_impl(rfk_ctx* ctx, const rfk_cross_attn_weights* w,
                                           const rfk_half* q_in, rfk_half* out, const rfk_half* residual,
-                                          rfk_half* proj_buf,
+                                          rfk_half* proj_buf, float* norm_ss, int k_prescaled,
                                           float* score_buf, const rfk_half* K_cached,
                                           const rfk_half* V_cached, int B, int Sq, int Sk, int n_keys,
                                           int q_dim, int dim, int num_heads,
@@ -278,18 +281,46 @@ static int cross_attention_impl(rfk_ctx* ctx, const rfk_cross_attn_weights* w,
     rfk_half* Q = proj_buf;                          // [Mq, dim] projection, later the attention output
     rfk_half* Q_bhsd = proj_buf + (size_t)Mq * dim;  // [B,H,Sq,hd]
     rfk_half* K_rot = Q_bhsd + (size_t)Mq * dim;     // [B,H,Sk,hd]
-    TRY(rfk_linear(ctx, q_in, w->q_proj_w, w->q_proj_b, Q, Mq, dim, q_dim, stream));
-    const float* g[1] = {w->q_norm_gamma};
-    rfk_half* o[1] = {Q_bhsd};
-    const int rope[1] = {q_rope_cos != nullptr};
-    TRY(project_epilogue(Q, dim, 1, g, o, rope, q_rope_cos, q_rope_sin, B, Sq, num_heads, hd, 0, K_rot, stream));
-    const rfk_half* K_use = K_cached;
-    if (k_rope_cos) {
-        TRY(rfk_rope_one_oop(K_cached, K_rot, k_rope_cos, k_rope_sin, B, num_heads, Sk, hd, Sk, Sk, 0, stream));
-        K_use = K_rot;
+    // Deferred Q-RMSNorm: the projection writes Q head-split and the rows' sums of squares, the attention kernel scales
+    // each row's scores by 1 / rms, and the norm's weight rides on the keys (multiplied in by the rotation kernel, here
+    // or by the caller). One kernel (norm + head split) and 18 MB of traffic less per layer. Needs: no query rotation
+    // (the view decoder's query tables are the identity), keys that are rotated here or arrive prescaled, head size 64.
+    const bool deferred = norm_ss && w->q_norm_gamma && !w->q_proj_b && !q_rope_cos && hd == 64 && (k_prescaled || k_rope_cos) &&
+                          (reinterpret_cast<uintptr_t>(w->q_norm_gamma) & 15u) == 0;
+    if (k_prescaled && !deferred) return RFK_EUNSUPPORTED;  // prescaled keys only make sense with the deferred norm
+    if (deferred) {
+        int rc = rfk_gemm_f16_heads(q_in, q_dim, w->q_proj_w, q_dim, Q_bhsd, 0, norm_ss, 1, Mq, dim, q_dim, Sq, num_heads, stream);
+        if (rc == RFK_OK) {
+            const rfk_half* K_use = K_cached;
+            if (!k_prescaled) {
+                rc = rfk_rope_one_oop_strided(K_cached, K_rot, k_rope_cos, k_rope_sin, B, (long long)num_heads * Sk * hd,
+                                              (long long)num_heads * Sk * hd, (long long)Sk * hd, num_heads, Sk, hd, Sk, Sk,
+                                              w->q_norm_gamma, 0, stream);
+                K_use = K_rot;
+            }
+            if (rc == RFK_OK)
+                rc = rfk_flash_attention_rowscale(Q_bhsd, K_use, V_cached, Q, norm_ss, dim / 256, dim, kEpsFp16, B, num_heads, Sq,
+                                                  Sk, n_keys, hd, 1, 1.0f / sqrtf((float)hd), stream);
+        }
+        if (rc != RFK_OK && rc != RFK_EUNSUPPORTED) return rc;
+        if (rc == RFK_EUNSUPPORTED && k_prescaled) return rc;  // prescaled keys cannot serve the separate-norm route
+        if (rc == RFK_OK) goto out_projection;
     }
-    TRY(attention_core(ctx, Q_bhsd, K_use, V_cached, Q /* [B,Sq,dim] */, score_buf, B, num_heads, Sq, Sk, n_keys,
-                       hd, 1, stream));
+    {
+        TRY(rfk_linear(ctx, q_in, w->q_proj_w, w->q_proj_b, Q, Mq, dim, q_dim, stream));
+        const float* g[1] = {w->q_norm_gamma};
+        rfk_half* o[1] = {Q_bhsd};
+        const int rope[1] = {q_rope_cos != nullptr};
+        TRY(project_epilogue(Q, dim, 1, g, o, rope, q_rope_cos, q_rope_sin, B, Sq, num_heads, hd, 0, K_rot, stream));
+        const rfk_half* K_use = K_cached;
+        if (k_rope_cos) {
+            TRY(rfk_rope_one_oop(K_cached, K_rot, k_rope_cos, k_rope_sin, B, num_heads, Sk, hd, Sk, Sk, 0, stream));
+            K_use = K_rot;
+        }
+        TRY(attention_core(ctx, Q_bhsd, K_use, V_cached, Q /* [B,Sq,dim] */, score_buf, B, num_heads, Sq, Sk, n_keys,
+                           hd, 1, stream));
+    }
+out_projection:
     if (residual && !w->out_proj_b)
         return gemm_nt_residual(ctx, (cudaStream_t)stream, Mq, q_dim, dim, (const __half*)Q, dim, (const __half*)w->out_proj_w,
                                 dim, (__half*)out, q_dim, (const __half*)residual, q_dim);
@@ -305,21 +336,36 @@ extern "C" int rfk_cross_attention_cached(rfk_ctx* ctx, const rfk_cross_attn_wei
                                           const rfk_half* q_rope_cos, const rfk_half* q_rope_sin,
                                           const rfk_half* k_rope_cos, const rfk_half* k_rope_sin,
                                           rfk_stream_t stream) {
-    return cross_attention_impl(ctx, w, q_in, out, nullptr, proj_buf, score_buf, K_cached, V_cached, B, Sq, Sk, n_keys,
-                                q_dim, dim, num_heads, q_rope_cos, q_rope_sin, k_rope_cos, k_rope_sin, stream);
+    return cross_attention_impl(ctx, w, q_in, out, nullptr, proj_buf, nullptr, 0, score_buf, K_cached, V_cached, B, Sq, Sk,
+                                n_keys, q_dim, dim, num_heads, q_rope_cos, q_rope_sin, k_rope_cos, k_rope_sin, stream);
 }
 
 // Window attention over tokens that are already in window order: window_buf [BnW * ws2, dim] in,
 // qkv_buf [BnW * ws2, dim] out (still in window order); window_buf and scratch are overwritten.
+// norm_ss (may be NULL): scratch of 2 * M * (dim / 256) floats for the row statistics of the deferred QK-RMSNorm.
 static int swin_core(rfk_ctx* ctx, const rfk_mha_weights* w, rfk_half* window_buf, rfk_half* qkv_buf,
                      float* score_buf, rfk_half* scratch, int BnW, int nW, int ws2, int dim, int num_heads,
-                     const uint8_t* win_mask, rfk_stream_t stream) {
+                     const uint8_t* win_mask, rfk_stream_t stream, float* norm_ss = nullptr) {
     cudaStream_t st = (cudaStream_t)stream;
     const int hd = dim / num_heads, M = BnW * ws2, BH = BnW * num_heads;
-    TRY(rfk_linear(ctx, window_buf, w->in_proj_w, w->in_proj_b, qkv_buf, M, 3 * dim, dim, stream));
     rfk_half* Qt = scratch;
     rfk_half* Kt = scratch + (size_t)M * dim;
     rfk_half* Vt = scratch + (size_t)2 * M * dim;
+    // Deferred QK-RMSNorm: the packed projection writes q, k, v head-split per window and the sums of squares of the q and
+    // k rows; the window attention kernel normalises the two tiles while it stages them (same formula and rounding as
+    // the separate kernel). One kernel and 50 MB of traffic less per layer.
+    if (norm_ss && ws2 == 64 && hd == 64 && w->q_norm_gamma && w->k_norm_gamma && !w->in_proj_b) {
+        const int tiles = dim / 256;
+        int rc = rfk_gemm_f16_heads(window_buf, dim, w->in_proj_w, dim, Qt, (long long)M * dim, norm_ss, 3, M, 3 * dim, dim, ws2,
+                                    num_heads, stream);
+        if (rc == RFK_OK)
+            rc = rfk_window_attention_normed(Qt, Kt, Vt, window_buf, win_mask, norm_ss, norm_ss + (size_t)M * tiles, tiles,
+                                             w->q_norm_gamma, w->k_norm_gamma, dim, kEpsFp16, BnW, num_heads, ws2, hd, nW,
+                                             1.0f / sqrtf((float)hd), stream);
+        if (rc == RFK_OK) return rfk_linear(ctx, window_buf, w->out_proj_w, w->out_proj_b, qkv_buf, M, dim, dim, stream);
+        if (rc != RFK_EUNSUPPORTED) return rc;
+    }
+    TRY(rfk_linear(ctx, window_buf, w->in_proj_w, w->in_proj_b, qkv_buf, M, 3 * dim, dim, stream));
     const float* g[3] = {w->q_norm_gamma, w->k_norm_gamma, nullptr};
     rfk_half* o[3] = {Qt, Kt, Vt};
     const int no_rope[3] = {0, 0, 0};
@@ -385,14 +431,16 @@ extern "C" int rfk_self_attention(rfk_ctx* ctx, const rfk_mha_weights* w, const 
     return rfk_linear(ctx, qkv_buf, w->out_proj_w, w->out_proj_b, out, M, dim, dim, stream);
 }
 
-extern "C" int rfk_decoder_layer_forward_cached(
+// k_prescaled: K_cached is this view's rotated keys already multiplied by the cross-attention query norm's weight
+// (what rfk_session prepares for all layers at once); 0 for keys as the public entry point receives them.
+int rfk_layers::decoder_layer_impl(
     rfk_ctx* ctx, const rfk_decoder_layer_weights* w, rfk_half* x, const rfk_half* pending_residual,
     const rfk_half** pending_out, rfk_half* temp, rfk_half* proj_buf, rfk_half* qkv_buf, rfk_half* ffn_buf,
     rfk_half* window_buf, float* cross_score_buf, float* self_score_buf, const rfk_half* K_cached,
     const rfk_half* V_cached, int B, int Sq, int Sk, int n_keys, int dim, int num_heads, int ffn_hidden,
     int patch_h, int patch_w, int window_size, int shift_size, const uint8_t* shift_mask,
     const rfk_half* q_rope_cos, const rfk_half* q_rope_sin, const rfk_half* k_rope_cos,
-    const rfk_half* k_rope_sin, rfk_stream_t stream) {
+    const rfk_half* k_rope_sin, int k_prescaled, rfk_stream_t stream) {
     if (!ctx || !w || !x || !temp || !proj_buf || !qkv_buf || !ffn_buf || !window_buf) return RFK_EINVAL;
     if (Sq != patch_h * patch_w) return RFK_EINVAL;
     const int Mq = B * Sq;
@@ -406,10 +454,15 @@ extern "C" int rfk_decoder_layer_forward_cached(
     const bool win_ok = window_size > 0 && patch_h % window_size == 0 && patch_w % window_size == 0 &&
                         num_heads > 0 && dim % num_heads == 0 && dim % 8 == 0 && dim <= 2048 && a16(x) && a16(window_buf) &&
                         a16(temp) && a16(qkv_buf) && a16(w->self_attn_norm_gamma) && a16(w->ffn_norm_gamma);
+    // Row statistics of the deferred QK-norms live in buffers that are idle while they are needed: window_buf during the
+    // cross-attention, temp during the window attention (each holds Mq*dim halves; the statistics need Mq*dim/128 floats).
+    float* cross_ss = dim % 256 == 0 ? reinterpret_cast<float*>(window_buf) : nullptr;
+    float* swin_ss = dim % 256 == 0 ? reinterpret_cast<float*>(temp) : nullptr;
     if (win_ok) {
         if (!w->cross_attn.out_proj_b) {
-            TRY(cross_attention_impl(ctx, &w->cross_attn, temp, x, x, proj_buf, cross_score_buf, K_cached, V_cached, B, Sq, Sk,
-                                     n_keys, dim, dim, num_heads, q_rope_cos, q_rope_sin, k_rope_cos, k_rope_sin, stream));
+            TRY(cross_attention_impl(ctx, &w->cross_attn, temp, x, x, proj_buf, cross_ss, k_prescaled, cross_score_buf, K_cached,
+                                     V_cached, B, Sq, Sk, n_keys, dim, dim, num_heads, q_rope_cos, q_rope_sin, k_rope_cos,
+                                     k_rope_sin, stream));
             TRY(rfk_rmsnorm_residual_f16_windows(x, nullptr, w->self_attn_norm_gamma, window_buf, B, patch_h, patch_w, dim,
                                                  window_size, shift_size, 1, kEpsFp16, stream));
         } else {
@@ -422,7 +475,7 @@ extern "C" int rfk_decoder_layer_forward_cached(
         }
         const int ws2 = window_size * window_size, nW = (patch_h / window_size) * (patch_w / window_size);
         TRY(swin_core(ctx, &w->self_attn, window_buf, qkv_buf, self_score_buf, proj_buf, B * nW, nW, ws2, dim, num_heads,
-                      (shift_mask && shift_size > 0) ? shift_mask : nullptr, stream));
+                      (shift_mask && shift_size > 0) ? shift_mask : nullptr, stream, swin_ss));
         TRY(rfk_rmsnorm_residual_f16_windows(x, qkv_buf, w->ffn_norm_gamma, temp, B, patch_h, patch_w, dim, window_size,
                                              shift_size, 2, kEpsFp16, stream));
     } else {
@@ -442,6 +495,20 @@ extern "C" int rfk_decoder_layer_forward_cached(
     TRY(ffn_core(ctx, &w->ffn, temp, x, x, qkv_buf, Mq, dim, ffn_hidden, stream));
     if (pending_out) *pending_out = nullptr;
     return RFK_OK;
+}
+
+extern "C" int rfk_decoder_layer_forward_cached(
+    rfk_ctx* ctx, const rfk_decoder_layer_weights* w, rfk_half* x, const rfk_half* pending_residual,
+    const rfk_half** pending_out, rfk_half* temp, rfk_half* proj_buf, rfk_half* qkv_buf, rfk_half* ffn_buf,
+    rfk_half* window_buf, float* cross_score_buf, float* self_score_buf, const rfk_half* K_cached,
+    const rfk_half* V_cached, int B, int Sq, int Sk, int n_keys, int dim, int num_heads, int ffn_hidden,
+    int patch_h, int patch_w, int window_size, int shift_size, const uint8_t* shift_mask,
+    const rfk_half* q_rope_cos, const rfk_half* q_rope_sin, const rfk_half* k_rope_cos,
+    const rfk_half* k_rope_sin, rfk_stream_t stream) {
+    return rfk_layers::decoder_layer_impl(ctx, w, x, pending_residual, pending_out, temp, proj_buf, qkv_buf, ffn_buf, window_buf,
+                                          cross_score_buf, self_score_buf, K_cached, V_cached, B, Sq, Sk, n_keys, dim, num_heads,
+                                          ffn_hidden, patch_h, patch_w, window_size, shift_size, shift_mask, q_rope_cos,
+                                          q_rope_sin, k_rope_cos, k_rope_sin, 0, stream);
 }
 
 extern "C" int rfk_encoder_layer_forward_mixed(

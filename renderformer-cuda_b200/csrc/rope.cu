@@ -91,7 +91,7 @@ rope_apply_kernel(const T* src0, T* dst0, const T* src1, T* dst1,
                   const __half* __restrict__ cos_vals, const __half* __restrict__ sin_vals,
                   int batch, int num_heads, int seq_len, int rows_total, int head_dim,
                   long long src_rows, long long dst_rows, long long src_bstride, long long dst_bstride,
-                  long long tab_bstride) {
+                  long long tab_bstride, const float* __restrict__ col_scale, long long scale_bstride) {
     pdl_wait();
     pdl_trigger();
     const int cpt = head_dim / 16;
@@ -129,6 +129,14 @@ rope_apply_kernel(const T* src0, T* dst0, const T* src1, T* dst1,
             load8(sp + so, lo);
             load8(sp + so + half_d, hi);
             if (rotate) rotate8(lo, hi, cl, sl, ch, sh);
+            if (col_scale) {  // per-(head, element) factor applied to the rotated value before the one rounding
+                float g0[8], g1[8];
+                const float* gs = col_scale + (size_t)b * scale_bstride + (size_t)h * head_dim + j * 8;
+                ldg_float8(gs, g0);
+                ldg_float8(gs + half_d, g1);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) { lo[i] *= g0[i]; hi[i] *= g1[i]; }
+            }
             store8(dp + dofs, lo);
             store8(dp + dofs + half_d, hi);
         }
@@ -180,7 +188,7 @@ static int launch_rope(const T* src0, T* dst0, const T* src1, T* dst1, const __h
                        const __half* sin_vals, int batch, int num_heads, int seq_len,
                        int rows_total, int head_dim, long long src_rows, long long dst_rows,
                        cudaStream_t st, long long src_bstride = -1, long long dst_bstride = -1,
-                       long long tab_bstride = -1) {
+                       long long tab_bstride = -1, const float* col_scale = nullptr, long long scale_bstride = 0) {
     // batch strides in elements; by default the tensors and the tables are densely packed
     if (src_bstride < 0) src_bstride = (long long)num_heads * src_rows * head_dim;
     if (dst_bstride < 0) dst_bstride = (long long)num_heads * dst_rows * head_dim;
@@ -194,7 +202,8 @@ static int launch_rope(const T* src0, T* dst0, const T* src1, T* dst1, const __h
     const bool vec = head_dim % 16 == 0 && aligned16(src0) && aligned16(dst0) &&
                      (NT == 1 || (aligned16(src1) && aligned16(dst1))) && aligned16(cos_vals) &&
                      aligned16(sin_vals) && src_bstride % 8 == 0 && dst_bstride % 8 == 0 &&
-                     tab_bstride % 8 == 0;
+                     tab_bstride % 8 == 0 && (!col_scale || (aligned16(col_scale) && scale_bstride % 4 == 0));
+    if (col_scale && !vec) return RFK_EUNSUPPORTED;  // the scaled form exists in the vector kernel only
     if (vec) {
         const int cpt = head_dim / 16;
         // One head per thread unless the problem is large: at the benchmark size (47 MB) the
@@ -211,7 +220,7 @@ static int launch_rope(const T* src0, T* dst0, const T* src1, T* dst1, const __h
 #define RFK_ROPE(HPV)                                                                         \
     launch_pdl(rope_apply_kernel<T, NT, HPV>, dim3(grid), dim3(128), 0, st, src0, dst0, src1, dst1, \
                cos_vals, sin_vals, batch, num_heads, seq_len, rows_total, head_dim, src_rows,        \
-               dst_rows, src_bstride, dst_bstride, tab_bstride)
+               dst_rows, src_bstride, dst_bstride, tab_bstride, col_scale, scale_bstride)
         if (hp == 4) RFK_ROPE(4);
         else if (hp == 2) RFK_ROPE(2);
         else RFK_ROPE(1);
@@ -435,14 +444,15 @@ extern "C" int rfk_rope_one_oop_strided(const rfk_half* src, rfk_half* dst, cons
                                         const rfk_half* s, int batch, long long src_batch_stride,
                                         long long dst_batch_stride, long long table_batch_stride,
                                         int num_heads, int seq_len, int head_dim, int src_seq_stride,
-                                        int dst_seq_stride, rfk_stream_t stream) {
+                                        int dst_seq_stride, const float* col_scale,
+                                        long long col_scale_batch_stride, rfk_stream_t stream) {
     if (src_seq_stride < seq_len || dst_seq_stride < seq_len) return RFK_EINVAL;
-    if (src_batch_stride < 0 || dst_batch_stride < 0 || table_batch_stride < 0) return RFK_EINVAL;
+    if (src_batch_stride < 0 || dst_batch_stride < 0 || table_batch_stride < 0 || col_scale_batch_stride < 0) return RFK_EINVAL;
     return launch_rope<__half, 1>((const __half*)src, (__half*)dst, nullptr, nullptr,
                                   (const __half*)c, (const __half*)s, batch, num_heads, seq_len,
                                   seq_len, head_dim, src_seq_stride, dst_seq_stride,
                                   as_stream(stream), src_batch_stride, dst_batch_stride,
-                                  table_batch_stride);
+                                  table_batch_stride, (const float*)col_scale, col_scale_batch_stride);
 }
 
 extern "C" int rfk_qkv_norm_rope_transpose(const rfk_half* x, long long row_stride, int n_parts,

@@ -121,6 +121,8 @@ struct rfk_session {
     rfk_half *temp = nullptr, *proj = nullptr, *qkv = nullptr, *ffn = nullptr, *win = nullptr;
     float *score = nullptr, *self_score = nullptr;  // only allocated when a materialised attention path can be taken
     rfk_half* k_rot = nullptr;  // [dec_layers][heads][Se_pad][hd]: this view's rotated keys of every layer
+    float* q_gamma_all = nullptr;  // [dec_layers][dim]: the cross-attention query norm weights, contiguous
+    bool prescale = false;         // the rotation multiplies the keys by those weights (deferred Q-RMSNorm, see layers.cu)
     cudaEvent_t ev_fork = nullptr, ev_rot[RFK_MAX_LAYERS]{};
     uint8_t* shift_mask = nullptr;
     rfk_half* dft[kSlots][4] = {};  // the four decoder feature taps of each frame slot
@@ -175,12 +177,13 @@ int rfk_session::render_view(const float* pinned_cam, rfk_half* result_out, rfk_
     TRY_CUDA(cudaStreamWaitEvent(side_stream, ev_fork, 0));
     {
         const long long slab = (long long)(L.kv_layer_bytes / sizeof(__half));
+        const float* g0 = prescale ? q_gamma_all : nullptr;
         TRY(rfk_rope_one_oop_strided(kvK(0), kRot(0), k_cos, k_sin, 1, 2 * slab, slab, 0, m.num_heads, Se_pad, hd, Se_pad,
-                                     Se_pad, (rfk_stream_t)side_stream));
+                                     Se_pad, g0, 0, (rfk_stream_t)side_stream));
         TRY_CUDA(cudaEventRecord(ev_rot[0], side_stream));
         if (m.dec_layers > 1) {
             TRY(rfk_rope_one_oop_strided(kvK(1), kRot(1), k_cos, k_sin, m.dec_layers - 1, 2 * slab, slab, 0, m.num_heads,
-                                         Se_pad, hd, Se_pad, Se_pad, (rfk_stream_t)side_stream));
+                                         Se_pad, hd, Se_pad, Se_pad, g0 ? g0 + dim : nullptr, dim, (rfk_stream_t)side_stream));
             TRY_CUDA(cudaEventRecord(ev_rot[1], side_stream));
         }
     }
@@ -201,10 +204,10 @@ int rfk_session::render_view(const float* pinned_cam, rfk_half* result_out, rfk_
         // a tapped (or the last) layer finishes x itself; the others leave their FFN residual
         // to the first kernel of the next layer
         if (i < 2) TRY_CUDA(cudaStreamWaitEvent(stream, ev_rot[i], 0));
-        TRY(rfk_decoder_layer_forward_cached(ctx, &m.dec[i], rtok, pending, (tap || last) ? nullptr : &next_pending,
-                                             temp, proj, qkv, ffn, win, score, self_score, kRot(i), kvV(i), 1, nP,
-                                             Se_pad, n_keys, dim, m.num_heads, m.ffn_hidden, pH, pW, m.window_size,
-                                             shift, shift > 0 ? shift_mask : nullptr, nullptr, nullptr, nullptr, nullptr, s));
+        TRY(decoder_layer_impl(ctx, &m.dec[i], rtok, pending, (tap || last) ? nullptr : &next_pending,
+                               temp, proj, qkv, ffn, win, score, self_score, kRot(i), kvV(i), 1, nP,
+                               Se_pad, n_keys, dim, m.num_heads, m.ffn_hidden, pH, pW, m.window_size,
+                               shift, shift > 0 ? shift_mask : nullptr, nullptr, nullptr, nullptr, nullptr, prescale ? 1 : 0, s));
         pending = next_pending;
         if (tap)
             TRY_CUDA(cudaMemcpyAsync(taps_out[(i + 1) / L4 - 1], rtok, (size_t)nP * dim * sizeof(rfk_half),
@@ -287,6 +290,20 @@ extern "C" int rfk_session_create(const rfk_model* model, int n_tris, int img_re
     ALLOC(ffn, (size_t)nP * std::max(dim, ffn));
     ALLOC(win, (size_t)nP * dim);
     ALLOC(k_rot, (size_t)model->dec_layers * nh * Se_pad * d->hd);
+    ALLOC(q_gamma_all, (size_t)model->dec_layers * dim);
+    {
+        // Deferred Q-RMSNorm of the cross-attention (layers.cu): possible when the fused kernels serve the shape and every
+        // layer has a norm weight, no query bias and no window-path exclusions; then the key rotation folds the weights in.
+        bool ok = d->hd == 64 && dim % 256 == 0 && d->nP % 32 == 0 && d->pH % ws == 0 && dim <= 2048;
+        for (int i = 0; i < model->dec_layers && ok; ++i)
+            ok = model->dec[i].cross_attn.q_norm_gamma && !model->dec[i].cross_attn.q_proj_b && !model->dec[i].cross_attn.out_proj_b &&
+                 (reinterpret_cast<uintptr_t>(model->dec[i].cross_attn.q_norm_gamma) & 15u) == 0;
+        d->prescale = ok;
+        for (int i = 0; i < model->dec_layers && ok; ++i)
+            if (cudaMemcpy(d->q_gamma_all + (size_t)i * dim, model->dec[i].cross_attn.q_norm_gamma, (size_t)dim * sizeof(float),
+                           cudaMemcpyDeviceToDevice) != cudaSuccess)
+                return fail((int)cudaGetLastError());
+    }
     const bool fused_attention = d->hd == 64 || d->hd == 128;  // rfk_flash_attention serves these
     if (!fused_attention) ALLOC(score, (size_t)nh * nP * Se_pad);
     if (!(ws * ws == 64 && d->hd == 64)) ALLOC(self_score, (size_t)nWin * nh * ws * ws * ws * ws);
@@ -460,7 +477,16 @@ extern "C" int rfk_session_finalize(rfk_session* d) {
     // warm-up view (also lets cuBLAS pick and load its kernels before capture)
     float cam[17] = {1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 3, 0, 0, 0, 1, 0.7f};
     for (int k = 0; k < kSlots; ++k) memcpy(d->pin_cam[k], cam, sizeof(cam));
-    TRY(d->render_view(d->pin_cam[0], d->result[0], d->dft[0], d->image[0]));
+    {
+        int rc = d->render_view(d->pin_cam[0], d->result[0], d->dft[0], d->image[0]);
+        if (rc == RFK_EUNSUPPORTED && d->prescale) {  // the kernels of the deferred norm cannot run here: separate norm instead
+            TRY_CUDA(cudaStreamSynchronize(d->stream));
+            TRY_CUDA(cudaStreamSynchronize(d->side_stream));
+            d->prescale = false;
+            rc = d->render_view(d->pin_cam[0], d->result[0], d->dft[0], d->image[0]);
+        }
+        TRY(rc);
+    }
     TRY_CUDA(cudaStreamSynchronize(d->stream));
     if (!(d->flags & RFK_SESSION_NO_GRAPH)) {
         for (int k = 0; k < kSlots; ++k) {

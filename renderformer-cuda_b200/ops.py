@@ -165,6 +165,17 @@ def rope_one_oop(src, dst, cos_vals, sin_vals, batch, num_heads, seq_len, head_d
           seq_len if dst_seq_stride is None else dst_seq_stride, int(copy_tail), _stream())
 
 
+def rope_one_oop_strided(src, dst, cos_vals, sin_vals, batch, src_batch_stride, dst_batch_stride, table_batch_stride,
+                         num_heads, seq_len, head_dim, src_seq_stride=None, dst_seq_stride=None, col_scale=None,
+                         col_scale_batch_stride=0):
+    """rope_one_oop with explicit batch strides (elements) and an optional per-(head, element) factor
+    col_scale [batch][num_heads * head_dim] applied before the one rounding."""
+    _call("rfk_rope_one_oop_strided", _p(src, H, "src"), _p(dst, H, "dst"), _p(cos_vals, H, "cos"), _p(sin_vals, H, "sin"),
+          batch, src_batch_stride, dst_batch_stride, table_batch_stride, num_heads, seq_len, head_dim,
+          seq_len if src_seq_stride is None else src_seq_stride, seq_len if dst_seq_stride is None else dst_seq_stride,
+          _p(col_scale, F, "col_scale"), col_scale_batch_stride, _stream())
+
+
 def qkv_norm_rope_transpose(x, row_stride, gammas, outs, use_rope, cos_vals, sin_vals,
                             batch, seq_len, num_heads, head_dim, eps=K_EPS_FP16, out_seq_stride=0):
     n = len(outs)
@@ -255,6 +266,24 @@ def window_attention(q, k, v, o, mask, BnW, Hh, nW, window_tokens=64, head_dim=6
           window_tokens, head_dim, nW, float(scale if scale is not None else head_dim ** -0.5), _stream())
 
 
+def flash_attention_rowscale(q, k, v, o, q_row_ss, ss_tiles, norm_dim, B, Hh, Sq, Sk, n_keys, D, o_bshd=False, scale=None,
+                             eps=K_EPS_FP16):
+    """flash_attention whose rows are scaled by rsqrt(sum(q_row_ss[row]) / norm_dim + eps): the query's RMSNorm statistic
+    applied to the scores (the norm weight rides on the keys)."""
+    _call("rfk_flash_attention_rowscale", _p(q, H, "q"), _p(k, H, "k"), _p(v, H, "v"), _p(o, H, "o"), _p(q_row_ss, F, "q_row_ss"),
+          ss_tiles, norm_dim, eps, B, Hh, Sq, Sk, n_keys, D, int(o_bshd), float(scale if scale is not None else D ** -0.5),
+          _stream())
+
+
+def window_attention_normed(q, k, v, o, mask, q_row_ss, k_row_ss, ss_tiles, gamma_q, gamma_k, norm_dim, BnW, Hh, nW,
+                            window_tokens=64, head_dim=64, scale=None, eps=K_EPS_FP16):
+    """window_attention over un-normalised Q, K with the RMSNorm (row statistics + weights) applied while staging."""
+    _call("rfk_window_attention_normed", _p(q, H, "q"), _p(k, H, "k"), _p(v, H, "v"), _p(o, H, "o"), _mask_ptr(mask),
+          _p(q_row_ss, F, "q_row_ss"), _p(k_row_ss, F, "k_row_ss"), ss_tiles, _p(gamma_q, F, "gamma_q"),
+          _p(gamma_k, F, "gamma_k"), norm_dim, eps, BnW, Hh, window_tokens, head_dim, nW,
+          float(scale if scale is not None else head_dim ** -0.5), _stream())
+
+
 def flash_attention_set_path(path):
     """0 automatic, 1 mma.sync kernel, 2 tcgen05 kernel (head_dim 64)."""
     _call("rfk_flash_attention_set_path", int(path))
@@ -281,6 +310,13 @@ def gemm_f16(a, w, c, M, N, K, w_up=None, bias=None, residual=None, lda=None, ld
     _call("rfk_gemm_f16", _p(a, H, "a"), lda or K, _p(w, H, "w"), ldw or K, _p(w_up, H, "w_up"), _p(bias, H, "bias"),
           _p(residual, H, "residual"), (ldr or N) if residual is not None else 0, _p(c, H, "c"), ldc or N, M, N, K, epi,
           _stream())
+
+
+def gemm_f16_heads(a, w, out, row_ss, ss_parts_mask, M, N, K, seq_len, num_heads, part_stride=0, lda=None, ldw=None):
+    """Projection stored head-split ([groups][heads][seq_len][64] per part) with the rows' partial sums of squares
+    (rfk_gemm_f16_heads): the producer side of the deferred QK-RMSNorm."""
+    _call("rfk_gemm_f16_heads", _p(a, H, "a"), lda or K, _p(w, H, "w"), ldw or K, _p(out, H, "out"), part_stride,
+          _p(row_ss, F, "row_ss"), ss_parts_mask, M, N, K, seq_len, num_heads, _stream())
 
 
 def gemm_set_path(path):
