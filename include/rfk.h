@@ -156,7 +156,7 @@ int rfk_rope_one_oop(const rfk_half* src, rfk_half* dst,
  * shared table (table_batch_stride = 0) with batch = layers and src_batch_stride = two
  * cache slabs. col_scale (may be NULL): [batch][num_heads * head_dim] floats with batch stride
  * col_scale_batch_stride; the rotated value is multiplied by col_scale[b][h * head_dim + d] before its
- * one rounding to fp16 (the query's RMSNorm weight folded into the keys, see rfk_flash_attention_rowscale;
+ * one rounding to fp16 (the query's RMSNorm weight folded into the keys, see rfk_flash_attention_ex;
  * head_dim % 16 == 0 required then). Replaces one cudaMemcpyAsync + apply_rope_one pair per decoder layer —
  * src/layers/attention.cu:355-361. */
 int rfk_rope_one_oop_strided(const rfk_half* src, rfk_half* dst,
@@ -264,16 +264,27 @@ int rfk_flash_attention(const rfk_half* Q, const rfk_half* K, const rfk_half* V,
                         int B, int H, int Sq, int Sk, int n_keys, int D, int o_bshd, float scale,
                         rfk_stream_t stream);
 
-/* rfk_flash_attention for queries that come un-normalised out of rfk_gemm_f16_heads: q_row_ss [B*Sq][ss_tiles]
- * holds the partial sums of squares of each token's whole projection row (all heads); the kernel multiplies a
- * row's scores by rsqrt(sum / norm_dim + eps), which is what normalising the query first would do up to rounding.
- * The norm's per-element weight has no per-row form: the caller folds it into the keys (col_scale of
- * rfk_rope_one_oop_strided). tcgen05 kernel only (D = 64): RFK_EUNSUPPORTED otherwise, and callers normalise with
- * rfk_qkv_norm_rope_transpose instead.
+/* rfk_flash_attention with two optional extensions; tcgen05 kernel only (D = 64: RFK_EUNSUPPORTED otherwise).
+ * (1) Queries that come un-normalised out of rfk_gemm_f16_heads (q_row_ss != NULL): q_row_ss [B*Sq][ss_tiles] holds the
+ * partial sums of squares of each token's whole projection row (all heads); the kernel multiplies a row's scores by
+ * rsqrt(sum / norm_dim + eps), which is what normalising the query first would do up to rounding. The norm's
+ * per-element weight has no per-row form: the caller folds it into the keys (col_scale of rfk_rope_one_oop_strided).
+ * (2) Key split (workspace != NULL): the kernel's units of work are 256 queries of one head; a grid with fewer units
+ * than SMs (a 256 x 256 view has 64) leaves most of the machine idle, so with a workspace - and when the launcher's
+ * estimate says it pays - the units' key ranges are cut into one share per SM and merged by the CTA that finishes a
+ * unit last (nobody waits). workspace: rfk_flash_attention_workspace_bytes() bytes, 16-byte aligned, its first 1024
+ * bytes zero before the first launch (the kernel leaves them zero); launches that may overlap in time need separate
+ * workspaces. The result differs from the unsplit kernel's only by rounding (fp32 merge; fp16 probabilities relative to
+ * each piece's own maximum) and is bit-reproducible from launch to launch.
  * replaces rmsnorm(Q) -> transpose -> sdpa — src/layers/attention.cu:341-349,364-366 */
-int rfk_flash_attention_rowscale(const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,
-                                 const float* q_row_ss, int ss_tiles, int norm_dim, float eps, int B, int H,
-                                 int Sq, int Sk, int n_keys, int D, int o_bshd, float scale, rfk_stream_t stream);
+int rfk_flash_attention_ex(const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,
+                           const float* q_row_ss, int ss_tiles, int norm_dim, float eps, void* workspace,
+                           size_t workspace_bytes, int B, int H, int Sq, int Sk, int n_keys, int D, int o_bshd,
+                           float scale, rfk_stream_t stream);
+size_t rfk_flash_attention_workspace_bytes(void);
+/* 0: rfk_flash_attention_ex ignores its workspace (every unit whole), to time both schedules side by side; 1 (default):
+ * it cuts where that pays. Process-wide. No reference counterpart. */
+int rfk_flash_attention_set_split(int on);
 
 /* Which kernel serves rfk_flash_attention at D = 64: 0 automatic (the tcgen05 / tensor-memory
  * kernel; the mma.sync kernel only if the driver cannot encode tensor maps), 1 the mma.sync kernel,
@@ -328,7 +339,7 @@ int rfk_gemm_f16(const rfk_half* A, long long lda, const rfk_half* W, long long 
  * ss_parts_mask == 0): [parts][M][num_heads * 64 / 256] floats; entry (p, row, t) = sum of squares of the fp16-rounded
  * outputs of that row in columns [256 t, 256 t + 256) of part p, written (not accumulated, no zeroing needed, bit-
  * reproducible) for the parts whose bit is set in ss_parts_mask; the consumer adds the entries of a row and applies
- * rsqrt(sum / dim + eps) and the norm weight while it loads (rfk_flash_attention_rowscale, rfk_window_attention_normed).
+ * rsqrt(sum / dim + eps) and the norm weight while it loads (rfk_flash_attention_ex, rfk_window_attention_normed).
  * CTA-pair tcgen05 kernel only: RFK_EUNSUPPORTED (nothing launched) unless num_heads % 4 == 0, seq_len % 32 == 0,
  * M % seq_len == 0 and the alignment rules of rfk_gemm_f16 hold; callers then run the projection and
  * rfk_qkv_norm_rope_transpose separately.

@@ -32,6 +32,11 @@ typedef struct rfk_session rfk_session;  /* per-device, per-scene render session
  * replaces rf::CublasHandle — src/core/cuda_utils.h:50-59 */
 int rfk_ctx_create(rfk_ctx** out);
 int rfk_ctx_destroy(rfk_ctx* ctx);
+/* Gives the context the workspace of rfk_flash_attention_ex's key split (rfk.h; about 21 MB, allocated here,
+ * freed by rfk_ctx_destroy): the attention inside the layer functions called with this context then uses it. The
+ * workspace is shared by all of them, so their launches must not overlap in time (one stream, or streams ordered
+ * by events); rfk_session_create does this for the session's own context. No reference counterpart. */
+int rfk_ctx_reserve_attention_workspace(rfk_ctx* ctx);
 
 /* ------------------------------------------------------------- weight records */
 

@@ -447,9 +447,11 @@ window_attention_kernel(const __half* __restrict__ Q, const __half* __restrict__
 
 // attention_tc.cu
 extern std::atomic<int> g_attn_path;
+extern std::atomic<int> g_attn_split;
+size_t attention_tc_workspace_bytes();
 int launch_attention_tc(const __half* Q, const __half* K, const __half* V, __half* O, int B, int H, int Sq, int Sk,
                         int n_keys, int o_bshd, float scale, cudaStream_t st, const float* row_ss, int ss_tiles,
-                        int norm_dim, float norm_eps);
+                        int norm_dim, float norm_eps, void* ws, size_t ws_bytes);
 
 }  // namespace rfk
 
@@ -468,7 +470,7 @@ extern "C" int rfk_flash_attention(const rfk_half* Q, const rfk_half* K, const r
     const int path = g_attn_path.load(std::memory_order_relaxed);
     if (D == 64 && path != 1) {  // tcgen05 kernel; in automatic mode the mma.sync kernel takes over if it cannot run
         const int rc = launch_attention_tc((const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, B, H, Sq, Sk,
-                                           n_keys, o_bshd, scale, st, nullptr, 0, 0, 0.0f);
+                                           n_keys, o_bshd, scale, st, nullptr, 0, 0, 0.0f, nullptr, 0);
         if (rc != RFK_EUNSUPPORTED || path == 2) return rc;
     }
     if (D == 64)
@@ -480,17 +482,26 @@ extern "C" int rfk_flash_attention(const rfk_half* Q, const rfk_half* K, const r
     return RFK_EUNSUPPORTED;
 }
 
-extern "C" int rfk_flash_attention_rowscale(const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,
-                                            const float* q_row_ss, int ss_tiles, int norm_dim, float eps, int B, int H,
-                                            int Sq, int Sk, int n_keys, int D, int o_bshd, float scale, rfk_stream_t stream) {
-    if (!Q || !K || !V || !O || !q_row_ss || ss_tiles <= 0 || norm_dim <= 0 || B < 0 || H <= 0 || Sq < 0 || Sk <= 0 ||
-        n_keys <= 0 || n_keys > Sk || !(scale > 0.0f))
+extern "C" int rfk_flash_attention_ex(const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,
+                                      const float* q_row_ss, int ss_tiles, int norm_dim, float eps, void* workspace,
+                                      size_t workspace_bytes, int B, int H, int Sq, int Sk, int n_keys, int D, int o_bshd,
+                                      float scale, rfk_stream_t stream) {
+    if (!Q || !K || !V || !O || B < 0 || H <= 0 || Sq < 0 || Sk <= 0 || n_keys <= 0 || n_keys > Sk || !(scale > 0.0f))
         return RFK_EINVAL;
+    if (q_row_ss && (ss_tiles <= 0 || norm_dim <= 0)) return RFK_EINVAL;
+    if (workspace && workspace_bytes < attention_tc_workspace_bytes()) return RFK_EINVAL;
     if (B == 0 || Sq == 0) return RFK_OK;
     if (D != 64 || (long long)B * H > 65535 || g_attn_path.load(std::memory_order_relaxed) == 1) return RFK_EUNSUPPORTED;
-    if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O)) return RFK_EUNSUPPORTED;
+    if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O) || !aligned16(workspace)) return RFK_EUNSUPPORTED;
     return launch_attention_tc((const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, B, H, Sq, Sk, n_keys, o_bshd,
-                               scale, as_stream(stream), q_row_ss, ss_tiles, norm_dim, eps);
+                               scale, as_stream(stream), q_row_ss, ss_tiles, norm_dim, eps, workspace, workspace_bytes);
+}
+
+extern "C" size_t rfk_flash_attention_workspace_bytes(void) { return attention_tc_workspace_bytes(); }
+
+extern "C" int rfk_flash_attention_set_split(int on) {
+    g_attn_split.store(on ? 1 : 0, std::memory_order_relaxed);
+    return RFK_OK;
 }
 
 extern "C" int rfk_window_attention(const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,

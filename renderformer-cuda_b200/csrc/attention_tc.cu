@@ -29,6 +29,17 @@
 // Tensor memory: all 512 columns (per block S0, S1, S2, O: 64 each); shared memory 32 KB (Q) +
 // kStages x 16 KB; one CTA per SM. Every mbarrier wait is bounded; on a time-out the CTA raises an
 // error word, frees its tensor memory and returns.
+//
+// Key split for grids that do not fill the machine. A unit = 256 queries of one head over all keys = one CTA. With few
+// units (a 256 x 256 view has 64 of them for 148 SMs) most SMs idle, so when the caller supplies a workspace and the
+// estimate below says it pays, the key range of the units is cut into one equal share per SM; a share is one or two
+// pieces (it may cross a unit boundary), a piece is one CTA over a range of key tiles. A piece writes its un-normalised
+// O, running maximum and sum to the workspace and increments its unit's counter; the CTA that finds the counter
+// complete (no CTA ever waits for another) merges the unit's pieces, writes the output and zeroes the counter for the
+// next launch. A piece costs about 10 us beyond its tiles (pipeline fill, publishing, merging), which is why grids
+// that already fill the SMs once or more are left whole: measured, cutting the last partial round of a 256-unit grid
+// gains nothing.
+#include <algorithm>
 #include <cuda.h>  // CUtensorMap and its enums; the encoder itself is looked up at run time
 #include "attention_tc.cuh"
 #include "common.cuh"
@@ -55,6 +66,7 @@ struct __align__(8) Ctrl {
     uint64_t drain[2 * kBlocks];  // abort path only, one per issuing thread: completes once that thread's products have finished
     uint32_t tmem_base;
     int abort;
+    int merge;  // set by thread 0 of a split unit's last piece: this CTA merges the unit
 };
 
 // The shared-memory window is declared 1024-byte aligned (swizzled tiles need it) and the kernel checks it.
@@ -63,6 +75,26 @@ static_assert(sizeof(Ctrl) <= 512, "control block");
 static_assert(kSmemBytes + 1024 <= 227 * 1024, "one CTA per SM");
 
 enum : int { kErrTimeout = 1, kErrSmemAlign = 2 };
+
+// A CTA's share of a unit whose keys are split: key tiles [t0, t0 + nt) of unit `unit`; the unit's pieces own the
+// workspace slots [first, first + count), this one `slot`.
+struct Piece { uint16_t unit, t0, nt, first, count, slot; };
+constexpr int kMaxPieces = 320;
+struct WorkList {
+    int whole_units;  // CTAs [0, whole_units) take the unit of their index over all keys
+    int n_pieces;     // CTAs [whole_units, whole_units + n_pieces) take pieces[index - whole_units]
+    int q_blocks;     // units per head: ceil(Sq / 256)
+    Piece pieces[kMaxPieces];
+};
+// Workspace: 256 counters (one per split unit, zero between launches), then per slot 256 x {m, l}, then per slot the
+// un-normalised output as [16 groups of 4 columns][256 rows] float4 (a warp's 32 rows of one group are contiguous).
+constexpr int kUnitRows = kBlocks * BM;
+constexpr size_t kWsCounterBytes = 1024;
+constexpr size_t kWsMlBytes = (size_t)kMaxPieces * kUnitRows * 2 * sizeof(float);
+constexpr size_t kWsOBytes = (size_t)kMaxPieces * kUnitRows * HD * sizeof(float);
+constexpr size_t kWsBytes = kWsCounterBytes + kWsMlBytes + kWsOBytes;
+
+__device__ __forceinline__ void softmax_warps_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }  // warps 0-7 only
 
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
@@ -141,11 +173,24 @@ __device__ __forceinline__ void exp_half(uint32_t (&v)[32], uint32_t* pk /* may 
     }
 }
 
+// 32 fp32 values (as raw words) * inv -> fp16 -> 64 bytes at dst
+__device__ __forceinline__ void store_row_half(__half* dst, const uint32_t (&v)[32], float inv) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint4 o;
+        o.x = pack_half2(__uint_as_float(v[8 * c + 0]) * inv, __uint_as_float(v[8 * c + 1]) * inv);
+        o.y = pack_half2(__uint_as_float(v[8 * c + 2]) * inv, __uint_as_float(v[8 * c + 3]) * inv);
+        o.z = pack_half2(__uint_as_float(v[8 * c + 4]) * inv, __uint_as_float(v[8 * c + 5]) * inv);
+        o.w = pack_half2(__uint_as_float(v[8 * c + 6]) * inv, __uint_as_float(v[8 * c + 7]) * inv);
+        *reinterpret_cast<uint4*>(dst + c * 8) = o;
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, __half* __restrict__ O, int H, int Sq, int n_keys,
                     int o_bshd, float scale_log2e_all, const float* __restrict__ row_ss, int ss_tiles, float inv_norm_dim,
-                    float norm_eps) {
+                    float norm_eps, unsigned char* __restrict__ ws, const __grid_constant__ WorkList work) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const uint32_t base = tc::smem_addr(smem_raw);
     if (base & 1023u) {  // uniform over the CTA, nothing allocated yet
@@ -157,9 +202,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     volatile int* abort_flag = &ctrl->abort;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int q0 = blockIdx.x * (kBlocks * BM);
-    const int bh = blockIdx.y;
-    const int n_tiles = (n_keys + BN - 1) / BN;
+    // this CTA's work: a whole unit, or a piece of one (n_tiles key tiles from tile t0)
+    int unit = blockIdx.x, t0 = 0, n_tiles = (n_keys + BN - 1) / BN, split_count = 1, split_first = 0, split_slot = 0;
+    if ((int)blockIdx.x >= work.whole_units) {
+        const Piece& pc = work.pieces[blockIdx.x - work.whole_units];
+        unit = pc.unit; t0 = pc.t0; n_tiles = pc.nt; split_count = pc.count; split_first = pc.first; split_slot = pc.slot;
+    }
+    const int q0 = (unit % work.q_blocks) * kUnitRows;
+    const int bh = unit / work.q_blocks;
 
     if (tid == 0) {
         tc::mbar_init(&ctrl->q_full, 1);
@@ -170,6 +220,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
         for (int k = 0; k < 2 * kBlocks; ++k) tc::mbar_init(&ctrl->drain[k], 1);
         ctrl->abort = 0;
+        ctrl->merge = 0;
         tc::fence_barrier_init();
     }
     if (warp == 0) {  // one warp allocates the CTA's tensor memory and later frees it
@@ -196,8 +247,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 // stage s was last read by the products of tile j - kStages (phase j / kStages - 1 of kv_empty[s])
                 if (j >= kStages && !tc::mbar_wait(&ctrl->kv_empty[s], ((j / kStages) + 1) & 1, abort_flag)) break;
                 tc::mbar_arrive_expect_tx(&ctrl->kv_full[s], kStageBytes);
-                tc::tma_load_3d(sKV + s * kStageBytes, &map_k, 0, j * BN, bh, &ctrl->kv_full[s]);
-                tc::tma_load_3d(sKV + s * kStageBytes + kKBytes, &map_v, 0, j * BN, bh, &ctrl->kv_full[s]);
+                tc::tma_load_3d(sKV + s * kStageBytes, &map_k, 0, (t0 + j) * BN, bh, &ctrl->kv_full[s]);
+                tc::tma_load_3d(sKV + s * kStageBytes + kKBytes, &map_v, 0, (t0 + j) * BN, bh, &ctrl->kv_full[s]);
                 issued = j + 1;
             }
             if (*abort_flag) {
@@ -303,7 +354,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tc::tmem_ld32(tS + 32, vb);
             tc::tc_wait_ld(va);
             tc::tc_wait_ld(vb);
-            const int n_valid = min(BN, n_keys - j * BN);  // real keys among this tile's 64 columns
+            const int n_valid = min(BN, n_keys - (t0 + j) * BN);  // real keys among this tile's 64 columns
             float m_tile;
             if (n_valid == BN) {
                 float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
@@ -373,26 +424,79 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const int lbuf = buf == 0 ? kSBufs - 1 : buf - 1, lbuf_par = buf == 0 ? buf_par ^ 1 : buf_par;
             ok = tc::mbar_wait_warp(&ctrl->pv_done[blk][lbuf], lbuf_par, abort_flag);
         }
-        if (ok) {
-            tc::tc_fence_after();
-            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-            const int q = q0 + blk * BM + r;
-            const int b = bh / H, h = bh % H;
-            __half* dst = o_bshd ? O + (((size_t)b * Sq + q) * H + h) * HD : O + ((size_t)bh * Sq + q) * HD;
+        const int q = q0 + blk * BM + r;
+        __half* dst = o_bshd ? O + (((size_t)(bh / H) * Sq + q) * H + bh % H) * HD : O + ((size_t)bh * Sq + q) * HD;
+        if (split_count == 1) {
+            if (ok) {
+                tc::tc_fence_after();
+                const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
 #pragma unroll
-            for (int hc = 0; hc < 2; ++hc) {
-                tc::tmem_ld32(tO + hc * 32, va);
-                tc::tc_wait_ld(va);
-                if (q < Sq) {
+                for (int hc = 0; hc < 2; ++hc) {
+                    tc::tmem_ld32(tO + hc * 32, va);
+                    tc::tc_wait_ld(va);
+                    if (q < Sq) store_row_half(dst + hc * 32, va, inv);
+                }
+            }
+        } else {
+            // ---- a piece of a split unit: publish (m, l, O), count, and merge if this CTA completes the unit
+            float* ws_ml = reinterpret_cast<float*>(ws + kWsCounterBytes);
+            float* ws_o = reinterpret_cast<float*>(ws + kWsCounterBytes + kWsMlBytes);
+            const int row = blk * BM + r;
+            if (ok) {
+                tc::tc_fence_after();
+                uint4* po = reinterpret_cast<uint4*>(ws_o) + (size_t)split_slot * (HD / 4) * kUnitRows + row;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint4 o;
-                        o.x = pack_half2(__uint_as_float(va[8 * c + 0]) * inv, __uint_as_float(va[8 * c + 1]) * inv);
-                        o.y = pack_half2(__uint_as_float(va[8 * c + 2]) * inv, __uint_as_float(va[8 * c + 3]) * inv);
-                        o.z = pack_half2(__uint_as_float(va[8 * c + 4]) * inv, __uint_as_float(va[8 * c + 5]) * inv);
-                        o.w = pack_half2(__uint_as_float(va[8 * c + 6]) * inv, __uint_as_float(va[8 * c + 7]) * inv);
-                        *reinterpret_cast<uint4*>(dst + hc * 32 + c * 8) = o;
+                for (int hc = 0; hc < 2; ++hc) {
+                    tc::tmem_ld32(tO + hc * 32, va);
+                    tc::tc_wait_ld(va);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        __stcg(po + (hc * 8 + c) * kUnitRows, make_uint4(va[4 * c], va[4 * c + 1], va[4 * c + 2], va[4 * c + 3]));
+                }
+                // the exponent reference in exponent units (the row's own scale applied), so that pieces compare directly
+                __stcg(reinterpret_cast<float2*>(ws_ml + ((size_t)split_slot * kUnitRows + row) * 2), make_float2(m_run * scale_log2e, l_run));
+                __threadfence();
+            }
+            softmax_warps_sync();  // every softmax warp comes here, whatever its ok: the barrier cannot be left short
+            if (tid == 0) {
+                int merge = 0;
+                if (!*abort_flag) {
+                    int* counter = reinterpret_cast<int*>(ws) + (unit - work.whole_units);
+                    merge = atomicAdd(counter, 1) == split_count - 1;
+                    if (merge) {
+                        *counter = 0;  // every piece of the unit has arrived: ready for the next launch
+                        __threadfence();
                     }
+                }
+                ctrl->merge = merge;
+            }
+            softmax_warps_sync();
+            if (ctrl->merge && ok) {
+                float m_all = -INFINITY;
+                for (int p = 0; p < split_count; ++p)
+                    m_all = fmaxf(m_all, __ldcg(ws_ml + ((size_t)(split_first + p) * kUnitRows + row) * 2));
+                float l_all = 0.0f;
+                float* acc = reinterpret_cast<float*>(va);  // va, vb: this row's 64 merged outputs
+                float* acc2 = reinterpret_cast<float*>(vb);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) { acc[i] = 0.0f; acc2[i] = 0.0f; }
+                for (int p = 0; p < split_count; ++p) {  // in slot order, whichever CTA merges: the sum is reproducible
+                    const size_t pr = (size_t)(split_first + p) * kUnitRows + row;
+                    const float2 ml = __ldcg(reinterpret_cast<const float2*>(ws_ml + pr * 2));
+                    const float w = fast_exp2(ml.x - m_all);
+                    l_all += w * ml.y;
+                    const float4* src = reinterpret_cast<const float4*>(ws_o) + (size_t)(split_first + p) * (HD / 4) * kUnitRows + row;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const float4 a = __ldcg(src + c * kUnitRows), b = __ldcg(src + (8 + c) * kUnitRows);
+                        acc[4 * c] += w * a.x; acc[4 * c + 1] += w * a.y; acc[4 * c + 2] += w * a.z; acc[4 * c + 3] += w * a.w;
+                        acc2[4 * c] += w * b.x; acc2[4 * c + 1] += w * b.y; acc2[4 * c + 2] += w * b.z; acc2[4 * c + 3] += w * b.w;
+                    }
+                }
+                const float inv = l_all > 0.0f ? 1.0f / l_all : 0.0f;
+                if (q < Sq) {
+                    store_row_half(dst, va, inv);
+                    store_row_half(dst + 32, vb, inv);
                 }
             }
         }
@@ -411,6 +515,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 }  // namespace tcattn
 
 std::atomic<int> g_attn_path{0};  // 0 automatic, 1 mma.sync kernel, 2 tcgen05 kernel (head_dim 64 only)
+std::atomic<int> g_attn_split{1};  // 0: never split keys, even with a workspace (to time both side by side)
 
 namespace {
 
@@ -445,14 +550,58 @@ bool make_map(CUtensorMap* m, const void* base, long long n_heads, long long row
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Fills `w` for `units` units of `n_tiles` key tiles each on a device with `sms` SMs (see "Key split" above).
+// split = false, or the estimate says it does not pay: every unit whole.
+void plan_work(tcattn::WorkList& w, long long units, int n_tiles, int sms, bool split) {
+    using tcattn::Piece;
+    constexpr int kPieceCostTiles = 12;  // what a piece costs beyond its tiles (fill, publishing, merging), in tile times
+    w.whole_units = (int)units;
+    w.n_pieces = 0;
+    if (!split || sms <= 0 || units >= sms || units > 256 || n_tiles > 65535) return;  // 256 unit counters
+    const long long tiles = units * n_tiles;
+    constexpr int kMaxPiecesPerUnit = 8;  // the CTA that merges a unit reads its pieces one after the other
+    const int shares = (int)std::min<long long>(std::min(sms, tcattn::kMaxPieces / 2), units * kMaxPiecesPerUnit);
+    // whole: one round of n_tiles; split: a share's tiles plus the piece overhead. Cut only for a clear gain.
+    if ((tiles + shares - 1) / shares + kPieceCostTiles > (long long)n_tiles * 4 / 5) return;
+    Piece* pc = w.pieces;
+    int n = 0;
+    for (int s = 0; s < shares; ++s) {
+        long long b = tiles * s / shares;
+        const long long e = tiles * (s + 1) / shares;
+        while (b < e) {  // at most twice: a share is shorter than a unit
+            const long long u = b / n_tiles, pe = std::min(e, (u + 1) * n_tiles);
+            pc[n].unit = (uint16_t)u;
+            pc[n].t0 = (uint16_t)(b - u * n_tiles);
+            pc[n].nt = (uint16_t)(pe - b);
+            pc[n].slot = (uint16_t)n;
+            ++n;
+            b = pe;
+        }
+    }
+    for (int i = 0; i < n;) {  // pieces of a unit are consecutive here: give each its unit's slot range
+        int j = i;
+        while (j < n && pc[j].unit == pc[i].unit) ++j;
+        for (int k = i; k < j; ++k) { pc[k].first = (uint16_t)i; pc[k].count = (uint16_t)(j - i); }
+        i = j;
+    }
+    // longest first: in-order dispatch then hands the short pieces to the SMs that finish their long ones first
+    std::stable_sort(pc, pc + n, [](const Piece& a, const Piece& b) { return a.nt > b.nt; });
+    w.whole_units = 0;
+    w.n_pieces = n;
+}
+
 }  // namespace
 
-// Launches the tcgen05 kernel; the caller has validated pointers, alignment and sizes (D == 64).
+size_t attention_tc_workspace_bytes() { return tcattn::kWsBytes; }
+
+// Launches the tcgen05 kernel; the caller has validated pointers, alignment and sizes (D == 64). ws (may be NULL):
+// attention_tc_workspace_bytes() bytes whose first 1024 are zero, for the key split.
 int launch_attention_tc(const __half* Q, const __half* K, const __half* V, __half* O, int B, int H, int Sq, int Sk,
                         int n_keys, int o_bshd, float scale, cudaStream_t st, const float* row_ss, int ss_tiles,
-                        int norm_dim, float norm_eps) {
+                        int norm_dim, float norm_eps, void* ws, size_t ws_bytes) {
     // per-device "kernel attributes set" marks; setting them twice from racing threads is harmless
     static std::atomic<bool> configured[64];
+    static std::atomic<int> sm_count[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
@@ -464,15 +613,26 @@ int launch_attention_tc(const __half* Q, const __half* K, const __half* V, __hal
         e = cudaFuncSetAttribute(tcattn::attention_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return (int)e;
+        int sms = 0;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return (int)e;
+        sm_count[dev].store(sms, std::memory_order_relaxed);
         configured[dev].store(true, std::memory_order_release);
     }
     CUtensorMap mq, mk, mv;
     if (!make_map(&mq, Q, (long long)B * H, Sq, tcattn::BM) || !make_map(&mk, K, (long long)B * H, Sk, tcattn::BN) ||
         !make_map(&mv, V, (long long)B * H, Sk, tcattn::BN))
         return RFK_EUNSUPPORTED;
-    dim3 grid(ceil_div(Sq, tcattn::kBlocks * tcattn::BM), B * H);
+    tcattn::WorkList work;
+    work.q_blocks = ceil_div(Sq, tcattn::kUnitRows);
+    const long long units = (long long)B * H * work.q_blocks;
+    if (units > 0x7fffffffLL) return RFK_EUNSUPPORTED;
+    const bool split = ws && ws_bytes >= tcattn::kWsBytes && aligned16(ws) && g_attn_split.load(std::memory_order_relaxed);
+    plan_work(work, units, ceil_div(n_keys, tcattn::BN), sm_count[dev].load(std::memory_order_relaxed), split);
+    dim3 grid((unsigned)(work.whole_units + work.n_pieces));
     launch_pdl(tcattn::attention_tc_kernel, grid, dim3(tcattn::kThreads), tcattn::kSmemBytes, st, mq, mk, mv, O, H, Sq, n_keys,
-               o_bshd, scale * 1.4426950408889634f, row_ss, ss_tiles, norm_dim > 0 ? 1.0f / (float)norm_dim : 0.0f, norm_eps);
+               o_bshd, scale * 1.4426950408889634f, row_ss, ss_tiles, norm_dim > 0 ? 1.0f / (float)norm_dim : 0.0f, norm_eps,
+               static_cast<unsigned char*>(ws), work);
     return launch_status();
 }
 

@@ -81,7 +81,22 @@ extern "C" int rfk_ctx_destroy(rfk_ctx* ctx) {
     if (!ctx) return RFK_OK;
     cublasDestroy(ctx->blas);
     cudaFree(ctx->ws);
+    cudaFree(ctx->attn_ws);
     delete ctx;
+    return RFK_OK;
+}
+
+extern "C" int rfk_ctx_reserve_attention_workspace(rfk_ctx* ctx) {
+    if (!ctx) return RFK_EINVAL;
+    if (ctx->attn_ws) return RFK_OK;
+    const size_t bytes = rfk_flash_attention_workspace_bytes();
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaMemset(p, 0, 1024);  // the unit counters; the kernel returns them to zero after every launch
+    if (e != cudaSuccess) { cudaFree(p); return (int)e; }
+    ctx->attn_ws = p;
+    ctx->attn_ws_bytes = bytes;
     return RFK_OK;
 }
 
@@ -203,7 +218,12 @@ extern "C" int rfk_sdpa(rfk_ctx* ctx, const rfk_half* Q, const rfk_half* K, cons
 static int attention_core(rfk_ctx* ctx, const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,
                           float* score_buf, int B, int H, int Sq, int Sk, int n_keys, int D, int o_bshd,
                           rfk_stream_t stream) {
-    int rc = rfk_flash_attention(Q, K, V, O, B, H, Sq, Sk, n_keys, D, o_bshd, 1.0f / sqrtf((float)D), stream);
+    int rc = RFK_EUNSUPPORTED;
+    if (ctx->attn_ws)  // tcgen05 kernel with the balanced key split; declines what only the other kernels serve
+        rc = rfk_flash_attention_ex(Q, K, V, O, nullptr, 0, 0, 0.0f, ctx->attn_ws, ctx->attn_ws_bytes, B, H, Sq, Sk, n_keys, D,
+                                    o_bshd, 1.0f / sqrtf((float)D), stream);
+    if (rc == RFK_EUNSUPPORTED)
+        rc = rfk_flash_attention(Q, K, V, O, B, H, Sq, Sk, n_keys, D, o_bshd, 1.0f / sqrtf((float)D), stream);
     if (rc != RFK_EUNSUPPORTED) return rc;
     if (!score_buf) return RFK_EINVAL;  // the materialised path needs its score matrix
     return rfk_sdpa(ctx, Q, K, V, O, score_buf, nullptr, B, H, Sq, Sk, n_keys, D, o_bshd, stream);
@@ -299,8 +319,8 @@ static int cross_attention_impl(rfk_ctx* ctx, const rfk_cross_attn_weights* w,
                 K_use = K_rot;
             }
             if (rc == RFK_OK)
-                rc = rfk_flash_attention_rowscale(Q_bhsd, K_use, V_cached, Q, norm_ss, dim / 256, dim, kEpsFp16, B, num_heads, Sq,
-                                                  Sk, n_keys, hd, 1, 1.0f / sqrtf((float)hd), stream);
+                rc = rfk_flash_attention_ex(Q_bhsd, K_use, V_cached, Q, norm_ss, dim / 256, dim, kEpsFp16, ctx->attn_ws,
+                                            ctx->attn_ws_bytes, B, num_heads, Sq, Sk, n_keys, hd, 1, 1.0f / sqrtf((float)hd), stream);
         }
         if (rc != RFK_OK && rc != RFK_EUNSUPPORTED) return rc;
         if (rc == RFK_EUNSUPPORTED && k_prescaled) return rc;  // prescaled keys cannot serve the separate-norm route

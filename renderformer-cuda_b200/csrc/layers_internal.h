@@ -10,6 +10,8 @@ struct rfk_ctx {
     cublasHandle_t blas = nullptr;
     void* ws = nullptr;      // cuBLAS workspace, set explicitly so capture never allocates
     size_t ws_bytes = 0;
+    void* attn_ws = nullptr;  // split workspace of the attention kernel (rfk_ctx_reserve_attention_workspace), else NULL
+    size_t attn_ws_bytes = 0;
     int device = 0;
 };
 

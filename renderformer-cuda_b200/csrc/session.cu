@@ -258,6 +258,7 @@ extern "C" int rfk_session_create(const rfk_model* model, int n_tris, int img_re
     const int dim = model->dim, nh = model->num_heads, ffn = model->ffn_hidden, nP = d->nP, Se_pad = d->Se_pad;
     const int ws = model->window_size, nWin = (d->pH / ws) * (d->pW / ws);
     int rc = rfk_ctx_create(&d->ctx);
+    if (!rc) rc = rfk_ctx_reserve_attention_workspace(d->ctx);  // all attention launches of a session are on its one stream
     auto fail = [&](int code) { rfk_session_destroy(d); return code; };
     if (rc) return fail(rc);
     if (cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking) != cudaSuccess) return fail((int)cudaGetLastError());

@@ -266,13 +266,23 @@ def window_attention(q, k, v, o, mask, BnW, Hh, nW, window_tokens=64, head_dim=6
           window_tokens, head_dim, nW, float(scale if scale is not None else head_dim ** -0.5), _stream())
 
 
-def flash_attention_rowscale(q, k, v, o, q_row_ss, ss_tiles, norm_dim, B, Hh, Sq, Sk, n_keys, D, o_bshd=False, scale=None,
-                             eps=K_EPS_FP16):
-    """flash_attention whose rows are scaled by rsqrt(sum(q_row_ss[row]) / norm_dim + eps): the query's RMSNorm statistic
-    applied to the scores (the norm weight rides on the keys)."""
-    _call("rfk_flash_attention_rowscale", _p(q, H, "q"), _p(k, H, "k"), _p(v, H, "v"), _p(o, H, "o"), _p(q_row_ss, F, "q_row_ss"),
-          ss_tiles, norm_dim, eps, B, Hh, Sq, Sk, n_keys, D, int(o_bshd), float(scale if scale is not None else D ** -0.5),
-          _stream())
+def flash_attention_ex(q, k, v, o, B, Hh, Sq, Sk, n_keys, D, q_row_ss=None, ss_tiles=0, norm_dim=0, workspace=None,
+                       o_bshd=False, scale=None, eps=K_EPS_FP16):
+    """flash_attention (tcgen05 kernel) with optional row statistics - rows scaled by rsqrt(sum(q_row_ss[row]) / norm_dim +
+    eps), the query's RMSNorm applied to the scores while its weight rides on the keys - and an optional workspace
+    (flash_attention_workspace()) for the balanced key split."""
+    _call("rfk_flash_attention_ex", _p(q, H, "q"), _p(k, H, "k"), _p(v, H, "v"), _p(o, H, "o"), _p(q_row_ss, F, "q_row_ss"),
+          ss_tiles, norm_dim, eps, _p(workspace, U8, "workspace"), 0 if workspace is None else workspace.numel(), B, Hh, Sq, Sk,
+          n_keys, D, int(o_bshd), float(scale if scale is not None else D ** -0.5), _stream())
+
+
+def flash_attention_workspace():
+    """A zeroed workspace for flash_attention_ex's key split (one per stream of overlapping launches)."""
+    return torch.zeros(int(_lib().rfk_flash_attention_workspace_bytes()), dtype=U8, device="cuda")
+
+
+def flash_attention_set_split(on):
+    _call("rfk_flash_attention_set_split", int(bool(on)))
 
 
 def window_attention_normed(q, k, v, o, mask, q_row_ss, k_row_ss, ss_tiles, gamma_q, gamma_k, norm_dim, BnW, Hh, nW,

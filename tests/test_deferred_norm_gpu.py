@@ -1,7 +1,7 @@
 """GPU parity tests of the deferred QK-RMSNorm chain through the C ABI: the projection that stores its output
 head-split together with the rows' sums of squares (rfk_gemm_f16_heads), the key rotation that folds the query
 norm's weight into the keys (col_scale of rfk_rope_one_oop_strided), and the two attention kernels that apply the
-row statistic (rfk_flash_attention_rowscale, rfk_window_attention_normed). Each is checked against a torch fp32
+row statistic (rfk_flash_attention_ex, rfk_window_attention_normed). Each is checked against a torch fp32
 evaluation of the unfused sequence it replaces (linear -> rmsnorm -> head split -> attention,
 src/layers/attention.cu:336-366 and :511-566 of the reference), with the tolerance of the corresponding unfused
 kernel's own test."""
@@ -151,7 +151,7 @@ def test_rowscale_attention_equals_attention_over_normalised_queries(B, Hh, Sq, 
     o.gemm_f16_heads(a, w, q, ss, 1, B * Sq, dim, dim, Sq, Hh)
     Kg = (K.float() * gamma.view(1, Hh, 1, D)).half()              # what the rotation kernel's col_scale produces
     O = torch.full((B, Sq, dim), 7.0, device="cuda", dtype=H16)
-    o.flash_attention_rowscale(q, Kg, V, O, ss, tiles, dim, B, Hh, Sq, Sk, n_keys, D, o_bshd=True)
+    o.flash_attention_ex(q, Kg, V, O, B, Hh, Sq, Sk, n_keys, D, q_row_ss=ss, ss_tiles=tiles, norm_dim=dim, o_bshd=True)
     torch.cuda.synchronize()
     proj = (a.float() @ w.float().t()).half().float()              # the projection's one rounding, as the reference has it
     qn = proj * torch.rsqrt(proj.pow(2).mean(-1, keepdim=True) + EPS) * gamma
@@ -194,3 +194,54 @@ def test_normed_window_attention_equals_norm_then_window_attention(masked, BnW, 
     same = (O == O2).float().mean().item()
     assert same > 0.98, f"only {same:.3f} of the outputs are identical to the separate sequence"
     _close(O, O2, "normed window attention", atol=3e-3, rtol=3e-3, mean_tol=3e-5)
+
+
+@pytest.mark.parametrize("B,Hh,Sq,Sk,n_keys,cut", [
+    (1, 16, 1024, 5696, 5672, True),     # a 256 x 256 view: 64 units for 148 SMs, every unit cut
+    (2, 3, 300, 2048, 2001, True),       # 12 ragged units, many pieces per unit
+    (1, 1, 77, 4096, 4096, True),        # one unit: eight pieces (the merge is serial in one CTA, so pieces per unit are capped)
+    (1, 16, 4096, 5696, 5672, False),    # the 512 x 512 view fills the SMs: left whole
+    (1, 12, 2304, 1600, 1537, False),    # 108 short units: the pieces' overhead would eat the gain
+    (1, 4, 256, 64, 33, False),          # one tile per unit: nothing to cut
+])
+def test_key_split_equals_unsplit_attention(B, Hh, Sq, Sk, n_keys, cut):
+    """The key split changes the schedule, not the function. Where the launcher cuts, the outputs differ from the
+    unsplit kernel's by the fp32 merge and by the probabilities' fp16 rounding relative to each piece's own running
+    maximum (a few fp16 steps at most where the output is a small difference, less than one on average), the fp32 torch
+    attention is met with the flash attention test's tolerance, the unit counters are back to zero, and a second launch
+    on the same workspace gives the same bits as the first. Where it does not cut, the workspace changes nothing."""
+    o = _ops()
+    D = 64
+    g = torch.Generator(device="cuda").manual_seed(Sq * 3 + Sk)
+    Q = _rand(g, B, Hh, Sq, D)
+    K = _rand(g, B, Hh, Sk, D)
+    V = _rand(g, B, Hh, Sk, D)
+    ws = o.flash_attention_workspace()
+    whole = torch.full((B, Sq, Hh * D), 7.0, device="cuda", dtype=H16)
+    split = torch.full_like(whole, 7.0)
+    again = torch.full_like(whole, 7.0)
+    o.flash_attention_ex(Q, K, V, whole, B, Hh, Sq, Sk, n_keys, D, o_bshd=True)
+    o.flash_attention_ex(Q, K, V, split, B, Hh, Sq, Sk, n_keys, D, workspace=ws, o_bshd=True)
+    torch.cuda.synchronize()
+    assert int(ws[:1024].view(torch.int32).abs().sum()) == 0, "unit counters not returned to zero"
+    o.flash_attention_ex(Q, K, V, again, B, Hh, Sq, Sk, n_keys, D, workspace=ws, o_bshd=True)
+    torch.cuda.synchronize()
+    want = torch.nn.functional.scaled_dot_product_attention(Q.float(), K[:, :, :n_keys].float(), V[:, :, :n_keys].float())
+    _close(split.view(B, Sq, Hh, D).permute(0, 2, 1, 3), want, "split attention", atol=4e-3, rtol=4e-3, mean_tol=5e-4)
+    if not cut:
+        assert torch.equal(split, whole)
+    else:
+        assert not torch.equal(split, whole), "expected the launcher to cut this grid"
+        d = (split.float() - whole.float()).abs()
+        assert (d <= 2.0 ** -9 * whole.float().abs() + 2e-4).all(), f"split and unsplit outputs apart: {d.max().item():.3g}"
+        assert d.mean().item() < 2.0 ** -10 * whole.float().abs().mean().item(), "on average more than one fp16 step apart"
+    # which CTA merges depends on timing, the order of the merge's additions does not
+    assert torch.equal(again, split), "second launch on the same workspace differs"
+    o.flash_attention_set_split(False)
+    try:
+        off = torch.full_like(whole, 7.0)
+        o.flash_attention_ex(Q, K, V, off, B, Hh, Sq, Sk, n_keys, D, workspace=ws, o_bshd=True)
+        torch.cuda.synchronize()
+        assert torch.equal(off, whole)
+    finally:
+        o.flash_attention_set_split(True)
