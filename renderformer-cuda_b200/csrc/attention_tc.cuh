@@ -38,7 +38,14 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // or as soon as another thread of the CTA has raised *abort.
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000 * 1000;
 constexpr uint32_t kSpinLimit = 1u << 22;
-static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort) {
+// The slow paths are kept out of line, except in kernels that re-partition their registers between warpgroups
+// (setmaxnreg): with a call inside such a region ptxas did not finish compiling, so those define RFK_TC_WAIT_INLINE.
+#ifdef RFK_TC_WAIT_INLINE
+#define RFK_TC_SLOW_PATH __device__ __forceinline__
+#else
+#define RFK_TC_SLOW_PATH static __device__ __noinline__
+#endif
+RFK_TC_SLOW_PATH bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort) {
     const uint64_t t0 = global_timer_ns();
     for (uint32_t it = 0; it < kSpinLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -55,7 +62,7 @@ static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parit
 // work that this thread itself started - bulk copies into shared memory, tensor-core products - so that
 // nothing is still writing the CTA's shared or tensor memory when the CTA frees them. Ignores *abort.
 constexpr uint64_t kDrainLimitNs = 4ull * 1000 * 1000;
-static __device__ __noinline__ bool mbar_wait_drain(uint64_t* bar, uint32_t parity) {
+RFK_TC_SLOW_PATH bool mbar_wait_drain(uint64_t* bar, uint32_t parity) {
     const uint64_t t0 = global_timer_ns();
     for (uint32_t it = 0; it < kSpinLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
