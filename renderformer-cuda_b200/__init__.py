@@ -8,10 +8,11 @@ module at the repository root:
 
 Contents: `csrc/` (CUDA kernels and the C ABI of include/rfk.h), `build.py` (in-tree nvcc
 build), `_abi.py` (ctypes binding generated from the headers), `ops.py` (Python mirror of the
-reference's kernel operators). Importing the package does not load the shared library; the
-first operator call does, and raises if it has not been built.
+reference's kernel operators), `session.py` (layer records, session, view scheduler), `assets.py`
+(safetensors weights and scenes in, EXR / PNG out; include/rfk_io.h). Importing the package does not
+load the shared libraries; the first call does, and raises if they have not been built.
 """
-from . import _abi, ops  # noqa: F401
+from . import _abi, assets, ops  # noqa: F401
 from .ops import RfkError, version  # noqa: F401
 
-__all__ = ["ops", "RfkError", "version"]
+__all__ = ["ops", "assets", "RfkError", "version"]

@@ -20,6 +20,8 @@ _SCALARS = {
     "long long": ctypes.c_longlong,
     "unsigned long long": ctypes.c_ulonglong,
     "size_t": ctypes.c_size_t,
+    "int64_t": ctypes.c_int64,
+    "uint64_t": ctypes.c_uint64,
     "rfk_stream_t": ctypes.c_void_p,
     "void": None,
 }
@@ -68,7 +70,7 @@ def parse_header(path: Path) -> dict[str, tuple]:
     return out
 
 
-_HEADER_LIB = {"rfk.h": "librfk.so", "rfk_layers.h": "librfk_layers.so"}
+_HEADER_LIB = {"rfk.h": "librfk.so", "rfk_layers.h": "librfk_layers.so", "rfk_io.h": "librfk_io.so"}
 
 
 def declared_symbols() -> dict[str, dict[str, tuple]]:

@@ -30,6 +30,7 @@ NVCC_FLAGS = [
 ]
 
 LAYER_SOURCES = ["layers.cu", "session.cu", "dpt.cu"]
+IO_SOURCES = ["io.cpp"]   # host code (safetensors, EXR, PNG); needs the CUDA runtime for the upload, zlib for the PNG
 
 KERNEL_SOURCES = [
     "abi.cu", "rmsnorm.cu", "softmax.cu", "rope.cu", "layout.cu",
@@ -98,6 +99,7 @@ def build_all(force: bool = False, verbose: bool = False, ptxas_info: bool = Fal
     libs["rfk_layers"] = build_library(
         "rfk_layers", LAYER_SOURCES,
         ["-lcublas", "-lcudnn", f"-L{PKG}", "-lrfk", "-Xlinker", "-rpath=$ORIGIN"], force, verbose, ptxas_info)
+    libs["rfk_io"] = build_library("rfk_io", IO_SOURCES, ["-lz"], force, verbose, False)
     return libs
 
 

@@ -126,6 +126,14 @@ def suite() -> list[Entry]:
     e.append(Entry("window_attention [64 windows x 16 heads x 64x64x64, masked]", 5, 4 * 64 * HEADS * 64 * HD * 2 + 64 * 64 * 64,
                    win_set, "window_attention"))
 
+    def winnorm_set():
+        q, k, v, o, mask = win_set()
+        ss = torch.rand(2, 64 * 64, HEADS * HD // 256, device="cuda") * 256 + 1
+        g = torch.ones(HEADS * HD, device="cuda")
+        return (q, k, v, o, mask, ss, g)
+    e.append(Entry("window_attention_normed [same; q, k normalised while staged]", 5,
+                   4 * 64 * HEADS * 64 * HD * 2 + 64 * 64 * 64 + 2 * 64 * 64 * (HEADS * HD // 256) * 4, winnorm_set, "window_attention_normed"))
+
     def normwin_set():
         return (_r((4096, 1024), H16), _r((4096, 1024), H16), torch.ones(1024, device="cuda"), torch.empty(4096, 1024, device="cuda", dtype=H16))
     e.append(Entry("rmsnorm_residual_f16 -> windows [4096x1024]", 5, 4 * 4096 * 1024 * 2 + 4096, normwin_set, "rmsnorm_windows"))
@@ -198,6 +206,9 @@ class RfkBackend:
 
     def window_attention(self, q, k, v, o, mask):
         self.o.window_attention(q, k, v, o, mask, 64, HEADS, 64)
+
+    def window_attention_normed(self, q, k, v, o, mask, ss, g):
+        self.o.window_attention_normed(q, k, v, o, mask, ss[0], ss[1], ss.shape[-1], g, g, g.numel(), 64, HEADS, 64)
 
     def qkv_epilogue(self, x, outs, gamma, c, s):
         n = len(outs)
@@ -348,7 +359,40 @@ def gemm_table(iters: int = 20, nsets: int = 6) -> list[dict]:
                      "tflops_library": round(flop / (t_l * 1e-3) / 1e12, 1), "speedup": round(t_l / t_f, 3)})
         torch.cuda.empty_cache()
 
+    def heads_case(name, parts):
+        """Projection stored head-split with the rows' sums of squares (rfk_gemm_f16_heads) against the route it
+        replaces: the plain projection followed by the QK-norm + head-split kernel (rfk_qkv_norm_rope_transpose)."""
+        N, K = parts * dim, dim
+        a = [_r((M, K), H16) for _ in range(nsets)]
+        w = [_r((N, K), H16, K ** -0.5) for _ in range(nsets)]
+        c = [torch.empty(M, N, device="cuda", dtype=H16) for _ in range(nsets)]
+        out = [torch.empty(parts, M * dim, device="cuda", dtype=H16) for _ in range(nsets)]
+        outs = [[o[p] for p in range(parts)] for o in out]
+        ss = torch.empty(parts, M, dim // 256, device="cuda")
+        g = torch.ones(dim, device="cuda")
+        gam = [g, g, None][:parts] if parts == 3 else [g]
+        seq = M if parts == 1 else 64
+        heads = dim // HD
+
+        def fused(i):
+            ops.gemm_f16_heads(a[i], w[i], out[i], ss, 3 if parts == 3 else 1, M, N, K, seq, heads, part_stride=M * dim)
+
+        def separate(i):
+            ops.gemm_f16(a[i], w[i], c[i], M, N, K)
+            ops.qkv_norm_rope_transpose(c[i], N, gam, outs[i], [False] * parts, None, None, M // seq, seq, heads, HD)
+
+        ops.gemm_set_path(0)
+        t_f = _time_graph(fused, nsets, iters)
+        t_l = _time_graph(separate, nsets, iters)
+        flop = 2.0 * M * N * K
+        rows.append({"gemm": name, "M": M, "N": N, "K": K, "epilogue": "heads + row statistics", "us_tcgen05": round(t_f * 1e3, 2),
+                     "tflops_tcgen05": round(flop / (t_f * 1e-3) / 1e12, 1), "us_projection_then_norm_kernel": round(t_l * 1e3, 2),
+                     "speedup": round(t_l / t_f, 3)})
+        torch.cuda.empty_cache()
+
     case("q / out projection", dim, dim, "none", 2.0 * M * dim * dim)
+    heads_case("cross q projection -> heads", 1)
+    heads_case("swin in projection -> heads", 3)
     case("out projection + residual", dim, dim, "residual", 2.0 * M * dim * dim)
     case("swin in projection", 3 * dim, dim, "none", 2.0 * M * 3 * dim * dim)
     case("FFN w1|w3 + SwiGLU", ffn, dim, "swiglu", 2.0 * M * 2 * ffn * dim)
