@@ -322,20 +322,39 @@ window_attention_kernel(const __half* __restrict__ Q, const __half* __restrict__
         cp_async16(tile_ptr<HD>(sV, r, c), Vh + r * HD + c * 8, 16);
     }
     if (NORMED) {
-        for (int i = tid; i < kWinTokens * 8; i += kWinThreads) {
-            const int r = i >> 3, c = i & 7;
+        // A thread keeps one 8-column chunk (c) of four rows (r0 + 16 k) of both tiles: the weights of its columns are
+        // loaded once, and every global load is issued before the first value is needed.
+        const int c = tid & 7, r0 = tid >> 3;
+        constexpr int kRowsPerThread = kWinTokens * 8 / kWinThreads;  // 4
+        Half8 raw[2][kRowsPerThread];
+        float ss[2][kRowsPerThread];
+        float gq[8], gk[8];
+#pragma unroll
+        for (int k = 0; k < kRowsPerThread; ++k) {
+            const int r = r0 + k * (kWinThreads / 8);
+            raw[0][k] = ldg_half8(Qh + r * HD + c * 8);
+            raw[1][k] = ldg_half8(Kh + r * HD + c * 8);
             const long long row = (long long)bw * kWinTokens + r;   // token row in window order
+            float sq = 0.0f, sk = 0.0f;
+            for (int t = 0; t < nrm.tiles; ++t) {
+                sq += __ldg(nrm.q_ss + row * nrm.tiles + t);
+                sk += __ldg(nrm.k_ss + row * nrm.tiles + t);
+            }
+            ss[0][k] = sq;
+            ss[1][k] = sk;
+        }
+        ldg_float8(nrm.gamma_q + h * HD + c * 8, gq);
+        ldg_float8(nrm.gamma_k + h * HD + c * 8, gk);
+#pragma unroll
+        for (int k = 0; k < kRowsPerThread; ++k) {
+            const int r = r0 + k * (kWinThreads / 8);
 #pragma unroll
             for (int which = 0; which < 2; ++which) {
-                const float* ssp = (which ? nrm.k_ss : nrm.q_ss) + row * nrm.tiles;
-                float ss = 0.0f;
-                for (int t = 0; t < nrm.tiles; ++t) ss += __ldg(ssp + t);
-                const float rinv = rsqrtf(ss * nrm.inv_dim + nrm.eps);
-                float x[8], gm[8];
-                unpack8(ldg_half8((which ? Kh : Qh) + r * HD + c * 8), x);
-                ldg_float8((which ? nrm.gamma_k : nrm.gamma_q) + h * HD + c * 8, gm);
+                const float rinv = rsqrtf(ss[which][k] * nrm.inv_dim + nrm.eps);
+                float x[8];
+                unpack8(raw[which][k], x);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) x[e] = (x[e] * rinv) * gm[e];
+                for (int e = 0; e < 8; ++e) x[e] = (x[e] * rinv) * (which ? gk[e] : gq[e]);
                 *reinterpret_cast<Half8*>(tile_ptr<HD>(which ? sK : sQ, r, c)) = pack8(x);
             }
         }

@@ -444,13 +444,16 @@ def _main():
             w_q, w_in, w1, w3, w2 = (_r(s_, H16, 0.03) for s_ in ((dim, dim), (3 * dim, dim), (ffn, dim), (ffn, dim), (dim, ffn)))
             y, y3, act, res = (torch.empty(M, n, device="cuda", dtype=H16) for n in (dim, 3 * dim, ffn, dim))
             res.normal_()
+            ss = torch.empty(3, M, dim // 256, device="cuda")
             for _ in range(a.iters):
+                ops.gemm_f16_heads(x, w_q, y, ss, 1, M, dim, dim, M, HEADS)                              # cross q -> heads + statistics
+                ops.gemm_f16_heads(x, w_in, y3, ss, 3, M, 3 * dim, dim, 64, HEADS, part_stride=M * dim)  # swin q|k|v -> heads
                 ops.gemm_f16(x, w_q, y, M, dim, dim)                       # q / out projection
                 ops.gemm_f16(x, w_in, y3, M, 3 * dim, dim)                 # swin in projection
                 ops.gemm_f16(x, w1, act, M, ffn, dim, w_up=w3)             # FFN w1 | w3 + SwiGLU
                 ops.gemm_f16(xh, w2, res, M, dim, ffn, residual=res)       # FFN w2 + residual, in place
             torch.cuda.synchronize()
-            print(json.dumps({"kernel": "rfk_gemm_f16 x4 shapes", "launched": 4 * a.iters, "error_word": ops.gemm_error()}))
+            print(json.dumps({"kernel": "rfk_gemm_f16_heads x2 + rfk_gemm_f16 x4 shapes", "launched": 6 * a.iters, "error_word": ops.gemm_error()}))
         return
     globals()["SOFTMAX_ROWS"] = a.softmax_rows
     backend = RfkBackend()
