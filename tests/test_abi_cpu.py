@@ -55,6 +55,19 @@ def test_null_and_bad_shapes_are_rejected_without_a_device():
     assert lib.rfk_flash_attention(fake, fake, fake, fake, 1, 2, 16, 8, 8, 48, 0, 0.125, null) == -2   # head size
     assert lib.rfk_flash_attention(fake, fake, fake, fake, 0, 2, 16, 8, 8, 64, 0, 0.125, null) == 0    # empty batch
     assert lib.rfk_flash_attention_set_path(7) == -1
+    # the extended attention, the head-split projection and the normed window attention: checks before any device work
+    ws_bytes = lib.rfk_flash_attention_workspace_bytes()
+    assert ws_bytes > 20 << 20
+    assert lib.rfk_flash_attention_ex(fake, fake, fake, fake, null, 0, 0, 0.0, fake, ws_bytes - 1, 1, 2, 16, 8, 8, 64, 0, 0.125, null) == -1   # workspace too small
+    assert lib.rfk_flash_attention_ex(fake, fake, fake, fake, fake, 0, 128, 1e-3, null, 0, 1, 2, 16, 8, 8, 64, 0, 0.125, null) == -1     # statistics without tiles
+    assert lib.rfk_flash_attention_ex(fake, fake, fake, fake, null, 0, 0, 0.0, null, 0, 1, 2, 16, 8, 8, 128, 0, 0.125, null) == -2       # tcgen05 kernel: head size 64 only
+    assert lib.rfk_flash_attention_ex(fake, fake, fake, fake, null, 0, 0, 0.0, null, 0, 1, 2, 0, 8, 8, 64, 0, 0.125, null) == 0          # no queries
+    assert lib.rfk_gemm_f16_heads(fake, 64, fake, 64, fake, 0, null, 1, 64, 256, 64, 32, 4, null) == -1     # statistics asked for, no buffer
+    assert lib.rfk_gemm_f16_heads(fake, 64, fake, 64, fake, 0, null, 0, 64, 200, 64, 32, 4, null) == -1     # N not parts * heads * 64
+    assert lib.rfk_gemm_f16_heads(fake, 64, fake, 64, fake, 0, null, 0, 0, 256, 64, 32, 4, null) == 0       # no rows
+    assert lib.rfk_window_attention_normed(fake, fake, fake, fake, null, fake, fake, 4, fake, null, 1024, 1e-3, 4, 16, 64, 64, 4, 0.125, null) == -1  # no k weights
+    assert lib.rfk_window_attention_normed(fake, fake, fake, fake, null, fake, fake, 4, fake, fake, 1024, 1e-3, 4, 16, 49, 64, 4, 0.125, null) == -2  # 7x7 windows
+    assert lib.rfk_rope_one_oop_strided(fake, fake, fake, fake, 1, 0, 0, 0, 4, 8, 64, 8, 8, null, -1, null) == -1   # negative stride
     assert lib.rfk_window_attention(fake, fake, fake, fake, null, 4, 2, 49, 64, 4, 0.125, null) == -2  # 7x7 windows
     assert lib.rfk_rmsnorm_residual_f16_windows(fake, fake, fake, fake, 1, 10, 10, 64, 4, 0, 1, 1e-3, null) == -1
     assert lib.rfk_rmsnorm_residual_f16_windows(fake, fake, fake, ctypes.c_void_p(512), 1, 8, 8, 60, 4, 0, 3, 1e-3, null) == -1
