@@ -282,6 +282,12 @@ int rfk_flash_attention_ex(const rfk_half* Q, const rfk_half* K, const rfk_half*
                            size_t workspace_bytes, int B, int H, int Sq, int Sk, int n_keys, int D, int o_bshd,
                            float scale, rfk_stream_t stream);
 size_t rfk_flash_attention_workspace_bytes(void);
+/* The work list rfk_flash_attention_ex would launch for `units` units (256 queries of one head each) of `n_tiles`
+ * 64-key tiles on a device with `sms` SMs, given a workspace: units [0, *whole_units) run whole, then *n_pieces pieces
+ * in launch order, each six values {unit, first tile, tiles, first slot of its unit, pieces of its unit, own slot}
+ * written to pieces[6 i ..] for i < max_pieces. Host only: touches no device. Diagnostic; no reference counterpart. */
+int rfk_flash_attention_plan(long long units, int n_tiles, int sms, int* whole_units, int* n_pieces,
+                             unsigned short* pieces, int max_pieces);
 /* 0: rfk_flash_attention_ex ignores its workspace (every unit whole), to time both schedules side by side; 1 (default):
  * it cuts where that pays. Process-wide. No reference counterpart. */
 int rfk_flash_attention_set_split(int on);

@@ -20,6 +20,7 @@ _SCALARS = {
     "long long": ctypes.c_longlong,
     "unsigned long long": ctypes.c_ulonglong,
     "size_t": ctypes.c_size_t,
+    "unsigned short": ctypes.c_ushort,
     "int64_t": ctypes.c_int64,
     "uint64_t": ctypes.c_uint64,
     "rfk_stream_t": ctypes.c_void_p,

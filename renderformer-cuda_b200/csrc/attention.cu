@@ -468,6 +468,7 @@ window_attention_kernel(const __half* __restrict__ Q, const __half* __restrict__
 extern std::atomic<int> g_attn_path;
 extern std::atomic<int> g_attn_split;
 size_t attention_tc_workspace_bytes();
+int attention_tc_plan(long long units, int n_tiles, int sms, int* whole_units, int* n_pieces, unsigned short* pieces, int max_pieces);
 int launch_attention_tc(const __half* Q, const __half* K, const __half* V, __half* O, int B, int H, int Sq, int Sk,
                         int n_keys, int o_bshd, float scale, cudaStream_t st, const float* row_ss, int ss_tiles,
                         int norm_dim, float norm_eps, void* ws, size_t ws_bytes);
@@ -517,6 +518,11 @@ extern "C" int rfk_flash_attention_ex(const rfk_half* Q, const rfk_half* K, cons
 }
 
 extern "C" size_t rfk_flash_attention_workspace_bytes(void) { return attention_tc_workspace_bytes(); }
+
+extern "C" int rfk_flash_attention_plan(long long units, int n_tiles, int sms, int* whole_units, int* n_pieces,
+                                        unsigned short* pieces, int max_pieces) {
+    return attention_tc_plan(units, n_tiles, sms, whole_units, n_pieces, pieces, max_pieces);
+}
 
 extern "C" int rfk_flash_attention_set_split(int on) {
     g_attn_split.store(on ? 1 : 0, std::memory_order_relaxed);

@@ -574,7 +574,7 @@ void plan_work(tcattn::WorkList& w, long long units, int n_tiles, int sms, bool 
     constexpr int kPieceCostTiles = 12;  // what a piece costs beyond its tiles (fill, publishing, merging), in tile times
     w.whole_units = (int)units;
     w.n_pieces = 0;
-    if (!split || sms <= 0 || units >= sms || units > 256 || n_tiles > 65535) return;  // 256 unit counters
+    if (!split || sms <= 0 || units <= 0 || units >= sms || units > 256 || n_tiles > 65535) return;  // 256 unit counters
     const long long tiles = units * n_tiles;
     constexpr int kMaxPiecesPerUnit = 8;  // the CTA that merges a unit reads its pieces one after the other
     const int shares = (int)std::min<long long>(std::min(sms, tcattn::kMaxPieces / 2), units * kMaxPiecesPerUnit);
@@ -610,6 +610,21 @@ void plan_work(tcattn::WorkList& w, long long units, int n_tiles, int sms, bool 
 }  // namespace
 
 size_t attention_tc_workspace_bytes() { return tcattn::kWsBytes; }
+
+// The launcher's plan for a grid, without launching anything (host only: no device is touched).
+int attention_tc_plan(long long units, int n_tiles, int sms, int* whole_units, int* n_pieces, unsigned short* pieces, int max_pieces) {
+    if (units < 0 || n_tiles <= 0 || sms <= 0 || !whole_units || !n_pieces || max_pieces < 0 || (max_pieces && !pieces)) return RFK_EINVAL;
+    tcattn::WorkList w;
+    plan_work(w, units, n_tiles, sms, true);
+    *whole_units = w.whole_units;
+    *n_pieces = w.n_pieces;
+    for (int i = 0; i < w.n_pieces && i < max_pieces; ++i) {
+        const tcattn::Piece& pc = w.pieces[i];
+        const unsigned short rec[6] = {pc.unit, pc.t0, pc.nt, pc.first, pc.count, pc.slot};
+        for (int k = 0; k < 6; ++k) pieces[i * 6 + k] = rec[k];
+    }
+    return RFK_OK;
+}
 
 // Launches the tcgen05 kernel; the caller has validated pointers, alignment and sizes (D == 64). ws (may be NULL):
 // attention_tc_workspace_bytes() bytes whose first 1024 are zero, for the key split.
