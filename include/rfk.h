@@ -422,6 +422,34 @@ int rfk_add_bias_nchw(rfk_half* x, const rfk_half* bias, int N, int C, long long
 int rfk_permute_bsd_to_nchw(const rfk_half* in, rfk_half* out, int B, int S, int D,
                             rfk_stream_t stream);
 
+/* Channels-last ([N,H,W,C] fp16, C % 8 == 0, 16-byte aligned; RFK_EUNSUPPORTED otherwise) companions of the four
+ * operators above: the layout the DPT head runs on (csrc/dpt.cu), where the token maps need no permute, the library's
+ * tensor-core convolutions take their operands as they are and a 1x1 convolution is rfk_linear. Values are bit-identical
+ * to the NCHW operators applied one after the other (every intermediate is still rounded to fp16).
+ * No reference counterpart as functions: they stand for the same lines of src/layers/dpt.cu in another layout. */
+/* x[r,c] = act(half(x[r,c] + bias[c])) (+ residual[r,c]) in place over [rows, C]; bias and residual may be NULL,
+ * silu != 0 applies x * sigmoid(x): add_bias_nchw (+ silu_inplace) (+ residual_add) in one pass — dpt.cu:88-96,
+ * :289-298, :397-409 */
+int rfk_bias_act_residual_nhwc(rfk_half* x, const rfk_half* bias, const rfk_half* residual, long long rows, int C,
+                               int silu, rfk_stream_t stream);
+/* y = x * sigmoid(x), out of place (n % 8 == 0): saves the copy the reference's in-place form needs before a residual
+ * unit — dpt.cu:397-400 */
+int rfk_silu(const rfk_half* x, rfk_half* y, long long n, rfk_stream_t stream);
+/* [N,H_in,W_in,C] -> [N,H_out,W_out,C], bilinear, align_corners = true, the reference's expression term for term —
+ * dpt.cu:240-286 */
+int rfk_bilinear_upsample_nhwc(const rfk_half* in, rfk_half* out, int N, int H_in, int W_in, int H_out, int W_out, int C,
+                               rfk_stream_t stream);
+/* Second half of a transposed convolution whose stride equals its kernel size f (the head's x4 and x2 resize layers,
+ * dpt.cu:182-236, :372-380): in [N*H*W, f*f*C] is the GEMM of the input pixels with the filter laid out by
+ * rfk_permute_filter(mode 1); out [N, H*f, W*f, C] = the scattered pixels + bias[c] (bias may be NULL). */
+int rfk_depth_to_space_bias_nhwc(const rfk_half* in, const rfk_half* bias, rfk_half* out, int N, int H, int W, int C, int f,
+                                 rfk_stream_t stream);
+/* [N, HW, C] -> [N, C, HW], any C (the head's last layer, C = 3) */
+int rfk_permute_nhwc_to_nchw(const rfk_half* in, rfk_half* out, int N, long long HW, int C, rfk_stream_t stream);
+/* One-off filter layouts for the channels-last head. mode 0: convolution filter [K, C, RS] -> [K, RS, C]; mode 1:
+ * transposed-convolution filter [Cin = K, Cout = C, RS = f*f] -> GEMM weight [(p * Cout + co), ci]. */
+int rfk_permute_filter(const rfk_half* w, rfk_half* out, int K, int C, int RS, int mode, rfk_stream_t stream);
+
 /* y32 = 10^float(half(elu(x16))) - 1 in one launch — replaces the chain
  * elu -> k_fp16_to_fp32_s -> pow10_minus1, src/pipeline/render_session.cu:249-253 */
 int rfk_post_elu_pow10(const rfk_half* x, float* y, long long n, float alpha,

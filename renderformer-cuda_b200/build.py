@@ -34,7 +34,7 @@ IO_SOURCES = ["io.cpp"]   # host code (safetensors, EXR, PNG); needs the CUDA ru
 
 KERNEL_SOURCES = [
     "abi.cu", "rmsnorm.cu", "softmax.cu", "rope.cu", "layout.cu",
-    "activations.cu", "nerf_pe.cu", "raygen.cu", "geometry.cu", "attention.cu", "attention_tc.cu", "gemm_tc.cu", "dpt_glue.cu",
+    "activations.cu", "nerf_pe.cu", "raygen.cu", "geometry.cu", "attention.cu", "attention_tc.cu", "gemm_tc.cu", "dpt_glue.cu", "dpt_nhwc.cu",
 ]
 
 

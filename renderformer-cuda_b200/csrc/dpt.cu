@@ -1,17 +1,20 @@
-// DPT image head: the four decoder feature taps -> [out_dim, H, W] image, composed from library
-// convolutions (cuDNN for k > 1 and the transposed ones, cuBLAS for 1x1) and the rfk element-wise
-// kernels (token-map permute, NCHW bias add, SiLU, residual add, bilinear upsample).
+// DPT image head: the four decoder feature taps -> [out_dim, H, W] image.
 //
-// Reference: rf::dpt_forward, src/layers/dpt.cu:322-461 (BANANASJIM/renderformer-cuda), with
-// rf::conv2d (:100-178) and rf::conv_transpose2d (:182-236); same operator sequence and the same
-// library calls. What is different:
-//   - nothing is allocated on the launch path. The reference calls cudaMallocAsync / cudaFreeAsync
-//     for every intermediate inside dpt_forward (and so inside its captured graph); here
-//     rfk_dpt_create sizes every intermediate once, picks the cuDNN algorithms, allocates one
-//     workspace, and records the whole head as a list of steps over fixed buffers.
-//     rfk_dpt_forward only walks that list, so it can be captured.
-//   - bias adds, SiLU, residual adds, the upsampling and the permute are the rfk kernels
-//     (vectorised; the bilinear kernel is bit-identical to the reference's).
+// Reference: rf::dpt_forward, src/layers/dpt.cu:322-461 (BANANASJIM/renderformer-cuda), with rf::conv2d (:100-178) and
+// rf::conv_transpose2d (:182-236); same operator sequence, same roundings between the operators. What is different:
+//   - the head runs channels-last ([N, H, W, C] fp16). The decoder's token maps are already in that layout, so the
+//     reference's permute to NCHW is gone; the library's tensor-core convolution kernels take channels-last operands as
+//     they are (handed NCHW tensors they convert every operand on the way in and out: 69 conversion launches, 35 % of
+//     the head's time when it ran that way); a 1x1 convolution is a row-major GEMM and goes to rfk_linear, i.e. the
+//     tcgen05 projection kernel with the bias in its epilogue; the two transposed convolutions (kernel = stride) are that
+//     same GEMM followed by a depth-to-space scatter. Only the 3x3 convolutions remain library (cuDNN) calls. Filters
+//     are re-laid out once, at plan time.
+//   - bias, SiLU and residual adds that follow a convolution are one pass (rfk_bias_act_residual_nhwc), bit-identical
+//     to the separate operators; the copy the reference's in-place SiLU forces before a residual unit is gone.
+//   - nothing is allocated on the launch path. The reference calls cudaMallocAsync / cudaFreeAsync for every
+//     intermediate inside dpt_forward (and so inside its captured graph); here rfk_dpt_create sizes every intermediate
+//     once, picks the cuDNN algorithms, allocates one workspace, and records the whole head as a list of steps over
+//     fixed buffers. rfk_dpt_forward only walks that list, so it can be captured.
 #include "layers_internal.h"
 
 #include <cudnn.h>
@@ -62,14 +65,14 @@ struct rfk_dpt {
         cudnnTensorDescriptor_t d = nullptr;
         if (cudnnCreateTensorDescriptor(&d) != CUDNN_STATUS_SUCCESS) return nullptr;
         tdescs.push_back(d);
-        if (cudnnSetTensor4dDescriptor(d, CUDNN_TENSOR_NCHW, CUDNN_DATA_HALF, n, c, h, w_) != CUDNN_STATUS_SUCCESS) return nullptr;
+        if (cudnnSetTensor4dDescriptor(d, CUDNN_TENSOR_NHWC, CUDNN_DATA_HALF, n, c, h, w_) != CUDNN_STATUS_SUCCESS) return nullptr;
         return d;
     }
     cudnnFilterDescriptor_t filter(int k, int c, int r, int s) {
         cudnnFilterDescriptor_t d = nullptr;
         if (cudnnCreateFilterDescriptor(&d) != CUDNN_STATUS_SUCCESS) return nullptr;
         fdescs.push_back(d);
-        if (cudnnSetFilter4dDescriptor(d, CUDNN_DATA_HALF, CUDNN_TENSOR_NCHW, k, c, r, s) != CUDNN_STATUS_SUCCESS) return nullptr;
+        if (cudnnSetFilter4dDescriptor(d, CUDNN_DATA_HALF, CUDNN_TENSOR_NHWC, k, c, r, s) != CUDNN_STATUS_SUCCESS) return nullptr;
         return d;
     }
     cudnnConvolutionDescriptor_t conv(int pad, int stride) {
@@ -83,30 +86,29 @@ struct rfk_dpt {
         return d;
     }
 
-    // out [B, Cout, Ho, Wo] = conv(in [B, Cin, H, W], weight [Cout, Cin, k, k]) (+ bias). `in` may be null: then the step
-    // reads feature tap `feat_index` through `nchw_in` (already permuted by the previous step).
-    int add_conv(const rfk_half* in, const rfk_half* weight, const rfk_half* bias, rfk_half* o, int Cin, int H, int W, int Cout,
-                 int k, int stride, int pad) {
+    // o [B, Ho, Wo, Cout] = conv(in [B, H, W, Cin], weight [Cout, Cin, k, k] as the reference stores it) + bias, then SiLU
+    // if silu, then + residual if given. in == nullptr: the step reads feature tap `tap` ([B, pH*pW, dim] is [B, pH, pW, dim]).
+    int add_conv(const rfk_half* in, int tap, const rfk_half* weight, const rfk_half* bias, rfk_half* o, int Cin, int H, int W,
+                 int Cout, int k, int stride, int pad, bool silu = false, const rfk_half* residual = nullptr) {
         const int Ho = (H + 2 * pad - k) / stride + 1, Wo = (W + 2 * pad - k) / stride + 1;
-        const int Bn = B;
+        const long long rows_out = (long long)B * Ho * Wo;
         ++n_convs;
+        rfk_ctx* c = ctx;
         if (k == 1 && stride == 1 && pad == 0) {
-            // 1x1: per image out[Cout, HW] = weight[Cout, Cin] in[Cin, HW] (src/layers/dpt.cu:112-126)
-            rfk_ctx* c = ctx;
-            program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {
-                if (cublasSetStream(c->blas, st) != CUBLAS_STATUS_SUCCESS) return 1000;
-                const float one = 1.0f, zero = 0.0f;
-                for (int n = 0; n < Bn; ++n) {
-                    cublasStatus_t s = cublasGemmEx(c->blas, CUBLAS_OP_N, CUBLAS_OP_N, H * W, Cout, Cin, &one,
-                                                    in + (size_t)n * Cin * H * W, CUDA_R_16F, H * W, weight, CUDA_R_16F, Cin, &zero,
-                                                    o + (size_t)n * Cout * H * W, CUDA_R_16F, H * W, CUBLAS_COMPUTE_32F,
-                                                    CUBLAS_GEMM_DEFAULT);
-                    if (s != CUBLAS_STATUS_SUCCESS) return 1000 + (int)s;
-                }
-                return bias ? rfk_add_bias_nchw(o, bias, Bn, Cout, (long long)H * W, (rfk_stream_t)st) : RFK_OK;
+            // 1x1: out [B*H*W, Cout] = in [B*H*W, Cin] weight[Cout, Cin]^T (+ bias in the GEMM's epilogue) (src/layers/dpt.cu:112-126)
+            const long long M = (long long)B * H * W;
+            if (M > 0x7fffffffLL) return RFK_EUNSUPPORTED;
+            program.push_back([=](const rfk_half* const* feats, cudaStream_t st) -> int {
+                TRY(rfk_linear(c, in ? in : feats[tap], weight, bias, o, (int)M, Cout, Cin, (rfk_stream_t)st));
+                if (silu || residual) return rfk_bias_act_residual_nhwc(o, nullptr, residual, rows_out, Cout, silu, (rfk_stream_t)st);
+                return RFK_OK;
             });
             return RFK_OK;
         }
+        if (!in) return RFK_EINVAL;
+        rfk_half* wk = alloc((size_t)Cout * Cin * k * k);  // [Cout, k, k, Cin]
+        if (!wk) return (int)cudaErrorMemoryAllocation;
+        TRY(rfk_permute_filter(weight, wk, Cout, Cin, k * k, 0, nullptr));
         cudnnTensorDescriptor_t xd = tensor(B, Cin, H, W), yd = tensor(B, Cout, Ho, Wo);
         cudnnFilterDescriptor_t fd = filter(Cout, Cin, k, k);
         cudnnConvolutionDescriptor_t cd = conv(pad, stride);
@@ -114,7 +116,7 @@ struct rfk_dpt {
         int returned = 0;
         cudnnConvolutionFwdAlgoPerf_t perf[4];
         DNN_TRY(cudnnGetConvolutionForwardAlgorithm_v7(dnn, xd, fd, cd, yd, 4, &returned, perf));
-        if (returned < 1) return RFK_EUNSUPPORTED;
+        if (returned < 1 || perf[0].status != CUDNN_STATUS_SUCCESS) return RFK_EUNSUPPORTED;
         const cudnnConvolutionFwdAlgo_t algo = perf[0].algo;
         size_t ws = 0;
         DNN_TRY(cudnnGetConvolutionForwardWorkspaceSize(dnn, xd, fd, cd, yd, algo, &ws));
@@ -123,77 +125,69 @@ struct rfk_dpt {
         program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {
             const float one = 1.0f, zero = 0.0f;
             DNN_TRY(cudnnSetStream(self->dnn, st));
-            DNN_TRY(cudnnConvolutionForward(self->dnn, &one, xd, in, fd, weight, cd, algo, self->workspace, ws, &zero, yd, o));
-            return bias ? rfk_add_bias_nchw(o, bias, Bn, Cout, (long long)Ho * Wo, (rfk_stream_t)st) : RFK_OK;
+            DNN_TRY(cudnnConvolutionForward(self->dnn, &one, xd, in, fd, wk, cd, algo, self->workspace, ws, &zero, yd, o));
+            if (bias || silu || residual) return rfk_bias_act_residual_nhwc(o, bias, residual, rows_out, Cout, silu, (rfk_stream_t)st);
+            return RFK_OK;
         });
         return RFK_OK;
     }
 
-    // transposed convolution = data gradient of a convolution with the same filter (src/layers/dpt.cu:182-236)
+    // Transposed convolution with kernel = stride = f and no padding (the head's only kind, src/layers/dpt.cu:182-236,
+    // :372-380): every input pixel produces its own f x f block of output pixels, so it is one GEMM with the filter laid
+    // out as [(i, j, co), ci] followed by a scatter of the blocks (+ bias).
     int add_conv_transpose(const rfk_half* in, const rfk_half* weight, const rfk_half* bias, rfk_half* o, int Cin, int H, int W,
-                           int Cout, int k, int stride, int pad) {
-        const int Ho = (H - 1) * stride - 2 * pad + k, Wo = (W - 1) * stride - 2 * pad + k;
-        const int Bn = B;
+                           int Cout, int f) {
         ++n_convs;
-        cudnnTensorDescriptor_t dyd = tensor(B, Cin, H, W), dxd = tensor(B, Cout, Ho, Wo);
-        cudnnFilterDescriptor_t fd = filter(Cin, Cout, k, k);
-        cudnnConvolutionDescriptor_t cd = conv(pad, stride);
-        if (!dyd || !dxd || !fd || !cd) return RFK_EINVAL;
-        int returned = 0;
-        cudnnConvolutionBwdDataAlgoPerf_t perf[4];
-        DNN_TRY(cudnnGetConvolutionBackwardDataAlgorithm_v7(dnn, fd, dyd, cd, dxd, 4, &returned, perf));
-        if (returned < 1) return RFK_EUNSUPPORTED;
-        const cudnnConvolutionBwdDataAlgo_t algo = perf[0].algo;
-        size_t ws = 0;
-        DNN_TRY(cudnnGetConvolutionBackwardDataWorkspaceSize(dnn, fd, dyd, cd, dxd, algo, &ws));
-        ws_bytes = std::max(ws_bytes, ws);
-        rfk_dpt* self = this;
+        const long long M = (long long)B * H * W;
+        const long long N = (long long)f * f * Cout;
+        if (M > 0x7fffffffLL || N > 0x7fffffffLL) return RFK_EUNSUPPORTED;
+        rfk_half* wg = alloc((size_t)N * Cin);
+        rfk_half* blocks = alloc((size_t)M * N);
+        if (!wg || !blocks) return (int)cudaErrorMemoryAllocation;
+        TRY(rfk_permute_filter(weight, wg, Cin, Cout, f * f, 1, nullptr));
+        rfk_ctx* c = ctx;
+        const int Bn = B;
         program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {
-            const float one = 1.0f, zero = 0.0f;
-            DNN_TRY(cudnnSetStream(self->dnn, st));
-            DNN_TRY(cudnnConvolutionBackwardData(self->dnn, &one, fd, weight, dyd, in, cd, algo, self->workspace, ws, &zero, dxd, o));
-            return bias ? rfk_add_bias_nchw(o, bias, Bn, Cout, (long long)Ho * Wo, (rfk_stream_t)st) : RFK_OK;
+            TRY(rfk_linear(c, in, wg, nullptr, blocks, (int)M, (int)N, Cin, (rfk_stream_t)st));
+            return rfk_depth_to_space_bias_nhwc(blocks, bias, o, Bn, H, W, Cout, f, (rfk_stream_t)st);
         });
         return RFK_OK;
     }
 
-    // residual convolution unit, in place on x (src/layers/dpt.cu:397-409): x <- conv2(silu(conv1(silu(x)))) + x
-    int add_rcu(const rfk_rcu_weights& r, rfk_half* x, int F, int H, int W) {
+    // residual convolution unit (src/layers/dpt.cu:397-409): *result <- conv2(silu(conv1(silu(x)))) + x; x is left as it was
+    int add_rcu(const rfk_rcu_weights& r, const rfk_half* x, int F, int H, int W, rfk_half** result) {
         const long long n = (long long)B * F * H * W;
-        rfk_half* x_orig = alloc((size_t)n);
+        rfk_half* t0 = alloc((size_t)n);
         rfk_half* t1 = alloc((size_t)n);
-        if (!x_orig || !t1) return (int)cudaErrorMemoryAllocation;
-        program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {
-            cudaError_t e = cudaMemcpyAsync(x_orig, x, (size_t)n * sizeof(rfk_half), cudaMemcpyDeviceToDevice, st);
-            if (e != cudaSuccess) return (int)e;
-            return rfk_silu_inplace(x, n, (rfk_stream_t)st);
-        });
-        TRY(add_conv(x, r.conv1_w, r.conv1_b, t1, F, H, W, F, 3, 1, 1));
-        program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int { return rfk_silu_inplace(t1, n, (rfk_stream_t)st); });
-        TRY(add_conv(t1, r.conv2_w, r.conv2_b, x, F, H, W, F, 3, 1, 1));
-        program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int { return rfk_residual_add(x, x_orig, n, (rfk_stream_t)st); });
+        if (!t0 || !t1) return (int)cudaErrorMemoryAllocation;
+        program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int { return rfk_silu(x, t0, n, (rfk_stream_t)st); });
+        TRY(add_conv(t0, -1, r.conv1_w, r.conv1_b, t1, F, H, W, F, 3, 1, 1, /*silu=*/true));
+        TRY(add_conv(t1, -1, r.conv2_w, r.conv2_b, t0, F, H, W, F, 3, 1, 1, /*silu=*/false, /*residual=*/x));
+        *result = t0;
         return RFK_OK;
     }
 
-    // feature fusion block (src/layers/dpt.cu:411-426); returns the [B, F, th, tw] result buffer in *result
+    // feature fusion block (src/layers/dpt.cu:411-426); returns the [B, th, tw, F] result buffer in *result
     int add_refinenet(int i, rfk_half* path_in, rfk_half* lr, int ph, int pw, int th, int tw, rfk_half** result) {
         const int F = w.features_dim;
         const rfk_ffb_weights& f = w.refinenet[i];
         if (f.has_resconv1) {
             if (!lr) return RFK_EINVAL;
-            TRY(add_rcu(f.rcu1, lr, F, ph, pw));
+            rfk_half* r1 = nullptr;
+            TRY(add_rcu(f.rcu1, lr, F, ph, pw, &r1));
             const long long n = (long long)B * F * ph * pw;
-            program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int { return rfk_residual_add(path_in, lr, n, (rfk_stream_t)st); });
+            program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int { return rfk_residual_add(path_in, r1, n, (rfk_stream_t)st); });
         }
-        TRY(add_rcu(f.rcu2, path_in, F, ph, pw));
+        rfk_half* r2 = nullptr;
+        TRY(add_rcu(f.rcu2, path_in, F, ph, pw, &r2));
         rfk_half* up = alloc((size_t)B * F * th * tw);
         rfk_half* res = alloc((size_t)B * F * th * tw);
         if (!up || !res) return (int)cudaErrorMemoryAllocation;
         const int Bn = B;
         program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {
-            return rfk_bilinear_upsample(path_in, up, Bn, F, ph, pw, th, tw, (rfk_stream_t)st);
+            return rfk_bilinear_upsample_nhwc(r2, up, Bn, ph, pw, th, tw, F, (rfk_stream_t)st);
         });
-        TRY(add_conv(up, f.out_conv_w, f.out_conv_b, res, F, th, tw, F, 1, 1, 0));
+        TRY(add_conv(up, -1, f.out_conv_w, f.out_conv_b, res, F, th, tw, F, 1, 1, 0));
         *result = res;
         return RFK_OK;
     }
@@ -204,20 +198,15 @@ struct rfk_dpt {
         int rh[4], rw[4];
         for (int i = 0; i < 4; ++i) {
             const int C = w.out_channels[i];
-            rfk_half* nchw = alloc((size_t)B * dim * S);
             rfk_half* projected = alloc((size_t)B * C * S);
-            if (!nchw || !projected) return (int)cudaErrorMemoryAllocation;
-            const int Bn = B, Sn = S, dn = dim;
-            program.push_back([=](const rfk_half* const* feats, cudaStream_t st) -> int {
-                return rfk_permute_bsd_to_nchw(feats[i], nchw, Bn, Sn, dn, (rfk_stream_t)st);
-            });
-            TRY(add_conv(nchw, w.project_w[i], w.project_b[i], projected, dim, pH, pW, C, 1, 1, 0));
+            if (!projected) return (int)cudaErrorMemoryAllocation;
+            TRY(add_conv(nullptr, i, w.project_w[i], w.project_b[i], projected, dim, pH, pW, C, 1, 1, 0));  // straight off the token map
             if (i == 0 || i == 1) {  // x4 / x2 transposed convolution, kernel = stride
                 const int f = i == 0 ? 4 : 2;
                 rh[i] = pH * f; rw[i] = pW * f;
                 resized[i] = alloc((size_t)B * C * rh[i] * rw[i]);
                 if (!resized[i]) return (int)cudaErrorMemoryAllocation;
-                TRY(add_conv_transpose(projected, w.resize_w[i], w.resize_b[i], resized[i], C, pH, pW, C, f, f, 0));
+                TRY(add_conv_transpose(projected, w.resize_w[i], w.resize_b[i], resized[i], C, pH, pW, C, f));
             } else if (i == 2) {
                 rh[i] = pH; rw[i] = pW;
                 resized[i] = projected;
@@ -225,14 +214,14 @@ struct rfk_dpt {
                 rh[i] = (pH + 1) / 2; rw[i] = (pW + 1) / 2;
                 resized[i] = alloc((size_t)B * C * rh[i] * rw[i]);
                 if (!resized[i]) return (int)cudaErrorMemoryAllocation;
-                TRY(add_conv(projected, w.resize_w[i], w.resize_b[i], resized[i], C, pH, pW, C, 3, 2, 1));
+                TRY(add_conv(projected, -1, w.resize_w[i], w.resize_b[i], resized[i], C, pH, pW, C, 3, 2, 1));
             }
         }
         rfk_half* layer_rn[4];
         for (int i = 0; i < 4; ++i) {
             layer_rn[i] = alloc((size_t)B * F * rh[i] * rw[i]);
             if (!layer_rn[i]) return (int)cudaErrorMemoryAllocation;
-            TRY(add_conv(resized[i], w.layer_rn_w[i], nullptr, layer_rn[i], w.out_channels[i], rh[i], rw[i], F, 3, 1, 1));
+            TRY(add_conv(resized[i], -1, w.layer_rn_w[i], nullptr, layer_rn[i], w.out_channels[i], rh[i], rw[i], F, 3, 1, 1));
         }
         rfk_half *path4, *path3, *path2, *path1;
         TRY(add_refinenet(3, layer_rn[3], nullptr, rh[3], rw[3], rh[2], rw[2], &path4));
@@ -245,22 +234,27 @@ struct rfk_dpt {
         rfk_half* oc1 = alloc((size_t)B * fh * oh * ow);
         rfk_half* oc1_up = alloc((size_t)B * fh * full_h * full_w);
         rfk_half* oc2a = alloc((size_t)B * 32 * full_h * full_w);
-        out = alloc((size_t)B * w.out_dim * full_h * full_w);
-        if (!oc1 || !oc1_up || !oc2a || !out) return (int)cudaErrorMemoryAllocation;
-        TRY(add_conv(path1, w.output_conv1_w, w.output_conv1_b, oc1, F, oh, ow, fh, 3, 1, 1));
+        rfk_half* oc2b = alloc((size_t)B * w.out_dim * full_h * full_w);  // [B, H, W, out_dim]
+        out = alloc((size_t)B * w.out_dim * full_h * full_w);            // [B, out_dim, H, W]
+        if (!oc1 || !oc1_up || !oc2a || !oc2b || !out) return (int)cudaErrorMemoryAllocation;
+        TRY(add_conv(path1, -1, w.output_conv1_w, w.output_conv1_b, oc1, F, oh, ow, fh, 3, 1, 1));
         const int Bn = B;
         program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {
-            return rfk_bilinear_upsample(oc1, oc1_up, Bn, fh, oh, ow, full_h, full_w, (rfk_stream_t)st);
+            return rfk_bilinear_upsample_nhwc(oc1, oc1_up, Bn, oh, ow, full_h, full_w, fh, (rfk_stream_t)st);
         });
-        TRY(add_conv(oc1_up, w.output_conv2a_w, w.output_conv2a_b, oc2a, fh, full_h, full_w, 32, 3, 1, 1));
-        const long long n2a = (long long)B * 32 * full_h * full_w;
-        program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int { return rfk_silu_inplace(oc2a, n2a, (rfk_stream_t)st); });
-        TRY(add_conv(oc2a, w.output_conv2b_w, w.output_conv2b_b, out, 32, full_h, full_w, w.out_dim, 1, 1, 0));
+        TRY(add_conv(oc1_up, -1, w.output_conv2a_w, w.output_conv2a_b, oc2a, fh, full_h, full_w, 32, 3, 1, 1, /*silu=*/true));
+        TRY(add_conv(oc2a, -1, w.output_conv2b_w, w.output_conv2b_b, oc2b, 32, full_h, full_w, w.out_dim, 1, 1, 0));
+        rfk_half* image = out;
+        const int od = w.out_dim;
+        program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {  // the interface's image is planar
+            return rfk_permute_nhwc_to_nchw(oc2b, image, Bn, (long long)full_h * full_w, od, (rfk_stream_t)st);
+        });
         if (ws_bytes) {
             if (cudaMalloc(&workspace, ws_bytes) != cudaSuccess) return (int)cudaErrorMemoryAllocation;
             owned.push_back(workspace);
         }
-        return RFK_OK;
+        // the filter re-layouts above ran on the default stream: they must be complete before the first forward
+        return (int)cudaDeviceSynchronize();
     }
 };
 
@@ -279,6 +273,10 @@ extern "C" int rfk_dpt_create(rfk_ctx* ctx, const rfk_dpt_weights* w, int B, int
                               rfk_dpt** out) {
     if (!ctx || !w || !out || B <= 0 || dim <= 0 || patch_h <= 0 || patch_w <= 0 || patch_size <= 0) return RFK_EINVAL;
     if (w->features_dim <= 0 || w->features_dim % 2 || w->out_dim <= 0) return RFK_EINVAL;
+    // the channels-last element-wise kernels move 8 channels per access
+    if (w->features_dim % 16 || dim % 8) return RFK_EUNSUPPORTED;
+    for (int i = 0; i < 4; ++i)
+        if (w->out_channels[i] % 8) return RFK_EUNSUPPORTED;
     for (int i = 0; i < 4; ++i)
         if (w->out_channels[i] <= 0 || !w->project_w[i] || !w->layer_rn_w[i] || (i != 2 && !w->resize_w[i])) return RFK_EINVAL;
     rfk_dpt* d = new rfk_dpt();

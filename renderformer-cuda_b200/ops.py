@@ -384,6 +384,34 @@ def permute_bsd_to_nchw(inp, out, B, S, D):
     _call("rfk_permute_bsd_to_nchw", _p(inp, H, "in"), _p(out, H, "out"), B, S, D, _stream())
 
 
+# channels-last ([N, H, W, C]) companions: the layout the DPT head runs on
+
+def bias_act_residual_nhwc(x, bias, residual, rows, C, silu=False):
+    """x[r, c] = act(half(x + bias[c])) (+ residual) in place; bias / residual may be None."""
+    _call("rfk_bias_act_residual_nhwc", _p(x, H, "x"), _p(bias, H, "bias"), _p(residual, H, "residual"), rows, C, int(silu), _stream())
+
+
+def silu(x, y, n):
+    _call("rfk_silu", _p(x, H, "x"), _p(y, H, "y"), n, _stream())
+
+
+def bilinear_upsample_nhwc(inp, out, N, H_in, W_in, H_out, W_out, C):
+    _call("rfk_bilinear_upsample_nhwc", _p(inp, H, "in"), _p(out, H, "out"), N, H_in, W_in, H_out, W_out, C, _stream())
+
+
+def depth_to_space_bias_nhwc(inp, bias, out, N, H_, W_, C, f):
+    _call("rfk_depth_to_space_bias_nhwc", _p(inp, H, "in"), _p(bias, H, "bias"), _p(out, H, "out"), N, H_, W_, C, f, _stream())
+
+
+def permute_nhwc_to_nchw(inp, out, N, HW, C):
+    _call("rfk_permute_nhwc_to_nchw", _p(inp, H, "in"), _p(out, H, "out"), N, HW, C, _stream())
+
+
+def permute_filter(w, out, K, C, RS, mode):
+    """mode 0: [K, C, RS] -> [K, RS, C]; mode 1: transposed-convolution filter [Cin, Cout, f*f] -> [(p, co), ci]."""
+    _call("rfk_permute_filter", _p(w, H, "w"), _p(out, H, "out"), K, C, RS, mode, _stream())
+
+
 def post_elu_pow10(x, y, n, alpha=1e-3):
     _call("rfk_post_elu_pow10", _p(x, H, "x"), _p(y, F, "y"), n, alpha, _stream())
 

@@ -127,3 +127,105 @@ def test_session_with_dpt_head_renders_an_image_and_replays_it():
     s.render_frame(c2w[0], float(fov[0]))
     assert torch.equal(s.download(), toks[True][0])
     s.close()
+
+
+# ---------------------------------------------------------------- channels-last companions (what the head runs on)
+
+def _ops():
+    import renderformer_cuda_b200 as pkg
+    return pkg.ops
+
+
+def _nhwc(t):   # [N, C, H, W] -> [N, H, W, C] contiguous
+    return t.permute(0, 2, 3, 1).contiguous()
+
+
+@pytest.mark.parametrize("bias,silu,res", [(True, False, False), (True, True, False), (True, False, True), (False, True, True),
+                                           (False, False, True), (True, True, True)])
+def test_fused_bias_activation_residual_equals_the_separate_operators(bias, silu, res):
+    """One channels-last pass against add_bias_nchw -> silu_inplace -> residual_add on the same values: bit-identical,
+    because every intermediate is still rounded to fp16."""
+    o = _ops()
+    g = torch.Generator(device="cuda").manual_seed(11)
+    N, C, Hh, Ww = 2, 48, 9, 13
+    x = torch.randn(N, C, Hh, Ww, device="cuda", generator=g).half()
+    b = torch.randn(C, device="cuda", generator=g).half()
+    r = torch.randn(N, C, Hh, Ww, device="cuda", generator=g).half()
+    want = x.clone()
+    if bias:
+        o.add_bias_nchw(want, b, N, C, Hh * Ww)
+    if silu:
+        o.silu_inplace(want, want.numel())
+    if res:
+        o.residual_add(want, r, want.numel())
+    got = _nhwc(x)
+    o.bias_act_residual_nhwc(got, b if bias else None, _nhwc(r) if res else None, N * Hh * Ww, C, silu)
+    torch.cuda.synchronize()
+    assert torch.equal(got, _nhwc(want))
+
+
+def test_out_of_place_silu_and_channels_last_upsample_equal_the_nchw_operators():
+    o = _ops()
+    g = torch.Generator(device="cuda").manual_seed(12)
+    N, C, Hi, Wi, Ho, Wo = 2, 24, 7, 5, 16, 11
+    x = torch.randn(N, C, Hi, Wi, device="cuda", generator=g).half()
+    want = torch.empty(N, C, Ho, Wo, device="cuda", dtype=H16)
+    o.bilinear_upsample(x, want, N, C, Hi, Wi, Ho, Wo)
+    got = torch.empty(N, Ho, Wo, C, device="cuda", dtype=H16)
+    o.bilinear_upsample_nhwc(_nhwc(x), got, N, Hi, Wi, Ho, Wo, C)
+    y = torch.empty_like(x)
+    o.silu(x, y, x.numel())
+    x2 = x.clone()
+    o.silu_inplace(x2, x2.numel())
+    torch.cuda.synchronize()
+    assert torch.equal(got, _nhwc(want))
+    assert torch.equal(y, x2)
+    # the same doubling as inside the head: 64 -> 128 at 256 channels
+    big = torch.randn(1, 256, 64, 64, device="cuda", generator=g).half()
+    w2 = torch.empty(1, 256, 128, 128, device="cuda", dtype=H16)
+    o.bilinear_upsample(big, w2, 1, 256, 64, 64, 128, 128)
+    g2 = torch.empty(1, 128, 128, 256, device="cuda", dtype=H16)
+    o.bilinear_upsample_nhwc(_nhwc(big), g2, 1, 64, 64, 128, 128, 256)
+    torch.cuda.synchronize()
+    assert torch.equal(g2, _nhwc(w2))
+
+
+@pytest.mark.parametrize("f,Cin,Cout", [(4, 32, 32), (2, 64, 40)])
+def test_transposed_convolution_as_gemm_and_scatter(f, Cin, Cout):
+    """kernel = stride transposed convolution = GEMM with the re-laid-out filter + depth-to-space (+ bias), against torch's
+    conv_transpose2d in fp32 (tolerance: one fp16 rounding of the product plus one of the bias add)."""
+    o = _ops()
+    g = torch.Generator(device="cuda").manual_seed(f)
+    N, Hh, Ww = 2, 6, 5
+    x = torch.randn(N, Cin, Hh, Ww, device="cuda", generator=g).half()
+    w = (torch.randn(Cin, Cout, f, f, device="cuda", generator=g) * Cin ** -0.5).half()
+    b = torch.randn(Cout, device="cuda", generator=g).half()
+    wg = torch.empty(f * f * Cout, Cin, device="cuda", dtype=H16)
+    o.permute_filter(w, wg, Cin, Cout, f * f, 1)
+    torch.cuda.synchronize()
+    assert torch.equal(wg.view(f * f, Cout, Cin), w.permute(2, 3, 1, 0).reshape(f * f, Cout, Cin))
+    xr = _nhwc(x).view(N * Hh * Ww, Cin)
+    blocks = (xr.float() @ wg.float().t()).half()                      # the GEMM the head runs through rfk_linear
+    got = torch.empty(N, Hh * f, Ww * f, Cout, device="cuda", dtype=H16)
+    o.depth_to_space_bias_nhwc(blocks, b, got, N, Hh, Ww, Cout, f)
+    torch.cuda.synchronize()
+    want = torch.nn.functional.conv_transpose2d(x.float(), w.float(), b.float(), stride=f)
+    err = (got.permute(0, 3, 1, 2).float() - want).abs()
+    assert (err <= 2e-3 + 2.0 ** -9 * want.abs()).all(), err.max().item()
+
+
+def test_filter_and_image_permutes_are_exact():
+    o = _ops()
+    g = torch.Generator(device="cuda").manual_seed(13)
+    w = torch.randn(24, 16, 3, 3, device="cuda", generator=g).half()
+    out = torch.empty(24, 3, 3, 16, device="cuda", dtype=H16)
+    o.permute_filter(w, out, 24, 16, 9, 0)
+    img = torch.randn(2, 10, 7, 3, device="cuda", generator=g).half()
+    planar = torch.empty(2, 3, 10, 7, device="cuda", dtype=H16)
+    o.permute_nhwc_to_nchw(img, planar, 2, 70, 3)
+    torch.cuda.synchronize()
+    assert torch.equal(out, w.permute(0, 2, 3, 1).contiguous())
+    assert torch.equal(planar, img.permute(0, 3, 1, 2).contiguous())
+    with pytest.raises(o.RfkError) as e:           # channel counts that are not multiples of 8 are refused, not mangled
+        o.bias_act_residual_nhwc(torch.zeros(4, 12, device="cuda", dtype=H16), None, None, 4, 12, True)
+    assert e.value.status == -2
