@@ -20,7 +20,10 @@
 #include <cudnn.h>
 
 #include <algorithm>
+#include <array>
 #include <functional>
+#include <map>
+#include <mutex>
 #include <vector>
 
 namespace {
@@ -37,6 +40,13 @@ namespace {
     } while (0)
 
 using Step = std::function<int(const rfk_half* const* feats, cudaStream_t st)>;
+
+// The algorithm measured fastest for a convolution problem, remembered for the life of the process: every head planned
+// for the same shapes then runs the same kernels (two sessions of one model produce the same bits), and later plans
+// skip the search. Key: device, batch, Cin, H, W, Cout, k, stride, pad.
+struct AlgoChoice { cudnnConvolutionFwdAlgo_t algo; size_t workspace; };
+std::mutex g_algo_mutex;
+std::map<std::array<int, 9>, AlgoChoice> g_algo_cache;
 
 }  // namespace
 
@@ -113,13 +123,35 @@ struct rfk_dpt {
         cudnnFilterDescriptor_t fd = filter(Cout, Cin, k, k);
         cudnnConvolutionDescriptor_t cd = conv(pad, stride);
         if (!xd || !yd || !fd || !cd) return RFK_EINVAL;
+        // The algorithm is measured, not guessed: the library runs its candidates on this problem once, here at plan
+        // time, and the fastest whose workspace fits the cap is kept (the heuristic's first choice ran the 128-channel
+        // 3x3 layers at a fifth of the tensor peak). Falls back to the heuristic if the search cannot run.
+        constexpr size_t kWorkspaceCap = 512ull << 20;
         int returned = 0;
-        cudnnConvolutionFwdAlgoPerf_t perf[4];
-        DNN_TRY(cudnnGetConvolutionForwardAlgorithm_v7(dnn, xd, fd, cd, yd, 4, &returned, perf));
-        if (returned < 1 || perf[0].status != CUDNN_STATUS_SUCCESS) return RFK_EUNSUPPORTED;
-        const cudnnConvolutionFwdAlgo_t algo = perf[0].algo;
+        cudnnConvolutionFwdAlgoPerf_t perf[16];
+        cudnnConvolutionFwdAlgo_t algo = CUDNN_CONVOLUTION_FWD_ALGO_IMPLICIT_PRECOMP_GEMM;
         size_t ws = 0;
-        DNN_TRY(cudnnGetConvolutionForwardWorkspaceSize(dnn, xd, fd, cd, yd, algo, &ws));
+        bool chosen = false;
+        const std::array<int, 9> key = {ctx->device, B, Cin, H, W, Cout, k, stride, pad};
+        {
+            std::lock_guard<std::mutex> lock(g_algo_mutex);
+            const auto it = g_algo_cache.find(key);
+            if (it != g_algo_cache.end()) { algo = it->second.algo; ws = it->second.workspace; chosen = true; }
+        }
+        if (!chosen && cudnnFindConvolutionForwardAlgorithm(dnn, xd, fd, cd, yd, 16, &returned, perf) == CUDNN_STATUS_SUCCESS) {
+            for (int a = 0; a < returned && !chosen; ++a)
+                if (perf[a].status == CUDNN_STATUS_SUCCESS && perf[a].memory <= kWorkspaceCap) { algo = perf[a].algo; ws = perf[a].memory; chosen = true; }
+            if (chosen) {
+                std::lock_guard<std::mutex> lock(g_algo_mutex);
+                g_algo_cache.emplace(key, AlgoChoice{algo, ws});
+            }
+        }
+        if (!chosen) {
+            DNN_TRY(cudnnGetConvolutionForwardAlgorithm_v7(dnn, xd, fd, cd, yd, 16, &returned, perf));
+            if (returned < 1 || perf[0].status != CUDNN_STATUS_SUCCESS) return RFK_EUNSUPPORTED;
+            algo = perf[0].algo;
+            DNN_TRY(cudnnGetConvolutionForwardWorkspaceSize(dnn, xd, fd, cd, yd, algo, &ws));
+        }
         ws_bytes = std::max(ws_bytes, ws);
         rfk_dpt* self = this;
         program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {

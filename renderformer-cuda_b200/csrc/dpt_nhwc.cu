@@ -26,7 +26,7 @@ bias_act_residual_nhwc_kernel(__half* __restrict__ x, const __half* __restrict__
     load8(x + i * 8, f);
     if (BIAS) {
         float b[8];
-        load8(bias + (int)(i % c8) * 8, b);
+        load8(bias + (int)((unsigned)i % (unsigned)c8) * 8, b);  // chunks < 2^32 (checked by the launcher)
 #pragma unroll
         for (int k = 0; k < 8; ++k) f[k] = __half2float(__float2half(f[k] + b[k]));
     }
@@ -59,18 +59,17 @@ silu_nhwc_kernel(const __half* __restrict__ x, __half* __restrict__ y, long long
 }
 
 // out[n, ho, wo, :] from in[n, :, :, :], align_corners = true; a thread owns 8 channels of one output pixel, so the
-// source coordinates and the two weights are computed once per 8 outputs and every access is 16 bytes.
+// source coordinates and the two weights are computed once per 8 outputs and every access is 16 bytes. Grid: x over
+// (wo, channel chunk) of one output row, y = ho, z = n: the row arithmetic is uniform over a CTA and the only
+// division left is a 32-bit one (with one thread per flat 64-bit index the three divisions cost more than the loads).
 __global__ void __launch_bounds__(256)
-bilinear_upsample_nhwc_kernel(const __half* __restrict__ in, __half* __restrict__ out, long long chunks, int H_in, int W_in,
-                              int H_out, int W_out, int c8) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= chunks) return;
-    const int cc = (int)(i % c8);
-    long long p = i / c8;
-    const int w_out = (int)(p % W_out);
-    p /= W_out;
-    const int h_out = (int)(p % H_out);
-    const long long n = p / H_out;
+bilinear_upsample_nhwc_kernel(const __half* __restrict__ in, __half* __restrict__ out, int H_in, int W_in, int H_out, int W_out,
+                              int c8) {
+    const unsigned idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (unsigned)W_out * (unsigned)c8) return;
+    const int w_out = (int)(idx / (unsigned)c8), cc = (int)(idx % (unsigned)c8);
+    const int h_out = blockIdx.y;
+    const long long n = blockIdx.z;
     const float h_scale = (H_out > 1) ? (float)(H_in - 1) / (H_out - 1) : 0.0f;
     const float w_scale = (W_out > 1) ? (float)(W_in - 1) / (W_out - 1) : 0.0f;
     const float h_in_f = h_out * h_scale, w_in_f = w_out * w_scale;
@@ -86,7 +85,7 @@ bilinear_upsample_nhwc_kernel(const __half* __restrict__ in, __half* __restrict_
     unpack8(ldg_half8(base + ((long long)h1 * W_in + w1) * C), v11);
 #pragma unroll
     for (int k = 0; k < 8; ++k) o[k] = bilerp_ref(v00[k], v01[k], v10[k], v11[k], hf, wf);
-    store8(out + i * 8, o);
+    store8(out + ((n * H_out + h_out) * W_out) * C + (long long)idx * 8, o);
 }
 
 // A transposed convolution whose stride equals its kernel size f, as GEMM + this scatter: in [N*H*W, f*f*C] holds, for
@@ -157,7 +156,7 @@ extern "C" int rfk_bias_act_residual_nhwc(rfk_half* x, const rfk_half* bias, con
     if (rows == 0) return RFK_OK;
     if (C % 8 || !aligned16(x) || (bias && !aligned16(bias)) || (residual && !aligned16(residual))) return RFK_EUNSUPPORTED;
     const long long chunks = rows * (C / 8);
-    if (chunks > 0x7fffffffLL * 256) return RFK_EUNSUPPORTED;
+    if (chunks > 0xffffffffLL) return RFK_EUNSUPPORTED;
     __half* px = (__half*)x;
     const __half *pb = (const __half*)bias, *pr = (const __half*)residual;
     cudaStream_t st = as_stream(stream);
@@ -187,10 +186,11 @@ extern "C" int rfk_bilinear_upsample_nhwc(const rfk_half* in, rfk_half* out, int
     if (!in || !out || N < 0 || C <= 0 || H_in <= 0 || W_in <= 0 || H_out <= 0 || W_out <= 0) return RFK_EINVAL;
     if (N == 0) return RFK_OK;
     if (C % 8 || !aligned16(in) || !aligned16(out)) return RFK_EUNSUPPORTED;
-    const long long chunks = (long long)N * H_out * W_out * (C / 8);
-    if (chunks > 0x7fffffffLL * 256) return RFK_EUNSUPPORTED;
-    bilinear_upsample_nhwc_kernel<<<(unsigned)ceil_div(chunks, 256), 256, 0, as_stream(stream)>>>(
-        (const __half*)in, (__half*)out, chunks, H_in, W_in, H_out, W_out, C / 8);
+    const long long per_row = (long long)W_out * (C / 8);
+    if (per_row > 0x7fffffffLL || H_out > 65535 || N > 65535) return RFK_EUNSUPPORTED;
+    dim3 grid((unsigned)ceil_div(per_row, 256), (unsigned)H_out, (unsigned)N);
+    bilinear_upsample_nhwc_kernel<<<grid, 256, 0, as_stream(stream)>>>((const __half*)in, (__half*)out, H_in, W_in, H_out, W_out,
+                                                                      C / 8);
     return launch_status();
 }
 
