@@ -446,6 +446,12 @@ int rfk_depth_to_space_bias_nhwc(const rfk_half* in, const rfk_half* bias, rfk_h
                                  rfk_stream_t stream);
 /* [N, HW, C] -> [N, C, HW], any C (the head's last layer, C = 3) */
 int rfk_permute_nhwc_to_nchw(const rfk_half* in, rfk_half* out, int N, long long HW, int C, rfk_stream_t stream);
+/* The head's last layer in one launch: 1x1 convolution from C_in channels-last channels (C_in % 8 == 0, <= 2048) to
+ * C_out <= 4 planes + bias: in [N*HW, C_in], weight [C_out, C_in], out [N, C_out, HW] (RFK_EUNSUPPORTED otherwise:
+ * callers then use rfk_linear + rfk_permute_nhwc_to_nchw). fp32 accumulation, product rounded to fp16 before the bias.
+ * replaces conv2d (1x1, cuBLAS) + add_bias_nchw at the end of rf::dpt_forward — dpt.cu:112-126, :456-459 */
+int rfk_pointwise_conv_to_planar(const rfk_half* in, const rfk_half* weight, const rfk_half* bias, rfk_half* out, int N,
+                                 long long HW, int C_in, int C_out, rfk_stream_t stream);
 /* One-off filter layouts for the channels-last head. mode 0: convolution filter [K, C, RS] -> [K, RS, C]; mode 1:
  * transposed-convolution filter [Cin = K, Cout = C, RS = f*f] -> GEMM weight [(p * Cout + co), ci]. */
 int rfk_permute_filter(const rfk_half* w, rfk_half* out, int K, int C, int RS, int mode, rfk_stream_t stream);

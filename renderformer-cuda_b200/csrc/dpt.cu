@@ -20,10 +20,7 @@
 #include <cudnn.h>
 
 #include <algorithm>
-#include <array>
 #include <functional>
-#include <map>
-#include <mutex>
 #include <vector>
 
 namespace {
@@ -40,13 +37,6 @@ namespace {
     } while (0)
 
 using Step = std::function<int(const rfk_half* const* feats, cudaStream_t st)>;
-
-// The algorithm measured fastest for a convolution problem, remembered for the life of the process: every head planned
-// for the same shapes then runs the same kernels (two sessions of one model produce the same bits), and later plans
-// skip the search. Key: device, batch, Cin, H, W, Cout, k, stride, pad.
-struct AlgoChoice { cudnnConvolutionFwdAlgo_t algo; size_t workspace; };
-std::mutex g_algo_mutex;
-std::map<std::array<int, 9>, AlgoChoice> g_algo_cache;
 
 }  // namespace
 
@@ -123,35 +113,16 @@ struct rfk_dpt {
         cudnnFilterDescriptor_t fd = filter(Cout, Cin, k, k);
         cudnnConvolutionDescriptor_t cd = conv(pad, stride);
         if (!xd || !yd || !fd || !cd) return RFK_EINVAL;
-        // The algorithm is measured, not guessed: the library runs its candidates on this problem once, here at plan
-        // time, and the fastest whose workspace fits the cap is kept (the heuristic's first choice ran the 128-channel
-        // 3x3 layers at a fifth of the tensor peak). Falls back to the heuristic if the search cannot run.
-        constexpr size_t kWorkspaceCap = 512ull << 20;
+        // The library's heuristic picks the algorithm. Measuring the candidates at plan time (cudnnFind...) was tried: no
+        // faster in the view (198 against 201 images/s, noise), and under a profiler, whose replays distort the
+        // timings, it chose a kernel 25 times slower - a plan must not depend on how it is being observed.
         int returned = 0;
-        cudnnConvolutionFwdAlgoPerf_t perf[16];
-        cudnnConvolutionFwdAlgo_t algo = CUDNN_CONVOLUTION_FWD_ALGO_IMPLICIT_PRECOMP_GEMM;
+        cudnnConvolutionFwdAlgoPerf_t perf[4];
+        DNN_TRY(cudnnGetConvolutionForwardAlgorithm_v7(dnn, xd, fd, cd, yd, 4, &returned, perf));
+        if (returned < 1 || perf[0].status != CUDNN_STATUS_SUCCESS) return RFK_EUNSUPPORTED;
+        const cudnnConvolutionFwdAlgo_t algo = perf[0].algo;
         size_t ws = 0;
-        bool chosen = false;
-        const std::array<int, 9> key = {ctx->device, B, Cin, H, W, Cout, k, stride, pad};
-        {
-            std::lock_guard<std::mutex> lock(g_algo_mutex);
-            const auto it = g_algo_cache.find(key);
-            if (it != g_algo_cache.end()) { algo = it->second.algo; ws = it->second.workspace; chosen = true; }
-        }
-        if (!chosen && cudnnFindConvolutionForwardAlgorithm(dnn, xd, fd, cd, yd, 16, &returned, perf) == CUDNN_STATUS_SUCCESS) {
-            for (int a = 0; a < returned && !chosen; ++a)
-                if (perf[a].status == CUDNN_STATUS_SUCCESS && perf[a].memory <= kWorkspaceCap) { algo = perf[a].algo; ws = perf[a].memory; chosen = true; }
-            if (chosen) {
-                std::lock_guard<std::mutex> lock(g_algo_mutex);
-                g_algo_cache.emplace(key, AlgoChoice{algo, ws});
-            }
-        }
-        if (!chosen) {
-            DNN_TRY(cudnnGetConvolutionForwardAlgorithm_v7(dnn, xd, fd, cd, yd, 16, &returned, perf));
-            if (returned < 1 || perf[0].status != CUDNN_STATUS_SUCCESS) return RFK_EUNSUPPORTED;
-            algo = perf[0].algo;
-            DNN_TRY(cudnnGetConvolutionForwardWorkspaceSize(dnn, xd, fd, cd, yd, algo, &ws));
-        }
+        DNN_TRY(cudnnGetConvolutionForwardWorkspaceSize(dnn, xd, fd, cd, yd, algo, &ws));
         ws_bytes = std::max(ws_bytes, ws);
         rfk_dpt* self = this;
         program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {
@@ -271,16 +242,32 @@ struct rfk_dpt {
         if (!oc1 || !oc1_up || !oc2a || !oc2b || !out) return (int)cudaErrorMemoryAllocation;
         TRY(add_conv(path1, -1, w.output_conv1_w, w.output_conv1_b, oc1, F, oh, ow, fh, 3, 1, 1));
         const int Bn = B;
-        program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {
-            return rfk_bilinear_upsample_nhwc(oc1, oc1_up, Bn, oh, ow, full_h, full_w, fh, (rfk_stream_t)st);
-        });
-        TRY(add_conv(oc1_up, -1, w.output_conv2a_w, w.output_conv2a_b, oc2a, fh, full_h, full_w, 32, 3, 1, 1, /*silu=*/true));
-        TRY(add_conv(oc2a, -1, w.output_conv2b_w, w.output_conv2b_b, oc2b, 32, full_h, full_w, w.out_dim, 1, 1, 0));
+        const rfk_half* oc2a_in = oc1_up;
+        if (oh == full_h && ow == full_w) {
+            // With patch size 8 the fusion path already is at full resolution: an align_corners resample onto the same
+            // grid has weights exactly 1 and 0, i.e. it is the identity (for finite values), and is not run.
+            oc2a_in = oc1;
+        } else {
+            program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {
+                return rfk_bilinear_upsample_nhwc(oc1, oc1_up, Bn, oh, ow, full_h, full_w, fh, (rfk_stream_t)st);
+            });
+        }
+        TRY(add_conv(oc2a_in, -1, w.output_conv2a_w, w.output_conv2a_b, oc2a, fh, full_h, full_w, 32, 3, 1, 1, /*silu=*/true));
         rfk_half* image = out;
         const int od = w.out_dim;
-        program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {  // the interface's image is planar
-            return rfk_permute_nhwc_to_nchw(oc2b, image, Bn, (long long)full_h * full_w, od, (rfk_stream_t)st);
-        });
+        const long long HWf = (long long)full_h * full_w;
+        const rfk_half *w2b = w.output_conv2b_w, *b2b = w.output_conv2b_b;
+        if (od <= 4) {  // 1x1 to the colour channels + bias, written planar, in one launch
+            ++n_convs;
+            program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {
+                return rfk_pointwise_conv_to_planar(oc2a, w2b, b2b, image, Bn, HWf, 32, od, (rfk_stream_t)st);
+            });
+        } else {
+            TRY(add_conv(oc2a, -1, w2b, b2b, oc2b, 32, full_h, full_w, od, 1, 1, 0));
+            program.push_back([=](const rfk_half* const*, cudaStream_t st) -> int {  // the interface's image is planar
+                return rfk_permute_nhwc_to_nchw(oc2b, image, Bn, HWf, od, (rfk_stream_t)st);
+            });
+        }
         if (ws_bytes) {
             if (cudaMalloc(&workspace, ws_bytes) != cudaSuccess) return (int)cudaErrorMemoryAllocation;
             owned.push_back(workspace);

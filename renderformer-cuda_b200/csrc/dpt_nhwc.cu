@@ -126,6 +126,41 @@ permute_nhwc_to_nchw_kernel(const __half* __restrict__ in, __half* __restrict__ 
     out[i] = in[(n * HW + hw) * C + c];
 }
 
+// The head's last layer: a 1x1 convolution to a few channels (C_out <= 4: the image's colour channels) + bias, written
+// planar. in [N*HW, C_in] channels-last, w [C_out, C_in], out [N, C_out, HW]; one thread per pixel: the pixel's C_in
+// values are read once (16 bytes at a time) and every output plane is written with consecutive threads on consecutive
+// pixels. fp32 accumulation over the channels in order, the product rounded to fp16 before the bias is added (as a
+// convolution followed by the bias kernel does).
+template <int COUT>
+__global__ void __launch_bounds__(256)
+pointwise_to_planar_kernel(const __half* __restrict__ in, const __half* __restrict__ w, const __half* __restrict__ bias,
+                           __half* __restrict__ out, long long HW, long long total, int c_in) {
+    extern __shared__ float sw[];  // [COUT][c_in]
+    for (int i = threadIdx.x; i < COUT * c_in; i += blockDim.x) sw[i] = __half2float(w[i]);
+    __syncthreads();
+    const long long p = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= total) return;
+    float acc[COUT];
+#pragma unroll
+    for (int o = 0; o < COUT; ++o) acc[o] = 0.0f;
+    const __half* px = in + p * c_in;
+    for (int c = 0; c < c_in; c += 8) {
+        float v[8];
+        load8(px + c, v);
+#pragma unroll
+        for (int o = 0; o < COUT; ++o)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[o] = fmaf(v[k], sw[o * c_in + c + k], acc[o]);
+    }
+    const long long n = p / HW, hw = p % HW;
+#pragma unroll
+    for (int o = 0; o < COUT; ++o) {
+        float r = __half2float(__float2half(acc[o]));
+        if (bias) r += __half2float(bias[o]);
+        out[(n * COUT + o) * HW + hw] = __float2half(r);
+    }
+}
+
 // One-off weight layouts (at plan time): mode 0: [K, C, RS] -> [K, RS, C] (filter for channels-last convolutions);
 // mode 1: transposed-convolution filter [Cin = K, Cout = C, RS = f*f] -> GEMM weight [(p * Cout + co)][ci].
 __global__ void __launch_bounds__(256)
@@ -222,5 +257,26 @@ extern "C" int rfk_permute_filter(const rfk_half* w, rfk_half* out, int K, int C
     if (total > 0x7fffffffLL * 256) return RFK_EUNSUPPORTED;
     permute_filter_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, as_stream(stream)>>>((const __half*)w, (__half*)out, K, C, RS,
                                                                                          mode);
+    return launch_status();
+}
+
+extern "C" int rfk_pointwise_conv_to_planar(const rfk_half* in, const rfk_half* weight, const rfk_half* bias, rfk_half* out, int N,
+                                            long long HW, int C_in, int C_out, rfk_stream_t stream) {
+    if (!in || !weight || !out || N < 0 || HW < 0 || C_in <= 0 || C_out <= 0) return RFK_EINVAL;
+    const long long total = (long long)N * HW;
+    if (total == 0) return RFK_OK;
+    if (C_out > 4 || C_in % 8 || C_in > 2048 || !aligned16(in)) return RFK_EUNSUPPORTED;
+    if (total > 0x7fffffffLL * 256) return RFK_EUNSUPPORTED;
+    const unsigned grid = (unsigned)ceil_div(total, 256);
+    const size_t smem = (size_t)C_out * C_in * sizeof(float);
+    cudaStream_t st = as_stream(stream);
+    const __half *pi = (const __half*)in, *pw = (const __half*)weight, *pb = (const __half*)bias;
+    __half* po = (__half*)out;
+    switch (C_out) {
+        case 1: pointwise_to_planar_kernel<1><<<grid, 256, smem, st>>>(pi, pw, pb, po, HW, total, C_in); break;
+        case 2: pointwise_to_planar_kernel<2><<<grid, 256, smem, st>>>(pi, pw, pb, po, HW, total, C_in); break;
+        case 3: pointwise_to_planar_kernel<3><<<grid, 256, smem, st>>>(pi, pw, pb, po, HW, total, C_in); break;
+        default: pointwise_to_planar_kernel<4><<<grid, 256, smem, st>>>(pi, pw, pb, po, HW, total, C_in); break;
+    }
     return launch_status();
 }

@@ -419,7 +419,7 @@ def _main():
     ap.add_argument("--peak", type=float, default=6455.6, help="HBM GB/s used for the fraction column")
     ap.add_argument("--softmax-rows", type=int, default=SOFTMAX_ROWS)
     ap.add_argument("--gemm", action="store_true", help="print the tcgen05-vs-library GEMM table instead")
-    ap.add_argument("--profile", choices=["attention", "gemm"],
+    ap.add_argument("--profile", choices=["attention", "gemm", "dpt"],
                     help="a few plain launches of the fused cross-attention (16 x 4096 queries x 5665 keys) or of the "
                          "decoder layer's projections through rfk_gemm_f16, for a profiler capture")
     a = ap.parse_args()
@@ -430,6 +430,34 @@ def _main():
     if a.profile:
         from . import ops
         H16 = torch.float16
+        if a.profile == "dpt":
+            # the DPT image head alone at the benchmark size (four [4096, 1024] token maps -> [3, 512, 512]), random weights
+            import ctypes
+            from . import _abi, session
+            L = _abi.load("rfk_layers.h")
+            model = session.Model.random(seed=4, dim=D, num_heads=HEADS, ffn_hidden=64, enc_layers=0, dec_layers=0, with_dpt=True)
+            ctx = session.Ctx()
+            head = ctypes.c_void_p()
+            rc = L.rfk_dpt_create(ctx.h, ctypes.byref(model.dpt_c), 1, D, RES // 8, RES // 8, 8, ctypes.byref(head))
+            assert rc == 0, rc
+            feats = [_r((NP, D), H16) for _ in range(4)]
+            taps = (ctypes.c_void_p * 4)(*[f.data_ptr() for f in feats])
+            img = torch.empty(3, RES, RES, device="cuda", dtype=H16)
+            st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+            torch.cuda.synchronize()
+            t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+            for i in range(a.iters + 1):
+                if i == 1:
+                    t0.record()
+                assert L.rfk_dpt_forward(head, taps, ctypes.c_void_p(img.data_ptr()), st) == 0
+            t1.record()
+            torch.cuda.synchronize()
+            print(json.dumps({"kernel": "rfk_dpt_forward 4 x [4096,1024] -> [3,512,512]", "launched": a.iters + 1,
+                              "us_per_forward_eager": round(t0.elapsed_time(t1) * 1e3 / max(a.iters, 1), 1),
+                              "convolutions": L.rfk_dpt_num_convolutions(head), "finite": bool(torch.isfinite(img.float()).all())}))
+            L.rfk_dpt_destroy(head)
+            ctx.close()
+            return
         if a.profile == "attention":
             Se = 5665; Sp = (Se + 7) & ~7
             q, k, v = _r((1, HEADS, NP, HD), H16), _r((1, HEADS, Sp, HD), H16), _r((1, HEADS, Sp, HD), H16)

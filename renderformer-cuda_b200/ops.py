@@ -407,6 +407,12 @@ def permute_nhwc_to_nchw(inp, out, N, HW, C):
     _call("rfk_permute_nhwc_to_nchw", _p(inp, H, "in"), _p(out, H, "out"), N, HW, C, _stream())
 
 
+def pointwise_conv_to_planar(inp, weight, bias, out, N, HW, C_in, C_out):
+    """1x1 convolution from channels-last C_in to C_out <= 4 planes + bias: in [N*HW, C_in] -> out [N, C_out, HW]."""
+    _call("rfk_pointwise_conv_to_planar", _p(inp, H, "in"), _p(weight, H, "weight"), _p(bias, H, "bias"), _p(out, H, "out"),
+          N, HW, C_in, C_out, _stream())
+
+
 def permute_filter(w, out, K, C, RS, mode):
     """mode 0: [K, C, RS] -> [K, RS, C]; mode 1: transposed-convolution filter [Cin, Cout, f*f] -> [(p, co), ci]."""
     _call("rfk_permute_filter", _p(w, H, "w"), _p(out, H, "out"), K, C, RS, mode, _stream())

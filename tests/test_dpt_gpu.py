@@ -229,3 +229,24 @@ def test_filter_and_image_permutes_are_exact():
     with pytest.raises(o.RfkError) as e:           # channel counts that are not multiples of 8 are refused, not mangled
         o.bias_act_residual_nhwc(torch.zeros(4, 12, device="cuda", dtype=H16), None, None, 4, 12, True)
     assert e.value.status == -2
+
+
+@pytest.mark.parametrize("C_in,C_out", [(32, 3), (64, 1), (8, 4)])
+def test_pointwise_convolution_to_planes(C_in, C_out):
+    """The head's last layer as one kernel against fp32 torch: product rounded to fp16, then the bias (tolerance: those
+    two roundings)."""
+    o = _ops()
+    g = torch.Generator(device="cuda").manual_seed(C_in)
+    N, HW = 2, 1000
+    x = torch.randn(N * HW, C_in, device="cuda", generator=g).half()
+    w = (torch.randn(C_out, C_in, device="cuda", generator=g) * C_in ** -0.5).half()
+    b = torch.randn(C_out, device="cuda", generator=g).half()
+    out = torch.full((N, C_out, HW), 7.0, device="cuda", dtype=H16)
+    o.pointwise_conv_to_planar(x, w, b, out, N, HW, C_in, C_out)
+    torch.cuda.synchronize()
+    want = ((x.float() @ w.float().t()).half().float() + b.float()).view(N, HW, C_out).permute(0, 2, 1)
+    err = (out.float() - want).abs()
+    assert (err <= 1e-3 + 2.0 ** -9 * want.abs()).all(), err.max().item()
+    with pytest.raises(o.RfkError) as e:
+        o.pointwise_conv_to_planar(x, w, b, out, N, HW, C_in, 5)
+    assert e.value.status == -2
