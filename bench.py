@@ -476,6 +476,7 @@ def run_views(args, rank, world, peak, peak_src):
     ref_arm = args.impl == "reference"
     model = S.Model.random(seed=4)
     n_streams = 1 if ref_arm else args.streams
+    Vf = 1 if ref_arm else max(1, args.views_per_frame)   # views rendered together as one batch (one frame)
     K = args.steps
     t0 = time.perf_counter()
     if ref_arm:
@@ -487,7 +488,7 @@ def run_views(args, rank, world, peak, peak_src):
     else:
         # pad_keys_attend: the reference attends its 7 zero pad keys (render_session.cu:229-230); the timed sessions
         # do the same so that both arms compute the same function
-        sched = S.ViewScheduler(model, N_TRIS, IMG_RES, streams_per_gpu=n_streams, pad_keys_attend=True)
+        sched = S.ViewScheduler(model, N_TRIS, IMG_RES, streams_per_gpu=n_streams, pad_keys_attend=True, views_per_frame=Vf)
         if rank == 0:
             sched.encode_scene(*make_scene())
         state = sched.session.scene_state
@@ -506,7 +507,7 @@ def run_views(args, rank, world, peak, peak_src):
     c2w, fov = make_cameras()
     c2w = c2w.pin_memory(); fl = fov.tolist()
     base = c2w.data_ptr()
-    host = torch.empty(max(2 * n_streams, 2), n_tokens, model.dim, dtype=torch.float16).pin_memory()
+    host = torch.empty(max(2 * n_streams, 2), *((Vf,) if Vf > 1 else ()), n_tokens, model.dim, dtype=torch.float16).pin_memory()
 
     def my_view(j):
         return (rank + j * world) % N_CAMERAS
@@ -526,20 +527,32 @@ def run_views(args, rank, world, peak, peak_src):
             torch.cuda.synchronize()
             return ms_sum, (time.perf_counter() - t) * 1e3
     else:
+        def submit(s_, ids):
+            """One frame: a single view, or Vf views (the last frame of a pass padded by repeating its last view)."""
+            if Vf == 1:
+                s_.render_frame_raw(base + ids[0] * 64, fl[ids[0]])
+                return
+            ids = ids + [ids[-1]] * (Vf - len(ids))
+            cams = (ctypes.c_float * (16 * Vf))()
+            for i, v in enumerate(ids):
+                ctypes.memmove(ctypes.addressof(cams) + i * 64, base + v * 64, 64)
+            fv = (ctypes.c_float * Vf)(*[fl[v] for v in ids])
+            s_.render_frames_raw(ctypes.addressof(cams), ctypes.addressof(fv))
+
         def loop(k, download, streams=n_streams, views=None):
-            # the sessions take the views in turn; each brackets its own stream with events, all start from an
+            # the sessions take the frames in turn; each brackets its own stream with events, all start from an
             # idle device, and the device time is that of the session that finishes last
             ses = sched.sessions[:streams]
             torch.cuda.synchronize()
             t = time.perf_counter()
             for s_ in ses:
                 s_.mark_begin()
-            for j in range(k):
-                v = my_view(j) if views is None else views[j]
-                s_ = ses[j % streams]
-                s_.render_frame_raw(base + v * 64, fl[v])
+            for f in range((k + Vf - 1) // Vf):
+                ids = [my_view(j) if views is None else views[j] for j in range(f * Vf, min(k, (f + 1) * Vf))]
+                s_ = ses[f % streams]
+                submit(s_, ids)
                 if download:
-                    s_.download_async(host[j % (2 * streams)])
+                    s_.download_async(host[f % (2 * streams)])
             ms_dev = max(s_.mark_end() for s_ in ses)   # waits for the render and the copy streams
             torch.cuda.synchronize()
             return ms_dev, (time.perf_counter() - t) * 1e3
@@ -580,9 +593,10 @@ def run_views(args, rank, world, peak, peak_src):
 
     image = None
     if not args.no_image:
-        image = image_figure(args, rank, world, ref_arm, state, base, fl, n_streams, pipe)
+        image = image_figure(args, rank, world, ref_arm, state, base, fl, n_streams, pipe, Vf)
     parity = None
-    checksum = float(host[(len(mine) - 1) % max(2 * n_streams, 2)].float().abs().mean())
+    last_frame = ((len(mine) + Vf - 1) // Vf - 1) % max(2 * n_streams, 2)
+    checksum = float((host[last_frame][(len(mine) - 1) % Vf] if Vf > 1 else host[last_frame]).float().abs().mean())
     if not ref_arm and rank == 0 and not args.no_parity:
         parity = parity_vs_reference(model, sched, state, base, fl, host)
     if rank != 0:
@@ -598,8 +612,9 @@ def run_views(args, rank, world, peak, peak_src):
         "config": {"workload": "BASELINE configs[4]: decoder stack of renderformer-v1.1-swin-large shapes (dim 1024, 16x64 "
                                "heads, FFN 4096, 12 layers, fp16) per 512x512 view over a 5633-triangle scene, 64 look-at "
                                "cameras; encoder K/V cache computed once on rank 0 and NCCL-broadcast; views sharded "
-                               "round-robin, one view per GPU per step; DPT head not included",
-                   "views_in_flight_per_gpu": n_streams,
+                               "round-robin, one view per GPU per step (rfk arm: views_per_frame views go through the decoder together "
+                               "as one batch, results bit-identical to one at a time); DPT head not included",
+                   "views_in_flight_per_gpu": n_streams * Vf, "frames_in_flight_per_gpu": n_streams, "views_per_frame": Vf,
                    "timing": f"{N_REPS} repetitions of {K} steps per figure, median; value_min/value_max over the repetitions",
                    "value_min": vstat["min"], "value_max": vstat["max"],
                    "single_stream_value": single,
@@ -628,16 +643,19 @@ def run_views(args, rank, world, peak, peak_src):
         pipe.close()
     else:
         ses = sched.session
-        line["graph_nodes_per_view"] = ses.graph_nodes
-        line["rfk_kernels_per_view"] = ses.kernels_per_view
-        line["gpu_launches"] = ses.kernels_per_view * K * N_REPS
+        frames = (K + Vf - 1) // Vf
+        line["graph_nodes_per_view"] = round(ses.graph_nodes / Vf, 2)     # a frame of Vf views is one graph
+        line["graph_nodes_per_frame"] = ses.graph_nodes
+        line["rfk_kernels_per_view"] = round(ses.kernels_per_view / Vf, 2)
+        line["rfk_kernels_per_frame"] = ses.kernels_per_view
+        line["gpu_launches"] = ses.kernels_per_view * frames * N_REPS
         line["roofline"] = attention_roofline(N_TRIS, model.num_register_tokens, model.num_heads, ses.n_tokens,
                                               model.head_dim)
         sched.close()
     return line
 
 
-def image_figure(args, rank, world, ref_arm, state, cam_base, fovs, n_streams, ref_pipe):
+def image_figure(args, rank, world, ref_arm, state, cam_base, fovs, n_streams, ref_pipe, Vf=1):
     """The same views carried on to an image: decoder stack + DPT head (random-init weights of the v1.1 head: 256
     features, taps of 256/512/1024/1024 channels) + ELU / 10^x - 1, the [3, 512, 512] fp32 image copied to pinned host
     memory every view; host wall clock, 3 repetitions of K steps, median. Reported beside the decoder-only headline,
@@ -647,7 +665,7 @@ def image_figure(args, rank, world, ref_arm, state, cam_base, fovs, n_streams, r
     from renderformer_cuda_b200 import session as S
     K = args.steps
     model = S.Model.random(seed=4, with_dpt=True)          # same seed: the decoder weights are those of the headline model
-    himg = torch.empty(max(2 * n_streams, 2), 3, IMG_RES, IMG_RES, dtype=torch.float32).pin_memory()
+    himg = torch.empty(max(2 * n_streams, 2), *((Vf,) if Vf > 1 else ()), 3, IMG_RES, IMG_RES, dtype=torch.float32).pin_memory()
     if ref_arm:
         from oracle import ref_pipeline as RP
         head = RP.ImageHead(model, ref_pipe, IMG_RES)
@@ -664,20 +682,30 @@ def image_figure(args, rank, world, ref_arm, state, cam_base, fovs, n_streams, r
             return (time.perf_counter() - t) * 1e3
         closer = head.close
     else:
-        sessions = [S.RenderSession(model, N_TRIS, IMG_RES, scene_state=state, pad_keys_attend=True) for _ in range(n_streams)]
+        sessions = [S.RenderSession(model, N_TRIS, IMG_RES, scene_state=state, pad_keys_attend=True, views_per_frame=Vf)
+                    for _ in range(n_streams)]
         for s_ in sessions:
             s_.finalize()
 
         def loop(k):
             torch.cuda.synchronize()
             t = time.perf_counter()
-            for j in range(k):
-                v = (rank + j * world) % N_CAMERAS
-                s_ = sessions[j % n_streams]
-                if j >= n_streams:   # this session's previous frame first (waits for it; the other sessions keep the GPU busy)
-                    s_.download_image(himg[j % (2 * n_streams)])
-                s_.render_frame_raw(cam_base + v * 64, fovs[v])
-            for i_, s_ in enumerate(sessions[:min(k, n_streams)]):
+            n_frames = (k + Vf - 1) // Vf
+            for f in range(n_frames):
+                ids = [(rank + j * world) % N_CAMERAS for j in range(f * Vf, min(k, (f + 1) * Vf))]
+                s_ = sessions[f % n_streams]
+                if f >= n_streams:   # this session's previous frame first (waits for it; the other sessions keep the GPU busy)
+                    s_.download_image(himg[f % (2 * n_streams)])
+                if Vf == 1:
+                    s_.render_frame_raw(cam_base + ids[0] * 64, fovs[ids[0]])
+                else:
+                    ids = ids + [ids[-1]] * (Vf - len(ids))
+                    cams = (ctypes.c_float * (16 * Vf))()
+                    for i, v in enumerate(ids):
+                        ctypes.memmove(ctypes.addressof(cams) + i * 64, cam_base + v * 64, 64)
+                    fv = (ctypes.c_float * Vf)(*[fovs[v] for v in ids])
+                    s_.render_frames_raw(ctypes.addressof(cams), ctypes.addressof(fv))
+            for i_, s_ in enumerate(sessions[:min(n_frames, n_streams)]):
                 s_.download_image(himg[i_])
             torch.cuda.synchronize()
             return (time.perf_counter() - t) * 1e3
@@ -696,7 +724,7 @@ def image_figure(args, rank, world, ref_arm, state, cam_base, fovs, n_streams, r
     closer()
     st = _stats(wall, world * K)
     return {"views_per_s": st["median"], "min": st["min"], "max": st["max"], "d2h_bytes_per_view": 3 * IMG_RES * IMG_RES * 4,
-            "image_finite": finite, "views_in_flight_per_gpu": n_streams,
+            "image_finite": finite, "views_in_flight_per_gpu": n_streams * Vf, "views_per_frame": Vf,
             "note": "decoder stack + DPT head + post-process per view, image to pinned host memory; wall clock"}
 
 
@@ -712,10 +740,20 @@ def parity_vs_reference(model, sched, state, cam_base, fovs, host):
     except Exception as e:  # the reference libraries did not travel
         return {"unavailable": f"{type(e).__name__}: {e}"}
     ses = sched.session
-    ses.render_frame_raw(cam_base, fovs[0])
-    got = ses.download().float()
-    pipe.render(cam_base, fovs[0]); pipe.wait(); pipe.download(host[0])
-    want = host[0].float()
+    if ses.views_per_frame == 1:
+        ses.render_frame_raw(cam_base, fovs[0])
+        got = ses.download().float()
+    else:                                   # view 0 in every place of a frame; place 0 is compared
+        V = ses.views_per_frame
+        cams = (ctypes.c_float * (16 * V))()
+        for i in range(V):
+            ctypes.memmove(ctypes.addressof(cams) + i * 64, cam_base, 64)
+        fv = (ctypes.c_float * V)(*[fovs[0]] * V)
+        ses.render_frames_raw(ctypes.addressof(cams), ctypes.addressof(fv))
+        got = ses.download()[0].float()
+    row = host[0] if ses.views_per_frame == 1 else host[0][0]     # one view's worth of pinned memory
+    pipe.render(cam_base, fovs[0]); pipe.wait(); pipe.download(row)
+    want = row.float()
     pipe.close()
     err = (got - want).abs()
     tol = 2e-3 + 2.0 ** -10 * want.abs()
@@ -731,7 +769,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="rfk", choices=["rfk", "reference"])
     ap.add_argument("--workload", default="views", choices=["views", "kernels"])
-    ap.add_argument("--streams", type=int, default=3, help="views in flight per GPU (rfk arm): sessions sharing one scene state")
+    ap.add_argument("--streams", type=int, default=2, help="frames in flight per GPU (rfk arm): sessions sharing one scene state")
+    ap.add_argument("--views-per-frame", type=int, default=4,
+                    help="views rendered together as one batch per frame (rfk arm; 4 fills the SMs evenly at 512x512)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernel-table", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the one-frame comparison with the reference pipeline")

@@ -276,11 +276,13 @@ int rfk_flash_attention(const rfk_half* Q, const rfk_half* K, const rfk_half* V,
  * bytes zero before the first launch (the kernel leaves them zero); launches that may overlap in time need separate
  * workspaces. The result differs from the unsplit kernel's only by rounding (fp32 merge; fp16 probabilities relative to
  * each piece's own maximum) and is bit-reproducible from launch to launch.
+ * (3) Shared values (v_shared != 0): V is [H, Sk, D], one set for all B batch elements - views of one scene rendered
+ * together have their own queries and (rotated) keys but the same values.
  * replaces rmsnorm(Q) -> transpose -> sdpa — src/layers/attention.cu:341-349,364-366 */
 int rfk_flash_attention_ex(const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,
                            const float* q_row_ss, int ss_tiles, int norm_dim, float eps, void* workspace,
-                           size_t workspace_bytes, int B, int H, int Sq, int Sk, int n_keys, int D, int o_bshd,
-                           float scale, rfk_stream_t stream);
+                           size_t workspace_bytes, int v_shared, int B, int H, int Sq, int Sk, int n_keys, int D,
+                           int o_bshd, float scale, rfk_stream_t stream);
 size_t rfk_flash_attention_workspace_bytes(void);
 /* The work list rfk_flash_attention_ex would launch for `units` units (256 queries of one head each) of `n_tiles`
  * 64-key tiles on a device with `sms` SMs, given a workspace: units [0, *whole_units) run whole, then *n_pieces pieces

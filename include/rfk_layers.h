@@ -321,6 +321,16 @@ size_t rfk_scene_state_bytes(const rfk_model* model, int n_tris);
  * replaces the allocation half of rf::RenderSession::create — src/pipeline/render_session.cu:258-295,418-462 */
 int rfk_session_create(const rfk_model* model, int n_tris, int img_res, void* scene_state,
                        int flags, rfk_session** out);
+/* The same with views_per_frame (1..64) views rendered together: a frame is then a batch of that many views of the
+ * scene, each with its own camera, that go through the decoder as one batch (rfk_session_render_frames). Throughput
+ * mode: the projections see views_per_frame times the rows and the cross-attention that many times the work units,
+ * which is what fills all SMs evenly (four views at 512 x 512: 1024 units on 148 SMs instead of 256); a frame's
+ * results are the views' results back to back, bit-identical to rendering them one by one. Needs the fused attention
+ * route (head size 64, dim % 256 == 0, QK-norm weights present): RFK_EUNSUPPORTED otherwise. No reference counterpart
+ * (the reference renders one view at a time, render_session.cu:501-548). */
+int rfk_session_create_batched(const rfk_model* model, int n_tris, int img_res, void* scene_state, int flags,
+                               int views_per_frame, rfk_session** out);
+int rfk_session_views_per_frame(rfk_session* s);
 int rfk_session_destroy(rfk_session* s);
 
 /* Scene preprocessing, 12-layer encoder and K/V cache build into the scene state.
@@ -342,6 +352,11 @@ int rfk_session_finalize(rfk_session* s);
  * downloading: the host can stay one frame ahead of the device.
  * replaces rf::RenderSession::render_frame_async — render_session.cu:515-527 */
 int rfk_session_render_frame(rfk_session* s, const float* h_c2w, float fov_rad);
+/* One frame of a session created with views_per_frame = V: h_c2w [V][16] and fov_rad [V] (HOST). Results, feature
+ * taps and images of the frame hold the V views back to back ([V, tokens, dim], [V, channels, res, res]); the download
+ * calls copy all of them (bytes >= V times the single-view size). rfk_session_render_frame is this call for V = 1 and
+ * returns RFK_EINVAL on a session with V > 1. */
+int rfk_session_render_frames(rfk_session* s, const float* h_c2w, const float* fov_rad);
 /* Blocks until the last submitted frame is done; *ms (optional) receives its device time.
  * replaces rf::RenderSession::get_frame_result — render_session.cu:539-548 */
 int rfk_session_wait(rfk_session* s, float* ms);

@@ -471,7 +471,7 @@ size_t attention_tc_workspace_bytes();
 int attention_tc_plan(long long units, int n_tiles, int sms, int* whole_units, int* n_pieces, unsigned short* pieces, int max_pieces);
 int launch_attention_tc(const __half* Q, const __half* K, const __half* V, __half* O, int B, int H, int Sq, int Sk,
                         int n_keys, int o_bshd, float scale, cudaStream_t st, const float* row_ss, int ss_tiles,
-                        int norm_dim, float norm_eps, void* ws, size_t ws_bytes);
+                        int norm_dim, float norm_eps, void* ws, size_t ws_bytes, int v_shared);
 
 }  // namespace rfk
 
@@ -490,7 +490,7 @@ extern "C" int rfk_flash_attention(const rfk_half* Q, const rfk_half* K, const r
     const int path = g_attn_path.load(std::memory_order_relaxed);
     if (D == 64 && path != 1) {  // tcgen05 kernel; in automatic mode the mma.sync kernel takes over if it cannot run
         const int rc = launch_attention_tc((const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, B, H, Sq, Sk,
-                                           n_keys, o_bshd, scale, st, nullptr, 0, 0, 0.0f, nullptr, 0);
+                                           n_keys, o_bshd, scale, st, nullptr, 0, 0, 0.0f, nullptr, 0, 0);
         if (rc != RFK_EUNSUPPORTED || path == 2) return rc;
     }
     if (D == 64)
@@ -504,8 +504,8 @@ extern "C" int rfk_flash_attention(const rfk_half* Q, const rfk_half* K, const r
 
 extern "C" int rfk_flash_attention_ex(const rfk_half* Q, const rfk_half* K, const rfk_half* V, rfk_half* O,
                                       const float* q_row_ss, int ss_tiles, int norm_dim, float eps, void* workspace,
-                                      size_t workspace_bytes, int B, int H, int Sq, int Sk, int n_keys, int D, int o_bshd,
-                                      float scale, rfk_stream_t stream) {
+                                      size_t workspace_bytes, int v_shared, int B, int H, int Sq, int Sk, int n_keys, int D,
+                                      int o_bshd, float scale, rfk_stream_t stream) {
     if (!Q || !K || !V || !O || B < 0 || H <= 0 || Sq < 0 || Sk <= 0 || n_keys <= 0 || n_keys > Sk || !(scale > 0.0f))
         return RFK_EINVAL;
     if (q_row_ss && (ss_tiles <= 0 || norm_dim <= 0)) return RFK_EINVAL;
@@ -514,7 +514,7 @@ extern "C" int rfk_flash_attention_ex(const rfk_half* Q, const rfk_half* K, cons
     if (D != 64 || (long long)B * H > 65535 || g_attn_path.load(std::memory_order_relaxed) == 1) return RFK_EUNSUPPORTED;
     if (!aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(O) || !aligned16(workspace)) return RFK_EUNSUPPORTED;
     return launch_attention_tc((const __half*)Q, (const __half*)K, (const __half*)V, (__half*)O, B, H, Sq, Sk, n_keys, o_bshd,
-                               scale, as_stream(stream), q_row_ss, ss_tiles, norm_dim, eps, workspace, workspace_bytes);
+                               scale, as_stream(stream), q_row_ss, ss_tiles, norm_dim, eps, workspace, workspace_bytes, v_shared != 0);
 }
 
 extern "C" size_t rfk_flash_attention_workspace_bytes(void) { return attention_tc_workspace_bytes(); }

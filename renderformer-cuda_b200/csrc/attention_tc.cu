@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, __half* __restrict__ O, int H, int Sq, int n_keys,
                     int o_bshd, float scale_log2e_all, const float* __restrict__ row_ss, int ss_tiles, float inv_norm_dim,
-                    float norm_eps, unsigned char* __restrict__ ws, const __grid_constant__ WorkList work) {
+                    float norm_eps, unsigned char* __restrict__ ws, int v_heads, const __grid_constant__ WorkList work) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const uint32_t base = tc::smem_addr(smem_raw);
     if (base & 1023u) {  // uniform over the CTA, nothing allocated yet
@@ -264,7 +264,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (j >= kStages && !tc::mbar_wait(&ctrl->kv_empty[s], ((j / kStages) + 1) & 1, abort_flag)) break;
                 tc::mbar_arrive_expect_tx(&ctrl->kv_full[s], kStageBytes);
                 tc::tma_load_3d(sKV + s * kStageBytes, &map_k, 0, (t0 + j) * BN, bh, &ctrl->kv_full[s]);
-                tc::tma_load_3d(sKV + s * kStageBytes + kKBytes, &map_v, 0, (t0 + j) * BN, bh, &ctrl->kv_full[s]);
+                tc::tma_load_3d(sKV + s * kStageBytes + kKBytes, &map_v, 0, (t0 + j) * BN, bh % v_heads, &ctrl->kv_full[s]);
                 issued = j + 1;
             }
             if (*abort_flag) {
@@ -626,11 +626,12 @@ int attention_tc_plan(long long units, int n_tiles, int sms, int* whole_units, i
     return RFK_OK;
 }
 
-// Launches the tcgen05 kernel; the caller has validated pointers, alignment and sizes (D == 64). ws (may be NULL):
+// Launches the tcgen05 kernel; the caller has validated pointers, alignment and sizes (D == 64). v_shared: V is
+// [H, Sk, D], one set of values for every batch element (views of one scene). ws (may be NULL):
 // attention_tc_workspace_bytes() bytes whose first 1024 are zero, for the key split.
 int launch_attention_tc(const __half* Q, const __half* K, const __half* V, __half* O, int B, int H, int Sq, int Sk,
                         int n_keys, int o_bshd, float scale, cudaStream_t st, const float* row_ss, int ss_tiles,
-                        int norm_dim, float norm_eps, void* ws, size_t ws_bytes) {
+                        int norm_dim, float norm_eps, void* ws, size_t ws_bytes, int v_shared) {
     // per-device "kernel attributes set" marks; setting them twice from racing threads is harmless
     static std::atomic<bool> configured[64];
     static std::atomic<int> sm_count[64];
@@ -653,7 +654,7 @@ int launch_attention_tc(const __half* Q, const __half* K, const __half* V, __hal
     }
     CUtensorMap mq, mk, mv;
     if (!make_map(&mq, Q, (long long)B * H, Sq, tcattn::BM) || !make_map(&mk, K, (long long)B * H, Sk, tcattn::BN) ||
-        !make_map(&mv, V, (long long)B * H, Sk, tcattn::BN))
+        !make_map(&mv, V, v_shared ? (long long)H : (long long)B * H, Sk, tcattn::BN))
         return RFK_EUNSUPPORTED;
     tcattn::WorkList work;
     work.q_blocks = ceil_div(Sq, tcattn::kUnitRows);
@@ -664,7 +665,7 @@ int launch_attention_tc(const __half* Q, const __half* K, const __half* V, __hal
     dim3 grid((unsigned)(work.whole_units + work.n_pieces));
     launch_pdl(tcattn::attention_tc_kernel, grid, dim3(tcattn::kThreads), tcattn::kSmemBytes, st, mq, mk, mv, O, H, Sq, n_keys,
                o_bshd, scale * 1.4426950408889634f, row_ss, ss_tiles, norm_dim > 0 ? 1.0f / (float)norm_dim : 0.0f, norm_eps,
-               static_cast<unsigned char*>(ws), work);
+               static_cast<unsigned char*>(ws), v_shared ? H : B * H, work);
     return launch_status();
 }
 

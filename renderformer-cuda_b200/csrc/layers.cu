@@ -220,7 +220,7 @@ static int attention_core(rfk_ctx* ctx, const rfk_half* Q, const rfk_half* K, co
                           rfk_stream_t stream) {
     int rc = RFK_EUNSUPPORTED;
     if (ctx->attn_ws)  // tcgen05 kernel with the balanced key split; declines what only the other kernels serve
-        rc = rfk_flash_attention_ex(Q, K, V, O, nullptr, 0, 0, 0.0f, ctx->attn_ws, ctx->attn_ws_bytes, B, H, Sq, Sk, n_keys, D,
+        rc = rfk_flash_attention_ex(Q, K, V, O, nullptr, 0, 0, 0.0f, ctx->attn_ws, ctx->attn_ws_bytes, 0, B, H, Sq, Sk, n_keys, D,
                                     o_bshd, 1.0f / sqrtf((float)D), stream);
     if (rc == RFK_EUNSUPPORTED)
         rc = rfk_flash_attention(Q, K, V, O, B, H, Sq, Sk, n_keys, D, o_bshd, 1.0f / sqrtf((float)D), stream);
@@ -284,11 +284,12 @@ extern "C" int rfk_precompute_cross_kv(rfk_ctx* ctx, const rfk_cross_attn_weight
 // `residual` (may be `out`, may be NULL): out = residual + attention output, the add being the epilogue of the
 // output projection.
 // norm_ss (may be NULL): scratch of B*Sq*(dim/256) floats for the row statistics of the deferred Q-RMSNorm;
-// k_prescaled: K_cached is already rotated AND multiplied by the query's norm weight (the session does both for all
+// cache_flags bit 1: V_cached is [H, Sk, hd], shared by all B batch elements (views of one scene rendered together).
+// cache_flags bit 0 (k_prescaled): K_cached is already rotated AND multiplied by the query's norm weight (the session does both for all
 // layers at once).
 static int cross_attention_impl(rfk_ctx* ctx, const rfk_cross_attn_weights* w,
                                           const rfk_half* q_in, rfk_half* out, const rfk_half* residual,
-                                          rfk_half* proj_buf, float* norm_ss, int k_prescaled,
+                                          rfk_half* proj_buf, float* norm_ss, int cache_flags,
                                           float* score_buf, const rfk_half* K_cached,
                                           const rfk_half* V_cached, int B, int Sq, int Sk, int n_keys,
                                           int q_dim, int dim, int num_heads,
@@ -305,6 +306,7 @@ static int cross_attention_impl(rfk_ctx* ctx, const rfk_cross_attn_weights* w,
     // each row's scores by 1 / rms, and the norm's weight rides on the keys (multiplied in by the rotation kernel, here
     // or by the caller). One kernel (norm + head split) and 18 MB of traffic less per layer. Needs: no query rotation
     // (the view decoder's query tables are the identity), keys that are rotated here or arrive prescaled, head size 64.
+    const int k_prescaled = cache_flags & 1, v_shared = (cache_flags >> 1) & 1;
     const bool deferred = norm_ss && w->q_norm_gamma && !w->q_proj_b && !q_rope_cos && hd == 64 && (k_prescaled || k_rope_cos) &&
                           (reinterpret_cast<uintptr_t>(w->q_norm_gamma) & 15u) == 0;
     if (k_prescaled && !deferred) return RFK_EUNSUPPORTED;  // prescaled keys only make sense with the deferred norm
@@ -320,12 +322,14 @@ static int cross_attention_impl(rfk_ctx* ctx, const rfk_cross_attn_weights* w,
             }
             if (rc == RFK_OK)
                 rc = rfk_flash_attention_ex(Q_bhsd, K_use, V_cached, Q, norm_ss, dim / 256, dim, kEpsFp16, ctx->attn_ws,
-                                            ctx->attn_ws_bytes, B, num_heads, Sq, Sk, n_keys, hd, 1, 1.0f / sqrtf((float)hd), stream);
+                                            ctx->attn_ws_bytes, v_shared, B, num_heads, Sq, Sk, n_keys, hd, 1,
+                                            1.0f / sqrtf((float)hd), stream);
         }
         if (rc != RFK_OK && rc != RFK_EUNSUPPORTED) return rc;
-        if (rc == RFK_EUNSUPPORTED && k_prescaled) return rc;  // prescaled keys cannot serve the separate-norm route
+        if (rc == RFK_EUNSUPPORTED && (k_prescaled || (v_shared && B > 1))) return rc;  // only the fused route serves these
         if (rc == RFK_OK) goto out_projection;
     }
+    if (v_shared && B > 1) return RFK_EUNSUPPORTED;  // the separate-norm route below reads V per batch element
     {
         TRY(rfk_linear(ctx, q_in, w->q_proj_w, w->q_proj_b, Q, Mq, dim, q_dim, stream));
         const float* g[1] = {w->q_norm_gamma};
@@ -451,7 +455,7 @@ extern "C" int rfk_self_attention(rfk_ctx* ctx, const rfk_mha_weights* w, const 
     return rfk_linear(ctx, qkv_buf, w->out_proj_w, w->out_proj_b, out, M, dim, dim, stream);
 }
 
-// k_prescaled: K_cached is this view's rotated keys already multiplied by the cross-attention query norm's weight
+// cache_flags: bit 1: V_cached is shared by the B batch elements; bit 0: K_cached is this view's rotated keys already multiplied by the cross-attention query norm's weight
 // (what rfk_session prepares for all layers at once); 0 for keys as the public entry point receives them.
 int rfk_layers::decoder_layer_impl(
     rfk_ctx* ctx, const rfk_decoder_layer_weights* w, rfk_half* x, const rfk_half* pending_residual,
@@ -460,7 +464,7 @@ int rfk_layers::decoder_layer_impl(
     const rfk_half* V_cached, int B, int Sq, int Sk, int n_keys, int dim, int num_heads, int ffn_hidden,
     int patch_h, int patch_w, int window_size, int shift_size, const uint8_t* shift_mask,
     const rfk_half* q_rope_cos, const rfk_half* q_rope_sin, const rfk_half* k_rope_cos,
-    const rfk_half* k_rope_sin, int k_prescaled, rfk_stream_t stream) {
+    const rfk_half* k_rope_sin, int cache_flags, rfk_stream_t stream) {
     if (!ctx || !w || !x || !temp || !proj_buf || !qkv_buf || !ffn_buf || !window_buf) return RFK_EINVAL;
     if (Sq != patch_h * patch_w) return RFK_EINVAL;
     const int Mq = B * Sq;
@@ -480,7 +484,7 @@ int rfk_layers::decoder_layer_impl(
     float* swin_ss = dim % 256 == 0 ? reinterpret_cast<float*>(temp) : nullptr;
     if (win_ok) {
         if (!w->cross_attn.out_proj_b) {
-            TRY(cross_attention_impl(ctx, &w->cross_attn, temp, x, x, proj_buf, cross_ss, k_prescaled, cross_score_buf, K_cached,
+            TRY(cross_attention_impl(ctx, &w->cross_attn, temp, x, x, proj_buf, cross_ss, cache_flags, cross_score_buf, K_cached,
                                      V_cached, B, Sq, Sk, n_keys, dim, dim, num_heads, q_rope_cos, q_rope_sin, k_rope_cos,
                                      k_rope_sin, stream));
             TRY(rfk_rmsnorm_residual_f16_windows(x, nullptr, w->self_attn_norm_gamma, window_buf, B, patch_h, patch_w, dim,

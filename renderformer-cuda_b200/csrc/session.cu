@@ -107,6 +107,7 @@ std::vector<uint8_t> build_window_mask(int rows, int cols, int ws, int shift) {
 struct rfk_session {
     rfk_model m{};
     int N = 0, res = 0, Se = 0, Se_pad = 0, pH = 0, pW = 0, nP = 0, hd = 0, flags = 0;
+    int V = 1;  // views per frame: a frame is V views of the scene rendered together as one batch (see render_view)
     rfk_ctx* ctx = nullptr;
     cudaStream_t stream = nullptr, copy_stream = nullptr, side_stream = nullptr;
     StateLayout L{};
@@ -114,7 +115,7 @@ struct rfk_session {
     std::vector<void*> owned;  // device allocations of this session
 
     // per-view buffers
-    float* cam_gpu = nullptr;  // [16 c2w | 1 fov | pad]
+    float* cam_gpu = nullptr;  // per view [16 c2w | 1 fov | pad to kCamStride]
     float* id_c2w = nullptr;
     rfk_half *vtri = nullptr, *vvn = nullptr, *vpos = nullptr, *k_cos = nullptr, *k_sin = nullptr;
     rfk_half *ray_pat = nullptr, *rtok = nullptr;
@@ -143,7 +144,8 @@ struct rfk_session {
     bool finalized = false;
 
     rfk_half* kvK(int layer) const { return (rfk_half*)(state + L.kv_off + (size_t)(2 * layer) * L.kv_layer_bytes); }
-    rfk_half* kRot(int layer) const { return k_rot + (size_t)layer * m.num_heads * Se_pad * hd; }
+    // rotated keys: [dec_layers][V][heads][Se_pad][hd], so that a layer's keys are one [V * heads, Se_pad, hd] batch
+    rfk_half* kRot(int layer, int view = 0) const { return k_rot + ((size_t)layer * V + view) * m.num_heads * Se_pad * hd; }
     rfk_half* kvV(int layer) const { return (rfk_half*)(state + L.kv_off + (size_t)(2 * layer + 1) * L.kv_layer_bytes); }
     rfk_half* tri16() const { return (rfk_half*)(state + L.tri_off); }
     rfk_half* vn16() const { return (rfk_half*)(state + L.vn_off); }
@@ -161,41 +163,57 @@ struct rfk_session {
     int render_view(const float* pinned_cam, rfk_half* result_out, rfk_half* const* taps_out, float* image_out);
 };
 
-// The per-view work; everything here is captured into the graph.
+// The work of one frame = V views; everything here is captured into the graph. The views of a frame go through the
+// decoder as one batch: every projection sees V * nP rows, the cross-attention V * heads * nP / 256 units of work (with
+// V = 4 at 512 x 512 that is 1024 units on 148 SMs, 6.9 rounds instead of the 1.7 of a single view, whose second,
+// partial round leaves 14 % of the machine idle), the window attention V * nW windows. Each view has its own camera,
+// geometry, rotary tables and rotated keys; the values of the K/V cache are shared by the batch.
+constexpr int kCamStride = 32;  // floats per view in the camera buffers
 int rfk_session::render_view(const float* pinned_cam, rfk_half* result_out, rfk_half* const* taps_out, float* image_out) {
     rfk_stream_t s = (rfk_stream_t)stream;
     const int dim = m.dim, nr = m.num_register_tokens, ps = m.patch_size;
-    TRY_CUDA(cudaMemcpyAsync(cam_gpu, pinned_cam, 17 * sizeof(float), cudaMemcpyHostToDevice, stream));
-    // world -> camera of triangles and normals, register-token positions, K RoPE tables
-    TRY(rfk_view_geometry(cam_gpu, tri16(), vn16(), center(), m.vt_rope_freqs, vtri, vvn, vpos, k_cos, k_sin, N, nr,
-                          Se_pad, m.rope_num_freqs, hd, s));
-    // The rotation of the cached keys by this view's tables is the same for every query and independent of the
+    const size_t tri_n = (size_t)N * 9, pos_n = (size_t)Se_pad * 9, tab_n = (size_t)Se_pad * hd;
+    const size_t pat_n = (size_t)nP * 3 * ps * ps;
+    TRY_CUDA(cudaMemcpyAsync(cam_gpu, pinned_cam, (size_t)V * kCamStride * sizeof(float), cudaMemcpyHostToDevice, stream));
+    // world -> camera of triangles and normals, register-token positions, K RoPE tables (per view)
+    for (int v = 0; v < V; ++v)
+        TRY(rfk_view_geometry(cam_gpu + v * kCamStride, tri16(), vn16(), center(), m.vt_rope_freqs, vtri + v * tri_n, vvn + v * tri_n,
+                              vpos + v * pos_n, k_cos + v * tab_n, k_sin + v * tab_n, N, nr, Se_pad, m.rope_num_freqs, hd, s));
+    // The rotation of the cached keys by a view's tables is the same for every query and independent of the
     // layers' data flow, so it runs on a second stream (a parallel branch of the graph) while the front end and the
-    // first layer's projections run. Two launches: layer 0 alone (the first attention waits only for 23 MB of work),
-    // then all remaining layers at once (one shared table, batch = layers, source stride = a K and a V slab).
+    // first layer's projections run. Two launches per view: layer 0 alone (the first attention waits only for 23 MB of
+    // work per view), then all remaining layers at once (one shared table, batch = layers, source stride = a K and a
+    // V slab, destination stride = the V views of a layer).
     TRY_CUDA(cudaEventRecord(ev_fork, stream));
     TRY_CUDA(cudaStreamWaitEvent(side_stream, ev_fork, 0));
     {
         const long long slab = (long long)(L.kv_layer_bytes / sizeof(__half));
+        const long long rot_slab = (long long)m.num_heads * Se_pad * hd;
         const float* g0 = prescale ? q_gamma_all : nullptr;
-        TRY(rfk_rope_one_oop_strided(kvK(0), kRot(0), k_cos, k_sin, 1, 2 * slab, slab, 0, m.num_heads, Se_pad, hd, Se_pad,
-                                     Se_pad, g0, 0, (rfk_stream_t)side_stream));
+        for (int v = 0; v < V; ++v)
+            TRY(rfk_rope_one_oop_strided(kvK(0), kRot(0, v), k_cos + v * tab_n, k_sin + v * tab_n, 1, 2 * slab, rot_slab, 0,
+                                         m.num_heads, Se_pad, hd, Se_pad, Se_pad, g0, 0, (rfk_stream_t)side_stream));
         TRY_CUDA(cudaEventRecord(ev_rot[0], side_stream));
         if (m.dec_layers > 1) {
-            TRY(rfk_rope_one_oop_strided(kvK(1), kRot(1), k_cos, k_sin, m.dec_layers - 1, 2 * slab, slab, 0, m.num_heads,
-                                         Se_pad, hd, Se_pad, Se_pad, g0 ? g0 + dim : nullptr, dim, (rfk_stream_t)side_stream));
+            for (int v = 0; v < V; ++v)
+                TRY(rfk_rope_one_oop_strided(kvK(1), kRot(1, v), k_cos + v * tab_n, k_sin + v * tab_n, m.dec_layers - 1, 2 * slab,
+                                             (long long)V * rot_slab, 0, m.num_heads, Se_pad, hd, Se_pad, Se_pad,
+                                             g0 ? g0 + dim : nullptr, dim, (rfk_stream_t)side_stream));
             TRY_CUDA(cudaEventRecord(ev_rot[1], side_stream));
         }
     }
     // camera-space rays (identity pose, as the reference does) written straight as patch tokens
-    TRY(rfk_ray_gen_patchify(id_c2w, cam_gpu + 16, nullptr, ray_pat, 1, res, ps, s));
-    TRY(rfk_linear(ctx, ray_pat, m.ray_enc_w, m.ray_enc_b, rtok, nP, dim, 3 * ps * ps, s));
-    TRY(rfk_rmsnorm(rtok, m.ray_enc_norm, rtok, nP, dim, kEpsFp16, s));
-    TRY(rfk_broadcast_add(rtok, m.ray_map_patch_token, (long long)nP * dim, dim, s));
+    for (int v = 0; v < V; ++v)
+        TRY(rfk_ray_gen_patchify(id_c2w, cam_gpu + v * kCamStride + 16, nullptr, ray_pat + v * pat_n, 1, res, ps, s));
+    const int rows = V * nP;
+    TRY(rfk_linear(ctx, ray_pat, m.ray_enc_w, m.ray_enc_b, rtok, rows, dim, 3 * ps * ps, s));
+    TRY(rfk_rmsnorm(rtok, m.ray_enc_norm, rtok, rows, dim, kEpsFp16, s));
+    TRY(rfk_broadcast_add(rtok, m.ray_map_patch_token, (long long)rows * dim, dim, s));
 
     const int n_keys = (flags & RFK_SESSION_PAD_KEYS_ATTEND) ? Se_pad : Se;
     const rfk_half* pending = nullptr;
     const int L4 = std::max(1, m.dec_layers / 4);
+    const int cache_flags = (prescale ? 1 : 0) | (V > 1 ? 2 : 0);  // keys rotated + weighted here; values shared by the views
     for (int i = 0; i < m.dec_layers; ++i) {
         const int shift = (i % 2 == 1) ? m.shift_size : 0;
         const bool tap = ((i + 1) % L4 == 0) && ((i + 1) / L4 <= 4);
@@ -205,19 +223,19 @@ int rfk_session::render_view(const float* pinned_cam, rfk_half* result_out, rfk_
         // to the first kernel of the next layer
         if (i < 2) TRY_CUDA(cudaStreamWaitEvent(stream, ev_rot[i], 0));
         TRY(decoder_layer_impl(ctx, &m.dec[i], rtok, pending, (tap || last) ? nullptr : &next_pending,
-                               temp, proj, qkv, ffn, win, score, self_score, kRot(i), kvV(i), 1, nP,
+                               temp, proj, qkv, ffn, win, score, self_score, kRot(i), kvV(i), V, nP,
                                Se_pad, n_keys, dim, m.num_heads, m.ffn_hidden, pH, pW, m.window_size,
-                               shift, shift > 0 ? shift_mask : nullptr, nullptr, nullptr, nullptr, nullptr, prescale ? 1 : 0, s));
+                               shift, shift > 0 ? shift_mask : nullptr, nullptr, nullptr, nullptr, nullptr, cache_flags, s));
         pending = next_pending;
         if (tap)
-            TRY_CUDA(cudaMemcpyAsync(taps_out[(i + 1) / L4 - 1], rtok, (size_t)nP * dim * sizeof(rfk_half),
+            TRY_CUDA(cudaMemcpyAsync(taps_out[(i + 1) / L4 - 1], rtok, (size_t)rows * dim * sizeof(rfk_half),
                                      cudaMemcpyDeviceToDevice, stream));
     }
-    TRY_CUDA(cudaMemcpyAsync(result_out, rtok, (size_t)nP * dim * sizeof(rfk_half), cudaMemcpyDeviceToDevice, stream));
+    TRY_CUDA(cudaMemcpyAsync(result_out, rtok, (size_t)rows * dim * sizeof(rfk_half), cudaMemcpyDeviceToDevice, stream));
     if (dpt) {
         // image head over this frame's taps, then ELU(1e-3) -> fp32 -> 10^x - 1 in one kernel (render_session.cu:239-253)
         TRY(rfk_dpt_forward(dpt, taps_out, nullptr, s));
-        TRY(rfk_post_elu_pow10(rfk_dpt_output(dpt), image_out, (long long)dptw.out_dim * res * res, 1e-3f, s));
+        TRY(rfk_post_elu_pow10(rfk_dpt_output(dpt), image_out, (long long)V * dptw.out_dim * res * res, 1e-3f, s));
     }
     return RFK_OK;
 }
@@ -241,13 +259,18 @@ static int check_model(const rfk_model* m) {
 
 extern "C" int rfk_session_create(const rfk_model* model, int n_tris, int img_res, void* scene_state, int flags,
                                   rfk_session** out) {
-    if (!out || !scene_state || n_tris <= 0 || img_res <= 0) return RFK_EINVAL;
+    return rfk_session_create_batched(model, n_tris, img_res, scene_state, flags, 1, out);
+}
+
+extern "C" int rfk_session_create_batched(const rfk_model* model, int n_tris, int img_res, void* scene_state, int flags,
+                                          int views_per_frame, rfk_session** out) {
+    if (!out || !scene_state || n_tris <= 0 || img_res <= 0 || views_per_frame <= 0 || views_per_frame > 64) return RFK_EINVAL;
     TRY(check_model(model));
     if (img_res % model->patch_size || (img_res / model->patch_size) % model->window_size) return RFK_EINVAL;
     rfk_session* d = new rfk_session();
     d->m = *model;
     if (model->dpt) { d->dptw = *model->dpt; d->m.dpt = &d->dptw; }
-    d->N = n_tris; d->res = img_res; d->flags = flags;
+    d->N = n_tris; d->res = img_res; d->flags = flags; d->V = views_per_frame;
     d->Se = model->num_register_tokens + n_tris;
     d->Se_pad = (d->Se + 7) & ~7;
     d->pH = d->pW = img_res / model->patch_size;
@@ -271,26 +294,27 @@ extern "C" int rfk_session_create(const rfk_model* model, int n_tris, int img_re
         if (cudaEventCreate(&d->ev_start[k]) != cudaSuccess || cudaEventCreate(&d->ev_done[k]) != cudaSuccess ||
             cudaEventCreateWithFlags(&d->ev_dl[k], cudaEventDisableTiming) != cudaSuccess)
             return fail((int)cudaGetLastError());
-        if (cudaHostAlloc((void**)&d->pin_cam[k], 32 * sizeof(float), cudaHostAllocDefault) != cudaSuccess)
+        if (cudaHostAlloc((void**)&d->pin_cam[k], (size_t)views_per_frame * kCamStride * sizeof(float), cudaHostAllocDefault) != cudaSuccess)
             return fail((int)cudaGetLastError());
     }
 #define ALLOC(ptr, count)                    \
     if ((rc = d->alloc(&d->ptr, (count)))) return fail(rc)
-    ALLOC(cam_gpu, 32);
+    const size_t V = (size_t)views_per_frame;
+    ALLOC(cam_gpu, V * kCamStride);
     ALLOC(id_c2w, 16);
-    ALLOC(vtri, (size_t)n_tris * 9);
-    ALLOC(vvn, (size_t)n_tris * 9);
-    ALLOC(vpos, (size_t)Se_pad * 9);
-    ALLOC(k_cos, (size_t)Se_pad * d->hd);
-    ALLOC(k_sin, (size_t)Se_pad * d->hd);
-    ALLOC(ray_pat, (size_t)nP * 3 * model->patch_size * model->patch_size);
-    ALLOC(rtok, (size_t)nP * dim);
-    ALLOC(temp, (size_t)nP * dim);
-    ALLOC(proj, std::max((size_t)2 * nP * dim + (size_t)nh * Se_pad * d->hd, (size_t)3 * nP * dim));
-    ALLOC(qkv, (size_t)nP * std::max(3 * dim, 2 * ffn));
-    ALLOC(ffn, (size_t)nP * std::max(dim, ffn));
-    ALLOC(win, (size_t)nP * dim);
-    ALLOC(k_rot, (size_t)model->dec_layers * nh * Se_pad * d->hd);
+    ALLOC(vtri, V * n_tris * 9);
+    ALLOC(vvn, V * n_tris * 9);
+    ALLOC(vpos, V * Se_pad * 9);
+    ALLOC(k_cos, V * Se_pad * d->hd);
+    ALLOC(k_sin, V * Se_pad * d->hd);
+    ALLOC(ray_pat, V * nP * 3 * model->patch_size * model->patch_size);
+    ALLOC(rtok, V * nP * dim);
+    ALLOC(temp, V * nP * dim);
+    ALLOC(proj, V * std::max((size_t)2 * nP * dim + (size_t)nh * Se_pad * d->hd, (size_t)3 * nP * dim));
+    ALLOC(qkv, V * nP * std::max(3 * dim, 2 * ffn));
+    ALLOC(ffn, V * nP * std::max(dim, ffn));
+    ALLOC(win, V * nP * dim);
+    ALLOC(k_rot, V * model->dec_layers * nh * Se_pad * d->hd);
     ALLOC(q_gamma_all, (size_t)model->dec_layers * dim);
     {
         // Deferred Q-RMSNorm of the cross-attention (layers.cu): possible when the fused kernels serve the shape and every
@@ -300,21 +324,22 @@ extern "C" int rfk_session_create(const rfk_model* model, int n_tris, int img_re
             ok = model->dec[i].cross_attn.q_norm_gamma && !model->dec[i].cross_attn.q_proj_b && !model->dec[i].cross_attn.out_proj_b &&
                  (reinterpret_cast<uintptr_t>(model->dec[i].cross_attn.q_norm_gamma) & 15u) == 0;
         d->prescale = ok;
+        if (!ok && views_per_frame > 1) return fail(RFK_EUNSUPPORTED);  // a batch of views needs the fused attention route
         for (int i = 0; i < model->dec_layers && ok; ++i)
             if (cudaMemcpy(d->q_gamma_all + (size_t)i * dim, model->dec[i].cross_attn.q_norm_gamma, (size_t)dim * sizeof(float),
                            cudaMemcpyDeviceToDevice) != cudaSuccess)
                 return fail((int)cudaGetLastError());
     }
     const bool fused_attention = d->hd == 64 || d->hd == 128;  // rfk_flash_attention serves these
-    if (!fused_attention) ALLOC(score, (size_t)nh * nP * Se_pad);
-    if (!(ws * ws == 64 && d->hd == 64)) ALLOC(self_score, (size_t)nWin * nh * ws * ws * ws * ws);
+    if (!fused_attention) ALLOC(score, V * nh * nP * Se_pad);
+    if (!(ws * ws == 64 && d->hd == 64)) ALLOC(self_score, V * nWin * nh * ws * ws * ws * ws);
     ALLOC(shift_mask, (size_t)nWin * ws * ws * ws * ws);
     for (int k = 0; k < kSlots; ++k)
-        for (int j = 0; j < 4; ++j) ALLOC(dft[k][j], (size_t)nP * dim);
-    for (int k = 0; k < kSlots; ++k) ALLOC(result[k], (size_t)nP * dim);
+        for (int j = 0; j < 4; ++j) ALLOC(dft[k][j], V * nP * dim);
+    for (int k = 0; k < kSlots; ++k) ALLOC(result[k], V * nP * dim);
     if (model->dpt) {
-        for (int k = 0; k < kSlots; ++k) ALLOC(image[k], (size_t)d->dptw.out_dim * img_res * img_res);
-        if ((rc = rfk_dpt_create(d->ctx, &d->dptw, 1, dim, d->pH, d->pW, model->patch_size, &d->dpt))) return fail(rc);
+        for (int k = 0; k < kSlots; ++k) ALLOC(image[k], V * d->dptw.out_dim * img_res * img_res);
+        if ((rc = rfk_dpt_create(d->ctx, &d->dptw, views_per_frame, dim, d->pH, d->pW, model->patch_size, &d->dpt))) return fail(rc);
     }
 #undef ALLOC
     const float id[16] = {1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1};
@@ -477,10 +502,11 @@ extern "C" int rfk_session_finalize(rfk_session* d) {
     TRY_CUDA(cudaMemcpy(d->shift_mask, mask.data(), mask.size(), cudaMemcpyHostToDevice));
     // warm-up view (also lets cuBLAS pick and load its kernels before capture)
     float cam[17] = {1, 0, 0, 0, 0, 1, 0, 0, 0, 0, 1, 3, 0, 0, 0, 1, 0.7f};
-    for (int k = 0; k < kSlots; ++k) memcpy(d->pin_cam[k], cam, sizeof(cam));
+    for (int k = 0; k < kSlots; ++k)
+        for (int v = 0; v < d->V; ++v) memcpy(d->pin_cam[k] + v * kCamStride, cam, sizeof(cam));
     {
         int rc = d->render_view(d->pin_cam[0], d->result[0], d->dft[0], d->image[0]);
-        if (rc == RFK_EUNSUPPORTED && d->prescale) {  // the kernels of the deferred norm cannot run here: separate norm instead
+        if (rc == RFK_EUNSUPPORTED && d->prescale && d->V == 1) {  // the kernels of the deferred norm cannot run here: separate norm instead
             TRY_CUDA(cudaStreamSynchronize(d->stream));
             TRY_CUDA(cudaStreamSynchronize(d->side_stream));
             d->prescale = false;
@@ -515,18 +541,20 @@ extern "C" int rfk_session_finalize(rfk_session* d) {
     return RFK_OK;
 }
 
-extern "C" int rfk_session_render_frame(rfk_session* d, const float* h_c2w, float fov_rad) {
-    if (!d || !h_c2w || !d->finalized) return RFK_EINVAL;
+extern "C" int rfk_session_render_frames(rfk_session* d, const float* h_c2w, const float* fov_rad) {
+    if (!d || !h_c2w || !fov_rad || !d->finalized) return RFK_EINVAL;
     const int k = (int)(d->frames % kSlots);
     // the slot's previous frame (two frames ago) must have left the device, and its download
-    // must have finished, before its pinned camera and result buffer are reused
+    // must have finished, before its pinned cameras and result buffer are reused
     if (d->frames >= kSlots) TRY_CUDA(cudaEventSynchronize(d->ev_done[k]));
     if (d->dl_pending[k]) {
         TRY_CUDA(cudaEventSynchronize(d->ev_dl[k]));
         d->dl_pending[k] = false;
     }
-    memcpy(d->pin_cam[k], h_c2w, 16 * sizeof(float));
-    d->pin_cam[k][16] = fov_rad;
+    for (int v = 0; v < d->V; ++v) {
+        memcpy(d->pin_cam[k] + v * kCamStride, h_c2w + v * 16, 16 * sizeof(float));
+        d->pin_cam[k][v * kCamStride + 16] = fov_rad[v];
+    }
     TRY_CUDA(cudaEventRecord(d->ev_start[k], d->stream));
     if (d->exec[k]) TRY_CUDA(cudaGraphLaunch(d->exec[k], d->stream));
     else TRY(d->render_view(d->pin_cam[k], d->result[k], d->dft[k], d->image[k]));
@@ -534,6 +562,13 @@ extern "C" int rfk_session_render_frame(rfk_session* d, const float* h_c2w, floa
     d->frames++;
     return RFK_OK;
 }
+
+extern "C" int rfk_session_render_frame(rfk_session* d, const float* h_c2w, float fov_rad) {
+    if (!d || d->V != 1) return RFK_EINVAL;  // a session of V views per frame takes its cameras V at a time
+    return rfk_session_render_frames(d, h_c2w, &fov_rad);
+}
+
+extern "C" int rfk_session_views_per_frame(rfk_session* d) { return d ? d->V : 0; }
 
 extern "C" int rfk_session_wait(rfk_session* d, float* ms) {
     if (!d || d->frames == 0) return RFK_EINVAL;
@@ -568,7 +603,7 @@ extern "C" int rfk_session_image(rfk_session* d, const float** image, int* chann
 
 extern "C" int rfk_session_download_image(rfk_session* d, float* h_out, size_t bytes) {
     if (!d || !d->dpt || !h_out || d->frames == 0) return RFK_EINVAL;
-    const size_t need = (size_t)d->dptw.out_dim * d->res * d->res * sizeof(float);
+    const size_t need = (size_t)d->V * d->dptw.out_dim * d->res * d->res * sizeof(float);
     if (bytes < need) return RFK_EINVAL;
     const int k = (int)((d->frames - 1) % kSlots);
     TRY_CUDA(cudaStreamWaitEvent(d->copy_stream, d->ev_done[k], 0));
@@ -579,7 +614,7 @@ extern "C" int rfk_session_download_image(rfk_session* d, float* h_out, size_t b
 
 extern "C" int rfk_session_download_async(rfk_session* d, rfk_half* h_out, size_t bytes) {
     if (!d || !h_out || d->frames == 0) return RFK_EINVAL;
-    const size_t need = (size_t)d->nP * d->m.dim * sizeof(rfk_half);
+    const size_t need = (size_t)d->V * d->nP * d->m.dim * sizeof(rfk_half);
     if (bytes < need) return RFK_EINVAL;
     const int k = (int)((d->frames - 1) % kSlots);
     TRY_CUDA(cudaStreamWaitEvent(d->copy_stream, d->ev_done[k], 0));

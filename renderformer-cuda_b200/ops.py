@@ -267,13 +267,13 @@ def window_attention(q, k, v, o, mask, BnW, Hh, nW, window_tokens=64, head_dim=6
 
 
 def flash_attention_ex(q, k, v, o, B, Hh, Sq, Sk, n_keys, D, q_row_ss=None, ss_tiles=0, norm_dim=0, workspace=None,
-                       o_bshd=False, scale=None, eps=K_EPS_FP16):
+                       o_bshd=False, scale=None, eps=K_EPS_FP16, v_shared=False):
     """flash_attention (tcgen05 kernel) with optional row statistics - rows scaled by rsqrt(sum(q_row_ss[row]) / norm_dim +
     eps), the query's RMSNorm applied to the scores while its weight rides on the keys - and an optional workspace
-    (flash_attention_workspace()) for the balanced key split."""
+    (flash_attention_workspace()) for the key split; v_shared: v is [Hh, Sk, D], the same values for every batch element."""
     _call("rfk_flash_attention_ex", _p(q, H, "q"), _p(k, H, "k"), _p(v, H, "v"), _p(o, H, "o"), _p(q_row_ss, F, "q_row_ss"),
-          ss_tiles, norm_dim, eps, _p(workspace, U8, "workspace"), 0 if workspace is None else workspace.numel(), B, Hh, Sq, Sk,
-          n_keys, D, int(o_bshd), float(scale if scale is not None else D ** -0.5), _stream())
+          ss_tiles, norm_dim, eps, _p(workspace, U8, "workspace"), 0 if workspace is None else workspace.numel(), int(v_shared),
+          B, Hh, Sq, Sk, n_keys, D, int(o_bshd), float(scale if scale is not None else D ** -0.5), _stream())
 
 
 def flash_attention_workspace():

@@ -276,8 +276,11 @@ class RenderSession:
     for a scene, then render_frame / wait / download per camera view."""
 
     def __init__(self, model: Model, n_tris: int, img_res: int = 512, scene_state: torch.Tensor | None = None,
-                 pad_keys_attend: bool = False, use_graph: bool = True):
+                 pad_keys_attend: bool = False, use_graph: bool = True, views_per_frame: int = 1):
+        """views_per_frame > 1: a frame is that many views rendered together as one batch (rfk_session_create_batched);
+        cameras go in through render_frames, results come back as [views_per_frame, n_tokens, dim]."""
         self.model, self.n_tris, self.img_res = model, n_tris, img_res
+        self.views_per_frame = int(views_per_frame)
         lib = _lib()
         lib.rfk_scene_state_bytes.restype = ctypes.c_size_t
         nbytes = lib.rfk_scene_state_bytes(ctypes.byref(model.c), n_tris)
@@ -290,10 +293,11 @@ class RenderSession:
         self.scene_state = scene_state
         flags = (RFK_SESSION_PAD_KEYS_ATTEND if pad_keys_attend else 0) | (0 if use_graph else RFK_SESSION_NO_GRAPH)
         self.h = VP()
-        _check("rfk_session_create", lib.rfk_session_create(ctypes.byref(model.c), n_tris, img_res,
-                                                            scene_state.data_ptr(), flags, ctypes.byref(self.h)))
+        _check("rfk_session_create_batched", lib.rfk_session_create_batched(ctypes.byref(model.c), n_tris, img_res,
+                                                                            scene_state.data_ptr(), flags, self.views_per_frame,
+                                                                            ctypes.byref(self.h)))
         self.n_tokens = (img_res // model.patch_size) ** 2
-        self.result_bytes = self.n_tokens * model.dim * 2
+        self.result_bytes = self.n_tokens * model.dim * 2          # per view
 
     def encode_scene(self, tri: torch.Tensor, vn: torch.Tensor, tex: torch.Tensor):
         """tri, vn [N,3,3] fp32 (world space), tex [N, texture_channels] fp16. Runs the scene
@@ -317,6 +321,20 @@ class RenderSession:
         """Same with a raw host pointer to 16 floats (no per-call conversion)."""
         _check("rfk_session_render_frame", _lib().rfk_session_render_frame(self.h, VP(c2w_ptr), ctypes.c_float(fov_rad)))
 
+    def render_frames(self, c2ws, fovs):
+        """One frame of views_per_frame views: c2ws [V, 4, 4] (or [V, 16]) and fovs [V], host arrays / CPU tensors."""
+        V = self.views_per_frame
+        flat = [float(x) for x in (c2ws.reshape(-1).tolist() if hasattr(c2ws, "reshape") else c2ws)]
+        fv = [float(x) for x in (fovs.tolist() if hasattr(fovs, "tolist") else fovs)]
+        if len(flat) != 16 * V or len(fv) != V:
+            raise ValueError(f"render_frames takes {V} cameras")
+        _check("rfk_session_render_frames", _lib().rfk_session_render_frames(self.h, (ctypes.c_float * (16 * V))(*flat),
+                                                                             (ctypes.c_float * V)(*fv)))
+
+    def render_frames_raw(self, c2w_ptr: int, fov_ptr: int):
+        """Same with raw host pointers to [V][16] and [V] floats."""
+        _check("rfk_session_render_frames", _lib().rfk_session_render_frames(self.h, VP(c2w_ptr), VP(fov_ptr)))
+
     def wait(self) -> float:
         ms = ctypes.c_float()
         _check("rfk_session_wait", _lib().rfk_session_wait(self.h, ctypes.byref(ms)))
@@ -326,9 +344,12 @@ class RenderSession:
         """The last frame's token map [n_tokens, dim] fp16 as a device tensor (via the host)."""
         return self.download().to(self.model.device)
 
+    def _frame_shape(self, *per_view):
+        return per_view if self.views_per_frame == 1 else (self.views_per_frame, *per_view)
+
     def download(self, host: torch.Tensor | None = None) -> torch.Tensor:
         if host is None:
-            host = torch.empty(self.n_tokens, self.model.dim, dtype=torch.float16).pin_memory()
+            host = torch.empty(*self._frame_shape(self.n_tokens, self.model.dim), dtype=torch.float16).pin_memory()
         _check("rfk_session_download", _lib().rfk_session_download(self.h, host.data_ptr(), host.numel() * 2))
         return host
 
@@ -336,7 +357,7 @@ class RenderSession:
         """The last frame's image [out_dim, img_res, img_res] fp32 (models with a DPT head), waits for the frame."""
         m = self.model
         if host is None:
-            host = torch.empty(m.dpt_out_dim, self.img_res, self.img_res, dtype=torch.float32).pin_memory()
+            host = torch.empty(*self._frame_shape(m.dpt_out_dim, self.img_res, self.img_res), dtype=torch.float32).pin_memory()
         _check("rfk_session_download_image", _lib().rfk_session_download_image(self.h, host.data_ptr(), host.numel() * 4))
         return host
 
@@ -403,7 +424,7 @@ class ViewScheduler:
     inject a host-only stand-in to drive this class without a GPU."""
 
     def __init__(self, model: Model, n_tris: int, img_res: int = 512, process_group=None, pad_keys_attend=False,
-                 streams_per_gpu: int = 1, session_factory=None):
+                 streams_per_gpu: int = 1, session_factory=None, views_per_frame: int = 1):
         import torch.distributed as dist
         self.dist = dist if (dist.is_available() and dist.is_initialized()) else None
         self.group = process_group
@@ -411,9 +432,13 @@ class ViewScheduler:
         self.world = self.dist.get_world_size(process_group) if self.dist else 1
         if streams_per_gpu < 1:
             raise ValueError("streams_per_gpu must be at least 1")
+        if views_per_frame < 1:
+            raise ValueError("views_per_frame must be at least 1")
+        self.views_per_frame = views_per_frame
         if session_factory is None:
             def session_factory(scene_state):
-                return RenderSession(model, n_tris, img_res, scene_state=scene_state, pad_keys_attend=pad_keys_attend)
+                return RenderSession(model, n_tris, img_res, scene_state=scene_state, pad_keys_attend=pad_keys_attend,
+                                     views_per_frame=views_per_frame)
         self.session = session_factory(None)
         self.sessions = [self.session] + [session_factory(self.session.scene_state) for _ in range(streams_per_gpu - 1)]
         self.broadcast_ms = 0.0
@@ -472,6 +497,8 @@ class ViewScheduler:
 
     def _render_list(self, views, base, stride, fl, out, out_pos) -> list[int]:
         """Renders `views` in order; returns those NOT rendered because a session call raised."""
+        if self.views_per_frame > 1:
+            return self._render_list_batched(views, base, stride, fl, out, out_pos)
         n = len(self.sessions)
         for j, v in enumerate(views):
             if self.failed:
@@ -486,12 +513,50 @@ class ViewScheduler:
                 return list(views[j:])
         return []
 
+    def _render_list_batched(self, views, base, stride, fl, out, out_pos) -> list[int]:
+        """The same for sessions that take views_per_frame views per frame: the list is cut into frames (the last one
+        padded by repeating its last view; the padding's results are dropped). A frame's cameras are gathered first,
+        because a rank's views are strided in the caller's array."""
+        V, n = self.views_per_frame, len(self.sessions)
+        n_frames = (len(views) + V - 1) // V
+        self._tail_rows = None
+        for f in range(n_frames):
+            ids = list(views[f * V:(f + 1) * V])
+            real = len(ids)
+            ids += [ids[-1]] * (V - real)
+            if self.failed:
+                return list(views[f * V:])
+            ses = self.sessions[f % n]
+            try:
+                cams = (ctypes.c_float * (16 * V))()          # the call copies them into the session's pinned slot
+                for i, v in enumerate(ids):
+                    ctypes.memmove(ctypes.addressof(cams) + i * 64, base + v * stride, 64)
+                fovs = (ctypes.c_float * V)(*[fl[v] for v in ids])
+                ses.render_frames_raw(ctypes.addressof(cams), ctypes.addressof(fovs))
+                if out is not None:
+                    if real == V:
+                        ses.download_async(out[out_pos + f * V: out_pos + (f + 1) * V])
+                    else:                      # partial last frame: through a scratch frame, copied out after the drain
+                        if getattr(self, "_tail", None) is None:
+                            self._tail = torch.empty(V, *out.shape[1:], dtype=out.dtype).pin_memory()
+                        ses.download_async(self._tail)
+                        self._tail_rows = (out, out_pos + f * V, real)
+            except Exception as e:
+                self.failed, self.last_error = True, e
+                return list(views[f * V:])
+        return []
+
     def _drain(self):
         for ses in self.sessions:
             try:
                 ses.drain()
             except Exception as e:
                 self.failed, self.last_error = True, e
+        rows = getattr(self, "_tail_rows", None)
+        if rows is not None and not self.failed:
+            out, pos, real = rows
+            out[pos:pos + real].copy_(self._tail[:real])
+        self._tail_rows = None
 
     def render(self, c2ws: torch.Tensor, fovs: torch.Tensor, out: torch.Tensor | None = None) -> list[int]:
         """c2ws [V,4,4] fp32 and fovs [V] fp32 (radians) on the HOST. Renders this rank's views;

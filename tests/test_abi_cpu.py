@@ -58,10 +58,10 @@ def test_null_and_bad_shapes_are_rejected_without_a_device():
     # the extended attention, the head-split projection and the normed window attention: checks before any device work
     ws_bytes = lib.rfk_flash_attention_workspace_bytes()
     assert ws_bytes > 20 << 20
-    assert lib.rfk_flash_attention_ex(fake, fake, fake, fake, null, 0, 0, 0.0, fake, ws_bytes - 1, 1, 2, 16, 8, 8, 64, 0, 0.125, null) == -1   # workspace too small
-    assert lib.rfk_flash_attention_ex(fake, fake, fake, fake, fake, 0, 128, 1e-3, null, 0, 1, 2, 16, 8, 8, 64, 0, 0.125, null) == -1     # statistics without tiles
-    assert lib.rfk_flash_attention_ex(fake, fake, fake, fake, null, 0, 0, 0.0, null, 0, 1, 2, 16, 8, 8, 128, 0, 0.125, null) == -2       # tcgen05 kernel: head size 64 only
-    assert lib.rfk_flash_attention_ex(fake, fake, fake, fake, null, 0, 0, 0.0, null, 0, 1, 2, 0, 8, 8, 64, 0, 0.125, null) == 0          # no queries
+    assert lib.rfk_flash_attention_ex(fake, fake, fake, fake, null, 0, 0, 0.0, fake, ws_bytes - 1, 0, 1, 2, 16, 8, 8, 64, 0, 0.125, null) == -1   # workspace too small
+    assert lib.rfk_flash_attention_ex(fake, fake, fake, fake, fake, 0, 128, 1e-3, null, 0, 0, 1, 2, 16, 8, 8, 64, 0, 0.125, null) == -1     # statistics without tiles
+    assert lib.rfk_flash_attention_ex(fake, fake, fake, fake, null, 0, 0, 0.0, null, 0, 0, 1, 2, 16, 8, 8, 128, 0, 0.125, null) == -2       # tcgen05 kernel: head size 64 only
+    assert lib.rfk_flash_attention_ex(fake, fake, fake, fake, null, 0, 0, 0.0, null, 0, 0, 1, 2, 0, 8, 8, 64, 0, 0.125, null) == 0          # no queries
     assert lib.rfk_gemm_f16_heads(fake, 64, fake, 64, fake, 0, null, 1, 64, 256, 64, 32, 4, null) == -1     # statistics asked for, no buffer
     assert lib.rfk_gemm_f16_heads(fake, 64, fake, 64, fake, 0, null, 0, 64, 200, 64, 32, 4, null) == -1     # N not parts * heads * 64
     assert lib.rfk_gemm_f16_heads(fake, 64, fake, 64, fake, 0, null, 0, 0, 256, 64, 32, 4, null) == 0       # no rows
