@@ -538,7 +538,9 @@ class ViewScheduler:
                         ses.download_async(out[out_pos + f * V: out_pos + (f + 1) * V])
                     else:                      # partial last frame: through a scratch frame, copied out after the drain
                         if getattr(self, "_tail", None) is None:
-                            self._tail = torch.empty(V, *out.shape[1:], dtype=out.dtype).pin_memory()
+                            self._tail = torch.empty(V, *out.shape[1:], dtype=out.dtype)
+                            if out.is_pinned():
+                                self._tail = self._tail.pin_memory()
                         ses.download_async(self._tail)
                         self._tail_rows = (out, out_pos + f * V, real)
             except Exception as e:

@@ -140,3 +140,65 @@ def test_view_scheduler_single_rank_failure_raises():
     except session.SchedulerError as e:
         raised = "[1, 2]" in str(e)
     assert raised
+
+
+class FakeBatchedSession(FakeSession):
+    """Stand-in for a session whose frame holds several views: a frame's rows are its views' fovs plus one scene byte."""
+
+    def __init__(self, scene_state, views, fail_after=None):
+        super().__init__(scene_state, fail_after)
+        self.views, self.frames = views, []
+
+    def render_frames_raw(self, cams_ptr, fovs_ptr):
+        import ctypes
+        assert self.finalized
+        if self.fail_after is not None and self.count >= self.fail_after:
+            raise session.RfkLayersError("injected failure of this rank's device")
+        self.count += 1
+        self.last_fovs = list((ctypes.c_float * self.views).from_address(fovs_ptr))
+        cams = list((ctypes.c_float * (16 * self.views)).from_address(cams_ptr))
+        self.frames.append((self.last_fovs, cams[::16]))          # element [0,0] of each camera carries its view id
+
+    def download_async(self, host):
+        assert host.shape[0] == self.views
+        for i, f in enumerate(self.last_fovs):
+            host[i].fill_(f + float(self.scene_state[1]))
+
+
+def _batched(n_views, per_frame, streams=1, fail_after=None):
+    made = []
+
+    def factory(st):
+        made.append(FakeBatchedSession(st, per_frame, fail_after))
+        return made[-1]
+    sched = session.ViewScheduler(None, 0, session_factory=factory, streams_per_gpu=streams, views_per_frame=per_frame)
+    sched.load_scene("tri", "vn", "tex")
+    c2ws = torch.zeros(n_views, 4, 4)
+    c2ws[:, 0, 0] = torch.arange(n_views, dtype=torch.float32)
+    return sched, made, c2ws, torch.arange(n_views, dtype=torch.float32)
+
+
+def test_view_scheduler_cuts_views_into_frames_and_pads_the_last_one():
+    for n_views, per_frame, streams in [(8, 4, 1), (11, 4, 2), (3, 4, 1), (5, 2, 3)]:
+        sched, made, c2ws, fovs = _batched(n_views, per_frame, streams)
+        out = torch.full((n_views, 4), -1.0)
+        done = sched.render(c2ws, fovs, out)
+        assert done == list(range(n_views))
+        assert torch.equal(out, (fovs + 4.0)[:, None].expand(n_views, 4))    # padded views never reach `out`
+        frames = [f for s in made for f in s.frames]
+        assert len(frames) == -(-n_views // per_frame)
+        assert [len(s.frames) for s in made] == [len(range(i, len(frames), streams)) for i in range(streams)]
+        for fv, cam_ids in frames:
+            assert fv == cam_ids                      # every camera travelled with its own fov
+        tail = max(frames, key=lambda f: f[0][0])[0]
+        assert tail[-1] == float(n_views - 1) and all(v == tail[-1] for v in tail[(n_views - 1) % per_frame:])
+
+
+def test_view_scheduler_batched_single_rank_failure_raises():
+    sched, made, c2ws, fovs = _batched(9, 4, fail_after=1)
+    try:
+        sched.render(c2ws, fovs, torch.zeros(9, 4))
+        raised = False
+    except session.SchedulerError:
+        raised = True
+    assert raised and sched.failed and made[0].count == 1
