@@ -386,21 +386,30 @@ def measured_tensor_peak():
     return 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
 
 
-def attention_roofline(n_tris, nr, heads, n_tokens, head_dim, iters=12):
-    """Dominant rfk kernel of a view: the fused cross-attention (tcgen05 / tensor-memory kernel
-    at head_dim 64). A contraction, so its bound is the tensor pipe: achieved = 4*H*Sq*n_keys*D flop per
+ATTENTION_TRAFFIC = {1: 31654912, 4: 106805888}   # DRAM bytes per launch, by views per launch
+
+
+def attention_roofline(n_tris, nr, heads, n_tokens, head_dim, views=1, iters=12):
+    """Dominant rfk kernel of a frame: the fused cross-attention (tcgen05 / tensor-memory kernel
+    at head_dim 64). A contraction, so its bound is the tensor pipe: achieved = 4*V*H*Sq*n_keys*D flop per
     launch / average launch duration, timed live with CUDA events (graph replay of `iters`
-    launches, K/V/Q rotated over two buffer sets), at the exact shape the session launches."""
+    launches, K/V/Q rotated over two buffer sets), in the form the session launches for a frame of
+    `views` views: own queries and rotated keys per view, one set of values, the queries' RMSNorm
+    applied from their row statistics."""
     import torch
     import renderformer_cuda_b200 as pkg
     Se = nr + n_tris; Se_pad = (Se + 7) & ~7
+    V, dim = views, heads * head_dim
     sets = []
     for _ in range(2):
-        q = torch.randn(1, heads, n_tokens, head_dim, device="cuda").half()
-        k = torch.randn(1, heads, Se_pad, head_dim, device="cuda").half()
-        v = torch.randn(1, heads, Se_pad, head_dim, device="cuda").half()
-        sets.append((q, k, v, torch.empty(1, n_tokens, heads * head_dim, device="cuda", dtype=torch.float16)))
-    fn = lambda i: pkg.ops.flash_attention(*sets[i % 2], 1, heads, n_tokens, Se_pad, Se, head_dim, o_bshd=True)
+        q = torch.randn(V, heads, n_tokens, head_dim, device="cuda").half()
+        k = torch.randn(V, heads, Se_pad, head_dim, device="cuda").half()
+        v = torch.randn(heads, Se_pad, head_dim, device="cuda").half()
+        ss = torch.rand(V, n_tokens, dim // 256, device="cuda") * 256.0 + 1.0
+        sets.append((q, k, v, torch.empty(V, n_tokens, dim, device="cuda", dtype=torch.float16), ss))
+    ws = pkg.ops.flash_attention_workspace()
+    fn = lambda i: pkg.ops.flash_attention_ex(*sets[i % 2][:4], V, heads, n_tokens, Se_pad, Se, head_dim, q_row_ss=sets[i % 2][4],
+                                              ss_tiles=dim // 256, norm_dim=dim, workspace=ws, o_bshd=True, v_shared=True)
     for i in range(3):
         fn(i)
     g = torch.cuda.CUDAGraph()
@@ -413,22 +422,22 @@ def attention_roofline(n_tris, nr, heads, n_tokens, head_dim, iters=12):
     st.record(); g.replay(); en.record()
     torch.cuda.synchronize()
     ms = st.elapsed_time(en) / iters
-    flop = 4.0 * heads * n_tokens * Se * head_dim
+    flop = 4.0 * V * heads * n_tokens * Se * head_dim
     tf = flop / (ms * 1e-3) / 1e12
     peak, src = measured_tensor_peak()
-    alg_bytes = 2 * (2 * heads * n_tokens * head_dim + 2 * heads * Se_pad * head_dim)
-    del sets
+    alg_bytes = 2 * (2 * V * heads * n_tokens * head_dim + (V + 1) * heads * Se_pad * head_dim)   # Q, O, K per view; V once
+    del sets, ws
     torch.cuda.empty_cache()
     name = "attention_tc_kernel (tcgen05)" if head_dim == 64 else f"flash_attention_kernel<{head_dim}> (mma.sync)"
     err = pkg.ops.flash_attention_error(clear=False)
     if err:
         raise RuntimeError(f"tcgen05 attention kernel reported error word {err}")
-    return {"bound": "tensor", "kernel": f"{name} [{heads}x{n_tokens} queries x {Se} keys]",
+    return {"bound": "tensor", "kernel": f"{name} [{V} views x {heads}x{n_tokens} queries x {Se} keys]",
             "achieved": round(tf, 1), "peak": peak, "unit": "TFLOP/s", "frac": round(tf / peak, 3), "peak_source": src,
-            "us_per_launch": round(ms * 1e3, 1), "flop_per_launch": flop, "algorithmic_bytes": alg_bytes,
-            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel at this shape inside this
-            # benchmark, from one ncu capture
-            "traffic": 31654912 if head_dim == 64 else None}
+            "us_per_launch": round(ms * 1e3, 1), "views_per_launch": V, "flop_per_launch": flop, "algorithmic_bytes": alg_bytes,
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel in this form, from one ncu
+            # capture each (one view; a frame of four views)
+            "traffic": ATTENTION_TRAFFIC.get(V) if head_dim == 64 else None}
 
 
 N_REPS = 7   # the K-step loop is timed this many times per figure; the median is reported
@@ -650,7 +659,7 @@ def run_views(args, rank, world, peak, peak_src):
         line["rfk_kernels_per_frame"] = ses.kernels_per_view
         line["gpu_launches"] = ses.kernels_per_view * frames * N_REPS
         line["roofline"] = attention_roofline(N_TRIS, model.num_register_tokens, model.num_heads, ses.n_tokens,
-                                              model.head_dim)
+                                              model.head_dim, views=Vf)
         sched.close()
     return line
 

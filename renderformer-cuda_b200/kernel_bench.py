@@ -422,6 +422,7 @@ def _main():
     ap.add_argument("--profile", choices=["attention", "gemm", "dpt"],
                     help="a few plain launches of the fused cross-attention (16 x 4096 queries x 5665 keys) or of the "
                          "decoder layer's projections through rfk_gemm_f16, for a profiler capture")
+    ap.add_argument("--views", type=int, default=1, help="--profile attention: views per launch (a frame of the batched session)")
     a = ap.parse_args()
     if a.gemm:
         for row in gemm_table(a.iters):
@@ -460,12 +461,23 @@ def _main():
             return
         if a.profile == "attention":
             Se = 5665; Sp = (Se + 7) & ~7
-            q, k, v = _r((1, HEADS, NP, HD), H16), _r((1, HEADS, Sp, HD), H16), _r((1, HEADS, Sp, HD), H16)
-            o = torch.empty(1, NP, HEADS * HD, device="cuda", dtype=H16)
-            for _ in range(a.iters):
-                ops.flash_attention(q, k, v, o, 1, HEADS, NP, Sp, Se, HD, o_bshd=True)
+            V = a.views
+            if V == 1:
+                q, k, v = _r((1, HEADS, NP, HD), H16), _r((1, HEADS, Sp, HD), H16), _r((1, HEADS, Sp, HD), H16)
+                o = torch.empty(1, NP, HEADS * HD, device="cuda", dtype=H16)
+                for _ in range(a.iters):
+                    ops.flash_attention(q, k, v, o, 1, HEADS, NP, Sp, Se, HD, o_bshd=True)
+            else:
+                # a frame of V views as the session launches it: own queries and rotated keys per view, one set of
+                # values, the queries' RMSNorm applied from their row statistics
+                q, k, v = _r((V, HEADS, NP, HD), H16), _r((V, HEADS, Sp, HD), H16), _r((HEADS, Sp, HD), H16)
+                o = torch.empty(V, NP, HEADS * HD, device="cuda", dtype=H16)
+                ss = torch.rand(V, NP, D // 256, device="cuda") * 256.0 + 1.0
+                for _ in range(a.iters):
+                    ops.flash_attention_ex(q, k, v, o, V, HEADS, NP, Sp, Se, HD, q_row_ss=ss, ss_tiles=D // 256, norm_dim=D,
+                                           o_bshd=True, v_shared=True)
             torch.cuda.synchronize()
-            print(json.dumps({"kernel": "flash_attention 16x4096x5665 d64", "launched": a.iters, "error_word": ops.flash_attention_error()}))
+            print(json.dumps({"kernel": f"flash_attention {V}x16x4096x5665 d64", "launched": a.iters, "error_word": ops.flash_attention_error()}))
         else:
             M, dim, ffn = NP, D, 4096
             x, xh = _r((M, dim), H16), _r((M, ffn), H16)
