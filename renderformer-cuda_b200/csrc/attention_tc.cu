@@ -16,7 +16,10 @@
 //                next two tiles ready and never wait for a product.
 //   warps 0-7    softmax (block = warp / 4): a thread owns one query row = its tensor-memory lane,
 //                so row maximum and row sum are thread-local (no shuffles). The 64 scores come to
-//                registers with tcgen05.ld; P = exp2(...) is rounded to fp16 and stored back with
+//                registers with tcgen05.ld; the common tile exponentiates them against the running
+//                reference right away and checks afterwards that this was admissible (the exact path,
+//                with the tile's maximum first, runs for the first tile, a padded last tile and a
+//                failed check); P = exp2(...) is rounded to fp16 and stored back with
 //                tcgen05.st over the first 32 columns of the same score buffer, from where
 //   warps 9-10   one thread per block issues O += P V with P as the A operand from tensor memory
 //                and V (MN-major) from shared memory: P never passes through shared memory. The
@@ -116,8 +119,13 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 }
 
 // 2^x for two values on the FMA pipes (no special-function unit): x = n + f with n = round(x),
-// 2^f from a degree-4 polynomial on [-0.5, 0.5] (relative error 2.6e-6, far below the fp16 rounding
-// of the result), and n added into the exponent field. Inputs below -125 give a value near 2^-125.
+// 2^f from a polynomial on [-0.5, 0.5] and n added into the exponent field. Degree 3 (the default;
+// relative error 7.5e-5, a sixth of the fp16 rounding of the result) or, with -DRFK_ATTN_POLY_DEG=4,
+// degree 4 (2.6e-6). Inputs below -125 give a value near 2^-125; the result is only good for inputs
+// below 128 (the caller checks the largest it passes).
+#ifndef RFK_ATTN_POLY_DEG
+#define RFK_ATTN_POLY_DEG 3
+#endif
 __device__ __forceinline__ float2 exp2_poly(float2 x) {
     constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: x + kMagic holds round(x) in its low mantissa bits
     x.x = fmaxf(x.x, -125.0f);
@@ -125,16 +133,22 @@ __device__ __forceinline__ float2 exp2_poly(float2 x) {
     const float2 t = __fadd2_rn(x, make_float2(kMagic, kMagic));
     const float2 n = __fadd2_rn(t, make_float2(-kMagic, -kMagic));
     const float2 f = __ffma2_rn(n, make_float2(-1.0f, -1.0f), x);
+#if RFK_ATTN_POLY_DEG == 3
+    float2 p = __ffma2_rn(f, make_float2(0.05517136f, 0.05517136f), make_float2(0.2426111f, 0.2426111f));
+    p = __ffma2_rn(p, f, make_float2(0.69326103f, 0.69326103f));
+    p = __ffma2_rn(p, f, make_float2(0.99992806f, 0.99992806f));
+#else
     float2 p = __ffma2_rn(f, make_float2(0.009570092f, 0.009570092f), make_float2(0.05591786f, 0.05591786f));
     p = __ffma2_rn(p, f, make_float2(0.24024744f, 0.24024744f));
     p = __ffma2_rn(p, f, make_float2(0.6931218f, 0.6931218f));
     p = __ffma2_rn(p, f, make_float2(0.9999993f, 0.9999993f));
+#endif
     return make_float2(__uint_as_float(__float_as_uint(p.x) + (__float_as_uint(t.x) << 23)),
                        __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(t.y) << 23)));
 }
 
-// 32 raw scores (columns col0 .. col0+31 of the tile) -> 32 probabilities exp2(s * c - mc), packed
-// two fp16 per word into pk[0..16); their fp32 sums are added to acc0 / acc1 (two lanes each).
+// 32 raw scores -> 32 probabilities exp2(s * c - mc), packed two fp16 per word into pk[0..16); their
+// fp32 sums are added to acc0 / acc1 (two lanes each).
 // Packed fp32x2 multiply-adds and adds halve the instruction count around the exponentials. The
 // special-function unit (16 exponentials per clock and SM) is the scarcest resource of this kernel,
 // so of every four pairs, those selected by kPolyMask take the polynomial path instead.
@@ -142,9 +156,13 @@ __device__ __forceinline__ float2 exp2_poly(float2 x) {
 #define RFK_ATTN_POLY_MASK 0x1
 #endif
 constexpr int kPolyMask = RFK_ATTN_POLY_MASK;
-template <bool MASKED>
-__device__ __forceinline__ void exp_half(uint32_t (&v)[32], uint32_t* pk /* may alias v */, int col0, int n_valid, float c,
-                                         float mc, float2& acc0, float2& acc1) {
+#ifndef RFK_ATTN_POLY_PERIOD
+#define RFK_ATTN_POLY_PERIOD 4
+#endif
+__device__ __forceinline__ constexpr bool poly_pair(int pair) { return (kPolyMask >> (pair % RFK_ATTN_POLY_PERIOD)) & 1; }
+
+__device__ __forceinline__ void exp_half(uint32_t (&v)[32], uint32_t* pk /* may alias v */, float c, float mc, float2& acc0,
+                                         float2& acc1, float& poly_max) {
     const float2 c2 = make_float2(c, c), nm2 = make_float2(-mc, -mc);
     // three passes over the registers, each a run of independent instructions: exponents, exponentials
     // (back to back, so that one warp alone can keep the special-function unit busy), then sums and packing
@@ -156,18 +174,16 @@ __device__ __forceinline__ void exp_half(uint32_t (&v)[32], uint32_t* pk /* may 
     }
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-        if ((kPolyMask >> ((i >> 1) & 3)) & 1) continue;  // this pair takes the polynomial path below
-        float p = fast_exp2(__uint_as_float(v[i]));
-        if (MASKED && col0 + i >= n_valid) p = 0.0f;  // last tile: keys at or beyond n_keys contribute nothing
-        v[i] = __float_as_uint(p);
+        if (poly_pair(i >> 1)) continue;  // this pair takes the polynomial path below
+        v[i] = __float_as_uint(fast_exp2(__uint_as_float(v[i])));
     }
     if (kPolyMask) {
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-            if ((kPolyMask >> ((i >> 1) & 3)) & 1) {
-                float2 p = exp2_poly(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
-                if (MASKED && col0 + i >= n_valid) p.x = 0.0f;
-                if (MASKED && col0 + i + 1 >= n_valid) p.y = 0.0f;
+            if (poly_pair(i >> 1)) {
+                // the polynomial path is only good for exponents below 128: the caller checks the largest it was given
+                poly_max = fmax3(poly_max, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                const float2 p = exp2_poly(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
                 v[i] = __float_as_uint(p.x);
                 v[i + 1] = __float_as_uint(p.y);
             }
@@ -341,6 +357,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         regs_take();
         // ------------------------------------------------------------ softmax, warps 0-7 (query block = warp / 4)
         constexpr unsigned kFull = 0xffffffffu;
+        constexpr float kSumLimit = 256.0f;  // 2^kRescaleThreshold
+        constexpr uint32_t kNegInf = 0xff800000u;
         constexpr float kRescaleThreshold = 8.0f;  // in exponent units: P stays below 2^8, well inside fp16
         const int blk = warp >> 2;
         const int r = (warp & 3) * 32 + lane;                       // query row within the block = its tensor-memory lane
@@ -367,50 +385,62 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             ok = tc::mbar_wait_warp(&ctrl->s_full[blk][buf], buf_par, abort_flag);
             if (!ok) break;
             tc::tc_fence_after();
-            tc::tmem_ld32(tS, va);
-            tc::tmem_ld32(tS + 32, vb);
-            tc::tc_wait_ld(va);
-            tc::tc_wait_ld(vb);
             const int n_valid = min(BN, n_keys - (t0 + j) * BN);  // real keys among this tile's 64 columns
-            float m_tile;
-            if (n_valid == BN) {
-                float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-#pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    m0 = fmax3(m0, __uint_as_float(va[i]), __uint_as_float(va[i + 1]));
-                    m1 = fmax3(m1, __uint_as_float(va[i + 2]), __uint_as_float(va[i + 3]));
-                    m2 = fmax3(m2, __uint_as_float(vb[i]), __uint_as_float(vb[i + 1]));
-                    m3 = fmax3(m3, __uint_as_float(vb[i + 2]), __uint_as_float(vb[i + 3]));
-                }
-                m_tile = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-            } else {
-                m_tile = -INFINITY;
+            tc::tmem_ld32(tS, va);
+            tc::tc_wait_ld(va);
+            tc::tmem_ld32(tS + 32, vb);  // in flight during the first half's arithmetic
+            if (n_valid != BN) {  // last tile: keys at or beyond n_keys score -inf, i.e. contribute nothing
+                tc::tc_wait_ld(vb);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    if (i < n_valid) m_tile = fmaxf(m_tile, __uint_as_float(va[i]));
-                    if (32 + i < n_valid) m_tile = fmaxf(m_tile, __uint_as_float(vb[i]));
+                    if (i >= n_valid) va[i] = kNegInf;
+                    if (32 + i >= n_valid) vb[i] = kNegInf;
                 }
             }
-            // The running maximum only follows when it would move by more than the threshold; until then
-            // the probabilities of this row are scaled by up to 2^threshold, which cancels in O / l.
-            const bool move = (m_tile - m_run) * scale_log2e > kRescaleThreshold;  // first tile: m_run = -inf
-            const float m_new = move ? m_tile : m_run;
-            const float mc = m_new * scale_log2e;
-            const bool any_move = __any_sync(kFull, move);  // rare after the first tiles: keeps alpha off the common path
-            float alpha = 1.0f;
-            if (any_move && move) alpha = fast_exp2((m_run - m_new) * scale_log2e);  // first tile: 0
-            // P = exp2(scale * log2e * (S - max)), two fp16 per 32-bit column: keys 2i, 2i+1 in column i.
-            // The packed words overwrite the scores they came from: va[0..16) and vb[0..16).
-            float2 acc0 = make_float2(0.0f, 0.0f), acc1 = make_float2(0.0f, 0.0f);
-            if (n_valid == BN) {
-                exp_half<false>(va, va, 0, n_valid, scale_log2e, mc, acc0, acc1);
-                exp_half<false>(vb, vb, 32, n_valid, scale_log2e, mc, acc0, acc1);
-            } else {
-                exp_half<true>(va, va, 0, n_valid, scale_log2e, mc, acc0, acc1);
-                exp_half<true>(vb, vb, 32, n_valid, scale_log2e, mc, acc0, acc1);
-            }
+            // The running maximum only follows a tile's maximum when it would move by more than the threshold; until
+            // then the probabilities of the row are scaled by up to 2^threshold, which cancels in O / l. So the common
+            // tile leaves the reference where it is, and its exponentials start from the reference already known,
+            // without this tile's maximum ahead of them: if afterwards no row's probabilities sum to more than
+            // 2^threshold, none of them exceeded it and the tile is done. Otherwise (and for the first and the last
+            // tile) the scores are read again, the maximum is taken and the same code runs once more.
+            float2 acc0, acc1;
+            float m_new = m_run, alpha = 1.0f;
+            bool any_move = false, need_max = j == 0 || n_valid != BN;
+#pragma unroll 1
+            for (;;) {
+                acc0 = make_float2(0.0f, 0.0f);
+                acc1 = make_float2(0.0f, 0.0f);
+                if (need_max) {
+                    tc::tc_wait_ld(vb);
+                    float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) va[16 + i] = vb[i];  // va = the 32 columns of P
+                    for (int i = 0; i < 32; i += 4) {
+                        m0 = fmax3(m0, __uint_as_float(va[i]), __uint_as_float(va[i + 1]));
+                        m1 = fmax3(m1, __uint_as_float(va[i + 2]), __uint_as_float(va[i + 3]));
+                        m2 = fmax3(m2, __uint_as_float(vb[i]), __uint_as_float(vb[i + 1]));
+                        m3 = fmax3(m3, __uint_as_float(vb[i + 2]), __uint_as_float(vb[i + 3]));
+                    }
+                    const float m_tile = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+                    const bool move = (m_tile - m_run) * scale_log2e > kRescaleThreshold;  // first tile: m_run = -inf
+                    m_new = move ? m_tile : m_run;
+                    any_move = __any_sync(kFull, move);
+                    if (any_move && move) alpha = fast_exp2((m_run - m_new) * scale_log2e);  // first tile: 0
+                }
+                // P = exp2(scale * log2e * (S - max)), two fp16 per 32-bit column: keys 2i, 2i+1 in column i;
+                // the 32 packed words end up in va, which is what the store below takes
+                const float mc = m_new * scale_log2e;
+                float poly_max = -INFINITY;
+                exp_half(va, va, scale_log2e, mc, acc0, acc1, poly_max);
+                tc::tc_wait_ld(vb);
+                exp_half(vb, va + 16, scale_log2e, mc, acc0, acc1, poly_max);
+                if (need_max) break;
+                const float sum = (acc0.x + acc0.y) + (acc1.x + acc1.y);
+                if (!__any_sync(kFull, !(sum <= kSumLimit) || poly_max > kRescaleThreshold)) break;
+                need_max = true;
+                tc::tmem_ld32(tS, va);
+                tc::tc_wait_ld(va);
+                tc::tmem_ld32(tS + 32, vb);
+            }
             if (j > 0 && any_move) {  // rescale this warp's 32 rows of O (vb is free here)
                 // O belongs to the tensor core until the previous tile's P V is done. Having seen s_full of tile j,
                 // P V of tile j - 4 (the previous phase of this barrier) is known complete: the parity is unambiguous.
