@@ -462,6 +462,8 @@ def _main():
         if a.profile == "attention":
             Se = 5665; Sp = (Se + 7) & ~7
             V = a.views
+            if V < 1:
+                ap.error("--views must be at least 1")
             if V == 1:
                 q, k, v = _r((1, HEADS, NP, HD), H16), _r((1, HEADS, Sp, HD), H16), _r((1, HEADS, Sp, HD), H16)
                 o = torch.empty(1, NP, HEADS * HD, device="cuda", dtype=H16)
