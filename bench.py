@@ -790,6 +790,17 @@ def main():
     args.warmup = max(args.warmup, 3)
     globals()["N_REPS"] = max(1, args.reps)
 
+    # Standard output carries the one JSON line and nothing else: libraries loaded below write progress notes to file
+    # descriptor 1 from C (the reference's cuDNN plan builder does), so descriptor 1 is pointed at standard error for
+    # the run and the line goes to a duplicate of the original.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj):
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(obj) + "\n").encode())
+
     import torch
     if not torch.cuda.is_available():
         sys.exit("bench.py needs a CUDA device: there is no CPU fallback")
@@ -801,7 +812,7 @@ def main():
             backend = RefBackend()
         except Exception as e:  # reference libraries did not travel / did not build
             if rank == 0:
-                print(json.dumps({"impl": "reference", "unavailable": f"{type(e).__name__}: {e}"}))
+                emit({"impl": "reference", "unavailable": f"{type(e).__name__}: {e}"})
             return
     else:
         backend = rfk_backend()
@@ -821,7 +832,7 @@ def main():
             line["impl"] = "reference"
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_views() if args.workload == "views" else cpu_baseline_kernels()
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
