@@ -581,6 +581,40 @@ def test_tcgen05_attention_full_size_matches_mma_sync_kernel(tc_path):
     _close(O, Om, "tcgen05 vs mma.sync attention", atol=4e-3, rtol=4e-3, mean_tol=3e-4)
 
 
+@pytest.mark.parametrize("case", ["rising", "spike_in_polynomial_slot", "spike_beyond_2_pow_128", "falling"])
+def test_tcgen05_attention_when_the_running_reference_is_wrong(tc_path, case):
+    """The softmax warps exponentiate a tile against the running reference before they know the tile's maximum and redo
+    the tile if that was inadmissible. Inputs built to make it so: scores that rise along the keys (every tile fails the
+    check), one key per tile that beats the reference by far and sits where the polynomial exponential is used (columns 0, 1
+    of every group of 8), one that beats it by more than 2^128 (fp32 overflow in the first pass), and, as the control,
+    scores that fall along the keys (no tile after the first fails). Against torch fp32 attention; finite everywhere."""
+    pkg, D = tc_path, 64
+    B, Hh, Sq, Sk = 1, 2, 256, 1024
+    g = torch.Generator(device="cuda").manual_seed(5)
+    Q = torch.randn(B, Hh, Sq, D, device="cuda", generator=g).half()
+    K = torch.randn(B, Hh, Sk, D, device="cuda", generator=g).half()
+    V = torch.randn(B, Hh, Sk, D, device="cuda", generator=g).half()
+    qdir = torch.nn.functional.normalize(Q.float().mean(2, keepdim=True), dim=-1)          # [B,H,1,D]: a direction most queries share
+    Q = (Q.float() + 6.0 * qdir).half()                                                       # ... made dominant
+    ramp = torch.linspace(0.0, 1.0, Sk, device="cuda").view(1, 1, Sk, 1)
+    if case == "rising":
+        K = (K.float() + 40.0 * ramp * qdir).half()           # the scaled score grows by ~30 over the keys, ~2 per tile
+    elif case == "falling":
+        K = (K.float() - 40.0 * ramp * qdir).half()
+    else:
+        boost = 60.0 if case == "spike_in_polynomial_slot" else 250.0   # scaled score + boost * 6 / 8 exponent-ish units
+        Kf = K.float()
+        Kf[:, :, 64 * 3 + 8, :] += boost * qdir[:, :, 0, :]   # tile 3, column 8: first pair of a group of four pairs
+        Kf[:, :, 64 * 9 + 1, :] += 1.5 * boost * qdir[:, :, 0, :]   # tile 9, column 1
+        K = Kf.half()
+    O = torch.full_like(Q, 7.0)
+    pkg.ops.flash_attention(Q, K, V, O, B, Hh, Sq, Sk, Sk, D)
+    torch.cuda.synchronize()
+    assert torch.isfinite(O.float()).all()
+    want = torch.nn.functional.scaled_dot_product_attention(Q.float(), K.float(), V.float())
+    _close(O, want, "tcgen05 attention, " + case, atol=4e-3, rtol=4e-3, mean_tol=5e-4)
+
+
 @pytest.mark.parametrize("masked", [False, True])
 def test_window_attention_matches_fp32_attention(masked):
     """Fused swin window attention (64 tokens x 64 keys per window and head) against torch fp32: plain, and with a
