@@ -156,6 +156,7 @@ __device__ __forceinline__ float2 exp2_poly(float2 x) {
 #define RFK_ATTN_POLY_MASK 0x1
 #endif
 constexpr int kPolyMask = RFK_ATTN_POLY_MASK;
+
 #ifndef RFK_ATTN_POLY_PERIOD
 #define RFK_ATTN_POLY_PERIOD 4
 #endif
@@ -189,15 +190,26 @@ __device__ __forceinline__ void exp_half(uint32_t (&v)[32], uint32_t* pk /* may 
             }
         }
     }
+    // four independent chains of packed adds (with two, the adds of a half waited on each other: -3 % with four), the
+    // packing written ahead of the adds (the compiler keeps this order; -1 %)
+    float2 a2 = make_float2(0.0f, 0.0f), a3 = make_float2(0.0f, 0.0f);
 #pragma unroll
-    for (int i = 0; i < 32; i += 4) {
+    for (int i = 0; i < 32; i += 8) {
         const float2 p0 = make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
         const float2 p1 = make_float2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-        acc0 = __fadd2_rn(acc0, p0);
-        acc1 = __fadd2_rn(acc1, p1);
+        const float2 p2 = make_float2(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+        const float2 p3 = make_float2(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
         pk[i >> 1] = pack_half2(p0.x, p0.y);
         pk[(i >> 1) + 1] = pack_half2(p1.x, p1.y);
+        pk[(i >> 1) + 2] = pack_half2(p2.x, p2.y);
+        pk[(i >> 1) + 3] = pack_half2(p3.x, p3.y);
+        acc0 = __fadd2_rn(acc0, p0);
+        acc1 = __fadd2_rn(acc1, p1);
+        a2 = __fadd2_rn(a2, p2);
+        a3 = __fadd2_rn(a3, p3);
     }
+    acc0 = __fadd2_rn(acc0, a2);
+    acc1 = __fadd2_rn(acc1, a3);
 }
 
 // 32 fp32 values (as raw words) * inv -> fp16 -> 64 bytes at dst
